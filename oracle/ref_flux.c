@@ -1,0 +1,93 @@
+/*
+ * TEST INFRASTRUCTURE, not product code.
+ *
+ * Thin exported wrappers around the `static` FLUX.2 prologue / attention
+ * helpers of the reference. The reference source is compiled where it lies
+ * (include path given by the Makefile's REF variable); nothing of it is
+ * copied here. The wrappers only forward arguments.
+ *
+ * Reference functions reached (iris_transformer_flux.c):
+ *   apply_qk_norm :1289, compute_rope_2d :823, compute_rope_2d_with_t_offset
+ *   :887, apply_rope_2d :952, compute_rope_text :981, mha_forward :1585,
+ *   joint_attention :1682, ensure_attn_scores :1382.
+ */
+#include "iris_transformer_flux.c"
+
+/* Timing accumulators the reference expects from iris_sample.c:29-58. */
+double iris_timing_transformer_total, iris_timing_transformer_double;
+double iris_timing_transformer_single, iris_timing_transformer_final;
+
+void ref_flux_qk_norm(float *q, float *k, const float *qw, const float *kw,
+                      int seq, int heads, int head_dim, float eps) {
+    apply_qk_norm(q, k, qw, kw, seq, heads, head_dim, eps);
+}
+
+void ref_flux_rope_text(float *cos_out, float *sin_out, int txt_seq, int axis_dim, float theta) {
+    compute_rope_text(cos_out, sin_out, txt_seq, axis_dim, theta);
+}
+
+void ref_flux_rope_2d(float *cos_out, float *sin_out, int ph, int pw, int axis_dim, float theta) {
+    compute_rope_2d(cos_out, sin_out, ph, pw, axis_dim, theta);
+}
+
+void ref_flux_rope_2d_t(float *cos_out, float *sin_out, int ph, int pw, int axis_dim,
+                        float theta, int t_offset) {
+    compute_rope_2d_with_t_offset(cos_out, sin_out, ph, pw, axis_dim, theta, t_offset);
+}
+
+void ref_flux_apply_rope_2d(float *x, const float *cos_f, const float *sin_f,
+                            int seq, int heads, int head_dim) {
+    apply_rope_2d(x, cos_f, sin_f, seq, heads, head_dim, head_dim / 4);
+}
+
+static int flux_ctx(iris_transformer_flux_t *tf, int img_seq, int txt_seq, int heads, int head_dim) {
+    memset(tf, 0, sizeof(*tf));
+    tf->num_heads = heads;
+    tf->head_dim = head_dim;
+    tf->hidden_size = heads * head_dim;
+    tf->axis_dim = head_dim / 4;
+    tf->rope_theta = 2000.0f;
+    size_t n = (size_t)(img_seq + txt_seq) * heads * head_dim;
+    tf->attn_cat_k = malloc(n * sizeof(float));
+    tf->attn_cat_v = malloc(n * sizeof(float));
+    if (!tf->attn_cat_k || !tf->attn_cat_v) return -1;
+    return ensure_attn_scores(tf, img_seq, txt_seq);
+}
+
+static void flux_ctx_free(iris_transformer_flux_t *tf) {
+    free(tf->attn_cat_k);
+    free(tf->attn_cat_v);
+    free(tf->attn_scores);
+}
+
+/* Joint attention of a double block: K/V concatenated as [TEXT, IMAGE]. */
+int ref_flux_joint_attention(float *img_out, float *txt_out,
+                             const float *img_q, const float *img_k, const float *img_v,
+                             const float *txt_q, const float *txt_k, const float *txt_v,
+                             int img_seq, int txt_seq, int heads, int head_dim) {
+    iris_transformer_flux_t tf;
+    if (flux_ctx(&tf, img_seq, txt_seq, heads, head_dim) != 0) { flux_ctx_free(&tf); return -1; }
+    joint_attention(img_out, txt_out, img_q, img_k, img_v, txt_q, txt_k, txt_v,
+                    img_seq, txt_seq, heads, head_dim, &tf);
+    flux_ctx_free(&tf);
+    return 0;
+}
+
+/* Self attention of a single block over the already concatenated sequence. */
+int ref_flux_mha(float *out, const float *q, const float *k, const float *v,
+                 int seq, int heads, int head_dim) {
+    iris_transformer_flux_t tf;
+    if (flux_ctx(&tf, seq, 0, heads, head_dim) != 0) { flux_ctx_free(&tf); return -1; }
+    mha_forward(out, q, k, v, seq, heads, head_dim, &tf);
+    flux_ctx_free(&tf);
+    return 0;
+}
+
+int ref_flux_attn_threads(int heads) {
+#ifdef USE_BLAS
+    return get_attn_num_threads(heads);
+#else
+    (void)heads;
+    return 1;
+#endif
+}
