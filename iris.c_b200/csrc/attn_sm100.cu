@@ -1,0 +1,766 @@
+/*
+ * Joint attention for sm_100a: TMA loads, tcgen05 MMAs accumulating in
+ * tensor memory, online softmax with one thread per query row.
+ *
+ * Takes the argument domain of the transformer blocks (the reference's own
+ * fast-path test, iris_cuda.cu:884-886, tightened to what TMA needs):
+ * head_dim 128, heads == kv_heads, non-causal, optional key mask, bf16
+ * [seq, heads*128] views with 16-byte aligned bases and ldi % 8 == 0.
+ *
+ * Work decomposition
+ *   One CTA owns 256 consecutive queries of one head as two 128-row tiles
+ *   and walks the keys in tiles of 128. CTAs of the same head are adjacent
+ *   in the grid, so the K/V of a head (2.4 MB at 4608 keys) are shared
+ *   through L2.
+ *
+ * Warps (320 threads)
+ *   0-3   softmax of query tile 0: thread r owns row r of S / P / O
+ *   4-7   softmax of query tile 1
+ *   8     TMA producer (one lane): Q once, then K0 V0 K1 V1 ... through a
+ *         ring of 32 KB slots guarded by full / empty mbarriers
+ *   9     MMA issuer (one lane), owner of the TMEM allocation
+ *
+ * Tensor memory (512 columns x 128 lanes, fp32)
+ *   [  0,128) S0   [128,256) S1   [256,384) O0   [384,512) O1
+ *   P_t (bf16, 64 columns) overwrites the first half of S_t: a softmax
+ *   thread has read its whole S row before it stores P.
+ *
+ * MMA issue order per key tile j (all from one thread, executed in order):
+ *   PV0(j)  QK0(j+1)  PV1(j)  QK1(j+1)
+ *   S_t = Q_t K^T : both operands from shared memory, K-major, 128B swizzle
+ *   O_t += P_t V  : P from tensor memory, V from shared memory, MN-major
+ *   While the tensor pipe works for tile t, the softmax warpgroup of the
+ *   other tile turns its S into P, so the two overlap.
+ *
+ * Online softmax (base 2, scale * log2(e) folded into one FMA per score):
+ *   the reference value m of a row only moves when the row maximum grows by
+ *   more than 8 (a factor 256), so the O rescale in tensor memory is rare;
+ *   P <= 256 keeps full precision in bf16 and fp32. P is rounded to bf16 for
+ *   the MMA while the row sum keeps the unrounded value, as the reference
+ *   kernel does (iris_cuda.cu:819-831). Masked and out-of-range keys score
+ *   -inf; a row without any valid key yields zeros (iris_cuda.cu:811, :853).
+ *
+ * Every wait on an mbarrier is bounded in time: when the limit passes the
+ * CTA records where in the device status word, raises a CTA-wide abort flag,
+ * drains what it has in flight (again bounded), frees its tensor memory and
+ * returns. Loads never use cluster multicast.
+ */
+#include "common.cuh"
+
+#include <cuda.h>
+#include <math.h>
+
+namespace iris_b200 {
+
+namespace sm100 {
+
+static constexpr int kTileQ = 128;            /* rows of one query tile / MMA M */
+static constexpr int kTileK = 128;            /* keys per tile / MMA N of S */
+static constexpr int kHeadDim = 128;
+static constexpr int kStages = 5;             /* K / V ring slots */
+static constexpr int kHalfBytes = 128 * 64 * 2;         /* one [128 x 64] bf16 swizzled box */
+static constexpr int kTileBytes = 2 * kHalfBytes;       /* one [128 x 128] bf16 operand */
+static constexpr int kThreads = 320;
+static constexpr int kSmemQ = 0;
+static constexpr int kSmemKV = 2 * kTileBytes;
+static constexpr int kSmemBar = kSmemKV + kStages * kTileBytes;
+static constexpr int kSmemBytes = kSmemBar + 256 + 1024;   /* + barriers + alignment slack */
+static constexpr float kRescaleThreshold = 8.0f;
+static constexpr unsigned long long kWaitLimitNs = 1000000000ull;   /* 1 s */
+
+/* mbarrier slots inside the barrier block (8 bytes each) */
+enum {
+    BAR_Q_FULL = 0,
+    BAR_KV_FULL = 1,                      /* kStages */
+    BAR_KV_EMPTY = BAR_KV_FULL + kStages, /* kStages */
+    BAR_S_FULL = BAR_KV_EMPTY + kStages,  /* 2 */
+    BAR_P_FULL = BAR_S_FULL + 2,          /* 2 */
+    BAR_O_DONE = BAR_P_FULL + 2,          /* 2 */
+    BAR_DRAIN = BAR_O_DONE + 2,
+    BAR_COUNT
+};
+static constexpr int kSmemTmemPtr = BAR_COUNT * 8;      /* u32 */
+static constexpr int kSmemAbort = kSmemTmemPtr + 4;     /* u32 */
+
+struct Params {
+    uint16_t *out;
+    int ldo;
+    int seq_q, seq_k, heads;
+    int nqblk;                 /* 256-row query blocks per head */
+    float scale_log2;
+    const uint32_t *mask_bits; /* packed key mask, bit j of word j/32, or NULL */
+    unsigned int *status;      /* [0] flag, [1] site, [2] block, [3] aux */
+    /* state carried across key chunks (ring / split-K), or NULL */
+    float *o_acc;              /* [seq_q, heads*128] fp32, normalised partial output */
+    float *lse_acc;            /* [heads, seq_q] fp32, log2-sum-exp of the keys seen so far */
+    int acc_mode;              /* 0: single pass; 1: first chunk (write state); 2: merge into state;
+                                  3: merge with the state and write the final bf16 output */
+    /* descriptor fields, in 16-byte units */
+    uint32_t qk_sbo, v_lbo, v_sbo;
+    float *debug;              /* bring-up dump, or NULL */
+};
+
+/* ---------------- PTX wrappers ---------------- */
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+struct Ctx {
+    uint32_t bars;                  /* shared address of the barrier block */
+    volatile uint32_t *abort_flag;  /* generic pointer to the CTA abort word */
+    unsigned int *status;
+};
+
+/* Bounded wait. Returns false when the CTA is aborting. `site` identifies
+ * the caller in the status word. */
+__device__ __noinline__ bool mbar_wait_slow(const Ctx &c, uint32_t bar, uint32_t parity, int site) {
+    unsigned long long t0 = global_ns();
+    for (uint32_t spin = 0;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 63u) {
+            if (*c.abort_flag) return false;
+            if (global_ns() - t0 > kWaitLimitNs || spin > (1u << 26)) {
+                *c.abort_flag = 1u;
+                if (atomicCAS(c.status, 0u, 1u) == 0u) {
+                    c.status[1] = (unsigned)site;
+                    c.status[2] = blockIdx.x;
+                    c.status[3] = parity;
+                }
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(const Ctx &c, int idx, uint32_t parity, int site) {
+    uint32_t bar = c.bars + idx * 8;
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(c, bar, parity, site);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+/* D[tmem] (+)= A[smem] * B[smem] */
+__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+/* D[tmem] (+)= A[tmem] * B[smem] */
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+
+/* 32 consecutive fp32 columns of this thread's TMEM lane. */
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t *r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+          "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(taddr) : "memory");
+}
+
+/* Two floats -> packed bf16 pair (lo in bits 0-15), round to nearest even. */
+__device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+/* Shared memory matrix descriptor (tcgen05), 128-byte swizzle:
+ * start address, leading / stride byte offsets in 16-byte units, version 1. */
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo16, uint32_t sbo16) {
+    uint64_t d = (uint64_t)((addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)(lbo16 & 0x3FFFu) << 16;
+    d |= (uint64_t)(sbo16 & 0x3FFFu) << 32;
+    d |= 1ull << 46;       /* descriptor version of sm_100 */
+    d |= 2ull << 61;       /* SWIZZLE_128B */
+    return d;
+}
+
+/* Instruction descriptor, kind::f16: fp32 accumulate, bf16 operands,
+ * M = 128, N = 128; bit 16 selects an MN-major B operand. */
+static constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+static constexpr uint32_t kIdescQK = kIdescBase;
+static constexpr uint32_t kIdescPV = kIdescBase | (1u << 16);
+
+/* ---------------- roles ---------------- */
+
+__device__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmq, const CUtensorMap *tmk,
+                         const CUtensorMap *tmv, uint32_t smem, int head, int q0, int ntq, int nkv) {
+    const int col = head * kHeadDim;
+    mbar_expect_tx(c.bars + BAR_Q_FULL * 8, ntq * kTileBytes);
+    for (int t = 0; t < ntq; t++)
+        for (int half = 0; half < 2; half++)
+            tma_load_2d(smem + kSmemQ + t * kTileBytes + half * kHalfBytes, tmq, col + half * 64,
+                        q0 + t * kTileQ, c.bars + BAR_Q_FULL * 8);
+    int issued = 0;
+    for (int it = 0; it < 2 * nkv; it++, issued++) {
+        int slot = it % kStages, round = it / kStages;
+        if (round > 0 && !mbar_wait(c, BAR_KV_EMPTY + slot, (round - 1) & 1, 100 + slot)) break;
+        uint32_t full = c.bars + (BAR_KV_FULL + slot) * 8;
+        mbar_expect_tx(full, kTileBytes);
+        const CUtensorMap *map = (it & 1) ? tmv : tmk;
+        for (int half = 0; half < 2; half++)
+            tma_load_2d(smem + kSmemKV + slot * kTileBytes + half * kHalfBytes, map, col + half * 64,
+                        (it >> 1) * kTileK, full);
+    }
+    if (*c.abort_flag) {
+        /* Nobody may be consuming any more: wait for the copies still in flight. */
+        for (int it = issued > kStages ? issued - kStages : 0; it < issued; it++)
+            mbar_wait(c, BAR_KV_FULL + it % kStages, (it / kStages) & 1, 190);
+    }
+}
+
+__device__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem, int ntq, int nkv) {
+    uint32_t ok = 1;
+    /* it-th ring item: K_j is item 2j, V_j item 2j+1 */
+    auto wait_item = [&](int it, int site) {
+        return mbar_wait(c, BAR_KV_FULL + it % kStages, (it / kStages) & 1, site);
+    };
+    auto slot_addr = [&](int it) { return smem + kSmemKV + (it % kStages) * kTileBytes; };
+    auto issue_qk = [&](int t, int it) {
+        uint32_t qa = smem + kSmemQ + t * kTileBytes, ka = slot_addr(it);
+#pragma unroll
+        for (int ks = 0; ks < kHeadDim / 16; ks++) {
+            uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+            mma_ss(tmem + t * 128, make_desc(qa + off, 1, p.qk_sbo), make_desc(ka + off, 1, p.qk_sbo),
+                   kIdescQK, ks > 0);
+        }
+        tc_commit(c.bars + (BAR_S_FULL + t) * 8);
+    };
+    auto issue_pv = [&](int t, int it, int first) {
+        uint32_t va = slot_addr(it);
+#pragma unroll
+        for (int ks = 0; ks < kTileK / 16; ks++)
+            mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8,
+                   make_desc(va + ks * 16 * 128, p.v_lbo, p.v_sbo), kIdescPV, (!first) || ks > 0);
+        tc_commit(c.bars + (BAR_O_DONE + t) * 8);
+    };
+
+    ok = mbar_wait(c, BAR_Q_FULL, 0, 200) && wait_item(0, 201);
+    if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < ntq; t++) issue_qk(t, 0);
+        tc_commit(c.bars + (BAR_KV_EMPTY + 0) * 8);
+    }
+    for (int j = 0; ok && j < nkv; j++) {
+        int itv = 2 * j + 1, itk = 2 * j + 2;
+        if (!(ok = wait_item(itv, 210))) break;
+        for (int t = 0; t < ntq; t++) {
+            if (!(ok = mbar_wait(c, BAR_P_FULL + t, j & 1, 220 + t))) break;
+            tc_fence_after();
+            issue_pv(t, itv, j == 0);
+            if (t == ntq - 1) tc_commit(c.bars + (BAR_KV_EMPTY + itv % kStages) * 8);
+            if (j + 1 < nkv) {
+                if (t == 0 && !(ok = wait_item(itk, 230))) break;
+                tc_fence_after();
+                issue_qk(t, itk);
+                if (t == ntq - 1) tc_commit(c.bars + (BAR_KV_EMPTY + itk % kStages) * 8);
+            }
+        }
+    }
+    if (!ok) {
+        /* Let what was issued finish before the tensor memory goes away. */
+        tc_commit(c.bars + BAR_DRAIN * 8);
+        uint32_t bar = c.bars + BAR_DRAIN * 8;
+        unsigned long long t0 = global_ns();
+        while (!mbar_try_wait(bar, 0) && global_ns() - t0 < kWaitLimitNs) {}
+    }
+}
+
+/* Valid-key bits of key tile j (bit b of word w = key j*128 + 32w + b). */
+__device__ __forceinline__ void tile_bits(const Params &p, int j, uint32_t bits[4]) {
+    int n = p.seq_k - j * kTileK;                 /* keys left, >= 1 */
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        int left = n - 32 * w;
+        uint32_t b = left >= 32 ? 0xFFFFFFFFu : (left <= 0 ? 0u : ((1u << left) - 1u));
+        if (p.mask_bits) b &= p.mask_bits[j * 4 + w];    /* padded to whole tiles by the packer */
+        bits[w] = b;
+    }
+}
+
+/* Scores of masked / out-of-range keys become -inf. */
+__device__ __forceinline__ void mask_chunk(uint32_t *v, uint32_t bits) {
+#pragma unroll
+    for (int i = 0; i < 32; i++)
+        if (!((bits >> i) & 1u)) v[i] = 0xFF800000u;
+}
+
+template <bool DEBUG>
+__device__ void softmax_wg(const Ctx &c, const Params &p, uint32_t tmem, int t, int head, int q0, int nkv) {
+    const int row = threadIdx.x & 127;                     /* row of the tile == TMEM lane */
+    const uint32_t lane_base = (uint32_t)(row & ~31) << 16;
+    const uint32_t tS = tmem + lane_base + t * 128;
+    const uint32_t tO = tmem + lane_base + 256 + t * 128;
+    const int qrow = q0 + t * kTileQ + row;
+    const float sl2 = p.scale_log2;
+    float m_ref = -INFINITY;     /* reference of the exponentials, in scaled log2 units */
+    float l = 0.0f;
+    bool ok = true;
+
+    for (int j = 0; j < nkv; j++) {
+        /* One decision per warp: the TMEM accesses below are warp-collective. */
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_S_FULL + t, j & 1, 300 + t)))) break;
+        tc_fence_after();
+
+        const bool partial = (j == nkv - 1 && (p.seq_k & (kTileK - 1)) != 0) || p.mask_bits != nullptr;
+        uint32_t bits[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
+        if (partial) tile_bits(p, j, bits);
+
+        /* Pass 1: row maximum, 32 columns at a time, next chunk in flight. */
+        uint32_t v[2][32];
+        float mx = -INFINITY;
+        tmem_ld32(tS, v[0]);
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+            tc_wait_ld();
+            if (ch < 3) tmem_ld32(tS + (ch + 1) * 32, v[(ch + 1) & 1]);
+            uint32_t *cur = v[ch & 1];
+            if (DEBUG && p.debug && j == 0) {
+                float *dst = p.debug + ((size_t)blockIdx.x * 256 + t * 128 + row) * 128 + ch * 32;
+#pragma unroll
+                for (int i = 0; i < 32; i++) dst[i] = __uint_as_float(cur[i]);
+            }
+            if (partial) mask_chunk(cur, bits[ch]);
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
+        }
+        float m_cand = fmaxf(m_ref, mx * sl2);
+
+        if (j == 0) {
+            m_ref = m_cand;
+        } else {
+            bool need = m_cand > m_ref + kRescaleThreshold;
+            if (__any_sync(0xffffffffu, need)) {
+                /* PV(j-1) of this tile has completed (it was issued before
+                 * the QK that filled S) and PV(j) waits for our arrival: O
+                 * is ours to rescale. */
+                float alpha = need ? ex2(m_ref - m_cand) : 1.0f;
+                if (need) {
+                    l *= alpha;
+                    m_ref = m_cand;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    tmem_ld32(tO + i * 32, v[0]);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 32; e++) v[0][e] = __float_as_uint(__uint_as_float(v[0][e]) * alpha);
+                    tmem_st32(tO + i * 32, v[0]);
+                }
+            }
+        }
+
+        /* Pass 2: P = 2^(s * scale_log2 - m_ref) as bf16 pairs over the first
+         * 64 columns of S. Chunk ch reads S columns [32ch, 32ch + 32) and
+         * writes P columns [16ch, 16ch + 16), all of them already consumed. */
+        const float neg_ref = m_ref == -INFINITY ? 0.0f : -m_ref;
+        float sum0 = 0.0f, sum1 = 0.0f;
+        tmem_ld32(tS, v[0]);
+#pragma unroll
+        for (int ch = 0; ch < 4; ch++) {
+            tc_wait_ld();
+            if (ch < 3) tmem_ld32(tS + (ch + 1) * 32, v[(ch + 1) & 1]);
+            uint32_t *cur = v[ch & 1];
+            if (partial) mask_chunk(cur, bits[ch]);
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                float p0 = ex2(fmaf(__uint_as_float(cur[2 * i]), sl2, neg_ref));
+                float p1 = ex2(fmaf(__uint_as_float(cur[2 * i + 1]), sl2, neg_ref));
+                sum0 += p0;
+                sum1 += p1;
+                pk[i] = cvt_bf16x2(p0, p1);
+            }
+            tmem_st16(tS + ch * 16, pk);
+        }
+        l += sum0 + sum1;
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(c.bars + (BAR_P_FULL + t) * 8);
+    }
+
+    /* Epilogue: O / l -> bf16 rows of the output slice of this head. */
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_O_DONE + t, (nkv - 1) & 1, 310 + t));
+    if (!ok) return;
+    tc_fence_after();
+    const bool valid = qrow < p.seq_q;
+    float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    if (DEBUG && p.debug) {
+        float *dst = p.debug + (size_t)gridDim.x * 256 * 128 + ((size_t)blockIdx.x * 256 + t * 128 + row) * 2;
+        dst[0] = m_ref;
+        dst[1] = l;
+    }
+
+    /* Chunked state: this launch saw only part of the keys. lse = m + log2(l). */
+    float w_prev = 0.0f, w_cur = 1.0f;
+    float *acc_row = nullptr;
+    if (p.acc_mode != 0 && valid) {
+        acc_row = p.o_acc + (size_t)qrow * ((size_t)p.heads * kHeadDim) + (size_t)head * kHeadDim;
+        float *lse_p = p.lse_acc + (size_t)head * p.seq_q + qrow;
+        float lse_cur = l > 0.0f ? m_ref + log2f(l) : -INFINITY;
+        if (p.acc_mode >= 2) {
+            float lse_prev = *lse_p;
+            float lse_new = fmaxf(lse_prev, lse_cur);
+            if (lse_new == -INFINITY) {
+                w_prev = 0.0f; w_cur = 0.0f;
+            } else {
+                float a = exp2f(lse_prev - lse_new), b = exp2f(lse_cur - lse_new);
+                lse_new += log2f(a + b);
+                w_prev = a / (a + b);
+                w_cur = b / (a + b);
+            }
+            lse_cur = lse_new;
+        }
+        if (p.acc_mode != 3) *lse_p = lse_cur;
+    }
+    const bool write_state = p.acc_mode == 1 || p.acc_mode == 2;
+    const bool read_state = p.acc_mode >= 2;
+    const bool write_out = p.acc_mode == 0 || p.acc_mode == 3;
+    const bool vec16 = (p.ldo & 7) == 0;
+    uint16_t *orow = p.out ? p.out + (size_t)qrow * p.ldo + (size_t)head * kHeadDim : nullptr;
+
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t o[32];
+        tmem_ld32(tO + i * 32, o);
+        tc_wait_ld();
+        if (!valid) continue;
+        float f[32];
+#pragma unroll
+        for (int e = 0; e < 32; e++) f[e] = __uint_as_float(o[e]) * inv * w_cur;
+        if (read_state) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+                float4 pr = *reinterpret_cast<const float4 *>(acc_row + i * 32 + e);
+                f[e] += pr.x * w_prev; f[e + 1] += pr.y * w_prev;
+                f[e + 2] += pr.z * w_prev; f[e + 3] += pr.w * w_prev;
+            }
+        }
+        if (write_state) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+                *reinterpret_cast<float4 *>(acc_row + i * 32 + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+        }
+        if (write_out) {
+            uint32_t pkd[16];
+#pragma unroll
+            for (int e = 0; e < 16; e++) pkd[e] = cvt_bf16x2(f[2 * e], f[2 * e + 1]);
+            if (vec16) {
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    *reinterpret_cast<uint4 *>(orow + i * 32 + e * 8) =
+                        make_uint4(pkd[4 * e], pkd[4 * e + 1], pkd[4 * e + 2], pkd[4 * e + 3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 16; e++) *reinterpret_cast<uint32_t *>(orow + i * 32 + e * 2) = pkd[e];
+            }
+        }
+    }
+}
+
+template <bool DEBUG>
+__global__ void __launch_bounds__(kThreads, 1)
+k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
+                  const __grid_constant__ CUtensorMap tmv, const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    /* The swizzled operand tiles need 1024-byte alignment. */
+    const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *smem_gen = smem_raw + (smem - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    Ctx c;
+    c.bars = smem + kSmemBar;
+    c.abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemAbort);
+    c.status = p.status;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemTmemPtr);
+
+    const int head = blockIdx.x / p.nqblk;
+    const int q0 = (blockIdx.x - head * p.nqblk) * 2 * kTileQ;
+    const int ntq = (p.seq_q - q0 > kTileQ) ? 2 : 1;
+    const int nkv = (p.seq_k + kTileK - 1) / kTileK;
+
+    if (threadIdx.x == 0) {
+        mbar_init(c.bars + BAR_Q_FULL * 8, 1);
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(c.bars + (BAR_KV_FULL + s) * 8, 1);
+            mbar_init(c.bars + (BAR_KV_EMPTY + s) * 8, 1);
+        }
+        for (int t = 0; t < 2; t++) {
+            mbar_init(c.bars + (BAR_S_FULL + t) * 8, 1);
+            mbar_init(c.bars + (BAR_P_FULL + t) * 8, 128);
+            mbar_init(c.bars + (BAR_O_DONE + t) * 8, 1);
+        }
+        mbar_init(c.bars + BAR_DRAIN * 8, 1);
+        *c.abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 9) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem + kSmemBar + kSmemTmemPtr), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        if (warp < 4 * ntq) softmax_wg<DEBUG>(c, p, tmem, warp >> 2, head, q0, nkv);
+    } else if (lane == 0) {
+        if (warp == 8) producer(c, p, &tmq, &tmk, &tmv, smem, head, q0, ntq, nkv);
+        else mma_issuer(c, p, smem, tmem, ntq, nkv);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+/* key_mask (int per key, 0 = ignore) -> one bit per key, padded with zero
+ * bits to a whole number of 128-key tiles. */
+__global__ void k_pack_mask(uint32_t *bits, const int *key_mask, int seq_k, int nwords) {
+    int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= nwords) return;
+    uint32_t b = 0;
+    for (int i = 0; i < 32; i++) {
+        int key = w * 32 + i;
+        if (key < seq_k && key_mask[key] != 0) b |= 1u << i;
+    }
+    bits[w] = b;
+}
+
+/* Rows of a bf16 [seq, heads*128] slice set to zero (attention over no keys). */
+__global__ void k_zero_rows(uint16_t *out, int ldo, int seq, int width) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t n = (size_t)seq * width;
+    if (i < n) out[(i / width) * ldo + (i % width)] = 0;
+}
+
+}  // namespace sm100
+
+/* ---------------- host side ---------------- */
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn(void) {
+    static EncodeTiledFn fn = NULL;
+    static int tried = 0;
+    if (!tried) {
+        tried = 1;
+        void *sym = NULL;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)sym;
+        else
+            (void)cudaGetLastError();
+    }
+    return fn;
+}
+
+/* 2-D map over a bf16 [seq, heads*128] column slice with row stride ld:
+ * box of 64 columns x 128 rows, 128-byte swizzle, zero fill outside. */
+static bool make_map(CUtensorMap *map, const void *base, int seq, int width, int ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error(IRIS_B200_ECUDA, "cuTensorMapEncodeTiled lookup", NULL);
+        return false;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)seq};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char msg[64];
+        snprintf(msg, sizeof(msg), "CUresult %d", (int)r);
+        set_error(IRIS_B200_ECUDA, "cuTensorMapEncodeTiled", msg);
+        return false;
+    }
+    return true;
+}
+
+bool sm100_supported(const void *out, int ldo, const void *q, const void *k, const void *v, int ldi,
+                     int heads, int kv_heads, int head_dim, int causal, float scale) {
+    uintptr_t bits = (uintptr_t)out | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v;
+    return head_dim == sm100::kHeadDim && heads == kv_heads && !causal && scale > 0.0f &&
+           ldi % 8 == 0 && ldo % 2 == 0 && (bits & 15) == 0 && (ldo % 8 == 0 || ((uintptr_t)out & 3) == 0);
+}
+
+static uint32_t *g_mask_bits = NULL;
+static size_t g_mask_words = 0;
+
+/* acc_mode / o_acc / lse_acc: see sm100::Params. debug: bring-up dump. */
+int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, const uint16_t *k,
+                           const uint16_t *v, int ldi, int seq_q, int seq_k, int heads, float scale,
+                           const int *key_mask, int acc_mode, float *o_acc, float *lse_acc,
+                           float *debug, const uint32_t *desc_override) {
+    using namespace sm100;
+    static int configured = 0;
+    if (!configured) {
+        if (!cuda_ok(cudaFuncSetAttribute(k_attention_sm100<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemBytes), "attention smem opt-in") ||
+            !cuda_ok(cudaFuncSetAttribute(k_attention_sm100<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          kSmemBytes), "attention smem opt-in"))
+            return IRIS_B200_ECUDA;
+        configured = 1;
+    }
+    if (seq_k <= 0) {
+        if (acc_mode == 0) {
+            size_t n = (size_t)seq_q * heads * kHeadDim;
+            k_zero_rows<<<(unsigned)((n + 255) / 256), 256, 0, g.stream>>>(out, ldo, seq_q, heads * kHeadDim);
+            return after_launch("attention (zero)") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+        }
+        set_error(IRIS_B200_EINVAL, "attention", "empty key chunk");
+        return IRIS_B200_EINVAL;
+    }
+    Params p = {};
+    int nkv = (seq_k + kTileK - 1) / kTileK;
+    if (key_mask) {
+        size_t words = (size_t)nkv * 4;
+        if (words > g_mask_words) {
+            if (g_mask_bits) {
+                cuda_ok(cudaStreamSynchronize(g.stream), "sync");
+                cuda_ok(cudaFree(g_mask_bits), "free");
+            }
+            g_mask_bits = NULL;
+            g_mask_words = 0;
+            size_t cap = words < 1024 ? 1024 : words * 2;
+            if (cudaMalloc((void **)&g_mask_bits, cap * 4) != cudaSuccess) {
+                (void)cudaGetLastError();
+                set_error(IRIS_B200_ENOMEM, "mask scratch", NULL);
+                return IRIS_B200_ENOMEM;
+            }
+            g_mask_words = cap;
+        }
+        k_pack_mask<<<(unsigned)((words + 127) / 128), 128, 0, g.stream>>>(g_mask_bits, key_mask, seq_k, (int)words);
+        if (!after_launch("attention (mask pack)")) return IRIS_B200_ECUDA;
+        p.mask_bits = g_mask_bits;
+    }
+    CUtensorMap tmq, tmk, tmv;
+    if (!make_map(&tmq, q, seq_q, heads * kHeadDim, ldi) || !make_map(&tmk, k, seq_k, heads * kHeadDim, ldi) ||
+        !make_map(&tmv, v, seq_k, heads * kHeadDim, ldi))
+        return IRIS_B200_ECUDA;
+    p.out = out;
+    p.ldo = ldo;
+    p.seq_q = seq_q;
+    p.seq_k = seq_k;
+    p.heads = heads;
+    p.nqblk = (seq_q + 2 * kTileQ - 1) / (2 * kTileQ);
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = g.dev_status;
+    p.o_acc = o_acc;
+    p.lse_acc = lse_acc;
+    p.acc_mode = acc_mode;
+    p.qk_sbo = desc_override ? desc_override[0] : 1024 / 16;        /* 8 rows of 128 B */
+    p.v_lbo = desc_override ? desc_override[1] : kHalfBytes / 16;   /* next 64-dim half */
+    p.v_sbo = desc_override ? desc_override[2] : 1024 / 16;         /* next 8 keys */
+    p.debug = debug;
+    unsigned grid = (unsigned)(p.nqblk * heads);
+    if (debug)
+        k_attention_sm100<true><<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk, tmv, p);
+    else
+        k_attention_sm100<false><<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk, tmv, p);
+    return after_launch("attention (tcgen05)") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+void sm100_release(void) {
+    if (g_mask_bits) cuda_ok(cudaFree(g_mask_bits), "free");
+    g_mask_bits = NULL;
+    g_mask_words = 0;
+}
+
+}  // namespace iris_b200

@@ -1,0 +1,214 @@
+/*
+ * Prologue of the attention path: per-head RMSNorm, pair rotation (RoPE) and
+ * bf16 store, in place on the Q / K column slices of the fused projection
+ * output. HBM-bound: every element is read once and written once.
+ *
+ * Fast kernel (head_dim 128, 16-byte aligned rows): 16 lanes own one
+ * (token, head) unit, each lane one 16-byte vector of 8 consecutive bf16, so
+ * a warp moves 512 contiguous bytes (two adjacent heads) per access. With
+ * consecutive pairs both members of a pair sit in the same lane; with
+ * split-half pairing lane l exchanges with lane l ^ 8. The sum of squares is
+ * reduced with four shuffles inside the 16-lane group. Several units are in
+ * flight per thread so that enough bytes are outstanding to fill the HBM
+ * pipe. Q and K of a block go through one launch.
+ *
+ * Arithmetic follows the reference kernel (iris_cuda.cu:403-420): widen to
+ * fp32, inv = rsqrt(mean(x^2) + eps), a = x * (inv * w), rotate, one
+ * round-to-nearest-even to bf16.
+ */
+#include "common.cuh"
+
+#include "iris_dev.h"
+
+namespace iris_b200 {
+
+static constexpr int kUnroll = 4;        /* units in flight per 16-lane group */
+static constexpr int kThreads = 256;
+
+struct alignas(16) Vec8 {
+    uint32_t w[4];
+};
+
+template <bool SPLIT_HALF>
+__global__ void __launch_bounds__(kThreads)
+k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
+                     const float *__restrict__ wq, const float *__restrict__ wk,
+                     const float *__restrict__ rope_cos, const float *__restrict__ rope_sin,
+                     int seq, int heads, float eps) {
+    const int lane16 = threadIdx.x & 15;
+    const long long group = ((long long)blockIdx.x * kThreads + threadIdx.x) >> 4;
+    const long long ngroups = ((long long)gridDim.x * kThreads) >> 4;
+    const int per_tok = k ? 2 * heads : heads;      /* units of one token: Q heads then K heads */
+    const long long units = (long long)seq * per_tok;
+
+    /* This lane always owns dims [8 * lane16, 8 * lane16 + 8) of a head. */
+    float wqv[8], wkv[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        wqv[i] = wq[lane16 * 8 + i];
+        wkv[i] = k ? wk[lane16 * 8 + i] : 0.0f;
+    }
+    /* Pairs whose angle this lane needs: consecutive -> pairs 4l..4l+3;
+     * split-half -> pairs 8(l & 7)..+7, shared with lane l ^ 8. */
+    const int rope_off = SPLIT_HALF ? (lane16 & 7) * 8 : lane16 * 4;
+
+    for (long long u0 = group * kUnroll; u0 < units; u0 += ngroups * kUnroll) {
+        Vec8 v[kUnroll];
+        uint16_t *ptr[kUnroll];
+        int tok[kUnroll];
+        bool isk[kUnroll];
+#pragma unroll
+        for (int i = 0; i < kUnroll; i++) {
+            long long u = u0 + i;
+            bool ok = u < units;
+            long long s = ok ? u / per_tok : 0;
+            int hu = ok ? (int)(u - s * per_tok) : 0;
+            isk[i] = hu >= heads;
+            int h = isk[i] ? hu - heads : hu;
+            tok[i] = (int)s;
+            ptr[i] = ok ? (isk[i] ? k : q) + s * ld + h * 128 + lane16 * 8 : nullptr;
+            if (ok) v[i] = *reinterpret_cast<const Vec8 *>(ptr[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < kUnroll; i++) {
+            /* Uniform inside the 16-lane group: all its lanes share the unit. */
+            bool ok = ptr[i] != nullptr;
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                x[2 * j] = ok ? bf_lo(v[i].w[j]) : 0.0f;
+                x[2 * j + 1] = ok ? bf_hi(v[i].w[j]) : 0.0f;
+            }
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) ss += x[j] * x[j];
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] *= inv * (isk[i] ? wkv[j] : wqv[j]);
+
+            if (SPLIT_HALF) {
+                float c[8], sn[8];
+                if (ok) {
+                    const float4 *cp = reinterpret_cast<const float4 *>(rope_cos + (size_t)tok[i] * 64 + rope_off);
+                    const float4 *sp = reinterpret_cast<const float4 *>(rope_sin + (size_t)tok[i] * 64 + rope_off);
+                    float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+                    c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w;
+                    c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+                    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w;
+                    sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+                }
+                bool upper = lane16 >= 8;       /* holds the second member of each pair */
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float other = __shfl_xor_sync(0xffffffffu, x[j], 8);
+                    if (ok) x[j] = upper ? x[j] * c[j] + other * sn[j] : x[j] * c[j] - other * sn[j];
+                }
+            } else if (ok) {
+                float4 c = *reinterpret_cast<const float4 *>(rope_cos + (size_t)tok[i] * 64 + rope_off);
+                float4 s = *reinterpret_cast<const float4 *>(rope_sin + (size_t)tok[i] * 64 + rope_off);
+                float cc[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    float a = x[2 * j], b = x[2 * j + 1];
+                    x[2 * j] = a * cc[j] - b * sn[j];
+                    x[2 * j + 1] = b * cc[j] + a * sn[j];
+                }
+            }
+            if (ok) {
+                Vec8 o;
+#pragma unroll
+                for (int j = 0; j < 4; j++) o.w[j] = pack_bf16x2(x[2 * j], x[2 * j + 1]);
+                *reinterpret_cast<Vec8 *>(ptr[i]) = o;
+            }
+        }
+    }
+}
+
+/* Any even head_dim, any alignment: one warp per (token, head), 2-byte
+ * accesses. Covers the argument domains the fast kernel does not. */
+__global__ void k_head_norm_rope_any(uint16_t *x, int ld, const float *w,
+                                     const float *rope_cos, const float *rope_sin,
+                                     int seq, int heads, int head_dim, float eps, int split_half) {
+    int lane = threadIdx.x & 31;
+    long long unit = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    long long units = (long long)seq * heads;
+    if (unit >= units) return;
+    int s = (int)(unit / heads), h = (int)(unit % heads), half = head_dim / 2;
+    uint16_t *v = x + (size_t)s * ld + (size_t)h * head_dim;
+    float ss = 0.0f;
+    for (int d = lane; d < head_dim; d += 32) {
+        float a = bf2f(v[d]);
+        ss += a * a;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    float inv = rsqrtf(ss / head_dim + eps);
+    for (int i = lane; i < half; i += 32) {
+        int i0 = split_half ? i : 2 * i, i1 = split_half ? i + half : 2 * i + 1;
+        float a = bf2f(v[i0]) * (inv * w[i0]), b = bf2f(v[i1]) * (inv * w[i1]);
+        float c = rope_cos[(size_t)s * half + i], sn = rope_sin[(size_t)s * half + i];
+        v[i0] = f2bf(a * c - b * sn);
+        v[i1] = f2bf(b * c + a * sn);
+    }
+}
+
+static bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+static int launch_prologue(uint16_t *q, uint16_t *k, int ld, const float *wq, const float *wk,
+                           const float *rope_cos, const float *rope_sin, int seq, int heads,
+                           int head_dim, float eps, int split_half) {
+    if (!require_device("head_norm_rope")) return IRIS_B200_ENODEV;
+    if (seq <= 0 || heads <= 0) return IRIS_B200_OK;
+    if (head_dim <= 0 || (head_dim & 1) || !q || !wq || !rope_cos || !rope_sin || (k && !wk)) {
+        set_error(IRIS_B200_EINVAL, "head_norm_rope", "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    bool fast = head_dim == 128 && ld % 8 == 0 && aligned16(q) && (!k || aligned16(k)) &&
+                aligned16(rope_cos) && aligned16(rope_sin);
+    if (fast) {
+        long long units = (long long)seq * heads * (k ? 2 : 1);
+        long long groups = (units + kUnroll - 1) / kUnroll;
+        long long blocks = (groups * 16 + kThreads - 1) / kThreads;
+        long long cap = (long long)g.sm_count * 8;     /* 8 x 256 threads fill an SM */
+        if (blocks > cap) blocks = cap;
+        if (split_half)
+            k_head_norm_rope_128<true><<<(unsigned)blocks, kThreads, 0, g.stream>>>(
+                q, k, ld, wq, wk, rope_cos, rope_sin, seq, heads, eps);
+        else
+            k_head_norm_rope_128<false><<<(unsigned)blocks, kThreads, 0, g.stream>>>(
+                q, k, ld, wq, wk, rope_cos, rope_sin, seq, heads, eps);
+        return after_launch("head_norm_rope") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+    }
+    for (int pass = 0; pass < (k ? 2 : 1); pass++) {
+        long long units = (long long)seq * heads;
+        unsigned blocks = (unsigned)((units * 32 + 255) / 256);
+        k_head_norm_rope_any<<<blocks, 256, 0, g.stream>>>(pass ? k : q, ld, pass ? wk : wq, rope_cos,
+                                                           rope_sin, seq, heads, head_dim, eps, split_half);
+        if (!after_launch("head_norm_rope")) return IRIS_B200_ECUDA;
+    }
+    return IRIS_B200_OK;
+}
+
+}  // namespace iris_b200
+
+using namespace iris_b200;
+
+extern "C" void iris_dev_head_norm_rope(uint16_t *x, int ld, const float *w,
+                                        const float *rope_cos, const float *rope_sin,
+                                        int seq, int heads, int head_dim, float eps,
+                                        int split_half) {
+    launch_prologue(x, NULL, ld, w, NULL, rope_cos, rope_sin, seq, heads, head_dim, eps, split_half);
+}
+
+extern "C" int iris_b200_qk_norm_rope(uint16_t *q, uint16_t *k, int ld,
+                                      const float *wq, const float *wk,
+                                      const float *rope_cos, const float *rope_sin,
+                                      int seq, int heads, int head_dim, float eps, int split_half) {
+    if (!k) {
+        set_error(IRIS_B200_EINVAL, "qk_norm_rope", "k is NULL");
+        return IRIS_B200_EINVAL;
+    }
+    return launch_prologue(q, k, ld, wq, wk, rope_cos, rope_sin, seq, heads, head_dim, eps, split_half);
+}
