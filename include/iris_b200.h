@@ -63,6 +63,13 @@ void *iris_b200_stream(void);
 int iris_b200_timer_start(void);
 float iris_b200_timer_stop_ms(void);
 
+/* Numbered timing marks (0 <= id < 8192): mark() records a CUDA event on the
+ * library's stream, mark_elapsed_ms() waits for `to` and returns the device
+ * time between two recorded marks (< 0 on error). Lets a caller time single
+ * kernels inside a longer region without leaving the stream. */
+int iris_b200_mark(int id);
+float iris_b200_mark_elapsed_ms(int from, int to);
+
 /* Number of kernel launches the library has enqueued since init. */
 unsigned long long iris_b200_launch_count(void);
 

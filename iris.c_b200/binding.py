@@ -45,6 +45,8 @@ SIGNATURES = {
     "iris_b200_timer_start": (INT, []),
     "iris_b200_timer_stop_ms": (FLT, []),
     "iris_b200_launch_count": (U64, []),
+    "iris_b200_mark": (INT, [INT]),
+    "iris_b200_mark_elapsed_ms": (FLT, [INT, INT]),
     "iris_b200_qk_norm_rope": (INT, [VP, VP, INT, VP, VP, VP, VP, INT, INT, INT, FLT, INT]),
     "iris_b200_attention_ex": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP, INT]),
     "iris_b200_attention_kernel_for": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT]),

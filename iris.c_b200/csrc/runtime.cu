@@ -175,6 +175,32 @@ float iris_b200_timer_stop_ms(void) {
 
 unsigned long long iris_b200_launch_count(void) { return g.launches; }
 
+/* Numbered timing marks: events created on first use, recorded on the
+ * library's stream. */
+static const int kMaxMarks = 8192;
+static cudaEvent_t g_marks[kMaxMarks];
+static unsigned char g_mark_made[kMaxMarks];
+
+int iris_b200_mark(int id) {
+    if (!require_device("mark")) return IRIS_B200_ENODEV;
+    if (id < 0 || id >= kMaxMarks) return IRIS_B200_EINVAL;
+    if (!g_mark_made[id]) {
+        if (!cuda_ok(cudaEventCreate(&g_marks[id]), "event create")) return IRIS_B200_ECUDA;
+        g_mark_made[id] = 1;
+    }
+    return cuda_ok(cudaEventRecord(g_marks[id], g.stream), "event record") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+float iris_b200_mark_elapsed_ms(int from, int to) {
+    if (!require_device("mark_elapsed")) return -1.0f;
+    if (from < 0 || to < 0 || from >= kMaxMarks || to >= kMaxMarks || !g_mark_made[from] || !g_mark_made[to])
+        return -1.0f;
+    float ms = -1.0f;
+    if (!cuda_ok(cudaEventSynchronize(g_marks[to]), "event sync")) return -1.0f;
+    if (!cuda_ok(cudaEventElapsedTime(&ms, g_marks[from], g_marks[to]), "event elapsed")) return -1.0f;
+    return ms;
+}
+
 int iris_b200_check_device_status(void) {
     if (!require_device("check_device_status")) return IRIS_B200_ENODEV;
     unsigned int st[4] = {0, 0, 0, 0};
@@ -237,8 +263,25 @@ void iris_dev_upload_2d(void *dst, size_t dst_stride, const void *src, size_t sr
     cuda_ok(cudaStreamSynchronize(g.stream), "sync");
 }
 
+/* Page-locked host memory is copied by the DMA engine directly; pageable
+ * memory goes through the pinned staging buffers. */
+static bool host_is_pinned(const void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return a.type == cudaMemoryTypeHost;
+}
+
 void iris_dev_upload(void *dst, const void *src, size_t bytes) {
-    if (bytes) iris_dev_upload_2d(dst, bytes, src, bytes, bytes, 1);
+    if (!bytes) return;
+    if (g.ready && host_is_pinned(src)) {
+        if (cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g.stream), "upload"))
+            cuda_ok(cudaStreamSynchronize(g.stream), "sync");
+        return;
+    }
+    iris_dev_upload_2d(dst, bytes, src, bytes, bytes, 1);
 }
 
 void iris_dev_download(void *dst, const void *src, size_t bytes) {
