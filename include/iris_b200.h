@@ -108,8 +108,10 @@ int iris_b200_attention_kernel_for(const void *out, int ldo, const void *q, cons
 /* Diagnostics for kernel bring-up: runs the tcgen05 kernel and dumps, into
  * `debug` (device, fp32), the raw scores S = Q K^T of the first key tile of
  * every CTA ([ctas * 256, 128]) followed by (m, l) per row ([ctas * 256, 2]);
- * ctas = ceil(seq_q / 256) * heads. desc_fields: NULL, or three shared
- * memory descriptor fields {qk_sbo, v_lbo, v_sbo} in 16-byte units. */
+ * ctas = ceil(seq_q / 256) * heads. desc_fields: NULL, or four words: the
+ * shared memory descriptor fields {qk_sbo, v_lbo, v_sbo} in 16-byte units
+ * and a mode (bit 0 skip the softmax arithmetic, bit 1 skip the PV MMAs,
+ * bit 2 skip the QK MMAs; results are then meaningless, only time is). */
 int iris_b200_attention_diag(uint16_t *out, int ldo,
                              const uint16_t *q, const uint16_t *k, const uint16_t *v,
                              int ldi, int seq_q, int seq_k, int heads, float scale,

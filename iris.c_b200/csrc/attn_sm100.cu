@@ -13,12 +13,14 @@
  *   in the grid, so the K/V of a head (2.4 MB at 4608 keys) are shared
  *   through L2.
  *
- * Warps (320 threads)
+ * Warps (384 threads)
  *   0-3   softmax of query tile 0: thread r owns row r of S / P / O
  *   4-7   softmax of query tile 1
  *   8     TMA producer (one lane): Q once, then K0 V0 K1 V1 ... through a
  *         ring of 32 KB slots guarded by full / empty mbarriers
  *   9     MMA issuer (one lane), owner of the TMEM allocation
+ *   10-11 idle: they complete the third warpgroup, which gives most of its
+ *         registers to the softmax warpgroups (setmaxnreg)
  *
  * Tensor memory (512 columns x 128 lanes, fp32)
  *   [  0,128) S0   [128,256) S1   [256,384) O0   [384,512) O1
@@ -60,12 +62,14 @@ static constexpr int kHeadDim = 128;
 static constexpr int kStages = 5;             /* K / V ring slots */
 static constexpr int kHalfBytes = 128 * 64 * 2;         /* one [128 x 64] bf16 swizzled box */
 static constexpr int kTileBytes = 2 * kHalfBytes;       /* one [128 x 128] bf16 operand */
-static constexpr int kThreads = 320;
+static constexpr int kThreads = 384;
 static constexpr int kSmemQ = 0;
 static constexpr int kSmemKV = 2 * kTileBytes;
 static constexpr int kSmemBar = kSmemKV + kStages * kTileBytes;
 static constexpr int kSmemBytes = kSmemBar + 256 + 1024;   /* + barriers + alignment slack */
 static constexpr float kRescaleThreshold = 8.0f;
+static constexpr bool kPolyExp = false;    /* evaluate one exponential in four on the FMA pipe */
+static constexpr int kRegsSoftmax = 216, kRegsOther = 72;   /* 2 * 224 + 56 <= 512 */
 static constexpr unsigned long long kWaitLimitNs = 1000000000ull;   /* 1 s */
 
 /* mbarrier slots inside the barrier block (8 bytes each) */
@@ -98,6 +102,7 @@ struct Params {
     /* descriptor fields, in 16-byte units */
     uint32_t qk_sbo, v_lbo, v_sbo;
     float *debug;              /* bring-up dump, or NULL */
+    int diag_mode;             /* diagnostics build: 1 skip softmax math, 2 skip PV MMAs, 4 skip QK MMAs */
 };
 
 /* ---------------- PTX wrappers ---------------- */
@@ -138,7 +143,7 @@ struct Ctx {
 
 /* Bounded wait. Returns false when the CTA is aborting. `site` identifies
  * the caller in the status word. */
-__device__ __noinline__ bool mbar_wait_slow(const Ctx &c, uint32_t bar, uint32_t parity, int site) {
+__device__ __forceinline__ bool mbar_wait_slow(const Ctx &c, uint32_t bar, uint32_t parity, int site) {
     unsigned long long t0 = global_ns();
     for (uint32_t spin = 0;; spin++) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -227,17 +232,23 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
           "r"(taddr) : "memory");
 }
 
-/* Two floats -> packed bf16 pair (lo in bits 0-15), round to nearest even. */
-__device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
-    uint32_t d;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-    return d;
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
+}
+
+/* 2^x on the FMA pipe: round x to the nearest integer n with the 1.5 * 2^23
+ * trick, cubic minimax polynomial for 2^f on f in [-0.5, 0.5] (relative
+ * error 1e-4, below the bf16 rounding of P), n added into the exponent. */
+__device__ __forceinline__ float ex2_poly(float x) {
+    x = fmaxf(x, -125.0f);
+    float t = x + 12582912.0f;
+    float f = x - (t - 12582912.0f);
+    float p = fmaf(f, 0.0555041086f, 0.2402265069f);
+    p = fmaf(p, f, 0.6931471806f);
+    p = fmaf(p, f, 1.0f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -263,9 +274,36 @@ static constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((12
 static constexpr uint32_t kIdescQK = kIdescBase;
 static constexpr uint32_t kIdescPV = kIdescBase | (1u << 16);
 
+/* Timestamps of CTA 0 for the first 16 key tiles (diagnostics build only):
+ * slot [who][j][k], who = 0 / 1 softmax warpgroup of tile 0 / 1, 2 = MMA. */
+__device__ __forceinline__ void stamp(const Params &p, int who, int j, int k) {
+    if (p.debug && blockIdx.x == 0 && j < 16 && (who == 2 || (threadIdx.x & 127) == 0)) {
+        unsigned long long c;
+        asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
+        float *base = p.debug + (size_t)gridDim.x * 256 * 130;
+        reinterpret_cast<uint32_t *>(base)[(who * 16 + j) * 8 + k] = (uint32_t)c;
+    }
+}
+
 /* ---------------- roles ---------------- */
 
-__device__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmq, const CUtensorMap *tmk,
+/* Position in the K/V ring: items are consumed in load order K0 V0 K1 V1 ... */
+struct Ring {
+    int slot;
+    uint32_t phase;
+    __device__ __forceinline__ void next() {
+        if (++slot == kStages) {
+            slot = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmq, const CUtensorMap *tmk,
                          const CUtensorMap *tmv, uint32_t smem, int head, int q0, int ntq, int nkv) {
     const int col = head * kHeadDim;
     mbar_expect_tx(c.bars + BAR_Q_FULL * 8, ntq * kTileBytes);
@@ -274,14 +312,15 @@ __device__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmq, 
             tma_load_2d(smem + kSmemQ + t * kTileBytes + half * kHalfBytes, tmq, col + half * 64,
                         q0 + t * kTileQ, c.bars + BAR_Q_FULL * 8);
     int issued = 0;
-    for (int it = 0; it < 2 * nkv; it++, issued++) {
-        int slot = it % kStages, round = it / kStages;
-        if (round > 0 && !mbar_wait(c, BAR_KV_EMPTY + slot, (round - 1) & 1, 100 + slot)) break;
-        uint32_t full = c.bars + (BAR_KV_FULL + slot) * 8;
+    Ring r = {0, 0u};
+    for (int it = 0; it < 2 * nkv; it++, issued++, r.next()) {
+        /* A slot is refilled once the MMAs that read its previous content are done. */
+        if (it >= kStages && !mbar_wait(c, BAR_KV_EMPTY + r.slot, r.phase ^ 1u, 100 + r.slot)) break;
+        uint32_t full = c.bars + (BAR_KV_FULL + r.slot) * 8;
         mbar_expect_tx(full, kTileBytes);
         const CUtensorMap *map = (it & 1) ? tmv : tmk;
         for (int half = 0; half < 2; half++)
-            tma_load_2d(smem + kSmemKV + slot * kTileBytes + half * kHalfBytes, map, col + half * 64,
+            tma_load_2d(smem + kSmemKV + r.slot * kTileBytes + half * kHalfBytes, map, col + half * 64,
                         (it >> 1) * kTileK, full);
     }
     if (*c.abort_flag) {
@@ -291,51 +330,75 @@ __device__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmq, 
     }
 }
 
-__device__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem, int ntq, int nkv) {
-    uint32_t ok = 1;
-    /* it-th ring item: K_j is item 2j, V_j item 2j+1 */
-    auto wait_item = [&](int it, int site) {
-        return mbar_wait(c, BAR_KV_FULL + it % kStages, (it / kStages) & 1, site);
-    };
-    auto slot_addr = [&](int it) { return smem + kSmemKV + (it % kStages) * kTileBytes; };
-    auto issue_qk = [&](int t, int it) {
-        uint32_t qa = smem + kSmemQ + t * kTileBytes, ka = slot_addr(it);
+template <bool DEBUG>
+__device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem, int ntq, int nkv) {
+    /* Descriptor words that never change: the high word (stride offset,
+     * version, swizzle mode) per operand kind, and the low word of each
+     * tile base (start address and leading offset, 16-byte units). A k-step
+     * only adds a constant to the low word. */
+    const uint32_t hi_qk = (uint32_t)(make_desc(0, 0, p.qk_sbo) >> 32);
+    const uint32_t hi_v = (uint32_t)(make_desc(0, 0, p.v_sbo) >> 32);
+    const uint32_t lo_q0 = (uint32_t)make_desc(smem + kSmemQ, 1, 0);
+    const uint32_t lo_k0 = (uint32_t)make_desc(smem + kSmemKV, 1, 0);
+    const uint32_t lo_v0 = (uint32_t)make_desc(smem + kSmemKV, p.v_lbo, 0);
+    bool ok;
+
+    auto issue_qk = [&](int t, int slot) {
+        const uint32_t lo_q = lo_q0 + t * (kTileBytes >> 4), lo_k = lo_k0 + slot * (kTileBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < kHeadDim / 16; ks++) {
-            uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-            mma_ss(tmem + t * 128, make_desc(qa + off, 1, p.qk_sbo), make_desc(ka + off, 1, p.qk_sbo),
-                   kIdescQK, ks > 0);
+            if (DEBUG && (p.diag_mode & 4)) break;
+            const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+            mma_ss(tmem + t * 128, desc64(lo_q + off, hi_qk), desc64(lo_k + off, hi_qk), kIdescQK, ks > 0);
         }
         tc_commit(c.bars + (BAR_S_FULL + t) * 8);
     };
-    auto issue_pv = [&](int t, int it, int first) {
-        uint32_t va = slot_addr(it);
+    auto issue_pv = [&](int t, int slot, bool first) {
+        const uint32_t lo_v = lo_v0 + slot * (kTileBytes >> 4);
+        if (DEBUG && (p.diag_mode & 2)) {
+        } else if (first) {
 #pragma unroll
-        for (int ks = 0; ks < kTileK / 16; ks++)
-            mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8,
-                   make_desc(va + ks * 16 * 128, p.v_lbo, p.v_sbo), kIdescPV, (!first) || ks > 0);
+            for (int ks = 0; ks < kTileK / 16; ks++)
+                mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, desc64(lo_v + ks * (16 * 128 >> 4), hi_v),
+                       kIdescPV, ks > 0);
+        } else {
+#pragma unroll
+            for (int ks = 0; ks < kTileK / 16; ks++)
+                mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, desc64(lo_v + ks * (16 * 128 >> 4), hi_v),
+                       kIdescPV, 1);
+        }
         tc_commit(c.bars + (BAR_O_DONE + t) * 8);
     };
 
-    ok = mbar_wait(c, BAR_Q_FULL, 0, 200) && wait_item(0, 201);
+    Ring r = {0, 0u};
+    ok = mbar_wait(c, BAR_Q_FULL, 0, 200) && mbar_wait(c, BAR_KV_FULL + r.slot, r.phase, 201);
     if (ok) {
         tc_fence_after();
-        for (int t = 0; t < ntq; t++) issue_qk(t, 0);
-        tc_commit(c.bars + (BAR_KV_EMPTY + 0) * 8);
+        for (int t = 0; t < ntq; t++) issue_qk(t, r.slot);
+        tc_commit(c.bars + (BAR_KV_EMPTY + r.slot) * 8);
+        r.next();
     }
     for (int j = 0; ok && j < nkv; j++) {
-        int itv = 2 * j + 1, itk = 2 * j + 2;
-        if (!(ok = wait_item(itv, 210))) break;
+        const Ring rv = r;              /* V_j */
+        r.next();
+        const Ring rk = r;              /* K_{j+1}, when there is one */
+        const bool more = j + 1 < nkv;
+        if (more) r.next();
+        if (!(ok = mbar_wait(c, BAR_KV_FULL + rv.slot, rv.phase, 210))) break;
         for (int t = 0; t < ntq; t++) {
+            if (DEBUG) stamp(p, 2, j, 4 * t);
             if (!(ok = mbar_wait(c, BAR_P_FULL + t, j & 1, 220 + t))) break;
             tc_fence_after();
-            issue_pv(t, itv, j == 0);
-            if (t == ntq - 1) tc_commit(c.bars + (BAR_KV_EMPTY + itv % kStages) * 8);
-            if (j + 1 < nkv) {
-                if (t == 0 && !(ok = wait_item(itk, 230))) break;
+            if (DEBUG) stamp(p, 2, j, 4 * t + 1);
+            issue_pv(t, rv.slot, j == 0);
+            if (t == ntq - 1) tc_commit(c.bars + (BAR_KV_EMPTY + rv.slot) * 8);
+            if (more) {
+                if (t == 0 && !(ok = mbar_wait(c, BAR_KV_FULL + rk.slot, rk.phase, 230))) break;
                 tc_fence_after();
-                issue_qk(t, itk);
-                if (t == ntq - 1) tc_commit(c.bars + (BAR_KV_EMPTY + itk % kStages) * 8);
+                if (DEBUG) stamp(p, 2, j, 4 * t + 2);
+                issue_qk(t, rk.slot);
+                if (t == ntq - 1) tc_commit(c.bars + (BAR_KV_EMPTY + rk.slot) * 8);
+                if (DEBUG) stamp(p, 2, j, 4 * t + 3);
             }
         }
     }
@@ -367,8 +430,29 @@ __device__ __forceinline__ void mask_chunk(uint32_t *v, uint32_t bits) {
         if (!((bits >> i) & 1u)) v[i] = 0xFF800000u;
 }
 
+/* One S row -> P (bf16 pairs into the first 64 columns of S) and the four
+ * partial row sums. POLY: one exponential in four runs on the FMA pipe. */
+template <bool POLY>
+__device__ __forceinline__ void exp_row(const uint32_t *s, float sl2, float neg_ref, float *sum4, uint32_t tS) {
+#pragma unroll
+    for (int ch = 0; ch < 4; ch++) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            float x0 = fmaf(__uint_as_float(s[ch * 32 + 2 * i]), sl2, neg_ref);
+            float x1 = fmaf(__uint_as_float(s[ch * 32 + 2 * i + 1]), sl2, neg_ref);
+            float p0 = ex2(x0);
+            float p1 = (POLY && (i & 1)) ? ex2_poly(x1) : ex2(x1);
+            sum4[(2 * i) & 3] += p0;
+            sum4[(2 * i + 1) & 3] += p1;
+            pk[i] = cvt_bf16x2(p0, p1);
+        }
+        tmem_st16(tS + ch * 16, pk);
+    }
+}
+
 template <bool DEBUG>
-__device__ void softmax_wg(const Ctx &c, const Params &p, uint32_t tmem, int t, int head, int q0, int nkv) {
+__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32_t tmem, int t, int head, int q0, int nkv) {
     const int row = threadIdx.x & 127;                     /* row of the tile == TMEM lane */
     const uint32_t lane_base = (uint32_t)(row & ~31) << 16;
     const uint32_t tS = tmem + lane_base + t * 128;
@@ -383,29 +467,43 @@ __device__ void softmax_wg(const Ctx &c, const Params &p, uint32_t tmem, int t, 
         /* One decision per warp: the TMEM accesses below are warp-collective. */
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_S_FULL + t, j & 1, 300 + t)))) break;
         tc_fence_after();
+        if (DEBUG) stamp(p, t, j, 0);
+        if (DEBUG && (p.diag_mode & 1)) {
+            tc_fence_before();
+            mbar_arrive(c.bars + (BAR_P_FULL + t) * 8);
+            continue;
+        }
 
         const bool partial = (j == nkv - 1 && (p.seq_k & (kTileK - 1)) != 0) || p.mask_bits != nullptr;
         uint32_t bits[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
         if (partial) tile_bits(p, j, bits);
 
-        /* Pass 1: row maximum, 32 columns at a time, next chunk in flight. */
-        uint32_t v[2][32];
-        float mx = -INFINITY;
-        tmem_ld32(tS, v[0]);
+        /* The whole S row of this thread: four loads in flight, one wait. */
+        uint32_t s[128];
 #pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-            tc_wait_ld();
-            if (ch < 3) tmem_ld32(tS + (ch + 1) * 32, v[(ch + 1) & 1]);
-            uint32_t *cur = v[ch & 1];
-            if (DEBUG && p.debug && j == 0) {
-                float *dst = p.debug + ((size_t)blockIdx.x * 256 + t * 128 + row) * 128 + ch * 32;
+        for (int ch = 0; ch < 4; ch++) tmem_ld32(tS + ch * 32, s + ch * 32);
+        tc_wait_ld();
+        if (DEBUG) stamp(p, t, j, 1);
+        if (DEBUG && p.debug && j == 0) {
+            float *dst = p.debug + ((size_t)blockIdx.x * 256 + t * 128 + row) * 128;
 #pragma unroll
-                for (int i = 0; i < 32; i++) dst[i] = __uint_as_float(cur[i]);
-            }
-            if (partial) mask_chunk(cur, bits[ch]);
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
+            for (int i = 0; i < 128; i++) dst[i] = __uint_as_float(s[i]);
         }
+        if (partial) {
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) mask_chunk(s + ch * 32, bits[ch]);
+        }
+        /* Row maximum over eight independent chains. */
+        float mx8[8];
+#pragma unroll
+        for (int a = 0; a < 8; a++) mx8[a] = fmaxf(__uint_as_float(s[2 * a]), __uint_as_float(s[2 * a + 1]));
+#pragma unroll
+        for (int i = 16; i < 128; i += 16) {
+#pragma unroll
+            for (int a = 0; a < 8; a++)
+                mx8[a] = max3(mx8[a], __uint_as_float(s[i + 2 * a]), __uint_as_float(s[i + 2 * a + 1]));
+        }
+        float mx = fmaxf(max3(mx8[0], mx8[1], mx8[2]), max3(mx8[3], mx8[4], fmaxf(mx8[5], fmaxf(mx8[6], mx8[7]))));
         float m_cand = fmaxf(m_ref, mx * sl2);
 
         if (j == 0) {
@@ -421,44 +519,36 @@ __device__ void softmax_wg(const Ctx &c, const Params &p, uint32_t tmem, int t, 
                     l *= alpha;
                     m_ref = m_cand;
                 }
-#pragma unroll
+#pragma unroll 1
                 for (int i = 0; i < 4; i++) {
-                    tmem_ld32(tO + i * 32, v[0]);
+                    uint32_t o[32];
+                    tmem_ld32(tO + i * 32, o);
                     tc_wait_ld();
 #pragma unroll
-                    for (int e = 0; e < 32; e++) v[0][e] = __float_as_uint(__uint_as_float(v[0][e]) * alpha);
-                    tmem_st32(tO + i * 32, v[0]);
+                    for (int e = 0; e < 32; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                    tmem_st32(tO + i * 32, o);
                 }
             }
         }
 
-        /* Pass 2: P = 2^(s * scale_log2 - m_ref) as bf16 pairs over the first
-         * 64 columns of S. Chunk ch reads S columns [32ch, 32ch + 32) and
-         * writes P columns [16ch, 16ch + 16), all of them already consumed. */
+        /* P = 2^(s * scale_log2 - m_ref) as bf16 pairs over the first 64
+         * columns of S (the row is in registers, so nothing is lost). One
+         * exponential in four is evaluated on the FMA pipe instead of the
+         * special-function unit, which is the scarcer of the two here. */
         const float neg_ref = m_ref == -INFINITY ? 0.0f : -m_ref;
-        float sum0 = 0.0f, sum1 = 0.0f;
-        tmem_ld32(tS, v[0]);
-#pragma unroll
-        for (int ch = 0; ch < 4; ch++) {
-            tc_wait_ld();
-            if (ch < 3) tmem_ld32(tS + (ch + 1) * 32, v[(ch + 1) & 1]);
-            uint32_t *cur = v[ch & 1];
-            if (partial) mask_chunk(cur, bits[ch]);
-            uint32_t pk[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                float p0 = ex2(fmaf(__uint_as_float(cur[2 * i]), sl2, neg_ref));
-                float p1 = ex2(fmaf(__uint_as_float(cur[2 * i + 1]), sl2, neg_ref));
-                sum0 += p0;
-                sum1 += p1;
-                pk[i] = cvt_bf16x2(p0, p1);
-            }
-            tmem_st16(tS + ch * 16, pk);
-        }
+        float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (DEBUG) stamp(p, t, j, 2);
+        /* Tiles with masked (-inf) scores keep every exponential on the
+         * special-function unit, which returns an exact 0 for them. */
+        if (partial) exp_row<false>(s, sl2, neg_ref, sum4, tS);
+        else exp_row<kPolyExp>(s, sl2, neg_ref, sum4, tS);
+        if (DEBUG) stamp(p, t, j, 3);
+        float sum0 = sum4[0] + sum4[2], sum1 = sum4[1] + sum4[3];
         l += sum0 + sum1;
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(c.bars + (BAR_P_FULL + t) * 8);
+        if (DEBUG) stamp(p, t, j, 4);
     }
 
     /* Epilogue: O / l -> bf16 rows of the output slice of this head. */
@@ -589,10 +679,15 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     const uint32_t tmem = *tmem_slot;
 
     if (warp < 8) {
+        /* The third warpgroup hands most of its registers to the softmax ones. */
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
         if (warp < 4 * ntq) softmax_wg<DEBUG>(c, p, tmem, warp >> 2, head, q0, nkv);
-    } else if (lane == 0) {
-        if (warp == 8) producer(c, p, &tmq, &tmk, &tmv, smem, head, q0, ntq, nkv);
-        else mma_issuer(c, p, smem, tmem, ntq, nkv);
+    } else {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
+        if (lane == 0) {
+            if (warp == 8) producer(c, p, &tmq, &tmk, &tmv, smem, head, q0, ntq, nkv);
+            else if (warp == 9) mma_issuer<DEBUG>(c, p, smem, tmem, ntq, nkv);
+        }
     }
 
     tc_fence_before();
@@ -689,6 +784,7 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, const uint
                            const int *key_mask, int acc_mode, float *o_acc, float *lse_acc,
                            float *debug, const uint32_t *desc_override) {
     using namespace sm100;
+    const int diag_mode = desc_override ? (int)desc_override[3] : 0;
     static int configured = 0;
     if (!configured) {
         if (!cuda_ok(cudaFuncSetAttribute(k_attention_sm100<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -749,6 +845,7 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, const uint
     p.v_lbo = desc_override ? desc_override[1] : kHalfBytes / 16;   /* next 64-dim half */
     p.v_sbo = desc_override ? desc_override[2] : 1024 / 16;         /* next 8 keys */
     p.debug = debug;
+    p.diag_mode = diag_mode;
     unsigned grid = (unsigned)(p.nqblk * heads);
     if (debug)
         k_attention_sm100<true><<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk, tmv, p);

@@ -22,7 +22,8 @@
 
 namespace iris_b200 {
 
-static constexpr int kUnroll = 4;        /* units in flight per 16-lane group */
+static constexpr int kUnroll = 2;        /* units in flight per 16-lane group */
+static constexpr int kBlocksPerSM = 5;   /* register budget: 65536 / (5 * 256) = 51 */
 static constexpr int kThreads = 256;
 
 struct alignas(16) Vec8 {
@@ -30,7 +31,7 @@ struct alignas(16) Vec8 {
 };
 
 template <bool SPLIT_HALF>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, kBlocksPerSM)
 k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
                      const float *__restrict__ wq, const float *__restrict__ wk,
                      const float *__restrict__ rope_cos, const float *__restrict__ rope_sin,
@@ -41,13 +42,8 @@ k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
     const int per_tok = k ? 2 * heads : heads;      /* units of one token: Q heads then K heads */
     const long long units = (long long)seq * per_tok;
 
-    /* This lane always owns dims [8 * lane16, 8 * lane16 + 8) of a head. */
-    float wqv[8], wkv[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        wqv[i] = wq[lane16 * 8 + i];
-        wkv[i] = k ? wk[lane16 * 8 + i] : 0.0f;
-    }
+    /* This lane always owns dims [8 * lane16, 8 * lane16 + 8) of a head; its
+     * eight weights are re-read (L1 hits) per unit to keep registers low. */
     /* Pairs whose angle this lane needs: consecutive -> pairs 4l..4l+3;
      * split-half -> pairs 8(l & 7)..+7, shared with lane l ^ 8. */
     const int rope_off = SPLIT_HALF ? (lane16 & 7) * 8 : lane16 * 4;
@@ -85,8 +81,12 @@ k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
 #pragma unroll
             for (int o = 1; o < 16; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
-#pragma unroll
-            for (int j = 0; j < 8; j++) x[j] *= inv * (isk[i] ? wkv[j] : wqv[j]);
+            {
+                const float4 *wp = reinterpret_cast<const float4 *>((isk[i] ? wk : wq) + lane16 * 8);
+                float4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
+                x[0] *= inv * w0.x; x[1] *= inv * w0.y; x[2] *= inv * w0.z; x[3] *= inv * w0.w;
+                x[4] *= inv * w1.x; x[5] *= inv * w1.y; x[6] *= inv * w1.z; x[7] *= inv * w1.w;
+            }
 
             if (SPLIT_HALF) {
                 float c[8], sn[8];
@@ -119,7 +119,7 @@ k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
             if (ok) {
                 Vec8 o;
 #pragma unroll
-                for (int j = 0; j < 4; j++) o.w[j] = pack_bf16x2(x[2 * j], x[2 * j + 1]);
+                for (int j = 0; j < 4; j++) o.w[j] = cvt_bf16x2(x[2 * j], x[2 * j + 1]);
                 *reinterpret_cast<Vec8 *>(ptr[i]) = o;
             }
         }
@@ -166,12 +166,12 @@ static int launch_prologue(uint16_t *q, uint16_t *k, int ld, const float *wq, co
         return IRIS_B200_EINVAL;
     }
     bool fast = head_dim == 128 && ld % 8 == 0 && aligned16(q) && (!k || aligned16(k)) &&
-                aligned16(rope_cos) && aligned16(rope_sin);
+                aligned16(rope_cos) && aligned16(rope_sin) && aligned16(wq) && (!k || aligned16(wk));
     if (fast) {
         long long units = (long long)seq * heads * (k ? 2 : 1);
         long long groups = (units + kUnroll - 1) / kUnroll;
         long long blocks = (groups * 16 + kThreads - 1) / kThreads;
-        long long cap = (long long)g.sm_count * 8;     /* 8 x 256 threads fill an SM */
+        long long cap = (long long)g.sm_count * kBlocksPerSM;   /* one resident wave */
         if (blocks > cap) blocks = cap;
         if (split_half)
             k_head_norm_rope_128<true><<<(unsigned)blocks, kThreads, 0, g.stream>>>(
