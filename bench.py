@@ -206,16 +206,42 @@ def run_b200(args):
         import torch.distributed as dist
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    name = args.workload or ("klein4b-1024" if world == 1 else "klein9b-cfg")
+    ring = args.mode == "ring"
+    name = args.workload or ("flux3-multiref" if ring else "klein4b-1024" if world == 1 else "klein9b-cfg")
     w = WORKLOADS[name]
     lib = load_lib()
     lib.init(local)
-    S, H = seq_len(w), w["heads"]
-    shard = shard_of(w, rank, world)
-    entries, h0, nh = shard if shard else ([], 0, 0)
-    width = nh * D                                  # this rank's column slice of every tensor
+    S_full, H = seq_len(w), w["heads"]
     cos, sin = rope_tables(w)
-    assert cos.shape == (S, 64)
+    assert cos.shape == (S_full, 64)
+    if ring:
+        # Sequence parallel: this rank owns a block of token rows (all heads);
+        # K/V chunks go round the ring inside iris_b200_ring_attention().
+        assert w["batch"] == 1
+        rows_of = np.zeros(world, np.int32)
+        a, b = C.c_int(), C.c_int()
+        row0 = 0
+        for r in range(world):
+            lib.iris_b200_seq_shard(S_full, world, r, C.byref(a), C.byref(b))
+            rows_of[r] = b.value
+            if r == rank:
+                row0 = a.value
+        S = int(rows_of[rank])
+        cos, sin = np.ascontiguousarray(cos[row0:row0 + S]), np.ascontiguousarray(sin[row0:row0 + S])
+        entries, h0, nh = [0], 0, H
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            buf = C.create_string_buffer(128)
+            assert lib.iris_b200_ring_unique_id(buf) == 0
+            ident = torch.tensor(list(buf.raw), dtype=torch.uint8, device="cuda")
+        if dist:
+            dist.broadcast(ident, src=0)
+        assert lib.iris_b200_ring_init(rank, world, bytes(ident.cpu().tolist())) == 0
+    else:
+        S = S_full
+        shard = shard_of(w, rank, world)
+        entries, h0, nh = shard if shard else ([], 0, 0)
+    width = nh * D                                  # this rank's column slice of every tensor
     d_cos, d_sin = lib.to_device(cos), lib.to_device(sin)
     d_w = lib.to_device(np.ones(D, np.float32))
     scale = 1.0 / np.sqrt(D)
@@ -241,7 +267,11 @@ def run_b200(args):
             lib.iris_b200_qk_norm_rope(q, k, 3 * width, d_w, d_w, d_cos, d_sin, S, nh, D, w["eps"], 0)
             if mark is not None:
                 lib.iris_b200_mark(mark)
-            lib.iris_dev_attention(dout, width, q, k, v, 3 * width, S, S, nh, nh, D, scale, 0, None)
+            if ring:
+                rc = lib.iris_b200_ring_attention(dout, width, q, k, v, 3 * width, rows_of.ctypes.data, nh, scale)
+                assert rc == 0, rc
+            else:
+                lib.iris_dev_attention(dout, width, q, k, v, 3 * width, S, S, nh, nh, D, scale, 0, None)
             if mark is not None:
                 lib.iris_b200_mark(mark + 1)
 
@@ -274,7 +304,7 @@ def run_b200(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
-    total_flops = attn_flops(w["batch"], H, S, S)
+    total_flops = attn_flops(w["batch"], H, S_full, S_full)
     value = total_flops / (ms_step * 1e-3) / 1e12
 
     # Dominant kernel alone (rank 0): mean launch duration from the marks.
@@ -285,7 +315,7 @@ def run_b200(args):
         durs = [d for d in durs if d > 0]
         if durs:
             kms = sum(durs) / len(durs)
-            achieved = attn_flops(1, nh, S, S) / (kms * 1e-3) / 1e12
+            achieved = attn_flops(1, nh, S, S_full) / (kms * 1e-3) / 1e12
             roof = {"bound": "tensor", "kernel": "k_attention_sm100", "achieved": round(achieved, 1),
                     "peak": bf16_peak, "peak_source": src + " bf16 burst", "unit": "TFLOP/s",
                     "frac": round(achieved / bf16_peak, 4), "frac_of_sustained": round(achieved / bf16_sust, 4),
@@ -323,6 +353,8 @@ def run_b200(args):
         t = torch.tensor([0.0], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     lib.check()
+    if ring:
+        lib.iris_b200_ring_destroy()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -335,8 +367,9 @@ def run_b200(args):
             "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": name, "batch": w["batch"], "heads": H, "head_dim": D, "tokens": S,
-                       "step": "qk_norm_rope + attention", "sharding": "none" if world == 1 else
+            "config": {"workload": name, "batch": w["batch"], "heads": H, "head_dim": D, "tokens": S_full,
+                       "step": "qk_norm_rope + attention", "sharding": "none" if world == 1 and not ring else
+                       "ring sequence parallel (NCCL send/recv of K/V chunks)" if ring else
                        "cfg batch x heads, no collective", "l2": "inputs rotate over %d buffer sets (%.0f MB)" %
                        (nsets, nsets * per_set / 1e6)},
             "per_gpu_tflops": round(value / world, 2),
@@ -471,6 +504,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--mode", default="shard", choices=["shard", "ring"],
+                    help="N > 1: independent cfg/head shards (default) or ring sequence parallelism")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -105,6 +105,59 @@ int iris_b200_attention_kernel_for(const void *out, int ldo, const void *q, cons
                                    const void *v, int ldi, int heads, int kv_heads,
                                    int head_dim, int causal);
 
+/* ---- multi-GPU decompositions (one process per GPU) ------------------------ */
+
+/* Heads [first, first + count) of rank `rank` when `heads` are split over
+ * `nranks`: the first heads % nranks ranks take one head more (30 heads over
+ * 8 ranks: 4 4 4 4 4 4 3 3). A rank then runs the ordinary attention on the
+ * column slice [first * head_dim, (first + count) * head_dim) of q, k, v and
+ * out: heads are independent, nothing is exchanged. */
+int iris_b200_head_shard(int heads, int nranks, int rank, int *first, int *count);
+
+/* Classifier-free guidance runs `batch` independent passes over the same
+ * image tokens (cond / uncond, iris_sample.c:698-712 in the reference runs
+ * them one after the other). The ranks form min(batch, nranks) groups; rank
+ * `rank` takes the entries first_entry, first_entry + entry_stride, ... and,
+ * inside its group, the heads [first_head, first_head + head_count). */
+int iris_b200_cfg_shard(int batch, int heads, int nranks, int rank,
+                        int *first_entry, int *entry_stride, int *first_head, int *head_count);
+
+/* Token rows [first, first + count) of a rank under sequence parallelism. */
+int iris_b200_seq_shard(int seq, int nranks, int rank, int *first, int *count);
+
+/* Rank whose K/V chunk is resident on `rank` at ring step `step`. */
+int iris_b200_ring_source(int rank, int step, int nranks);
+
+/* Attention of seq_q queries over ONE chunk of seq_k keys, merged into a
+ * state carried between chunks: o_state [seq_q, heads * 128] fp32 (the
+ * normalised output over the keys seen so far) and lse_state [heads, seq_q]
+ * fp32 (their log2-sum-exp). first: the state is written, not read. last:
+ * the merged result is written to `out` as bf16 and the state is left as it
+ * is. first && last is the plain attention (state may be NULL). q has row
+ * stride ldq, k and v share ldkv. tcgen05 kernel domain only (head_dim 128,
+ * aligned views); key_mask covers this chunk's keys. Used for split-K on one
+ * GPU and for every step of the ring. */
+int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq,
+                              const uint16_t *k, const uint16_t *v, int ldkv,
+                              int seq_q, int seq_k, int heads, float scale,
+                              const int *key_mask, float *o_state, float *lse_state,
+                              int first, int last);
+
+/* Ring sequence parallelism over NCCL (loaded at run time). One rank calls
+ * ring_unique_id(), the 128-byte id is handed to every rank by the caller's
+ * own means, then every rank calls ring_init(). ring_attention(): q, k, v are
+ * this rank's token rows (rows_of[rank] of them, row stride ldi), rows_of
+ * lists the row count of every rank; out receives the attention of the local
+ * queries over the keys of ALL ranks. K/V chunks travel to the next rank on a
+ * second stream while the attention of the resident chunk runs; a received
+ * chunk is in this GPU's memory before any kernel reads it. */
+int iris_b200_ring_unique_id(void *id128);
+int iris_b200_ring_init(int rank, int nranks, const void *id128);
+int iris_b200_ring_attention(uint16_t *out, int ldo,
+                             const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                             int ldi, const int *rows_of, int heads, float scale);
+void iris_b200_ring_destroy(void);
+
 /* Diagnostics for kernel bring-up: runs the tcgen05 kernel and dumps, into
  * `debug` (device, fp32), the raw scores S = Q K^T of the first key tile of
  * every CTA ([ctas * 256, 128]) followed by (m, l) per row ([ctas * 256, 2]);

@@ -50,6 +50,15 @@ SIGNATURES = {
     "iris_b200_qk_norm_rope": (INT, [VP, VP, INT, VP, VP, VP, VP, INT, INT, INT, FLT, INT]),
     "iris_b200_attention_ex": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP, INT]),
     "iris_b200_attention_kernel_for": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT]),
+    "iris_b200_head_shard": (INT, [INT, INT, INT, C.POINTER(INT), C.POINTER(INT)]),
+    "iris_b200_cfg_shard": (INT, [INT, INT, INT, INT, C.POINTER(INT), C.POINTER(INT), C.POINTER(INT), C.POINTER(INT)]),
+    "iris_b200_seq_shard": (INT, [INT, INT, INT, C.POINTER(INT), C.POINTER(INT)]),
+    "iris_b200_ring_source": (INT, [INT, INT, INT]),
+    "iris_b200_attention_chunk": (INT, [VP, INT, VP, INT, VP, VP, INT, INT, INT, INT, FLT, VP, VP, VP, INT, INT]),
+    "iris_b200_ring_unique_id": (INT, [VP]),
+    "iris_b200_ring_init": (INT, [INT, INT, VP]),
+    "iris_b200_ring_attention": (INT, [VP, INT, VP, VP, VP, INT, VP, INT, FLT]),
+    "iris_b200_ring_destroy": (None, []),
     "iris_b200_attention_diag": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, FLT, VP, VP, VP]),
 }
 

@@ -47,7 +47,7 @@ extern "C" int iris_b200_attention_ex(uint16_t *out, int ldo,
     }
     if (kernel == IRIS_B200_KERNEL_GENERIC) fast = false;
     if (fast)
-        return launch_attention_sm100(out, ldo, q, k, v, ldi, seq_q, seq_k, heads, scale, key_mask,
+        return launch_attention_sm100(out, ldo, q, ldi, k, v, ldi, seq_q, seq_k, heads, scale, key_mask,
                                       0, NULL, NULL, NULL, NULL);
     return launch_attention_generic(out, ldo, q, k, v, ldi, seq_q, seq_k, heads, kv_heads, head_dim,
                                     scale, causal, key_mask);
@@ -74,6 +74,6 @@ extern "C" int iris_b200_attention_diag(uint16_t *out, int ldo,
         set_error(IRIS_B200_EUNSUPPORTED, "attention_diag", "arguments outside the tcgen05 kernel's domain");
         return IRIS_B200_EUNSUPPORTED;
     }
-    return launch_attention_sm100(out, ldo, q, k, v, ldi, seq_q, seq_k, heads, scale, key_mask,
+    return launch_attention_sm100(out, ldo, q, ldi, k, v, ldi, seq_q, seq_k, heads, scale, key_mask,
                                   0, NULL, NULL, debug, desc_fields);
 }

@@ -779,8 +779,8 @@ static uint32_t *g_mask_bits = NULL;
 static size_t g_mask_words = 0;
 
 /* acc_mode / o_acc / lse_acc: see sm100::Params. debug: bring-up dump. */
-int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, const uint16_t *k,
-                           const uint16_t *v, int ldi, int seq_q, int seq_k, int heads, float scale,
+int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k,
+                           const uint16_t *v, int ldkv, int seq_q, int seq_k, int heads, float scale,
                            const int *key_mask, int acc_mode, float *o_acc, float *lse_acc,
                            float *debug, const uint32_t *desc_override) {
     using namespace sm100;
@@ -827,8 +827,8 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, const uint
         p.mask_bits = g_mask_bits;
     }
     CUtensorMap tmq, tmk, tmv;
-    if (!make_map(&tmq, q, seq_q, heads * kHeadDim, ldi) || !make_map(&tmk, k, seq_k, heads * kHeadDim, ldi) ||
-        !make_map(&tmv, v, seq_k, heads * kHeadDim, ldi))
+    if (!make_map(&tmq, q, seq_q, heads * kHeadDim, ldq) || !make_map(&tmk, k, seq_k, heads * kHeadDim, ldkv) ||
+        !make_map(&tmv, v, seq_k, heads * kHeadDim, ldkv))
         return IRIS_B200_ECUDA;
     p.out = out;
     p.ldo = ldo;

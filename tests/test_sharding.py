@@ -1,0 +1,142 @@
+"""Host-side logic of the multi-GPU decompositions, on CPU: shard arithmetic
+of the C library, and the ring schedule + state merge run as two gloo ranks
+with the CPU oracle standing in for the attention kernel."""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as ge
+    if not os.path.exists(os.path.join(ge.PKG_DIR, "libiris_b200.so")):
+        ge.build()
+    return ge.load_package().Lib()
+
+
+def head_shard(lib, heads, n, r):
+    a, b = C.c_int(), C.c_int()
+    assert lib.iris_b200_head_shard(heads, n, r, C.byref(a), C.byref(b)) == 0
+    return a.value, b.value
+
+
+def test_head_shards_cover_heads_exactly(lib):
+    assert [head_shard(lib, 30, 8, r)[1] for r in range(8)] == [4, 4, 4, 4, 4, 4, 3, 3]
+    assert [head_shard(lib, 30, 4, r)[1] for r in range(4)] == [8, 8, 7, 7]
+    for heads in (24, 30, 32, 7, 1):
+        for n in (1, 2, 3, 4, 8, 9):
+            spans = [head_shard(lib, heads, n, r) for r in range(n)]
+            pos = 0
+            for first, count in spans:
+                assert first == pos and count >= 0
+                pos += count
+            assert pos == heads
+            counts = [c for _, c in spans]
+            assert max(counts) - min(counts) <= 1
+    a, b = C.c_int(), C.c_int()
+    assert lib.iris_b200_head_shard(24, 4, 4, C.byref(a), C.byref(b)) == 1      # rank out of range
+    assert lib.iris_b200_head_shard(24, 0, 0, C.byref(a), C.byref(b)) == 1
+
+
+def cfg_shard(lib, batch, heads, n, r):
+    v = [C.c_int() for _ in range(4)]
+    assert lib.iris_b200_cfg_shard(batch, heads, n, r, *[C.byref(x) for x in v]) == 0
+    return tuple(x.value for x in v)
+
+
+def test_cfg_split_assigns_every_entry_head_once(lib):
+    # cond / uncond x 32 heads (the 9B base model) over 1, 2, 4, 8 GPUs
+    for n in (1, 2, 4, 8, 3, 5):
+        seen = np.zeros((2, 32), int)
+        for r in range(n):
+            e0, es, h0, nh = cfg_shard(lib, 2, 32, n, r)
+            for e in range(e0, 2, es):
+                seen[e, h0:h0 + nh] += 1
+        assert (seen == 1).all(), (n, seen)
+    assert cfg_shard(lib, 2, 32, 2, 1) == (1, 2, 0, 32)
+    assert cfg_shard(lib, 2, 32, 8, 5) == (1, 2, 8, 8)
+    assert cfg_shard(lib, 2, 32, 1, 0) == (0, 1, 0, 32)
+
+
+def test_ring_schedule_visits_every_chunk_once(lib):
+    for n in (1, 2, 4, 8):
+        for r in range(n):
+            src = [lib.iris_b200_ring_source(r, s, n) for s in range(n)]
+            assert sorted(src) == list(range(n)) and src[0] == r
+            # what arrives at step s + 1 is what the previous rank held at step s
+            for s in range(n - 1):
+                assert src[s + 1] == lib.iris_b200_ring_source((r - 1) % n, s, n)
+    assert lib.iris_b200_ring_source(0, 0, 0) == -1
+    a, b = C.c_int(), C.c_int()
+    assert lib.iris_b200_seq_shard(16896, 8, 3, C.byref(a), C.byref(b)) == 0 and (a.value, b.value) == (6336, 2112)
+
+
+WORKER = r'''
+import os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+sys.path.insert(0, os.path.join(ROOT, "tests")); sys.path.insert(0, ROOT)
+import oracle_lib as ol
+import __graft_entry__ as ge
+lib = ge.load_package().Lib()
+dist.init_process_group("gloo")
+rank, world = dist.get_rank(), dist.get_world_size()
+H, D, S = 2, 128, 150                       # 150 rows: uneven 75 / 75, 3 ranks would be 50 each
+import ctypes as C
+a, b = C.c_int(), C.c_int()
+rows_of = []
+for r in range(world):
+    lib.iris_b200_seq_shard(S, world, r, C.byref(a), C.byref(b)); rows_of.append((a.value, b.value))
+q, k, v = (ol.randn(10 + i, S, H * D) for i in range(3))
+r0, n = rows_of[rank]
+ql = q[r0:r0 + n]
+chunk = np.concatenate([k[r0:r0 + n], v[r0:r0 + n]], 1)
+out = np.zeros((n, H * D), np.float32); lse = np.full((n, H), -np.inf, np.float32)
+scale = 1 / np.sqrt(D)
+for s in range(world):
+    src = lib.iris_b200_ring_source(rank, s, world)
+    assert chunk.shape[0] == rows_of[src][1]
+    if s + 1 < world:                        # forward the resident chunk, receive the next
+        nxt_src = lib.iris_b200_ring_source(rank, s + 1, world)
+        recv = torch.empty((rows_of[nxt_src][1], 2 * H * D))
+        ops = [dist.P2POp(dist.isend, torch.from_numpy(chunk.copy()), (rank + 1) % world),
+               dist.P2POp(dist.irecv, recv, (rank - 1) % world)]
+        reqs = dist.batch_isend_irecv(ops)
+    kc, vc = chunk[:, :H * D], chunk[:, H * D:]
+    # chunk attention on the CPU oracle + its log2-sum-exp, merged like the kernel does
+    o_c = ol.dev_attention(ql, kc, vc, H)
+    sc = np.einsum("qhd,khd->hqk", ql.reshape(n, H, D), kc.reshape(-1, H, D)) * scale * np.log2(np.e)
+    lse_c = np.log2(np.exp2(sc - sc.max(2, keepdims=True)).sum(2)) + sc.max(2)          # [H, n]
+    lse_c = lse_c.T
+    new = np.logaddexp2(lse, lse_c)
+    wp, wc = np.exp2(lse - new), np.exp2(lse_c - new)
+    out = (out.reshape(n, H, D) * wp[:, :, None] + o_c.reshape(n, H, D) * wc[:, :, None]).reshape(n, H * D)
+    lse = new
+    if s + 1 < world:
+        for rq in reqs: rq.wait()
+        chunk = recv.numpy().copy()
+want = ol.dev_attention(q, k, v, H)[r0:r0 + n]
+err = float(np.abs(out - want).max())
+res = torch.tensor([err]); dist.all_reduce(res, op=dist.ReduceOp.MAX)
+if rank == 0: print("RING_MAX_ERR %.3e" % res.item())
+dist.destroy_process_group()
+'''
+
+
+def test_ring_schedule_and_merge_on_two_gloo_ranks(lib, tmp_path):
+    script = tmp_path / "ring_worker.py"
+    script.write_text("ROOT = %r\n" % ROOT + WORKER)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29431", str(script)],
+                         capture_output=True, text=True, env=env, timeout=240)
+    assert out.returncode == 0, out.stdout + out.stderr
+    line = [l for l in out.stdout.splitlines() if l.startswith("RING_MAX_ERR")][0]
+    assert float(line.split()[1]) < 2e-5
