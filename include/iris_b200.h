@@ -158,6 +158,30 @@ int iris_b200_ring_attention(uint16_t *out, int ldo,
                              int ldi, const int *rows_of, int heads, float scale);
 void iris_b200_ring_destroy(void);
 
+/* ---- attention without any allocation --------------------------------------- */
+
+/* No counterpart in the reference. Split-K attention (the keys are walked in
+ * `nsplit` chunks whose partial results are merged through a carried state)
+ * for callers that are not allowed to allocate device memory where they run
+ * attention: threads with real-time deadlines that must stay off the
+ * driver's allocator lock, hosts that gave away their whole memory budget at
+ * start-up. The carried state lives in a fixed 16.1 MiB array inside the
+ * library image (held on every GPU that loads the library until exit), so
+ * the call performs no cudaMalloc / cudaFree and calls no allocating routine.
+ *
+ * Limits: seq_q * heads * 128 <= iris_b200_attention_noalloc_max_elems()
+ * (4 Mi), else IRIS_B200_EINVAL with a message; tcgen05 kernel domain only
+ * (head_dim 128, heads == kv_heads, non-causal, aligned views, no key mask).
+ * The first call on a device looks up the array's device address; make that
+ * call before any stream capture. All calls share the array: calls whose
+ * kernels may overlap on the GPU race on it (calls on the library's one
+ * stream are ordered, hence safe). */
+int iris_b200_attention_noalloc(uint16_t *out, int ldo,
+                                const uint16_t *q, const uint16_t *k, const uint16_t *v,
+                                int ldi, int seq_q, int seq_k, int heads, float scale,
+                                int nsplit);
+size_t iris_b200_attention_noalloc_max_elems(void);
+
 /* Diagnostics for kernel bring-up: runs the tcgen05 kernel and dumps, into
  * `debug` (device, fp32), the raw scores S = Q K^T of the first key tile of
  * every CTA ([ctas * 256, 128]) followed by (m, l) per row ([ctas * 256, 2]);

@@ -59,6 +59,8 @@ SIGNATURES = {
     "iris_b200_ring_init": (INT, [INT, INT, VP]),
     "iris_b200_ring_attention": (INT, [VP, INT, VP, VP, VP, INT, VP, INT, FLT]),
     "iris_b200_ring_destroy": (None, []),
+    "iris_b200_attention_noalloc": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, FLT, INT]),
+    "iris_b200_attention_noalloc_max_elems": (SZ, []),
     "iris_b200_attention_diag": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, FLT, VP, VP, VP]),
 }
 
