@@ -37,10 +37,9 @@ k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
                      const float *__restrict__ rope_cos, const float *__restrict__ rope_sin,
                      int seq, int heads, float eps) {
     const int lane16 = threadIdx.x & 15;
-    const long long group = ((long long)blockIdx.x * kThreads + threadIdx.x) >> 4;
-    const long long ngroups = ((long long)gridDim.x * kThreads) >> 4;
+    const int group = (int)(((long long)blockIdx.x * kThreads + threadIdx.x) >> 4);
+    const int ngroups = (int)(((long long)gridDim.x * kThreads) >> 4);
     const int per_tok = k ? 2 * heads : heads;      /* units of one token: Q heads then K heads */
-    const long long units = (long long)seq * per_tok;
 
     /* This lane always owns dims [8 * lane16, 8 * lane16 + 8) of a head; its
      * eight weights are re-read (L1 hits) per unit to keep registers low. */
@@ -48,22 +47,31 @@ k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
      * split-half -> pairs 8(l & 7)..+7, shared with lane l ^ 8. */
     const int rope_off = SPLIT_HALF ? (lane16 & 7) * 8 : lane16 * 4;
 
-    for (long long u0 = group * kUnroll; u0 < units; u0 += ngroups * kUnroll) {
+    /* Units are dealt round-robin to the 16-lane groups; (token, unit in
+     * token) advance by a fixed step, so the loop has no division. */
+    const int step_tok = ngroups / per_tok, step_hu = ngroups - step_tok * per_tok;
+    int tok_next = group / per_tok, hu_next = group - tok_next * per_tok;
+
+    while (tok_next < seq) {
         Vec8 v[kUnroll];
         uint16_t *ptr[kUnroll];
         int tok[kUnroll];
         bool isk[kUnroll];
 #pragma unroll
         for (int i = 0; i < kUnroll; i++) {
-            long long u = u0 + i;
-            bool ok = u < units;
-            long long s = ok ? u / per_tok : 0;
-            int hu = ok ? (int)(u - s * per_tok) : 0;
+            bool ok = tok_next < seq;
+            int hu = hu_next;
+            tok[i] = tok_next;
             isk[i] = hu >= heads;
             int h = isk[i] ? hu - heads : hu;
-            tok[i] = (int)s;
-            ptr[i] = ok ? (isk[i] ? k : q) + s * ld + h * 128 + lane16 * 8 : nullptr;
+            ptr[i] = ok ? (isk[i] ? k : q) + (size_t)tok_next * ld + h * 128 + lane16 * 8 : nullptr;
             if (ok) v[i] = *reinterpret_cast<const Vec8 *>(ptr[i]);
+            tok_next += step_tok;
+            hu_next += step_hu;
+            if (hu_next >= per_tok) {
+                hu_next -= per_tok;
+                tok_next++;
+            }
         }
 #pragma unroll
         for (int i = 0; i < kUnroll; i++) {
