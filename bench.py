@@ -48,6 +48,11 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_attention_sm100 launch, from the ncu capture
+# summarised in profiles/k_attention_sm100_klein4b-1024.md (algorithmic Q+K+V+O: 113.2 MB).
+NCU_DRAM_BYTES_PER_LAUNCH = {"klein4b-1024": 90.7e6}
+
+
 def seq_len(w):
     return w["txt"] + w["img"][0] * w["img"][1] + sum(h * x for h, x in w["refs"])
 
@@ -319,7 +324,8 @@ def run_b200(args):
             roof = {"bound": "tensor", "kernel": "k_attention_sm100", "achieved": round(achieved, 1),
                     "peak": bf16_peak, "peak_source": src + " bf16 burst", "unit": "TFLOP/s",
                     "frac": round(achieved / bf16_peak, 4), "frac_of_sustained": round(achieved / bf16_sust, 4),
-                    "kernel_ms": round(kms, 4), "kernel_ms_min": round(min(durs), 4), "traffic": None}
+                    "kernel_ms": round(kms, 4), "kernel_ms_min": round(min(durs), 4),
+                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(name)}
 
     # End to end through the C-ABI with host buffers: upload of the step's
     # inputs from pinned memory, prologue, attention, download of the result.
@@ -356,9 +362,11 @@ def run_b200(args):
     if ring:
         lib.iris_b200_ring_destroy()
 
-    cpu = None
+    cpu = ref_gpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = cpu_reference(w, budget_s=20.0, steps=1, warmup=0)["cpu_baseline"]
+    if rank == 0 and world == 1 and not ring and entries and not args.no_ref_gpu:
+        ref_gpu = reference_gpu_kernels(lib, w, sets[0][0], (d_w, d_cos, d_sin), S, nh, scale)
 
     if rank == 0:
         out = {
@@ -376,7 +384,7 @@ def run_b200(args):
             "pct_bf16_peak": round(100 * value / world / bf16_peak, 2),
             "pct_bf16_sustained": round(100 * value / world / bf16_sust, 2),
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-            "roofline": roof, "cpu_baseline": cpu,
+            "roofline": roof, "cpu_baseline": cpu, "reference_gpu": ref_gpu,
         }
         print(json.dumps(out))
     if dist:
@@ -386,6 +394,45 @@ def run_b200(args):
 # ---------------------------------------------------------------------------
 # the reference arm / CPU baseline (the only part that may execute oracle/)
 # ---------------------------------------------------------------------------
+
+def reference_gpu_kernels(lib, w, bufs, consts, S, nh, scale, reps=20):
+    """The reference's own CUDA backend (iris_cuda.cu compiled unmodified for
+    sm_100 into oracle/_ref) on the same device buffers: its two prologue
+    launches and its mma.sync flash attention, timed by wall clock between
+    its stream syncs (it has no event API). Context for the B200 numbers:
+    what the reference itself achieves on this GPU."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    ref = ol.ref_cuda()
+    if ref is None or ref.iris_dev_init() != 1:
+        return None
+    dq, dout = bufs
+    d_w, d_cos, d_sin = consts
+    width = nh * D
+    q, k, v = dq, dq + width * 2, dq + 2 * width * 2
+    lib.iris_dev_sync()
+
+    def attn():
+        ref.iris_dev_attention(dout, width, q, k, v, 3 * width, S, S, nh, nh, D, scale, 0, None)
+
+    def pro():
+        ref.iris_dev_head_norm_rope(q, 3 * width, d_w, d_cos, d_sin, S, nh, D, w["eps"], 0)
+        ref.iris_dev_head_norm_rope(k, 3 * width, d_w, d_cos, d_sin, S, nh, D, w["eps"], 0)
+
+    out = {}
+    for name, fn in (("attention_ms", attn), ("prologue_ms", pro)):
+        for _ in range(3):
+            fn()
+        ref.iris_dev_sync()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        ref.iris_dev_sync()
+        out[name] = round((time.perf_counter() - t0) * 1e3 / reps, 4)
+    out["attention_tflops"] = round(attn_flops(1, nh, S, S) / (out["attention_ms"] * 1e-3) / 1e12, 1)
+    out["kernel"] = "reference k_flash_attention (mma.sync m16n8k16) + k_head_norm_rope x2, -arch=sm_100"
+    return out
+
 
 def cpu_reference(w, budget_s, steps, warmup):
     """Times the reference's CPU code for one step of workload `w` on the host
@@ -507,6 +554,7 @@ def main():
     ap.add_argument("--mode", default="shard", choices=["shard", "ring"],
                     help="N > 1: independent cfg/head shards (default) or ring sequence parallelism")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference's own CUDA kernels")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -112,6 +112,26 @@ def ref(kind="generic"):
     return lib
 
 
+@functools.lru_cache(None)
+def ref_cuda():
+    """The reference's own CUDA backend (iris_cuda.cu compiled unmodified for
+    sm_100), or None when it was not built or cannot load."""
+    path = os.path.join(ORACLE_DIR, "_ref", "libiris_ref_cuda.so")
+    if not os.path.exists(path):
+        return None
+    try:
+        lib = C.CDLL(path)
+    except OSError:
+        return None
+    VP = C.c_void_p
+    _sig(lib, "iris_dev_init", [], INT)
+    _sig(lib, "iris_dev_sync", [])
+    _sig(lib, "iris_dev_name", [], C.c_char_p)
+    _sig(lib, "iris_dev_head_norm_rope", [VP, INT, VP, VP, VP, INT, INT, INT, FLT, INT])
+    _sig(lib, "iris_dev_attention", [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP])
+    return lib
+
+
 # ---------------------------------------------------------------------------
 # numpy-level helpers shared by the tests
 # ---------------------------------------------------------------------------
