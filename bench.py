@@ -44,6 +44,8 @@ WORKLOADS = {
     "klein4b-1024": dict(family="flux2", heads=24, txt=512, img=(64, 64), refs=[], batch=1, eps=1e-6),
     "klein9b-cfg": dict(family="flux2", heads=32, txt=512, img=(64, 64), refs=[], batch=2, eps=1e-6),
     "zimage-turbo": dict(family="zimage", heads=30, txt=512, img=(64, 64), refs=[], batch=1, eps=1e-5),
+    # 4224 tokens: the per-rank chunk of flux3-multiref on 8 GPUs, as a 2-rank ring probe
+    "flux3-short": dict(family="flux3", heads=24, txt=512, img=(58, 64), refs=[], batch=1, eps=1e-6),
     "flux3-multiref": dict(family="flux3", heads=24, txt=512, img=(64, 64), refs=[(64, 64)] * 3, batch=1, eps=1e-6),
 }
 
@@ -269,6 +271,8 @@ def run_b200(args):
     def step(bufs, mark=None):
         for dq, dout in bufs:
             q, k, v = dq, dq + width * 2, dq + 2 * width * 2
+            if mark is not None:
+                lib.iris_b200_mark(mark + 2)
             lib.iris_b200_qk_norm_rope(q, k, 3 * width, d_w, d_w, d_cos, d_sin, S, nh, D, w["eps"], 0)
             if mark is not None:
                 lib.iris_b200_mark(mark)
@@ -293,10 +297,10 @@ def run_b200(args):
     launches0 = lib.iris_b200_launch_count()
     t_wall0 = time.time()
     lib.iris_b200_mark(0)
-    nmark = min(args.steps, 2000)
+    nmark = min(args.steps, 2500)
     for i in range(args.steps):
         if entries:
-            step(sets[i % nsets], 2 + 2 * i if (i < nmark and len(entries) == 1) else None)
+            step(sets[i % nsets], 2 + 3 * i if (i < nmark and len(entries) == 1) else None)
     lib.iris_b200_mark(1)
     barrier()
     t_wall1 = time.time()
@@ -313,10 +317,12 @@ def run_b200(args):
     value = total_flops / (ms_step * 1e-3) / 1e12
 
     # Dominant kernel alone (rank 0): mean launch duration from the marks.
-    roof = None
+    roof = prologue = None
     bf16_peak, bf16_sust, hbm_peak, src = peaks()
     if rank == 0 and entries and len(entries) == 1:
-        durs = [lib.iris_b200_mark_elapsed_ms(2 + 2 * i, 3 + 2 * i) for i in range(min(args.steps, nmark))]
+        durs = [lib.iris_b200_mark_elapsed_ms(2 + 3 * i, 3 + 3 * i) for i in range(min(args.steps, nmark))]
+        pdurs = [lib.iris_b200_mark_elapsed_ms(4 + 3 * i, 2 + 3 * i) for i in range(min(args.steps, nmark))]
+        pdurs = [d for d in pdurs if d > 0]
         durs = [d for d in durs if d > 0]
         if durs:
             kms = sum(durs) / len(durs)
@@ -326,6 +332,13 @@ def run_b200(args):
                     "frac": round(achieved / bf16_peak, 4), "frac_of_sustained": round(achieved / bf16_sust, 4),
                     "kernel_ms": round(kms, 4), "kernel_ms_min": round(min(durs), 4),
                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(name)}
+            if pdurs and not ring:
+                pms = sum(pdurs) / len(pdurs)
+                pbytes = 4.0 * S * nh * D * 2 + 2.0 * S * 64 * 4     # Q and K read + written, cos + sin read
+                prologue = {"bound": "hbm", "kernel": "k_head_norm_rope_128", "achieved": round(pbytes / pms / 1e6, 1),
+                            "peak": hbm_peak, "peak_source": src + " HBM copy", "unit": "GB/s",
+                            "frac": round(pbytes / pms / 1e6 / hbm_peak, 4), "kernel_ms": round(pms, 4),
+                            "kernel_ms_min": round(min(pdurs), 4), "bytes": pbytes}
 
     # End to end through the C-ABI with host buffers: upload of the step's
     # inputs from pinned memory, prologue, attention, download of the result.
@@ -384,7 +397,7 @@ def run_b200(args):
             "pct_bf16_peak": round(100 * value / world / bf16_peak, 2),
             "pct_bf16_sustained": round(100 * value / world / bf16_sust, 2),
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-            "roofline": roof, "cpu_baseline": cpu, "reference_gpu": ref_gpu,
+            "roofline": roof, "roofline_prologue": prologue, "cpu_baseline": cpu, "reference_gpu": ref_gpu,
         }
         print(json.dumps(out))
     if dist:

@@ -178,6 +178,19 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+/* True in exactly one lane of a converged warp. Code around it stays
+ * warp-uniform, so operands of the single-thread instructions (descriptors,
+ * addresses) can live in uniform registers. */
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -277,7 +290,7 @@ static constexpr uint32_t kIdescPV = kIdescBase | (1u << 16);
 /* Timestamps of CTA 0 for the first 16 key tiles (diagnostics build only):
  * slot [who][j][k], who = 0 / 1 softmax warpgroup of tile 0 / 1, 2 = MMA. */
 __device__ __forceinline__ void stamp(const Params &p, int who, int j, int k) {
-    if (p.debug && blockIdx.x == 0 && j < 16 && (who == 2 || (threadIdx.x & 127) == 0)) {
+    if (p.debug && blockIdx.x == 0 && j < 16 && (threadIdx.x & 31) == 0 && (who == 2 || (threadIdx.x & 127) == 0)) {
         unsigned long long c;
         asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
         float *base = p.debug + (size_t)gridDim.x * 256 * 130;
@@ -341,6 +354,7 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
     const uint32_t lo_q0 = (uint32_t)make_desc(smem + kSmemQ, 1, 0);
     const uint32_t lo_k0 = (uint32_t)make_desc(smem + kSmemKV, 1, 0);
     const uint32_t lo_v0 = (uint32_t)make_desc(smem + kSmemKV, p.v_lbo, 0);
+    const bool leader = elect_one();        /* the whole warp runs this code, one lane issues */
     bool ok;
 
     auto issue_qk = [&](int t, int slot) {
@@ -349,9 +363,10 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
         for (int ks = 0; ks < kHeadDim / 16; ks++) {
             if (DEBUG && (p.diag_mode & 4)) break;
             const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
-            mma_ss(tmem + t * 128, desc64(lo_q + off, hi_qk), desc64(lo_k + off, hi_qk), kIdescQK, ks > 0);
+            if (leader)
+                mma_ss(tmem + t * 128, desc64(lo_q + off, hi_qk), desc64(lo_k + off, hi_qk), kIdescQK, ks > 0);
         }
-        tc_commit(c.bars + (BAR_S_FULL + t) * 8);
+        if (leader) tc_commit(c.bars + (BAR_S_FULL + t) * 8);
     };
     auto issue_pv = [&](int t, int slot, bool first) {
         const uint32_t lo_v = lo_v0 + slot * (kTileBytes >> 4);
@@ -359,23 +374,25 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
         } else if (first) {
 #pragma unroll
             for (int ks = 0; ks < kTileK / 16; ks++)
-                mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, desc64(lo_v + ks * (16 * 128 >> 4), hi_v),
-                       kIdescPV, ks > 0);
+                if (leader)
+                    mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8,
+                           desc64(lo_v + ks * (16 * 128 >> 4), hi_v), kIdescPV, ks > 0);
         } else {
 #pragma unroll
             for (int ks = 0; ks < kTileK / 16; ks++)
-                mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8, desc64(lo_v + ks * (16 * 128 >> 4), hi_v),
-                       kIdescPV, 1);
+                if (leader)
+                    mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8,
+                           desc64(lo_v + ks * (16 * 128 >> 4), hi_v), kIdescPV, 1);
         }
-        tc_commit(c.bars + (BAR_O_DONE + t) * 8);
+        if (leader) tc_commit(c.bars + (BAR_O_DONE + t) * 8);
     };
 
     Ring r = {0, 0u};
-    ok = mbar_wait(c, BAR_Q_FULL, 0, 200) && mbar_wait(c, BAR_KV_FULL + r.slot, r.phase, 201);
+    ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_Q_FULL, 0, 200) && mbar_wait(c, BAR_KV_FULL + r.slot, r.phase, 201));
     if (ok) {
         tc_fence_after();
         for (int t = 0; t < ntq; t++) issue_qk(t, r.slot);
-        tc_commit(c.bars + (BAR_KV_EMPTY + r.slot) * 8);
+        if (leader) tc_commit(c.bars + (BAR_KV_EMPTY + r.slot) * 8);
         r.next();
     }
     for (int j = 0; ok && j < nkv; j++) {
@@ -384,27 +401,27 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
         const Ring rk = r;              /* K_{j+1}, when there is one */
         const bool more = j + 1 < nkv;
         if (more) r.next();
-        if (!(ok = mbar_wait(c, BAR_KV_FULL + rv.slot, rv.phase, 210))) break;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rv.slot, rv.phase, 210)))) break;
         for (int t = 0; t < ntq; t++) {
             if (DEBUG) stamp(p, 2, j, 4 * t);
-            if (!(ok = mbar_wait(c, BAR_P_FULL + t, j & 1, 220 + t))) break;
+            if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + t, j & 1, 220 + t)))) break;
             tc_fence_after();
             if (DEBUG) stamp(p, 2, j, 4 * t + 1);
             issue_pv(t, rv.slot, j == 0);
-            if (t == ntq - 1) tc_commit(c.bars + (BAR_KV_EMPTY + rv.slot) * 8);
+            if (t == ntq - 1 && leader) tc_commit(c.bars + (BAR_KV_EMPTY + rv.slot) * 8);
             if (more) {
-                if (t == 0 && !(ok = mbar_wait(c, BAR_KV_FULL + rk.slot, rk.phase, 230))) break;
+                if (t == 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rk.slot, rk.phase, 230)))) break;
                 tc_fence_after();
                 if (DEBUG) stamp(p, 2, j, 4 * t + 2);
                 issue_qk(t, rk.slot);
-                if (t == ntq - 1) tc_commit(c.bars + (BAR_KV_EMPTY + rk.slot) * 8);
+                if (t == ntq - 1 && leader) tc_commit(c.bars + (BAR_KV_EMPTY + rk.slot) * 8);
                 if (DEBUG) stamp(p, 2, j, 4 * t + 3);
             }
         }
     }
     if (!ok) {
         /* Let what was issued finish before the tensor memory goes away. */
-        tc_commit(c.bars + BAR_DRAIN * 8);
+        if (leader) tc_commit(c.bars + BAR_DRAIN * 8);
         uint32_t bar = c.bars + BAR_DRAIN * 8;
         unsigned long long t0 = global_ns();
         while (!mbar_try_wait(bar, 0) && global_ns() - t0 < kWaitLimitNs) {}
@@ -684,10 +701,8 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
         if (warp < 4 * ntq) softmax_wg<DEBUG>(c, p, tmem, warp >> 2, head, q0, nkv);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-        if (lane == 0) {
-            if (warp == 8) producer(c, p, &tmq, &tmk, &tmv, smem, head, q0, ntq, nkv);
-            else if (warp == 9) mma_issuer<DEBUG>(c, p, smem, tmem, ntq, nkv);
-        }
+        if (warp == 8 && lane == 0) producer(c, p, &tmq, &tmk, &tmv, smem, head, q0, ntq, nkv);
+        if (warp == 9) mma_issuer<DEBUG>(c, p, smem, tmem, ntq, nkv);
     }
 
     tc_fence_before();

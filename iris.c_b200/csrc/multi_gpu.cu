@@ -20,6 +20,7 @@
 #include "common.cuh"
 
 #include <dlfcn.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "kernels.h"
@@ -262,6 +263,20 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record");
     cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
 
+    /* IRIS_B200_RING_TRACE=1: per-step device times of the two streams on stderr. */
+    static int trace = -1;
+    if (trace < 0) {
+        const char *e = getenv("IRIS_B200_RING_TRACE");
+        trace = e && e[0] == '1';
+    }
+    enum { kMaxTrace = 64 };
+    static cudaEvent_t tev[kMaxTrace][4];
+    static int tev_made = 0;
+    if (trace && !tev_made) {
+        for (int i = 0; i < kMaxTrace; i++)
+            for (int j = 0; j < 4; j++) cudaEventCreate(&tev[i][j]);
+        tev_made = 1;
+    }
     const int next = (me + 1) % G, prev = (me + G - 1) % G;
     for (int s = 0; s < G; s++) {
         const int cur = s & 1, nxt = cur ^ 1;
@@ -271,6 +286,7 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
              * buffer was last read by the attention of step s - 1. */
             if (s >= 1) cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.computed[nxt], 0), "stream wait");
             const int incoming = iris_b200_ring_source(me, s + 1, G);
+            if (trace && s < kMaxTrace) cudaEventRecord(tev[s][0], ring.comm_stream);
             if (!nccl_ok(ring.group_start(), "ncclGroupStart")) return IRIS_B200_ECOMM;
             bool ok = nccl_ok(ring.send(ring.buf[cur], (size_t)rows_of[src] * 2 * width * 2, 1, next, ring.comm,
                                         ring.comm_stream), "ncclSend") &&
@@ -278,16 +294,32 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
                                         ring.comm, ring.comm_stream), "ncclRecv");
             if (!nccl_ok(ring.group_end(), "ncclGroupEnd") || !ok) return IRIS_B200_ECOMM;
             cuda_ok(cudaEventRecord(ring.received[nxt], ring.comm_stream), "event record");
+            if (trace && s < kMaxTrace) cudaEventRecord(tev[s][1], ring.comm_stream);
         }
         if (s >= 1) cuda_ok(cudaStreamWaitEvent(g.stream, ring.received[cur], 0), "stream wait");
         const uint16_t *kc = (const uint16_t *)ring.buf[cur];
+        if (trace && s < kMaxTrace) cudaEventRecord(tev[s][2], g.stream);
         int rc = iris_b200_attention_chunk(out, ldo, q, ldi, kc, kc + width, (int)(2 * width), rows, rows_of[src],
                                            heads, scale, NULL, ring.o_state, ring.lse_state, s == 0, s == G - 1);
         if (rc != IRIS_B200_OK) return rc;
         cuda_ok(cudaEventRecord(ring.computed[cur], g.stream), "event record");
+        if (trace && s < kMaxTrace) cudaEventRecord(tev[s][3], g.stream);
     }
     /* The send of the last forwarded chunk must not outlive the call. */
     cuda_ok(cudaEventRecord(ring.packed, ring.comm_stream), "event record");
     cuda_ok(cudaStreamWaitEvent(g.stream, ring.packed, 0), "stream wait");
+    if (trace) {
+        cudaStreamSynchronize(g.stream);
+        for (int s = 0; s < G && s < kMaxTrace; s++) {
+            float c0 = 0, c1 = 0, k0 = 0, k1 = 0;
+            if (s + 1 < G) {
+                cudaEventElapsedTime(&c0, tev[0][2], tev[s][0]);
+                cudaEventElapsedTime(&c1, tev[0][2], tev[s][1]);
+            }
+            cudaEventElapsedTime(&k0, tev[0][2], tev[s][2]);
+            cudaEventElapsedTime(&k1, tev[0][2], tev[s][3]);
+            fprintf(stderr, "ring rank %d step %d: comm [%.3f, %.3f] ms  attention [%.3f, %.3f] ms\n", me, s, c0, c1, k0, k1);
+        }
+    }
     return g.last_error;
 }
