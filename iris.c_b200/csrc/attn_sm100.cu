@@ -78,8 +78,8 @@ enum {
     BAR_KV_FULL = 1,                      /* kStages */
     BAR_KV_EMPTY = BAR_KV_FULL + kStages, /* kStages */
     BAR_S_FULL = BAR_KV_EMPTY + kStages,  /* 2 */
-    BAR_P_FULL = BAR_S_FULL + 2,          /* 2 */
-    BAR_O_DONE = BAR_P_FULL + 2,          /* 2 */
+    BAR_P_FULL = BAR_S_FULL + 2,          /* 4: [tile][half of the key tile] */
+    BAR_O_DONE = BAR_P_FULL + 4,          /* 2 */
     BAR_DRAIN = BAR_O_DONE + 2,
     BAR_COUNT
 };
@@ -368,23 +368,21 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
         }
         if (leader) tc_commit(c.bars + (BAR_S_FULL + t) * 8);
     };
-    auto issue_pv = [&](int t, int slot, bool first) {
-        const uint32_t lo_v = lo_v0 + slot * (kTileBytes >> 4);
+    /* Half h of the PV product of a key tile: keys [64 h, 64 h + 64). */
+    auto issue_pv = [&](int t, int h, int slot, bool first) {
+        const uint32_t lo_v = lo_v0 + slot * (kTileBytes >> 4) + h * (64 * 128 >> 4);
+        const uint32_t tp = tmem + t * 128 + h * 32, to = tmem + 256 + t * 128;
         if (DEBUG && (p.diag_mode & 2)) {
-        } else if (first) {
+        } else if (first && h == 0) {
 #pragma unroll
-            for (int ks = 0; ks < kTileK / 16; ks++)
-                if (leader)
-                    mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8,
-                           desc64(lo_v + ks * (16 * 128 >> 4), hi_v), kIdescPV, ks > 0);
+            for (int ks = 0; ks < 4; ks++)
+                if (leader) mma_ts(to, tp + ks * 8, desc64(lo_v + ks * (16 * 128 >> 4), hi_v), kIdescPV, ks > 0);
         } else {
 #pragma unroll
-            for (int ks = 0; ks < kTileK / 16; ks++)
-                if (leader)
-                    mma_ts(tmem + 256 + t * 128, tmem + t * 128 + ks * 8,
-                           desc64(lo_v + ks * (16 * 128 >> 4), hi_v), kIdescPV, 1);
+            for (int ks = 0; ks < 4; ks++)
+                if (leader) mma_ts(to, tp + ks * 8, desc64(lo_v + ks * (16 * 128 >> 4), hi_v), kIdescPV, 1);
         }
-        if (leader) tc_commit(c.bars + (BAR_O_DONE + t) * 8);
+        if (h == 1 && leader) tc_commit(c.bars + (BAR_O_DONE + t) * 8);
     };
 
     Ring r = {0, 0u};
@@ -404,10 +402,15 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rv.slot, rv.phase, 210)))) break;
         for (int t = 0; t < ntq; t++) {
             if (DEBUG) stamp(p, 2, j, 4 * t);
-            if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + t, j & 1, 220 + t)))) break;
+            /* The first 64 keys' P arrives while the softmax is still busy
+             * with the other 64: their PV runs under it. */
+            if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + 2 * t, j & 1, 220 + t)))) break;
+            tc_fence_after();
+            issue_pv(t, 0, rv.slot, j == 0);
+            if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + 2 * t + 1, j & 1, 224 + t)))) break;
             tc_fence_after();
             if (DEBUG) stamp(p, 2, j, 4 * t + 1);
-            issue_pv(t, rv.slot, j == 0);
+            issue_pv(t, 1, rv.slot, j == 0);
             if (t == ntq - 1 && leader) tc_commit(c.bars + (BAR_KV_EMPTY + rv.slot) * 8);
             if (more) {
                 if (t == 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rk.slot, rk.phase, 230)))) break;
@@ -447,12 +450,12 @@ __device__ __forceinline__ void mask_chunk(uint32_t *v, uint32_t bits) {
         if (!((bits >> i) & 1u)) v[i] = 0xFF800000u;
 }
 
-/* One S row -> P (bf16 pairs into the first 64 columns of S) and the four
- * partial row sums. POLY: one exponential in four runs on the FMA pipe. */
+/* Half an S row (64 scores) -> P (bf16 pairs into 32 columns at tP) and the
+ * four partial row sums. POLY: one exponential in four runs on the FMA pipe. */
 template <bool POLY>
-__device__ __forceinline__ void exp_row(const uint32_t *s, float sl2, float neg_ref, float *sum4, uint32_t tS) {
+__device__ __forceinline__ void exp_half(const uint32_t *s, float sl2, float neg_ref, float *sum4, uint32_t tP) {
 #pragma unroll
-    for (int ch = 0; ch < 4; ch++) {
+    for (int ch = 0; ch < 2; ch++) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) {
@@ -464,7 +467,7 @@ __device__ __forceinline__ void exp_row(const uint32_t *s, float sl2, float neg_
             sum4[(2 * i + 1) & 3] += p1;
             pk[i] = cvt_bf16x2(p0, p1);
         }
-        tmem_st16(tS + ch * 16, pk);
+        tmem_st16(tP + ch * 16, pk);
     }
 }
 
@@ -487,7 +490,8 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
         if (DEBUG) stamp(p, t, j, 0);
         if (DEBUG && (p.diag_mode & 1)) {
             tc_fence_before();
-            mbar_arrive(c.bars + (BAR_P_FULL + t) * 8);
+            mbar_arrive(c.bars + (BAR_P_FULL + 2 * t) * 8);
+            mbar_arrive(c.bars + (BAR_P_FULL + 2 * t + 1) * 8);
             continue;
         }
 
@@ -557,14 +561,17 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
         if (DEBUG) stamp(p, t, j, 2);
         /* Tiles with masked (-inf) scores keep every exponential on the
          * special-function unit, which returns an exact 0 for them. */
-        if (partial) exp_row<false>(s, sl2, neg_ref, sum4, tS);
-        else exp_row<kPolyExp>(s, sl2, neg_ref, sum4, tS);
-        if (DEBUG) stamp(p, t, j, 3);
-        float sum0 = sum4[0] + sum4[2], sum1 = sum4[1] + sum4[3];
-        l += sum0 + sum1;
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(c.bars + (BAR_P_FULL + t) * 8);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            if (partial) exp_half<false>(s + 64 * h, sl2, neg_ref, sum4, tS + 32 * h);
+            else exp_half<kPolyExp>(s + 64 * h, sl2, neg_ref, sum4, tS + 32 * h);
+            /* Hand each half of P to the MMA issuer as soon as it is stored. */
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(c.bars + (BAR_P_FULL + 2 * t + h) * 8);
+            if (DEBUG && h == 0) stamp(p, t, j, 3);
+        }
+        l += (sum4[0] + sum4[2]) + (sum4[1] + sum4[3]);
         if (DEBUG) stamp(p, t, j, 4);
     }
 
@@ -676,7 +683,8 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
         }
         for (int t = 0; t < 2; t++) {
             mbar_init(c.bars + (BAR_S_FULL + t) * 8, 1);
-            mbar_init(c.bars + (BAR_P_FULL + t) * 8, 128);
+            mbar_init(c.bars + (BAR_P_FULL + 2 * t) * 8, 128);
+            mbar_init(c.bars + (BAR_P_FULL + 2 * t + 1) * 8, 128);
             mbar_init(c.bars + (BAR_O_DONE + t) * 8, 1);
         }
         mbar_init(c.bars + BAR_DRAIN * 8, 1);
