@@ -335,7 +335,7 @@ def run_b200(args):
             if pdurs and not ring:
                 pms = sum(pdurs) / len(pdurs)
                 pbytes = 4.0 * S * nh * D * 2 + 2.0 * S * 64 * 4     # Q and K read + written, cos + sin read
-                prologue = {"bound": "hbm", "kernel": "k_head_norm_rope_128", "achieved": round(pbytes / pms / 1e6, 1),
+                prologue = {"bound": "hbm", "kernel": "k_head_norm_rope_128_tok", "achieved": round(pbytes / pms / 1e6, 1),
                             "peak": hbm_peak, "peak_source": src + " HBM copy", "unit": "GB/s",
                             "frac": round(pbytes / pms / 1e6 / hbm_peak, 4), "kernel_ms": round(pms, 4),
                             "kernel_ms_min": round(min(pdurs), 4), "bytes": pbytes}

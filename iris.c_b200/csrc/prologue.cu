@@ -3,14 +3,16 @@
  * bf16 store, in place on the Q / K column slices of the fused projection
  * output. HBM-bound: every element is read once and written once.
  *
- * Fast kernel (head_dim 128, 16-byte aligned rows): 16 lanes own one
- * (token, head) unit, each lane one 16-byte vector of 8 consecutive bf16, so
- * a warp moves 512 contiguous bytes (two adjacent heads) per access. With
- * consecutive pairs both members of a pair sit in the same lane; with
- * split-half pairing lane l exchanges with lane l ^ 8. The sum of squares is
- * reduced with four shuffles inside the 16-lane group. Several units are in
- * flight per thread so that enough bytes are outstanding to fill the HBM
- * pipe. Q and K of a block go through one launch.
+ * Fast kernels (head_dim 128, 16-byte aligned rows): 16 lanes own one
+ * (token, head) unit, each lane one 16-byte vector of 8 consecutive bf16.
+ * With consecutive pairs (the three transformers) both members of a pair sit
+ * in the same lane and a 16-lane group walks all heads of one token, so the
+ * token's angles and the weights are folded once into per-lane constants
+ * (k_head_norm_rope_128_tok). With split-half pairing lane l exchanges with
+ * lane l ^ 8 (k_head_norm_rope_128<true>). The sum of squares is reduced
+ * with four shuffles inside the 16-lane group. Several units are in flight
+ * per thread so that enough bytes are outstanding to fill the HBM pipe. Q
+ * and K of a block go through one launch.
  *
  * Arithmetic follows the reference kernel (iris_cuda.cu:403-420): widen to
  * fp32, inv = rsqrt(mean(x^2) + eps), a = x * (inv * w), rotate, one
@@ -134,6 +136,80 @@ k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
     }
 }
 
+/* Consecutive-pair kernel, token-major: a 16-lane group owns one (token,
+ * Q | K) row segment and walks its heads. The lane's four (cos, sin) pairs
+ * and eight weights are loaded once per token and folded into four products
+ * per pair (cos * w, sin * w), so a head costs one 16-byte load, the sum of
+ * squares, six FMA-pipe operations per pair and one 16-byte store. kHeadsInFlight
+ * heads are loaded before the first is used. */
+static constexpr int kHeadsInFlight = 4;
+
+__global__ void __launch_bounds__(kThreads, 4)
+k_head_norm_rope_128_tok(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
+                         const float *__restrict__ wq, const float *__restrict__ wk,
+                         const float *__restrict__ rope_cos, const float *__restrict__ rope_sin,
+                         int seq, int heads, float eps) {
+    const int lane16 = threadIdx.x & 15;
+    const int group = (int)(((long long)blockIdx.x * kThreads + threadIdx.x) >> 4);
+    const int ngroups = (int)(((long long)gridDim.x * kThreads) >> 4);
+    const int nseg = k ? 2 * seq : seq;             /* segment = (token, Q | K) */
+
+    /* Both groups of a warp run the same number of rounds (the shuffles
+     * below name the whole warp); a group past the end idles with `live` off. */
+    for (int seg0 = group & ~1; seg0 < nseg; seg0 += ngroups) {
+        const int seg = seg0 + (group & 1);
+        const bool live = seg < nseg;
+        const bool isk = live && seg >= seq;
+        const int tok = live ? (isk ? seg - seq : seg) : 0;
+        uint16_t *base = (isk ? k : q) + (size_t)tok * ld + lane16 * 8;
+        const float4 c = *reinterpret_cast<const float4 *>(rope_cos + (size_t)tok * 64 + lane16 * 4);
+        const float4 sn = *reinterpret_cast<const float4 *>(rope_sin + (size_t)tok * 64 + lane16 * 4);
+        const float4 *wp = reinterpret_cast<const float4 *>((isk ? wk : wq) + lane16 * 8);
+        const float4 w0 = __ldg(wp), w1 = __ldg(wp + 1);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, ss4[4] = {sn.x, sn.y, sn.z, sn.w};
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float cw0[4], sw1[4], cw1[4], sw0[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            cw0[j] = cc[j] * ww[2 * j];
+            sw1[j] = ss4[j] * ww[2 * j + 1];
+            cw1[j] = cc[j] * ww[2 * j + 1];
+            sw0[j] = ss4[j] * ww[2 * j];
+        }
+        for (int h0 = 0; h0 < heads; h0 += kHeadsInFlight) {
+            Vec8 v[kHeadsInFlight];
+#pragma unroll
+            for (int i = 0; i < kHeadsInFlight; i++)
+                if (live && h0 + i < heads) v[i] = *reinterpret_cast<const Vec8 *>(base + (h0 + i) * 128);
+#pragma unroll
+            for (int i = 0; i < kHeadsInFlight; i++) {
+                const bool ok = live && h0 + i < heads;
+                float x[8];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    x[2 * j] = ok ? bf_lo(v[i].w[j]) : 0.0f;
+                    x[2 * j + 1] = ok ? bf_hi(v[i].w[j]) : 0.0f;
+                }
+                float ss = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) ss = fmaf(x[j], x[j], ss);
+#pragma unroll
+                for (int o = 1; o < 16; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float inv = rsqrtf(ss * (1.0f / 128.0f) + eps);
+                if (ok) {
+                    Vec8 o;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float a = x[2 * j], b = x[2 * j + 1];
+                        o.w[j] = cvt_bf16x2((a * cw0[j] - b * sw1[j]) * inv, (b * cw1[j] + a * sw0[j]) * inv);
+                    }
+                    *reinterpret_cast<Vec8 *>(base + (h0 + i) * 128) = o;
+                }
+            }
+        }
+    }
+}
+
 /* Any even head_dim, any alignment: one warp per (token, head), 2-byte
  * accesses. Covers the argument domains the fast kernel does not. */
 __global__ void k_head_norm_rope_any(uint16_t *x, int ld, const float *w,
@@ -184,9 +260,13 @@ static int launch_prologue(uint16_t *q, uint16_t *k, int ld, const float *wq, co
         if (split_half)
             k_head_norm_rope_128<true><<<(unsigned)blocks, kThreads, 0, g.stream>>>(
                 q, k, ld, wq, wk, rope_cos, rope_sin, seq, heads, eps);
-        else
-            k_head_norm_rope_128<false><<<(unsigned)blocks, kThreads, 0, g.stream>>>(
+        else {
+            long long segs = (long long)seq * (k ? 2 : 1);
+            long long tb = (segs * 16 + kThreads - 1) / kThreads;
+            if (tb > (long long)g.sm_count * 4) tb = (long long)g.sm_count * 4;
+            k_head_norm_rope_128_tok<<<(unsigned)tb, kThreads, 0, g.stream>>>(
                 q, k, ld, wq, wk, rope_cos, rope_sin, seq, heads, eps);
+        }
         return after_launch("head_norm_rope") ? IRIS_B200_OK : IRIS_B200_ECUDA;
     }
     for (int pass = 0; pass < (k ? 2 : 1); pass++) {
