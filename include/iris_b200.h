@@ -148,9 +148,11 @@ int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq
  * own means, then every rank calls ring_init(). ring_attention(): q, k, v are
  * this rank's token rows (rows_of[rank] of them, row stride ldi), rows_of
  * lists the row count of every rank; out receives the attention of the local
- * queries over the keys of ALL ranks. K/V chunks travel to the next rank on a
- * second stream while the attention of the resident chunk runs; a received
- * chunk is in this GPU's memory before any kernel reads it. */
+ * queries over the keys of ALL ranks. At step s a rank works on the chunk of
+ * rank (rank - s) mod nranks, which its owner sends directly; all transfers
+ * are queued on a second stream at the start and overlap the attention of
+ * the earlier steps. A received chunk is in this GPU's memory before any
+ * kernel reads it. Up to 16 ranks. */
 int iris_b200_ring_unique_id(void *id128);
 int iris_b200_ring_init(int rank, int nranks, const void *id128);
 int iris_b200_ring_attention(uint16_t *out, int ldo,

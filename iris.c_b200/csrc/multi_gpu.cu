@@ -6,10 +6,11 @@
  *  - chunked attention: one launch sees a chunk of the keys and merges its
  *    result into a carried state (normalised fp32 output + log2-sum-exp per
  *    row), the building block of split-K and of the ring;
- *  - ring sequence parallelism: every rank keeps its query rows, the K/V
- *    chunks travel round the ring through NCCL send/recv on a second stream
- *    while the attention of the resident chunk runs. A received chunk lands
- *    in this GPU's own memory and is read from there by ordinary TMA loads.
+ *  - ring sequence parallelism: every rank keeps its query rows and walks the
+ *    K/V chunks of the other ranks in ring order; the chunks arrive through
+ *    NCCL send/recv on a second stream while the attention of earlier chunks
+ *    runs. A received chunk lands in this GPU's own memory and is read from
+ *    there by ordinary TMA loads.
  *
  * The reference has no multi-GPU code (iris_cuda.cu:122 always uses device
  * 0); these entry points are additions with no counterpart there.
@@ -96,6 +97,21 @@ extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t 
 
 /* ------------------------------------------------------------------------
  * NCCL ring
+ *
+ * Rank r holds the query rows and the K / V rows of its token block. Step s
+ * (s = 0 .. G-1) computes the attention of the local queries against the
+ * chunk of rank (r - s) mod G and merges it into the carried state. The
+ * chunk of step s is sent by its owner directly: at step s every rank sends
+ * its own chunk to rank r + s and receives from rank r - s (NVSwitch gives
+ * every pair full bandwidth, so nothing is relayed and no transfer waits
+ * for a computation). All transfers are queued on a communication stream
+ * when the call starts; each records an event the attention of its step
+ * waits for. A received chunk lies in this GPU's memory before a kernel
+ * reads it.
+ *
+ * The heads are processed as two independent halves on two streams: a ring
+ * step is a small problem (its CTAs fill the SMs about one and a half times),
+ * and the CTAs of one half fill the SMs the tail of the other leaves idle.
  * ------------------------------------------------------------------------ */
 
 namespace {
@@ -109,6 +125,8 @@ typedef int (*FnSendRecv)(void *, size_t, int, int, NcclComm, cudaStream_t);
 typedef int (*FnGroup)(void);
 typedef const char *(*FnErrStr)(int);
 
+enum { kMaxRanks = 16, kHeadGroups = 2 };
+
 struct Ring {
     void *dl;
     FnGetUniqueId get_id;
@@ -119,12 +137,12 @@ struct Ring {
     FnErrStr err_str;
     NcclComm comm;
     int rank, nranks;
-    cudaStream_t comm_stream;
-    cudaEvent_t computed[2], received[2], packed;
-    void *buf[2];
-    size_t buf_bytes[2];
-    float *o_state, *lse_state;
-    size_t o_bytes, lse_bytes;
+    cudaStream_t comm_stream, aux_stream;
+    cudaEvent_t received[kMaxRanks], packed, comm_done, join;
+    void *buf[kMaxRanks];                 /* [0] local chunk, [s] chunk of step s */
+    size_t buf_bytes[kMaxRanks];
+    float *o_state[kHeadGroups], *lse_state[kHeadGroups];
+    size_t o_bytes[kHeadGroups], lse_bytes[kHeadGroups];
 } ring = {};
 
 bool nccl_load(void) {
@@ -160,7 +178,7 @@ bool nccl_ok(int rc, const char *what) {
 bool grow(void **p, size_t *have, size_t need) {
     if (need <= *have) return true;
     if (*p) {
-        cuda_ok(cudaStreamSynchronize(g.stream), "sync");
+        cuda_ok(cudaDeviceSynchronize(), "sync");
         cuda_ok(cudaFree(*p), "free");
     }
     *p = NULL;
@@ -173,6 +191,13 @@ bool grow(void **p, size_t *have, size_t need) {
     *have = need;
     return true;
 }
+
+/* Launches of the library go to g.stream; this redirects them for a scope. */
+struct StreamScope {
+    cudaStream_t saved;
+    explicit StreamScope(cudaStream_t s) : saved(g.stream) { g.stream = s; }
+    ~StreamScope() { g.stream = saved; }
+};
 
 }  // namespace
 
@@ -187,7 +212,7 @@ extern "C" int iris_b200_ring_unique_id(void *id128) {
 
 extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
     if (!require_device("ring_init")) return IRIS_B200_ENODEV;
-    if (!id128 || nranks < 1 || rank < 0 || rank >= nranks || ring.comm) return IRIS_B200_EINVAL;
+    if (!id128 || nranks < 1 || nranks > kMaxRanks || rank < 0 || rank >= nranks || ring.comm) return IRIS_B200_EINVAL;
     if (!nccl_load()) return IRIS_B200_ECOMM;
     NcclId id;
     memcpy(&id, id128, sizeof(id));
@@ -197,42 +222,43 @@ extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
     }
     ring.rank = rank;
     ring.nranks = nranks;
-    if (!cuda_ok(cudaStreamCreateWithFlags(&ring.comm_stream, cudaStreamNonBlocking), "stream create"))
+    if (!cuda_ok(cudaStreamCreateWithFlags(&ring.comm_stream, cudaStreamNonBlocking), "stream create") ||
+        !cuda_ok(cudaStreamCreateWithFlags(&ring.aux_stream, cudaStreamNonBlocking), "stream create"))
         return IRIS_B200_ECUDA;
-    for (int i = 0; i < 2; i++) {
-        cuda_ok(cudaEventCreateWithFlags(&ring.computed[i], cudaEventDisableTiming), "event create");
+    for (int i = 0; i < kMaxRanks; i++)
         cuda_ok(cudaEventCreateWithFlags(&ring.received[i], cudaEventDisableTiming), "event create");
-    }
     cuda_ok(cudaEventCreateWithFlags(&ring.packed, cudaEventDisableTiming), "event create");
+    cuda_ok(cudaEventCreateWithFlags(&ring.comm_done, cudaEventDisableTiming), "event create");
+    cuda_ok(cudaEventCreateWithFlags(&ring.join, cudaEventDisableTiming), "event create");
     return g.last_error;
 }
 
 extern "C" void iris_b200_ring_destroy(void) {
     if (!ring.comm) return;
-    cuda_ok(cudaStreamSynchronize(g.stream), "sync");
-    cuda_ok(cudaStreamSynchronize(ring.comm_stream), "sync");
+    cuda_ok(cudaDeviceSynchronize(), "sync");
     ring.destroy(ring.comm);
     ring.comm = NULL;
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < kMaxRanks; i++) {
         if (ring.buf[i]) cuda_ok(cudaFree(ring.buf[i]), "free");
         ring.buf[i] = NULL;
         ring.buf_bytes[i] = 0;
-        cuda_ok(cudaEventDestroy(ring.computed[i]), "event destroy");
         cuda_ok(cudaEventDestroy(ring.received[i]), "event destroy");
     }
+    for (int i = 0; i < kHeadGroups; i++) {
+        if (ring.o_state[i]) cuda_ok(cudaFree(ring.o_state[i]), "free");
+        if (ring.lse_state[i]) cuda_ok(cudaFree(ring.lse_state[i]), "free");
+        ring.o_state[i] = ring.lse_state[i] = NULL;
+        ring.o_bytes[i] = ring.lse_bytes[i] = 0;
+    }
     cuda_ok(cudaEventDestroy(ring.packed), "event destroy");
-    if (ring.o_state) cuda_ok(cudaFree(ring.o_state), "free");
-    if (ring.lse_state) cuda_ok(cudaFree(ring.lse_state), "free");
-    ring.o_state = ring.lse_state = NULL;
-    ring.o_bytes = ring.lse_bytes = 0;
+    cuda_ok(cudaEventDestroy(ring.comm_done), "event destroy");
+    cuda_ok(cudaEventDestroy(ring.join), "event destroy");
     cuda_ok(cudaStreamDestroy(ring.comm_stream), "stream destroy");
+    cuda_ok(cudaStreamDestroy(ring.aux_stream), "stream destroy");
 }
 
-/* Every rank holds `rows` query rows and the K / V rows of the same tokens
- * (rows may differ per rank: rows_of[r], r = 0..nranks-1). Step s computes
- * the attention of the local queries against the chunk that started on rank
- * (rank - s) mod nranks while that chunk is already on its way to rank + 1.
- * Chunk layout in the ring buffers: [rows, 2 * heads * 128] (K | V). */
+/* rows_of[r]: token rows of rank r. q, k, v: this rank's rows, row stride
+ * ldi. Chunk layout in the buffers: [rows, 2 * heads * 128] (K | V). */
 extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
                                         const uint16_t *q, const uint16_t *k, const uint16_t *v,
                                         int ldi, const int *rows_of, int heads, float scale) {
@@ -244,17 +270,22 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     const int G = ring.nranks, me = ring.rank;
     const int rows = rows_of[me];
     const size_t width = (size_t)heads * 128;
-    int max_rows = 0;
-    for (int r = 0; r < G; r++) max_rows = rows_of[r] > max_rows ? rows_of[r] : max_rows;
-    const size_t chunk_bytes = (size_t)max_rows * 2 * width * 2;
-    for (int i = 0; i < 2; i++)
-        if (!grow(&ring.buf[i], &ring.buf_bytes[i], chunk_bytes)) return IRIS_B200_ENOMEM;
-    if (G > 1) {
-        if (!grow((void **)&ring.o_state, &ring.o_bytes, (size_t)rows * width * 4) ||
-            !grow((void **)&ring.lse_state, &ring.lse_bytes, (size_t)rows * heads * 4))
-            return IRIS_B200_ENOMEM;
+    const int ngroups = (G > 1 && heads % kHeadGroups == 0) ? kHeadGroups : 1;
+    const int hg = heads / ngroups;                         /* heads of one group */
+
+    for (int s = 0; s < G; s++) {
+        const int src = iris_b200_ring_source(me, s, G);
+        if (!grow(&ring.buf[s], &ring.buf_bytes[s], (size_t)rows_of[src] * 2 * width * 2)) return IRIS_B200_ENOMEM;
     }
-    /* The local chunk goes into buffer 0 as [rows, K | V]. */
+    if (G > 1) {
+        for (int i = 0; i < ngroups; i++)
+            if (!grow((void **)&ring.o_state[i], &ring.o_bytes[i], (size_t)rows * hg * 128 * 4) ||
+                !grow((void **)&ring.lse_state[i], &ring.lse_bytes[i], (size_t)rows * hg * 4))
+                return IRIS_B200_ENOMEM;
+    }
+
+    /* The local chunk goes into buffer 0 as [rows, K | V]; every earlier use
+     * of the buffers is ordered before this point on the library's stream. */
     if (!cuda_ok(cudaMemcpy2DAsync(ring.buf[0], 2 * width * 2, k, (size_t)ldi * 2, width * 2, rows,
                                    cudaMemcpyDeviceToDevice, g.stream), "pack K") ||
         !cuda_ok(cudaMemcpy2DAsync((char *)ring.buf[0] + width * 2, 2 * width * 2, v, (size_t)ldi * 2, width * 2,
@@ -263,63 +294,41 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record");
     cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
 
-    /* IRIS_B200_RING_TRACE=1: per-step device times of the two streams on stderr. */
-    static int trace = -1;
-    if (trace < 0) {
-        const char *e = getenv("IRIS_B200_RING_TRACE");
-        trace = e && e[0] == '1';
+    /* All transfers, in step order. */
+    for (int s = 1; s < G; s++) {
+        const int to = (me + s) % G, from = iris_b200_ring_source(me, s, G);
+        if (!nccl_ok(ring.group_start(), "ncclGroupStart")) return IRIS_B200_ECOMM;
+        bool ok = nccl_ok(ring.send(ring.buf[0], (size_t)rows * 2 * width * 2, 1, to, ring.comm, ring.comm_stream),
+                          "ncclSend") &&
+                  nccl_ok(ring.recv(ring.buf[s], (size_t)rows_of[from] * 2 * width * 2, 1, from, ring.comm,
+                                    ring.comm_stream), "ncclRecv");
+        if (!nccl_ok(ring.group_end(), "ncclGroupEnd") || !ok) return IRIS_B200_ECOMM;
+        cuda_ok(cudaEventRecord(ring.received[s], ring.comm_stream), "event record");
     }
-    enum { kMaxTrace = 64 };
-    static cudaEvent_t tev[kMaxTrace][4];
-    static int tev_made = 0;
-    if (trace && !tev_made) {
-        for (int i = 0; i < kMaxTrace; i++)
-            for (int j = 0; j < 4; j++) cudaEventCreate(&tev[i][j]);
-        tev_made = 1;
-    }
-    const int next = (me + 1) % G, prev = (me + G - 1) % G;
-    for (int s = 0; s < G; s++) {
-        const int cur = s & 1, nxt = cur ^ 1;
-        const int src = iris_b200_ring_source(me, s, G);           /* owner of the resident chunk */
-        if (s + 1 < G) {
-            /* Forward the resident chunk, receive the next one. The target
-             * buffer was last read by the attention of step s - 1. */
-            if (s >= 1) cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.computed[nxt], 0), "stream wait");
-            const int incoming = iris_b200_ring_source(me, s + 1, G);
-            if (trace && s < kMaxTrace) cudaEventRecord(tev[s][0], ring.comm_stream);
-            if (!nccl_ok(ring.group_start(), "ncclGroupStart")) return IRIS_B200_ECOMM;
-            bool ok = nccl_ok(ring.send(ring.buf[cur], (size_t)rows_of[src] * 2 * width * 2, 1, next, ring.comm,
-                                        ring.comm_stream), "ncclSend") &&
-                      nccl_ok(ring.recv(ring.buf[nxt], (size_t)rows_of[incoming] * 2 * width * 2, 1, prev,
-                                        ring.comm, ring.comm_stream), "ncclRecv");
-            if (!nccl_ok(ring.group_end(), "ncclGroupEnd") || !ok) return IRIS_B200_ECOMM;
-            cuda_ok(cudaEventRecord(ring.received[nxt], ring.comm_stream), "event record");
-            if (trace && s < kMaxTrace) cudaEventRecord(tev[s][1], ring.comm_stream);
-        }
-        if (s >= 1) cuda_ok(cudaStreamWaitEvent(g.stream, ring.received[cur], 0), "stream wait");
-        const uint16_t *kc = (const uint16_t *)ring.buf[cur];
-        if (trace && s < kMaxTrace) cudaEventRecord(tev[s][2], g.stream);
-        int rc = iris_b200_attention_chunk(out, ldo, q, ldi, kc, kc + width, (int)(2 * width), rows, rows_of[src],
-                                           heads, scale, NULL, ring.o_state, ring.lse_state, s == 0, s == G - 1);
-        if (rc != IRIS_B200_OK) return rc;
-        cuda_ok(cudaEventRecord(ring.computed[cur], g.stream), "event record");
-        if (trace && s < kMaxTrace) cudaEventRecord(tev[s][3], g.stream);
-    }
-    /* The send of the last forwarded chunk must not outlive the call. */
-    cuda_ok(cudaEventRecord(ring.packed, ring.comm_stream), "event record");
-    cuda_ok(cudaStreamWaitEvent(g.stream, ring.packed, 0), "stream wait");
-    if (trace) {
-        cudaStreamSynchronize(g.stream);
-        for (int s = 0; s < G && s < kMaxTrace; s++) {
-            float c0 = 0, c1 = 0, k0 = 0, k1 = 0;
-            if (s + 1 < G) {
-                cudaEventElapsedTime(&c0, tev[0][2], tev[s][0]);
-                cudaEventElapsedTime(&c1, tev[0][2], tev[s][1]);
-            }
-            cudaEventElapsedTime(&k0, tev[0][2], tev[s][2]);
-            cudaEventElapsedTime(&k1, tev[0][2], tev[s][3]);
-            fprintf(stderr, "ring rank %d step %d: comm [%.3f, %.3f] ms  attention [%.3f, %.3f] ms\n", me, s, c0, c1, k0, k1);
+    cuda_ok(cudaEventRecord(ring.comm_done, ring.comm_stream), "event record");
+
+    /* The head groups run side by side: group 0 on the library's stream,
+     * group 1 on the auxiliary one, joined again before the call returns. */
+    if (ngroups > 1) cuda_ok(cudaStreamWaitEvent(ring.aux_stream, ring.packed, 0), "stream wait");
+    int rc = IRIS_B200_OK;
+    for (int s = 0; s < G && rc == IRIS_B200_OK; s++) {
+        const int src = iris_b200_ring_source(me, s, G);
+        const uint16_t *kc = (const uint16_t *)ring.buf[s];
+        for (int grp = 0; grp < ngroups && rc == IRIS_B200_OK; grp++) {
+            cudaStream_t st = grp == 0 ? g.stream : ring.aux_stream;
+            if (s >= 1) cuda_ok(cudaStreamWaitEvent(st, ring.received[s], 0), "stream wait");
+            StreamScope scope(st);
+            const size_t col = (size_t)grp * hg * 128;
+            rc = iris_b200_attention_chunk(out + col, ldo, q + col, ldi, kc + col, kc + width + col,
+                                           (int)(2 * width), rows, rows_of[src], hg, scale, NULL,
+                                           ring.o_state[grp], ring.lse_state[grp], s == 0, s == G - 1);
         }
     }
-    return g.last_error;
+    if (ngroups > 1) {
+        cuda_ok(cudaEventRecord(ring.join, ring.aux_stream), "event record");
+        cuda_ok(cudaStreamWaitEvent(g.stream, ring.join, 0), "stream wait");
+    }
+    /* The sends of the local chunk must not outlive the call. */
+    cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done, 0), "stream wait");
+    return rc != IRIS_B200_OK ? rc : g.last_error;
 }
