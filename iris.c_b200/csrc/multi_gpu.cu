@@ -20,6 +20,7 @@
  */
 #include "common.cuh"
 
+#include <cuda.h>
 #include <dlfcn.h>
 #include <stdlib.h>
 #include <string.h>
@@ -124,6 +125,8 @@ typedef int (*FnCommDestroy)(NcclComm);
 typedef int (*FnSendRecv)(void *, size_t, int, int, NcclComm, cudaStream_t);
 typedef int (*FnGroup)(void);
 typedef const char *(*FnErrStr)(int);
+typedef int (*FnAllGather)(const void *, void *, size_t, int, NcclComm, cudaStream_t);
+typedef CUresult (*FnStreamValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
 
 enum { kMaxRanks = 16, kHeadGroups = 2 };
 
@@ -135,6 +138,7 @@ struct Ring {
     FnSendRecv send, recv;
     FnGroup group_start, group_end;
     FnErrStr err_str;
+    FnAllGather all_gather;
     NcclComm comm;
     int rank, nranks;
     cudaStream_t comm_stream, aux_stream;
@@ -143,7 +147,21 @@ struct Ring {
     size_t buf_bytes[kMaxRanks];
     float *o_state[kHeadGroups], *lse_state[kHeadGroups];
     size_t o_bytes[kHeadGroups], lse_bytes[kHeadGroups];
+    /* Copy-engine transport: chunks are pushed into the peers' slot pools
+     * (mapped through CUDA IPC) by cudaMemcpyAsync, flow-controlled by
+     * sequence numbers in device memory that streams wait on. */
+    int ce;                               /* 0 not set up, 1 in use, -1 unavailable (NCCL send/recv instead) */
+    FnStreamValue32 wait32, write32;
+    char *pool;                           /* kMaxRanks slots of slot_bytes: [0] local chunk, [s] step s */
+    size_t slot_bytes;
+    uint32_t *flags;                      /* arrive[kMaxRanks] | ack[kMaxRanks] | seq_words[8] */
+    char *peer_pool[kMaxRanks];
+    uint32_t *peer_flags[kMaxRanks];
+    void *xchg;                           /* device staging of the handle exchange */
+    uint32_t seq;
 } ring = {};
+
+enum { kFlagArrive = 0, kFlagAck = kMaxRanks, kFlagSeq = 2 * kMaxRanks, kFlagWords = 2 * kMaxRanks + 8 };
 
 bool nccl_load(void) {
     if (ring.dl) return true;
@@ -161,6 +179,7 @@ bool nccl_load(void) {
     ring.group_start = (FnGroup)dlsym(ring.dl, "ncclGroupStart");
     ring.group_end = (FnGroup)dlsym(ring.dl, "ncclGroupEnd");
     ring.err_str = (FnErrStr)dlsym(ring.dl, "ncclGetErrorString");
+    ring.all_gather = (FnAllGather)dlsym(ring.dl, "ncclAllGather");
     if (!ring.get_id || !ring.init_rank || !ring.destroy || !ring.send || !ring.recv || !ring.group_start ||
         !ring.group_end) {
         set_error(IRIS_B200_ECOMM, "dlsym nccl", "symbol missing");
@@ -201,6 +220,116 @@ struct StreamScope {
 
 }  // namespace
 
+
+namespace {
+
+struct IpcPair {
+    cudaIpcMemHandle_t pool, flags;
+};
+
+/* Unmap the peers' pools; every importer does this before any exporter frees. */
+void ce_close_peers(void) {
+    for (int r = 0; r < kMaxRanks; r++) {
+        if (ring.peer_pool[r]) cudaIpcCloseMemHandle(ring.peer_pool[r]);
+        if (ring.peer_flags[r]) cudaIpcCloseMemHandle(ring.peer_flags[r]);
+        ring.peer_pool[r] = NULL;
+        ring.peer_flags[r] = NULL;
+    }
+    (void)cudaGetLastError();
+}
+
+void ce_free_pool(void) {
+    if (ring.pool) cuda_ok(cudaFree(ring.pool), "free");
+    ring.pool = NULL;
+    ring.slot_bytes = 0;
+}
+
+/* All ranks have reached this point (an all-gather of a few bytes). */
+bool ce_barrier(void) {
+    if (!ring.xchg || !ring.all_gather) return false;
+    char *dev = (char *)ring.xchg;
+    return nccl_ok(ring.all_gather(dev + sizeof(IpcPair) * kMaxRanks, dev, 4, 1, ring.comm, g.stream), "ncclAllGather") &&
+           cuda_ok(cudaStreamSynchronize(g.stream), "sync");
+}
+
+/* Collective: every rank calls it with the same slot size. Allocates (or
+ * grows) the slot pool, exchanges the IPC handles through an NCCL all-gather
+ * and maps the peers' pools and flag words. Returns false, with the NCCL
+ * send/recv transport selected, when anything on the way is unavailable. */
+bool ce_setup(size_t slot_bytes) {
+    if (ring.ce < 0) return false;
+    if (ring.ce == 1 && slot_bytes <= ring.slot_bytes) return true;
+    const char *env = getenv("IRIS_B200_RING_TRANSPORT");
+    const int G = ring.nranks;
+    bool want = !(env && strcmp(env, "nccl") == 0) && ring.all_gather != NULL;
+    if (want && !ring.wait32) {
+        void *w = NULL, *wr = NULL;
+        cudaDriverEntryPointQueryResult q1, q2;
+        if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &w, cudaEnableDefault, &q1) != cudaSuccess ||
+            cudaGetDriverEntryPoint("cuStreamWriteValue32", &wr, cudaEnableDefault, &q2) != cudaSuccess ||
+            q1 != cudaDriverEntryPointSuccess || q2 != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            want = false;
+        }
+        ring.wait32 = (FnStreamValue32)w;
+        ring.write32 = (FnStreamValue32)wr;
+    }
+    if (!want) {
+        ring.ce = -1;
+        return false;
+    }
+    /* Nobody may still be pushing into a pool that is about to go away. */
+    cuda_ok(cudaDeviceSynchronize(), "sync");
+    if (!ring.xchg && !cuda_ok(cudaMalloc(&ring.xchg, sizeof(IpcPair) * (kMaxRanks + 1)), "malloc")) return false;
+    IpcPair *dev = (IpcPair *)ring.xchg;
+    if (!ce_barrier()) return false;                /* every rank's pushes are complete */
+    ce_close_peers();
+    if (!ce_barrier()) return false;                /* every mapping of the old pools is gone */
+    ce_free_pool();
+    if (!ring.flags) {
+        if (!cuda_ok(cudaMalloc((void **)&ring.flags, kFlagWords * 4), "malloc") ||
+            !cuda_ok(cudaMemset(ring.flags, 0, kFlagWords * 4), "memset"))
+            return false;
+    }
+    if (cudaMalloc((void **)&ring.pool, slot_bytes * G) != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_error(IRIS_B200_ENOMEM, "ring slot pool", NULL);
+        return false;
+    }
+    ring.slot_bytes = slot_bytes;
+    IpcPair mine, all[kMaxRanks];
+    if (!cuda_ok(cudaIpcGetMemHandle(&mine.pool, ring.pool), "cudaIpcGetMemHandle") ||
+        !cuda_ok(cudaIpcGetMemHandle(&mine.flags, ring.flags), "cudaIpcGetMemHandle") ||
+        !cuda_ok(cudaMemcpy(dev + kMaxRanks, &mine, sizeof(mine), cudaMemcpyHostToDevice), "memcpy") ||
+        !nccl_ok(ring.all_gather(dev + kMaxRanks, dev, sizeof(IpcPair), 1, ring.comm, g.stream), "ncclAllGather") ||
+        !cuda_ok(cudaStreamSynchronize(g.stream), "sync") ||
+        !cuda_ok(cudaMemcpy(all, dev, sizeof(IpcPair) * G, cudaMemcpyDeviceToHost), "memcpy"))
+        return false;
+    for (int r = 0; r < G; r++) {
+        if (r == ring.rank) continue;
+        void *pp = NULL, *pf = NULL;
+        if (!cuda_ok(cudaIpcOpenMemHandle(&pp, all[r].pool, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle") ||
+            !cuda_ok(cudaIpcOpenMemHandle(&pf, all[r].flags, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle"))
+            return false;
+        ring.peer_pool[r] = (char *)pp;
+        ring.peer_flags[r] = (uint32_t *)pf;
+    }
+    ring.ce = 1;
+    return true;
+}
+
+bool stream_value(FnStreamValue32 fn, cudaStream_t st, const uint32_t *addr, uint32_t value, unsigned flags,
+                  const char *what) {
+    CUresult r = fn((CUstream)st, (CUdeviceptr)(uintptr_t)addr, value, flags);
+    if (r == CUDA_SUCCESS) return true;
+    char msg[48];
+    snprintf(msg, sizeof(msg), "CUresult %d", (int)r);
+    set_error(IRIS_B200_ECUDA, what, msg);
+    return false;
+}
+
+}  // namespace
+
 extern "C" int iris_b200_ring_unique_id(void *id128) {
     if (!id128) return IRIS_B200_EINVAL;
     if (!nccl_load()) return IRIS_B200_ECOMM;
@@ -236,6 +365,15 @@ extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
 extern "C" void iris_b200_ring_destroy(void) {
     if (!ring.comm) return;
     cuda_ok(cudaDeviceSynchronize(), "sync");
+    ce_close_peers();
+    if (ring.ce == 1) ce_barrier();
+    ce_free_pool();
+    if (ring.flags) cuda_ok(cudaFree(ring.flags), "free");
+    if (ring.xchg) cuda_ok(cudaFree(ring.xchg), "free");
+    ring.flags = NULL;
+    ring.xchg = NULL;
+    ring.ce = 0;
+    ring.seq = 0;
     ring.destroy(ring.comm);
     ring.comm = NULL;
     for (int i = 0; i < kMaxRanks; i++) {
@@ -272,38 +410,61 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     const size_t width = (size_t)heads * 128;
     const int ngroups = (G > 1 && heads % kHeadGroups == 0) ? kHeadGroups : 1;
     const int hg = heads / ngroups;                         /* heads of one group */
+    int max_rows = 0;
+    for (int r = 0; r < G; r++) max_rows = rows_of[r] > max_rows ? rows_of[r] : max_rows;
+    const size_t slot_bytes = ((size_t)max_rows * 2 * width * 2 + 255) & ~(size_t)255;
 
-    for (int s = 0; s < G; s++) {
-        const int src = iris_b200_ring_source(me, s, G);
-        if (!grow(&ring.buf[s], &ring.buf_bytes[s], (size_t)rows_of[src] * 2 * width * 2)) return IRIS_B200_ENOMEM;
+    /* Transport: pushes by the copy engines into IPC-mapped slot pools when
+     * that can be set up, NCCL send/recv into private buffers otherwise. */
+    const bool ce = G > 1 && ce_setup(slot_bytes);
+    if (!ce) {
+        for (int s = 0; s < G; s++)
+            if (!grow(&ring.buf[s], &ring.buf_bytes[s], slot_bytes)) return IRIS_B200_ENOMEM;
     }
+    auto chunk = [&](int s) -> char * { return ce ? ring.pool + (size_t)s * ring.slot_bytes : (char *)ring.buf[s]; };
     if (G > 1) {
         for (int i = 0; i < ngroups; i++)
             if (!grow((void **)&ring.o_state[i], &ring.o_bytes[i], (size_t)rows * hg * 128 * 4) ||
                 !grow((void **)&ring.lse_state[i], &ring.lse_bytes[i], (size_t)rows * hg * 4))
                 return IRIS_B200_ENOMEM;
     }
+    const uint32_t seq = ++ring.seq;
+    uint32_t *seq_word = ce ? ring.flags + kFlagSeq + (seq & 7u) : NULL;
 
-    /* The local chunk goes into buffer 0 as [rows, K | V]; every earlier use
-     * of the buffers is ordered before this point on the library's stream. */
-    if (!cuda_ok(cudaMemcpy2DAsync(ring.buf[0], 2 * width * 2, k, (size_t)ldi * 2, width * 2, rows,
+    /* The local chunk goes into slot 0 as [rows, K | V]; every earlier use of
+     * the slots is ordered before this point on the library's stream. */
+    if (ce && !stream_value(ring.write32, g.stream, seq_word, seq, CU_STREAM_WRITE_VALUE_DEFAULT, "write seq"))
+        return IRIS_B200_ECUDA;
+    if (!cuda_ok(cudaMemcpy2DAsync(chunk(0), 2 * width * 2, k, (size_t)ldi * 2, width * 2, rows,
                                    cudaMemcpyDeviceToDevice, g.stream), "pack K") ||
-        !cuda_ok(cudaMemcpy2DAsync((char *)ring.buf[0] + width * 2, 2 * width * 2, v, (size_t)ldi * 2, width * 2,
-                                   rows, cudaMemcpyDeviceToDevice, g.stream), "pack V"))
+        !cuda_ok(cudaMemcpy2DAsync(chunk(0) + width * 2, 2 * width * 2, v, (size_t)ldi * 2, width * 2, rows,
+                                   cudaMemcpyDeviceToDevice, g.stream), "pack V"))
         return IRIS_B200_ECUDA;
     cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record");
     cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
 
-    /* All transfers, in step order. */
+    /* All transfers, in step order: at step s this rank's chunk is wanted by
+     * rank me + s, which keeps it in its slot s. */
+    const size_t my_bytes = (size_t)rows * 2 * width * 2;
     for (int s = 1; s < G; s++) {
         const int to = (me + s) % G, from = iris_b200_ring_source(me, s, G);
-        if (!nccl_ok(ring.group_start(), "ncclGroupStart")) return IRIS_B200_ECOMM;
-        bool ok = nccl_ok(ring.send(ring.buf[0], (size_t)rows * 2 * width * 2, 1, to, ring.comm, ring.comm_stream),
-                          "ncclSend") &&
-                  nccl_ok(ring.recv(ring.buf[s], (size_t)rows_of[from] * 2 * width * 2, 1, from, ring.comm,
-                                    ring.comm_stream), "ncclRecv");
-        if (!nccl_ok(ring.group_end(), "ncclGroupEnd") || !ok) return IRIS_B200_ECOMM;
-        cuda_ok(cudaEventRecord(ring.received[s], ring.comm_stream), "event record");
+        if (ce) {
+            /* `to` has finished reading what the previous call put there. */
+            if (!stream_value(ring.wait32, ring.comm_stream, ring.flags + kFlagAck + to, seq - 1,
+                              CU_STREAM_WAIT_VALUE_GEQ, "wait ack") ||
+                !cuda_ok(cudaMemcpyAsync(ring.peer_pool[to] + (size_t)s * ring.slot_bytes, chunk(0), my_bytes,
+                                         cudaMemcpyDefault, ring.comm_stream), "push chunk") ||
+                !cuda_ok(cudaMemcpyAsync(ring.peer_flags[to] + kFlagArrive + s, seq_word, 4, cudaMemcpyDefault,
+                                         ring.comm_stream), "push flag"))
+                return IRIS_B200_ECUDA;
+        } else {
+            if (!nccl_ok(ring.group_start(), "ncclGroupStart")) return IRIS_B200_ECOMM;
+            bool ok = nccl_ok(ring.send(chunk(0), my_bytes, 1, to, ring.comm, ring.comm_stream), "ncclSend") &&
+                      nccl_ok(ring.recv(chunk(s), (size_t)rows_of[from] * 2 * width * 2, 1, from, ring.comm,
+                                        ring.comm_stream), "ncclRecv");
+            if (!nccl_ok(ring.group_end(), "ncclGroupEnd") || !ok) return IRIS_B200_ECOMM;
+            cuda_ok(cudaEventRecord(ring.received[s], ring.comm_stream), "event record");
+        }
     }
     cuda_ok(cudaEventRecord(ring.comm_done, ring.comm_stream), "event record");
 
@@ -313,10 +474,18 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     int rc = IRIS_B200_OK;
     for (int s = 0; s < G && rc == IRIS_B200_OK; s++) {
         const int src = iris_b200_ring_source(me, s, G);
-        const uint16_t *kc = (const uint16_t *)ring.buf[s];
+        const uint16_t *kc = (const uint16_t *)chunk(s);
         for (int grp = 0; grp < ngroups && rc == IRIS_B200_OK; grp++) {
             cudaStream_t st = grp == 0 ? g.stream : ring.aux_stream;
-            if (s >= 1) cuda_ok(cudaStreamWaitEvent(st, ring.received[s], 0), "stream wait");
+            if (s >= 1) {
+                if (ce) {
+                    if (!stream_value(ring.wait32, st, ring.flags + kFlagArrive + s, seq, CU_STREAM_WAIT_VALUE_GEQ,
+                                      "wait chunk"))
+                        return IRIS_B200_ECUDA;
+                } else {
+                    cuda_ok(cudaStreamWaitEvent(st, ring.received[s], 0), "stream wait");
+                }
+            }
             StreamScope scope(st);
             const size_t col = (size_t)grp * hg * 128;
             rc = iris_b200_attention_chunk(out + col, ldo, q + col, ldi, kc + col, kc + width + col,
@@ -328,7 +497,16 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         cuda_ok(cudaEventRecord(ring.join, ring.aux_stream), "event record");
         cuda_ok(cudaStreamWaitEvent(g.stream, ring.join, 0), "stream wait");
     }
-    /* The sends of the local chunk must not outlive the call. */
+    if (ce) {
+        /* Tell every owner that its chunk has been consumed here. */
+        for (int s = 1; s < G && rc == IRIS_B200_OK; s++) {
+            const int src = iris_b200_ring_source(me, s, G);
+            if (!cuda_ok(cudaMemcpyAsync(ring.peer_flags[src] + kFlagAck + me, seq_word, 4, cudaMemcpyDefault,
+                                         g.stream), "push ack"))
+                rc = IRIS_B200_ECUDA;
+        }
+    }
+    /* The transfers of the local chunk must not outlive the call. */
     cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done, 0), "stream wait");
     return rc != IRIS_B200_OK ? rc : g.last_error;
 }
