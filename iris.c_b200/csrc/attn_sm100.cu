@@ -768,8 +768,32 @@ static EncodeTiledFn encode_fn(void) {
 }
 
 /* 2-D map over a bf16 [seq, heads*128] column slice with row stride ld:
- * box of 64 columns x 128 rows, 128-byte swizzle, zero fill outside. */
+ * box of 64 columns x 128 rows, 128-byte swizzle, zero fill outside. The
+ * callers pass the same views block after block, so encoded maps are kept in
+ * a small table keyed by the view (the map holds no data, only the address
+ * and shape; a table entry stays valid for any buffer at that address). */
+struct MapKey {
+    const void *base;
+    int seq, width, ld;
+};
+static struct {
+    MapKey key;
+    CUtensorMap map;
+    unsigned long long used;
+} g_maps[64];
+static unsigned long long g_map_clock = 0;
+
 static bool make_map(CUtensorMap *map, const void *base, int seq, int width, int ld) {
+    int victim = 0;
+    for (int i = 0; i < 64; i++) {
+        if (g_maps[i].used && g_maps[i].key.base == base && g_maps[i].key.seq == seq &&
+            g_maps[i].key.width == width && g_maps[i].key.ld == ld) {
+            g_maps[i].used = ++g_map_clock;
+            *map = g_maps[i].map;
+            return true;
+        }
+        if (g_maps[i].used < g_maps[victim].used) victim = i;
+    }
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error(IRIS_B200_ECUDA, "cuTensorMapEncodeTiled lookup", NULL);
@@ -788,6 +812,9 @@ static bool make_map(CUtensorMap *map, const void *base, int seq, int width, int
         set_error(IRIS_B200_ECUDA, "cuTensorMapEncodeTiled", msg);
         return false;
     }
+    g_maps[victim].key = MapKey{base, seq, width, ld};
+    g_maps[victim].map = *map;
+    g_maps[victim].used = ++g_map_clock;
     return true;
 }
 
