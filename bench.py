@@ -390,7 +390,7 @@ def run_b200(args):
             "data": "synthetic",
             "config": {"workload": name, "batch": w["batch"], "heads": H, "head_dim": D, "tokens": S_full,
                        "step": "qk_norm_rope + attention", "sharding": "none" if world == 1 and not ring else
-                       "ring sequence parallel (NCCL send/recv of K/V chunks)" if ring else
+                       "ring sequence parallel (K/V rows pushed peer to peer by the copy engines, NCCL for set-up)" if ring else
                        "cfg batch x heads, no collective", "l2": "inputs rotate over %d buffer sets (%.0f MB)" %
                        (nsets, nsets * per_set / 1e6)},
             "per_gpu_tflops": round(value / world, 2),

@@ -55,6 +55,11 @@ int iris_b200_set_device(int ordinal);
  * is how the two hot operations are embedded next to another backend that
  * owns the stream. NULL restores the internal stream. */
 int iris_b200_attach_stream(void *cuda_stream);
+/* The same switch without the wait for the work already enqueued: for hosts
+ * that run independent calls side by side on several streams (the cond and
+ * uncond attention of one step, the head groups of a long sequence) and
+ * order those streams themselves with events. No reference counterpart. */
+int iris_b200_use_stream(void *cuda_stream);
 void *iris_b200_stream(void);
 
 /* CUDA-event stopwatch on the library's stream: start() records an event,
@@ -186,11 +191,15 @@ size_t iris_b200_attention_noalloc_max_elems(void);
 
 /* Diagnostics for kernel bring-up: runs the tcgen05 kernel and dumps, into
  * `debug` (device, fp32), the raw scores S = Q K^T of the first key tile of
- * every CTA ([ctas * 256, 128]) followed by (m, l) per row ([ctas * 256, 2]);
- * ctas = ceil(seq_q / 256) * heads. desc_fields: NULL, or four words: the
+ * every CTA ([ctas * 256, 128]) followed by (m, l) per row ([ctas * 256, 2])
+ * and 512 words of device timestamps (cycle counts of CTA 0 per key tile,
+ * then wall-clock milestones of the first and the last CTA), so `debug`
+ * holds ctas * 256 * 130 + 512 floats; ctas = ceil(seq_q / 256) * heads.
+ * desc_fields: NULL, or four words: the
  * shared memory descriptor fields {qk_sbo, v_lbo, v_sbo} in 16-byte units
  * and a mode (bit 0 skip the softmax arithmetic, bit 1 skip the PV MMAs,
- * bit 2 skip the QK MMAs; results are then meaningless, only time is). */
+ * bit 2 skip the QK MMAs; results are then meaningless, only time is; bit 3
+ * leave out the S dump). */
 int iris_b200_attention_diag(uint16_t *out, int ldo,
                              const uint16_t *q, const uint16_t *k, const uint16_t *v,
                              int ldi, int seq_q, int seq_k, int heads, float scale,

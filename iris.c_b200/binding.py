@@ -41,6 +41,7 @@ SIGNATURES = {
     "iris_b200_check_device_status": (INT, []),
     "iris_b200_set_device": (INT, [INT]),
     "iris_b200_attach_stream": (INT, [VP]),
+    "iris_b200_use_stream": (INT, [VP]),
     "iris_b200_stream": (VP, []),
     "iris_b200_timer_start": (INT, []),
     "iris_b200_timer_stop_ms": (FLT, []),

@@ -102,7 +102,7 @@ struct Params {
     /* descriptor fields, in 16-byte units */
     uint32_t qk_sbo, v_lbo, v_sbo;
     float *debug;              /* bring-up dump, or NULL */
-    int diag_mode;             /* diagnostics build: 1 skip softmax math, 2 skip PV MMAs, 4 skip QK MMAs */
+    int diag_mode;             /* diagnostics build: 1 skip softmax math, 2 skip PV MMAs, 4 skip QK MMAs, 8 no S dump */
 };
 
 /* ---------------- PTX wrappers ---------------- */
@@ -298,6 +298,15 @@ __device__ __forceinline__ void stamp(const Params &p, int who, int j, int k) {
     }
 }
 
+/* Wall-clock (ns) milestones of the first and the last CTA (diagnostics build
+ * only): slot [3][first / last][k]. */
+__device__ __forceinline__ void stamp_ns(const Params &p, int k) {
+    if (p.debug && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
+        float *base = p.debug + (size_t)gridDim.x * 256 * 130;
+        reinterpret_cast<uint32_t *>(base)[(3 * 16 + (blockIdx.x == 0 ? 0 : 1)) * 8 + k] = (uint32_t)global_ns();
+    }
+}
+
 /* ---------------- roles ---------------- */
 
 /* Position in the K/V ring: items are consumed in load order K0 V0 K1 V1 ... */
@@ -488,6 +497,7 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_S_FULL + t, j & 1, 300 + t)))) break;
         tc_fence_after();
         if (DEBUG) stamp(p, t, j, 0);
+        if (DEBUG && j == 0 && threadIdx.x == 0) stamp_ns(p, 2);
         if (DEBUG && (p.diag_mode & 1)) {
             tc_fence_before();
             mbar_arrive(c.bars + (BAR_P_FULL + 2 * t) * 8);
@@ -505,7 +515,7 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
         for (int ch = 0; ch < 4; ch++) tmem_ld32(tS + ch * 32, s + ch * 32);
         tc_wait_ld();
         if (DEBUG) stamp(p, t, j, 1);
-        if (DEBUG && p.debug && j == 0) {
+        if (DEBUG && p.debug && j == 0 && !(p.diag_mode & 8)) {
             float *dst = p.debug + ((size_t)blockIdx.x * 256 + t * 128 + row) * 128;
 #pragma unroll
             for (int i = 0; i < 128; i++) dst[i] = __uint_as_float(s[i]);
@@ -576,9 +586,11 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
     }
 
     /* Epilogue: O / l -> bf16 rows of the output slice of this head. */
+    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 3);
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_O_DONE + t, (nkv - 1) & 1, 310 + t));
     if (!ok) return;
     tc_fence_after();
+    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 4);
     const bool valid = qrow < p.seq_q;
     float inv = l > 0.0f ? 1.0f / l : 0.0f;
     if (DEBUG && p.debug) {
@@ -652,6 +664,7 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
             }
         }
     }
+    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 5);
 }
 
 template <bool DEBUG>
@@ -674,6 +687,7 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     const int q0 = (blockIdx.x - head * p.nqblk) * 2 * kTileQ;
     const int ntq = (p.seq_q - q0 > kTileQ) ? 2 : 1;
     const int nkv = (p.seq_k + kTileK - 1) / kTileK;
+    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 0);
 
     if (threadIdx.x == 0) {
         mbar_init(c.bars + BAR_Q_FULL * 8, 1);
@@ -702,6 +716,7 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 1);
 
     if (warp < 8) {
         /* The third warpgroup hands most of its registers to the softmax ones. */
@@ -715,10 +730,12 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
 
     tc_fence_before();
     __syncthreads();
+    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 6);
     if (warp == 9) {
         tc_fence_after();
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+        if (DEBUG && lane == 0) stamp_ns(p, 7);
     }
 }
 

@@ -141,8 +141,8 @@ struct Ring {
     FnAllGather all_gather;
     NcclComm comm;
     int rank, nranks;
-    cudaStream_t comm_stream, aux_stream;
-    cudaEvent_t received[kMaxRanks], packed, comm_done, join;
+    cudaStream_t comm_stream, comm_stream2, aux_stream;   /* the second one only carries copy-engine pushes */
+    cudaEvent_t received[kMaxRanks], packed, comm_done, comm_done2, join;
     void *buf[kMaxRanks];                 /* [0] local chunk, [s] chunk of step s */
     size_t buf_bytes[kMaxRanks];
     float *o_state[kHeadGroups], *lse_state[kHeadGroups];
@@ -352,12 +352,14 @@ extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
     ring.rank = rank;
     ring.nranks = nranks;
     if (!cuda_ok(cudaStreamCreateWithFlags(&ring.comm_stream, cudaStreamNonBlocking), "stream create") ||
+        !cuda_ok(cudaStreamCreateWithFlags(&ring.comm_stream2, cudaStreamNonBlocking), "stream create") ||
         !cuda_ok(cudaStreamCreateWithFlags(&ring.aux_stream, cudaStreamNonBlocking), "stream create"))
         return IRIS_B200_ECUDA;
     for (int i = 0; i < kMaxRanks; i++)
         cuda_ok(cudaEventCreateWithFlags(&ring.received[i], cudaEventDisableTiming), "event create");
     cuda_ok(cudaEventCreateWithFlags(&ring.packed, cudaEventDisableTiming), "event create");
     cuda_ok(cudaEventCreateWithFlags(&ring.comm_done, cudaEventDisableTiming), "event create");
+    cuda_ok(cudaEventCreateWithFlags(&ring.comm_done2, cudaEventDisableTiming), "event create");
     cuda_ok(cudaEventCreateWithFlags(&ring.join, cudaEventDisableTiming), "event create");
     return g.last_error;
 }
@@ -390,8 +392,10 @@ extern "C" void iris_b200_ring_destroy(void) {
     }
     cuda_ok(cudaEventDestroy(ring.packed), "event destroy");
     cuda_ok(cudaEventDestroy(ring.comm_done), "event destroy");
+    cuda_ok(cudaEventDestroy(ring.comm_done2), "event destroy");
     cuda_ok(cudaEventDestroy(ring.join), "event destroy");
     cuda_ok(cudaStreamDestroy(ring.comm_stream), "stream destroy");
+    cuda_ok(cudaStreamDestroy(ring.comm_stream2), "stream destroy");
     cuda_ok(cudaStreamDestroy(ring.aux_stream), "stream destroy");
 }
 
@@ -417,7 +421,7 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     /* Transport: pushes by the copy engines into IPC-mapped slot pools when
      * that can be set up, NCCL send/recv into private buffers otherwise. */
     const bool ce = G > 1 && ce_setup(slot_bytes);
-    if (!ce) {
+    if (!ce && G > 1) {
         for (int s = 0; s < G; s++)
             if (!grow(&ring.buf[s], &ring.buf_bytes[s], slot_bytes)) return IRIS_B200_ENOMEM;
     }
@@ -430,32 +434,49 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     }
     const uint32_t seq = ++ring.seq;
     uint32_t *seq_word = ce ? ring.flags + kFlagSeq + (seq & 7u) : NULL;
+    const size_t my_bytes = (size_t)rows * 2 * width * 2;
+    const size_t row_bytes = width * 2, slot_pitch = 2 * width * 2;      /* a slot row is K | V */
 
-    /* The local chunk goes into slot 0 as [rows, K | V]; every earlier use of
-     * the slots is ordered before this point on the library's stream. */
-    if (ce && !stream_value(ring.write32, g.stream, seq_word, seq, CU_STREAM_WRITE_VALUE_DEFAULT, "write seq"))
-        return IRIS_B200_ECUDA;
-    if (!cuda_ok(cudaMemcpy2DAsync(chunk(0), 2 * width * 2, k, (size_t)ldi * 2, width * 2, rows,
-                                   cudaMemcpyDeviceToDevice, g.stream), "pack K") ||
-        !cuda_ok(cudaMemcpy2DAsync(chunk(0) + width * 2, 2 * width * 2, v, (size_t)ldi * 2, width * 2, rows,
-                                   cudaMemcpyDeviceToDevice, g.stream), "pack V"))
-        return IRIS_B200_ECUDA;
+    /* Step 0 reads the local rows. The copy engines take them from the
+     * caller's buffers as they are; NCCL wants them contiguous in slot 0. */
+    const uint16_t *k0 = k, *v0 = v;
+    int ld0 = ldi;
+    if (ce) {
+        /* Every earlier use of the sequence word is ordered before this
+         * point on the library's stream. */
+        if (!stream_value(ring.write32, g.stream, seq_word, seq, CU_STREAM_WRITE_VALUE_DEFAULT, "write seq"))
+            return IRIS_B200_ECUDA;
+    } else if (G > 1) {
+        if (!cuda_ok(cudaMemcpy2DAsync(chunk(0), slot_pitch, k, (size_t)ldi * 2, row_bytes, rows,
+                                       cudaMemcpyDeviceToDevice, g.stream), "pack K") ||
+            !cuda_ok(cudaMemcpy2DAsync(chunk(0) + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
+                                       cudaMemcpyDeviceToDevice, g.stream), "pack V"))
+            return IRIS_B200_ECUDA;
+        k0 = (const uint16_t *)chunk(0);
+        v0 = k0 + width;
+        ld0 = (int)(2 * width);
+    }
     cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record");
     cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
+    if (ce) cuda_ok(cudaStreamWaitEvent(ring.comm_stream2, ring.packed, 0), "stream wait");
 
-    /* All transfers, in step order: at step s this rank's chunk is wanted by
-     * rank me + s, which keeps it in its slot s. */
-    const size_t my_bytes = (size_t)rows * 2 * width * 2;
+    /* All transfers, in step order: at step s this rank's rows are wanted by
+     * rank me + s, which keeps them in its slot s. Pushes alternate between
+     * two streams so that the flag write of one overlaps the data of the next. */
     for (int s = 1; s < G; s++) {
         const int to = (me + s) % G, from = iris_b200_ring_source(me, s, G);
         if (ce) {
+            cudaStream_t cs = (s & 1) ? ring.comm_stream : ring.comm_stream2;
+            char *dst = ring.peer_pool[to] + (size_t)s * ring.slot_bytes;
             /* `to` has finished reading what the previous call put there. */
-            if (!stream_value(ring.wait32, ring.comm_stream, ring.flags + kFlagAck + to, seq - 1,
-                              CU_STREAM_WAIT_VALUE_GEQ, "wait ack") ||
-                !cuda_ok(cudaMemcpyAsync(ring.peer_pool[to] + (size_t)s * ring.slot_bytes, chunk(0), my_bytes,
-                                         cudaMemcpyDefault, ring.comm_stream), "push chunk") ||
-                !cuda_ok(cudaMemcpyAsync(ring.peer_flags[to] + kFlagArrive + s, seq_word, 4, cudaMemcpyDefault,
-                                         ring.comm_stream), "push flag"))
+            if (!stream_value(ring.wait32, cs, ring.flags + kFlagAck + to, seq - 1, CU_STREAM_WAIT_VALUE_GEQ,
+                              "wait ack") ||
+                !cuda_ok(cudaMemcpy2DAsync(dst, slot_pitch, k, (size_t)ldi * 2, row_bytes, rows, cudaMemcpyDefault, cs),
+                         "push K") ||
+                !cuda_ok(cudaMemcpy2DAsync(dst + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
+                                           cudaMemcpyDefault, cs), "push V") ||
+                !cuda_ok(cudaMemcpyAsync(ring.peer_flags[to] + kFlagArrive + s, seq_word, 4, cudaMemcpyDefault, cs),
+                         "push flag"))
                 return IRIS_B200_ECUDA;
         } else {
             if (!nccl_ok(ring.group_start(), "ncclGroupStart")) return IRIS_B200_ECOMM;
@@ -467,31 +488,45 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         }
     }
     cuda_ok(cudaEventRecord(ring.comm_done, ring.comm_stream), "event record");
+    if (ce) cuda_ok(cudaEventRecord(ring.comm_done2, ring.comm_stream2), "event record");
+
+    /* With many ranks a step is a small problem whose fixed costs (pipeline
+     * fill, state traffic) weigh: from step 2 on, two steps share a launch
+     * when their slots are adjacent rows of one buffer. */
+    bool even = ce && G >= 6 && ring.slot_bytes == my_bytes;
+    for (int r = 0; r < G && even; r++) even = rows_of[r] == rows;
+    const int pair_from = even ? 2 : G;
 
     /* The head groups run side by side: group 0 on the library's stream,
      * group 1 on the auxiliary one, joined again before the call returns. */
     if (ngroups > 1) cuda_ok(cudaStreamWaitEvent(ring.aux_stream, ring.packed, 0), "stream wait");
     int rc = IRIS_B200_OK;
-    for (int s = 0; s < G && rc == IRIS_B200_OK; s++) {
+    for (int s = 0; s < G && rc == IRIS_B200_OK;) {
+        const int nsteps = (s >= pair_from && s + 1 < G) ? 2 : 1;
         const int src = iris_b200_ring_source(me, s, G);
-        const uint16_t *kc = (const uint16_t *)chunk(s);
+        const uint16_t *kc = s == 0 ? k0 : (const uint16_t *)chunk(s);
+        const uint16_t *vc = s == 0 ? v0 : kc + width;
+        const int ldc = s == 0 ? ld0 : (int)(2 * width);
+        const int keys = nsteps == 2 ? 2 * rows : rows_of[src];
         for (int grp = 0; grp < ngroups && rc == IRIS_B200_OK; grp++) {
             cudaStream_t st = grp == 0 ? g.stream : ring.aux_stream;
-            if (s >= 1) {
+            for (int w = s; w < s + nsteps; w++) {
+                if (w == 0) continue;
                 if (ce) {
-                    if (!stream_value(ring.wait32, st, ring.flags + kFlagArrive + s, seq, CU_STREAM_WAIT_VALUE_GEQ,
+                    if (!stream_value(ring.wait32, st, ring.flags + kFlagArrive + w, seq, CU_STREAM_WAIT_VALUE_GEQ,
                                       "wait chunk"))
                         return IRIS_B200_ECUDA;
                 } else {
-                    cuda_ok(cudaStreamWaitEvent(st, ring.received[s], 0), "stream wait");
+                    cuda_ok(cudaStreamWaitEvent(st, ring.received[w], 0), "stream wait");
                 }
             }
             StreamScope scope(st);
             const size_t col = (size_t)grp * hg * 128;
-            rc = iris_b200_attention_chunk(out + col, ldo, q + col, ldi, kc + col, kc + width + col,
-                                           (int)(2 * width), rows, rows_of[src], hg, scale, NULL,
-                                           ring.o_state[grp], ring.lse_state[grp], s == 0, s == G - 1);
+            rc = iris_b200_attention_chunk(out + col, ldo, q + col, ldi, kc + col, vc + col, ldc, rows, keys, hg,
+                                           scale, NULL, ring.o_state[grp], ring.lse_state[grp], s == 0,
+                                           s + nsteps == G);
         }
+        s += nsteps;
     }
     if (ngroups > 1) {
         cuda_ok(cudaEventRecord(ring.join, ring.aux_stream), "event record");
@@ -506,7 +541,8 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
                 rc = IRIS_B200_ECUDA;
         }
     }
-    /* The transfers of the local chunk must not outlive the call. */
+    /* The transfers of the local rows must not outlive the call. */
     cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done, 0), "stream wait");
+    if (ce) cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done2, 0), "stream wait");
     return rc != IRIS_B200_OK ? rc : g.last_error;
 }

@@ -157,6 +157,13 @@ int iris_b200_attach_stream(void *cuda_stream) {
     return IRIS_B200_OK;
 }
 
+int iris_b200_use_stream(void *cuda_stream) {
+    if (!require_device("use_stream")) return IRIS_B200_ENODEV;
+    g.stream = cuda_stream ? (cudaStream_t)cuda_stream : g.own_stream;
+    g.owns_stream = cuda_stream == NULL;
+    return IRIS_B200_OK;
+}
+
 void *iris_b200_stream(void) { return g.ready ? (void *)g.stream : NULL; }
 
 int iris_b200_timer_start(void) {

@@ -106,12 +106,15 @@ def test_chunk_argument_checks(lib):
     lib.iris_b200_clear_error()
 
 
-def test_nccl_ring_on_two_gpus():
+@pytest.mark.parametrize("nproc,transport", [(2, "auto"), (2, "nccl"), (8, "auto")])
+def test_ring_across_gpus(nproc, transport):
+    """One process per GPU; `auto` pushes the chunks with the copy engines,
+    `nccl` forces the send/recv transport."""
     import torch
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0")
-    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+    if torch.cuda.device_count() < nproc:
+        pytest.skip("needs %d GPUs" % nproc)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", IRIS_B200_RING_TRANSPORT=transport)
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % nproc,
                           "--master-addr", "127.0.0.1", "--master-port", "29437",
                           os.path.join(ROOT, "tests", "ring_gpu_worker.py")],
                          capture_output=True, text=True, env=env, timeout=600)
