@@ -80,7 +80,8 @@ enum {
     BAR_S_FULL = BAR_KV_EMPTY + kStages,  /* 2 */
     BAR_P_FULL = BAR_S_FULL + 2,          /* 4: [tile][half of the key tile] */
     BAR_O_DONE = BAR_P_FULL + 4,          /* 2 */
-    BAR_DRAIN = BAR_O_DONE + 2,
+    BAR_Q_EMPTY = BAR_O_DONE + 2,         /* the QK products of a work item are complete */
+    BAR_DRAIN,
     BAR_COUNT
 };
 static constexpr int kSmemTmemPtr = BAR_COUNT * 8;      /* u32 */
@@ -91,6 +92,7 @@ struct Params {
     int ldo;
     int seq_q, seq_k, heads;
     int nqblk;                 /* 256-row query blocks per head */
+    int items;                 /* work items: nqblk * heads, dealt round-robin to the CTAs */
     float scale_log2;
     const uint32_t *mask_bits; /* packed key mask, bit j of word j/32, or NULL */
     unsigned int *status;      /* [0] flag, [1] site, [2] block, [3] aux */
@@ -293,16 +295,18 @@ __device__ __forceinline__ void stamp(const Params &p, int who, int j, int k) {
     if (p.debug && blockIdx.x == 0 && j < 16 && (threadIdx.x & 31) == 0 && (who == 2 || (threadIdx.x & 127) == 0)) {
         unsigned long long c;
         asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
-        float *base = p.debug + (size_t)gridDim.x * 256 * 130;
+        float *base = p.debug + (size_t)p.items * 256 * 130;
         reinterpret_cast<uint32_t *>(base)[(who * 16 + j) * 8 + k] = (uint32_t)c;
     }
 }
 
 /* Wall-clock (ns) milestones of the first and the last CTA (diagnostics build
- * only): slot [3][first / last][k]. */
+ * only): slot [3][first / last][k]; k = 0 entry, 1 set-up done, 2 first S of
+ * the first item, 3 its last softmax done, 4 its last PV done, 5 its output
+ * written, 6 first S of the second item, 7 all warps done. */
 __device__ __forceinline__ void stamp_ns(const Params &p, int k) {
     if (p.debug && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
-        float *base = p.debug + (size_t)gridDim.x * 256 * 130;
+        float *base = p.debug + (size_t)p.items * 256 * 130;
         reinterpret_cast<uint32_t *>(base)[(3 * 16 + (blockIdx.x == 0 ? 0 : 1)) * 8 + k] = (uint32_t)global_ns();
     }
 }
@@ -321,29 +325,53 @@ struct Ring {
     }
 };
 
+/* A work item is one 256-row query block of one head. CTA b runs items
+ * b, b + gridDim.x, ... one after the other: while the softmax warps write
+ * the output of one item, the Q / K / V tiles of the next are already in
+ * shared memory and its first QK products are in flight. */
+struct Item {
+    int head, q0, ntq;
+};
+__device__ __forceinline__ Item item_of(const Params &p, int item) {
+    Item w;
+    w.head = item / p.nqblk;
+    w.q0 = (item - w.head * p.nqblk) * 2 * kTileQ;
+    w.ntq = (p.seq_q - w.q0 > kTileQ) ? 2 : 1;
+    return w;
+}
+
 __device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
     return ((uint64_t)hi << 32) | lo;
 }
 
 __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmq, const CUtensorMap *tmk,
-                         const CUtensorMap *tmv, uint32_t smem, int head, int q0, int ntq, int nkv) {
-    const int col = head * kHeadDim;
-    mbar_expect_tx(c.bars + BAR_Q_FULL * 8, ntq * kTileBytes);
-    for (int t = 0; t < ntq; t++)
-        for (int half = 0; half < 2; half++)
-            tma_load_2d(smem + kSmemQ + t * kTileBytes + half * kHalfBytes, tmq, col + half * 64,
-                        q0 + t * kTileQ, c.bars + BAR_Q_FULL * 8);
+                         const CUtensorMap *tmv, uint32_t smem, int nkv) {
     int issued = 0;
     Ring r = {0, 0u};
-    for (int it = 0; it < 2 * nkv; it++, issued++, r.next()) {
-        /* A slot is refilled once the MMAs that read its previous content are done. */
-        if (it >= kStages && !mbar_wait(c, BAR_KV_EMPTY + r.slot, r.phase ^ 1u, 100 + r.slot)) break;
-        uint32_t full = c.bars + (BAR_KV_FULL + r.slot) * 8;
-        mbar_expect_tx(full, kTileBytes);
-        const CUtensorMap *map = (it & 1) ? tmv : tmk;
-        for (int half = 0; half < 2; half++)
-            tma_load_2d(smem + kSmemKV + r.slot * kTileBytes + half * kHalfBytes, map, col + half * 64,
-                        (it >> 1) * kTileK, full);
+    bool ok = true;
+    for (int item = blockIdx.x, n = 0; ok && item < p.items; item += gridDim.x, n++) {
+        const Item w = item_of(p, item);
+        const int col = w.head * kHeadDim;
+        /* The Q tiles are replaced once every QK product of the previous item is done. */
+        if (n > 0 && !mbar_wait(c, BAR_Q_EMPTY, (n - 1) & 1, 110)) break;
+        mbar_expect_tx(c.bars + BAR_Q_FULL * 8, w.ntq * kTileBytes);
+        for (int t = 0; t < w.ntq; t++)
+            for (int half = 0; half < 2; half++)
+                tma_load_2d(smem + kSmemQ + t * kTileBytes + half * kHalfBytes, tmq, col + half * 64,
+                            w.q0 + t * kTileQ, c.bars + BAR_Q_FULL * 8);
+        for (int it = 0; it < 2 * nkv; it++, issued++, r.next()) {
+            /* A slot is refilled once the MMAs that read its previous content are done. */
+            if (issued >= kStages && !mbar_wait(c, BAR_KV_EMPTY + r.slot, r.phase ^ 1u, 100 + r.slot)) {
+                ok = false;
+                break;
+            }
+            uint32_t full = c.bars + (BAR_KV_FULL + r.slot) * 8;
+            mbar_expect_tx(full, kTileBytes);
+            const CUtensorMap *map = (it & 1) ? tmv : tmk;
+            for (int half = 0; half < 2; half++)
+                tma_load_2d(smem + kSmemKV + r.slot * kTileBytes + half * kHalfBytes, map, col + half * 64,
+                            (it >> 1) * kTileK, full);
+        }
     }
     if (*c.abort_flag) {
         /* Nobody may be consuming any more: wait for the copies still in flight. */
@@ -353,7 +381,7 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
 }
 
 template <bool DEBUG>
-__device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem, int ntq, int nkv) {
+__device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem, int nkv) {
     /* Descriptor words that never change: the high word (stride offset,
      * version, swizzle mode) per operand kind, and the low word of each
      * tile base (start address and leading offset, 16-byte units). A k-step
@@ -364,7 +392,7 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
     const uint32_t lo_k0 = (uint32_t)make_desc(smem + kSmemKV, 1, 0);
     const uint32_t lo_v0 = (uint32_t)make_desc(smem + kSmemKV, p.v_lbo, 0);
     const bool leader = elect_one();        /* the whole warp runs this code, one lane issues */
-    bool ok;
+    bool ok = true;
 
     auto issue_qk = [&](int t, int slot) {
         const uint32_t lo_q = lo_q0 + t * (kTileBytes >> 4), lo_k = lo_k0 + slot * (kTileBytes >> 4);
@@ -395,41 +423,57 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
     };
 
     Ring r = {0, 0u};
-    ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_Q_FULL, 0, 200) && mbar_wait(c, BAR_KV_FULL + r.slot, r.phase, 201));
-    if (ok) {
+    uint32_t seen[2] = {0u, 0u};            /* key tiles of query tile t so far, over all items */
+    for (int item = blockIdx.x, n = 0; ok && item < p.items; item += gridDim.x, n++) {
+        const int ntq = item_of(p, item).ntq;
+        const int js = n == 0 ? 0 : 16;     /* timestamps cover the first item only */
+        ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_Q_FULL, n & 1, 200) && mbar_wait(c, BAR_KV_FULL + r.slot, r.phase, 201));
+        if (!ok) break;
         tc_fence_after();
+        /* S of tile t is free: the last PV of the previous item, issued
+         * before, read P from it, and the tensor pipe keeps the order. */
         for (int t = 0; t < ntq; t++) issue_qk(t, r.slot);
-        if (leader) tc_commit(c.bars + (BAR_KV_EMPTY + r.slot) * 8);
+        if (leader) {
+            tc_commit(c.bars + (BAR_KV_EMPTY + r.slot) * 8);
+            if (nkv == 1) tc_commit(c.bars + BAR_Q_EMPTY * 8);
+        }
         r.next();
-    }
-    for (int j = 0; ok && j < nkv; j++) {
-        const Ring rv = r;              /* V_j */
-        r.next();
-        const Ring rk = r;              /* K_{j+1}, when there is one */
-        const bool more = j + 1 < nkv;
-        if (more) r.next();
-        if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rv.slot, rv.phase, 210)))) break;
-        for (int t = 0; t < ntq; t++) {
-            if (DEBUG) stamp(p, 2, j, 4 * t);
-            /* The first 64 keys' P arrives while the softmax is still busy
-             * with the other 64: their PV runs under it. */
-            if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + 2 * t, j & 1, 220 + t)))) break;
-            tc_fence_after();
-            issue_pv(t, 0, rv.slot, j == 0);
-            if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + 2 * t + 1, j & 1, 224 + t)))) break;
-            tc_fence_after();
-            if (DEBUG) stamp(p, 2, j, 4 * t + 1);
-            issue_pv(t, 1, rv.slot, j == 0);
-            if (t == ntq - 1 && leader) tc_commit(c.bars + (BAR_KV_EMPTY + rv.slot) * 8);
-            if (more) {
-                if (t == 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rk.slot, rk.phase, 230)))) break;
+        for (int j = 0; ok && j < nkv; j++) {
+            const Ring rv = r;              /* V_j */
+            r.next();
+            const Ring rk = r;              /* K_{j+1}, when there is one */
+            const bool more = j + 1 < nkv;
+            if (more) r.next();
+            if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rv.slot, rv.phase, 210)))) break;
+            for (int t = 0; t < ntq; t++) {
+                const uint32_t par = (seen[t] + j) & 1u;
+                if (DEBUG) stamp(p, 2, j + js, 4 * t);
+                /* The first 64 keys' P arrives while the softmax is still busy
+                 * with the other 64: their PV runs under it. (With j == 0 the
+                 * softmax warps have also read the previous item's O by now.) */
+                if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + 2 * t, par, 220 + t)))) break;
                 tc_fence_after();
-                if (DEBUG) stamp(p, 2, j, 4 * t + 2);
-                issue_qk(t, rk.slot);
-                if (t == ntq - 1 && leader) tc_commit(c.bars + (BAR_KV_EMPTY + rk.slot) * 8);
-                if (DEBUG) stamp(p, 2, j, 4 * t + 3);
+                issue_pv(t, 0, rv.slot, j == 0);
+                if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + 2 * t + 1, par, 224 + t)))) break;
+                tc_fence_after();
+                if (DEBUG) stamp(p, 2, j + js, 4 * t + 1);
+                issue_pv(t, 1, rv.slot, j == 0);
+                if (t == ntq - 1 && leader) tc_commit(c.bars + (BAR_KV_EMPTY + rv.slot) * 8);
+                if (more) {
+                    if (t == 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rk.slot, rk.phase, 230)))) break;
+                    tc_fence_after();
+                    if (DEBUG) stamp(p, 2, j + js, 4 * t + 2);
+                    issue_qk(t, rk.slot);
+                    if (t == ntq - 1 && leader) {
+                        tc_commit(c.bars + (BAR_KV_EMPTY + rk.slot) * 8);
+                        /* That was the last read of this item's Q tiles. */
+                        if (j + 2 == nkv) tc_commit(c.bars + BAR_Q_EMPTY * 8);
+                    }
+                    if (DEBUG) stamp(p, 2, j + js, 4 * t + 3);
+                }
             }
         }
+        for (int t = 0; t < ntq; t++) seen[t] += (uint32_t)nkv;
     }
     if (!ok) {
         /* Let what was issued finish before the tensor memory goes away. */
@@ -480,8 +524,11 @@ __device__ __forceinline__ void exp_half(const uint32_t *s, float sl2, float neg
     }
 }
 
+/* One work item of query tile t. `cnt`: key tiles this tile has been through
+ * before (the barrier phases run on over the items). False when aborting. */
 template <bool DEBUG>
-__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32_t tmem, int t, int head, int q0, int nkv) {
+__device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, uint32_t tmem, int t, int item, int head,
+                                             int q0, int nkv, uint32_t cnt, int js) {
     const int row = threadIdx.x & 127;                     /* row of the tile == TMEM lane */
     const uint32_t lane_base = (uint32_t)(row & ~31) << 16;
     const uint32_t tS = tmem + lane_base + t * 128;
@@ -494,10 +541,10 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
 
     for (int j = 0; j < nkv; j++) {
         /* One decision per warp: the TMEM accesses below are warp-collective. */
-        if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_S_FULL + t, j & 1, 300 + t)))) break;
+        if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_S_FULL + t, (cnt + j) & 1u, 300 + t)))) break;
         tc_fence_after();
-        if (DEBUG) stamp(p, t, j, 0);
-        if (DEBUG && j == 0 && threadIdx.x == 0) stamp_ns(p, 2);
+        if (DEBUG) stamp(p, t, j + js, 0);
+        if (DEBUG && j == 0 && threadIdx.x == 0 && js <= 16) stamp_ns(p, js == 0 ? 2 : 6);
         if (DEBUG && (p.diag_mode & 1)) {
             tc_fence_before();
             mbar_arrive(c.bars + (BAR_P_FULL + 2 * t) * 8);
@@ -514,9 +561,9 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) tmem_ld32(tS + ch * 32, s + ch * 32);
         tc_wait_ld();
-        if (DEBUG) stamp(p, t, j, 1);
+        if (DEBUG) stamp(p, t, j + js, 1);
         if (DEBUG && p.debug && j == 0 && !(p.diag_mode & 8)) {
-            float *dst = p.debug + ((size_t)blockIdx.x * 256 + t * 128 + row) * 128;
+            float *dst = p.debug + ((size_t)item * 256 + t * 128 + row) * 128;
 #pragma unroll
             for (int i = 0; i < 128; i++) dst[i] = __uint_as_float(s[i]);
         }
@@ -568,7 +615,7 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
          * special-function unit, which is the scarcer of the two here. */
         const float neg_ref = m_ref == -INFINITY ? 0.0f : -m_ref;
         float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (DEBUG) stamp(p, t, j, 2);
+        if (DEBUG) stamp(p, t, j + js, 2);
         /* Tiles with masked (-inf) scores keep every exponential on the
          * special-function unit, which returns an exact 0 for them. */
 #pragma unroll
@@ -579,22 +626,22 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(c.bars + (BAR_P_FULL + 2 * t + h) * 8);
-            if (DEBUG && h == 0) stamp(p, t, j, 3);
+            if (DEBUG && h == 0) stamp(p, t, j + js, 3);
         }
         l += (sum4[0] + sum4[2]) + (sum4[1] + sum4[3]);
-        if (DEBUG) stamp(p, t, j, 4);
+        if (DEBUG) stamp(p, t, j + js, 4);
     }
 
     /* Epilogue: O / l -> bf16 rows of the output slice of this head. */
-    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 3);
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_O_DONE + t, (nkv - 1) & 1, 310 + t));
-    if (!ok) return;
+    if (DEBUG && threadIdx.x == 0 && js == 0) stamp_ns(p, 3);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_O_DONE + t, (cnt + nkv - 1) & 1u, 310 + t));
+    if (!ok) return false;
     tc_fence_after();
-    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 4);
+    if (DEBUG && threadIdx.x == 0 && js == 0) stamp_ns(p, 4);
     const bool valid = qrow < p.seq_q;
     float inv = l > 0.0f ? 1.0f / l : 0.0f;
     if (DEBUG && p.debug) {
-        float *dst = p.debug + (size_t)gridDim.x * 256 * 128 + ((size_t)blockIdx.x * 256 + t * 128 + row) * 2;
+        float *dst = p.debug + (size_t)p.items * 256 * 128 + ((size_t)item * 256 + t * 128 + row) * 2;
         dst[0] = m_ref;
         dst[1] = l;
     }
@@ -664,7 +711,23 @@ __device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32
             }
         }
     }
-    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 5);
+    if (DEBUG && threadIdx.x == 0 && js == 0) stamp_ns(p, 5);
+    /* The reads of O above are complete (each was waited for); the fence
+     * orders them before the arrival that lets the next item's PV start. */
+    tc_fence_before();
+    return true;
+}
+
+/* The softmax warpgroup of query tile t, over the work items of this CTA. */
+template <bool DEBUG>
+__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32_t tmem, int t, int nkv) {
+    uint32_t cnt = 0;
+    for (int item = blockIdx.x, n = 0; item < p.items; item += gridDim.x, n++) {
+        const Item w = item_of(p, item);
+        if (t >= w.ntq) continue;
+        if (!softmax_item<DEBUG>(c, p, tmem, t, item, w.head, w.q0, nkv, cnt, n == 0 ? 0 : (n == 1 ? 16 : 32))) return;
+        cnt += (uint32_t)nkv;
+    }
 }
 
 template <bool DEBUG>
@@ -683,9 +746,6 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     c.status = p.status;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemTmemPtr);
 
-    const int head = blockIdx.x / p.nqblk;
-    const int q0 = (blockIdx.x - head * p.nqblk) * 2 * kTileQ;
-    const int ntq = (p.seq_q - q0 > kTileQ) ? 2 : 1;
     const int nkv = (p.seq_k + kTileK - 1) / kTileK;
     if (DEBUG && threadIdx.x == 0) stamp_ns(p, 0);
 
@@ -701,6 +761,7 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
             mbar_init(c.bars + (BAR_P_FULL + 2 * t + 1) * 8, 128);
             mbar_init(c.bars + (BAR_O_DONE + t) * 8, 1);
         }
+        mbar_init(c.bars + BAR_Q_EMPTY * 8, 1);
         mbar_init(c.bars + BAR_DRAIN * 8, 1);
         *c.abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -721,21 +782,20 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     if (warp < 8) {
         /* The third warpgroup hands most of its registers to the softmax ones. */
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-        if (warp < 4 * ntq) softmax_wg<DEBUG>(c, p, tmem, warp >> 2, head, q0, nkv);
+        softmax_wg<DEBUG>(c, p, tmem, warp >> 2, nkv);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-        if (warp == 8 && lane == 0) producer(c, p, &tmq, &tmk, &tmv, smem, head, q0, ntq, nkv);
-        if (warp == 9) mma_issuer<DEBUG>(c, p, smem, tmem, ntq, nkv);
+        if (warp == 8 && lane == 0) producer(c, p, &tmq, &tmk, &tmv, smem, nkv);
+        if (warp == 9) mma_issuer<DEBUG>(c, p, smem, tmem, nkv);
     }
 
     tc_fence_before();
     __syncthreads();
-    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 6);
+    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 7);
     if (warp == 9) {
         tc_fence_after();
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
-        if (DEBUG && lane == 0) stamp_ns(p, 7);
     }
 }
 
@@ -903,6 +963,7 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, c
     p.seq_k = seq_k;
     p.heads = heads;
     p.nqblk = (seq_q + 2 * kTileQ - 1) / (2 * kTileQ);
+    p.items = p.nqblk * heads;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = g.dev_status;
     p.o_acc = o_acc;
@@ -913,7 +974,18 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, c
     p.v_sbo = desc_override ? desc_override[2] : 1024 / 16;         /* next 8 keys */
     p.debug = debug;
     p.diag_mode = diag_mode;
-    unsigned grid = (unsigned)(p.nqblk * heads);
+    /* One CTA per SM at most (shared and tensor memory allow no more); each
+     * walks its share of the work items. */
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) {
+            (void)cudaGetLastError();
+            sm_count = 148;
+        }
+    }
+    unsigned grid = (unsigned)(p.items < sm_count ? p.items : sm_count);
     if (debug)
         k_attention_sm100<true><<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk, tmv, p);
     else
