@@ -59,13 +59,14 @@ namespace sm100 {
 static constexpr int kTileQ = 128;            /* rows of one query tile / MMA M */
 static constexpr int kTileK = 128;            /* keys per tile / MMA N of S */
 static constexpr int kHeadDim = 128;
-static constexpr int kStages = 5;             /* K / V ring slots */
+static constexpr int kStages = 4;             /* K / V ring slots */
 static constexpr int kHalfBytes = 128 * 64 * 2;         /* one [128 x 64] bf16 swizzled box */
 static constexpr int kTileBytes = 2 * kHalfBytes;       /* one [128 x 128] bf16 operand */
 static constexpr int kThreads = 384;
 static constexpr int kSmemQ = 0;
 static constexpr int kSmemKV = 2 * kTileBytes;
-static constexpr int kSmemBar = kSmemKV + kStages * kTileBytes;
+static constexpr int kSmemStage = kSmemKV + kStages * kTileBytes;   /* output staging: 8 warps x 4 KB */
+static constexpr int kSmemBar = kSmemStage + 8 * 4096;
 static constexpr int kSmemBytes = kSmemBar + 256 + 1024;   /* + barriers + alignment slack */
 static constexpr float kRescaleThreshold = 8.0f;
 static constexpr bool kPolyExp = false;    /* evaluate one exponential in four on the FMA pipe */
@@ -527,8 +528,8 @@ __device__ __forceinline__ void exp_half(const uint32_t *s, float sl2, float neg
 /* One work item of query tile t. `cnt`: key tiles this tile has been through
  * before (the barrier phases run on over the items). False when aborting. */
 template <bool DEBUG>
-__device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, uint32_t tmem, int t, int item, int head,
-                                             int q0, int nkv, uint32_t cnt, int js) {
+__device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsigned char *stage, uint32_t tmem, int t,
+                                             int item, int head, int q0, int nkv, uint32_t cnt, int js) {
     const int row = threadIdx.x & 127;                     /* row of the tile == TMEM lane */
     const uint32_t lane_base = (uint32_t)(row & ~31) << 16;
     const uint32_t tS = tmem + lane_base + t * 128;
@@ -674,40 +675,60 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, uint
     const bool vec16 = (p.ldo & 7) == 0;
     uint16_t *orow = p.out ? p.out + (size_t)qrow * p.ldo + (size_t)head * kHeadDim : nullptr;
 
+    /* Two passes of 64 columns. The bf16 rows go through a 4 KB staging area
+     * private to the warp (32 rows x 128 bytes, 16-byte chunks XOR-swizzled by
+     * the row so that neither side has bank conflicts): a thread owns a row
+     * of the accumulator, but eight threads writing 128 contiguous bytes of
+     * one output row is what the memory system wants. */
+    const int lane = threadIdx.x & 31, wrow0 = row & ~31;
+    unsigned char *stage_w = stage + (size_t)(t * 4 + (wrow0 >> 5)) * 4096;
+    const float f_cur = inv * w_cur;
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint32_t o[32];
-        tmem_ld32(tO + i * 32, o);
+    for (int half = 0; half < 2; half++) {
+        uint32_t o[64];
+        tmem_ld32(tO + half * 64, o);
+        tmem_ld32(tO + half * 64 + 32, o + 32);
         tc_wait_ld();
-        if (!valid) continue;
-        float f[32];
 #pragma unroll
-        for (int e = 0; e < 32; e++) f[e] = __uint_as_float(o[e]) * inv * w_cur;
-        if (read_state) {
+        for (int e = 0; e < 64; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * f_cur);
+        if (read_state && valid) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-                float4 pr = *reinterpret_cast<const float4 *>(acc_row + i * 32 + e);
-                f[e] += pr.x * w_prev; f[e + 1] += pr.y * w_prev;
-                f[e + 2] += pr.z * w_prev; f[e + 3] += pr.w * w_prev;
+            for (int e = 0; e < 64; e += 4) {
+                float4 pr = *reinterpret_cast<const float4 *>(acc_row + half * 64 + e);
+                o[e] = __float_as_uint(__uint_as_float(o[e]) + pr.x * w_prev);
+                o[e + 1] = __float_as_uint(__uint_as_float(o[e + 1]) + pr.y * w_prev);
+                o[e + 2] = __float_as_uint(__uint_as_float(o[e + 2]) + pr.z * w_prev);
+                o[e + 3] = __float_as_uint(__uint_as_float(o[e + 3]) + pr.w * w_prev);
             }
         }
-        if (write_state) {
+        if (write_state && valid) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 4)
-                *reinterpret_cast<float4 *>(acc_row + i * 32 + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+            for (int e = 0; e < 64; e += 4)
+                *reinterpret_cast<uint4 *>(acc_row + half * 64 + e) = make_uint4(o[e], o[e + 1], o[e + 2], o[e + 3]);
         }
         if (write_out) {
-            uint32_t pkd[16];
+            uint32_t pkd[32];
 #pragma unroll
-            for (int e = 0; e < 16; e++) pkd[e] = cvt_bf16x2(f[2 * e], f[2 * e + 1]);
+            for (int e = 0; e < 32; e++) pkd[e] = cvt_bf16x2(__uint_as_float(o[2 * e]), __uint_as_float(o[2 * e + 1]));
             if (vec16) {
 #pragma unroll
-                for (int e = 0; e < 4; e++)
-                    *reinterpret_cast<uint4 *>(orow + i * 32 + e * 8) =
-                        make_uint4(pkd[4 * e], pkd[4 * e + 1], pkd[4 * e + 2], pkd[4 * e + 3]);
-            } else {
+                for (int ch = 0; ch < 8; ch++)
+                    *reinterpret_cast<uint4 *>(stage_w + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
+                        make_uint4(pkd[4 * ch], pkd[4 * ch + 1], pkd[4 * ch + 2], pkd[4 * ch + 3]);
+                __syncwarp();
+                const int ch = lane & 7;
 #pragma unroll
-                for (int e = 0; e < 16; e++) *reinterpret_cast<uint32_t *>(orow + i * 32 + e * 2) = pkd[e];
+                for (int k = 0; k < 8; k++) {
+                    const int r = k * 4 + (lane >> 3);
+                    const uint4 val = *reinterpret_cast<const uint4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4));
+                    const int grow = q0 + t * kTileQ + wrow0 + r;
+                    if (grow < p.seq_q)
+                        *reinterpret_cast<uint4 *>(p.out + (size_t)grow * p.ldo + (size_t)head * kHeadDim + half * 64 + ch * 8) = val;
+                }
+                __syncwarp();
+            } else if (valid) {
+#pragma unroll
+                for (int e = 0; e < 32; e++) *reinterpret_cast<uint32_t *>(orow + half * 64 + e * 2) = pkd[e];
             }
         }
     }
@@ -720,12 +741,13 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, uint
 
 /* The softmax warpgroup of query tile t, over the work items of this CTA. */
 template <bool DEBUG>
-__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, uint32_t tmem, int t, int nkv) {
+__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, unsigned char *stage, uint32_t tmem, int t,
+                                           int nkv) {
     uint32_t cnt = 0;
     for (int item = blockIdx.x, n = 0; item < p.items; item += gridDim.x, n++) {
         const Item w = item_of(p, item);
         if (t >= w.ntq) continue;
-        if (!softmax_item<DEBUG>(c, p, tmem, t, item, w.head, w.q0, nkv, cnt, n == 0 ? 0 : (n == 1 ? 16 : 32))) return;
+        if (!softmax_item<DEBUG>(c, p, stage, tmem, t, item, w.head, w.q0, nkv, cnt, n == 0 ? 0 : (n == 1 ? 16 : 32))) return;
         cnt += (uint32_t)nkv;
     }
 }
@@ -782,7 +804,7 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     if (warp < 8) {
         /* The third warpgroup hands most of its registers to the softmax ones. */
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-        softmax_wg<DEBUG>(c, p, tmem, warp >> 2, nkv);
+        softmax_wg<DEBUG>(c, p, smem_gen + kSmemStage, tmem, warp >> 2, nkv);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
         if (warp == 8 && lane == 0) producer(c, p, &tmq, &tmk, &tmv, smem, nkv);
