@@ -93,7 +93,14 @@ struct Params {
     int ldo;
     int seq_q, seq_k, heads;
     int nqblk;                 /* 256-row query blocks per head */
-    int items;                 /* work items: nqblk * heads, dealt round-robin to the CTAs */
+    int items;                 /* work items: nqblk * heads * nsplit, dealt round-robin to the CTAs */
+    int nkv;                   /* 128-key tiles */
+    /* Key split: the two halves of the keys of a query block are separate
+     * work items; whichever half finishes second merges the other's partial. */
+    int nsplit;                /* 1 or 2 */
+    float *part_o;             /* [nqblk * heads, 256, 128] fp32, unnormalised O of the half that finished first */
+    float2 *part_ml;           /* [nqblk * heads, 256] its (row maximum, row sum) */
+    unsigned int *tickets;     /* [nqblk * heads, 8 warps, 2]: arrivals, partial ready; zero between launches */
     float scale_log2;
     const uint32_t *mask_bits; /* packed key mask, bit j of word j/32, or NULL */
     unsigned int *status;      /* [0] flag, [1] site, [2] block, [3] aux */
@@ -331,13 +338,19 @@ struct Ring {
  * the output of one item, the Q / K / V tiles of the next are already in
  * shared memory and its first QK products are in flight. */
 struct Item {
+    int qitem;          /* query block index over all heads */
     int head, q0, ntq;
+    int j0, nj;         /* first key tile and number of key tiles */
 };
 __device__ __forceinline__ Item item_of(const Params &p, int item) {
     Item w;
-    w.head = item / p.nqblk;
-    w.q0 = (item - w.head * p.nqblk) * 2 * kTileQ;
+    w.qitem = p.nsplit == 2 ? item >> 1 : item;
+    const int ks = p.nsplit == 2 ? item & 1 : 0;
+    w.head = w.qitem / p.nqblk;
+    w.q0 = (w.qitem - w.head * p.nqblk) * 2 * kTileQ;
     w.ntq = (p.seq_q - w.q0 > kTileQ) ? 2 : 1;
+    w.j0 = ks * p.nkv / p.nsplit;
+    w.nj = (ks + 1) * p.nkv / p.nsplit - w.j0;
     return w;
 }
 
@@ -346,7 +359,7 @@ __device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
 }
 
 __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmq, const CUtensorMap *tmk,
-                         const CUtensorMap *tmv, uint32_t smem, int nkv) {
+                         const CUtensorMap *tmv, uint32_t smem) {
     int issued = 0;
     Ring r = {0, 0u};
     bool ok = true;
@@ -360,7 +373,7 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
             for (int half = 0; half < 2; half++)
                 tma_load_2d(smem + kSmemQ + t * kTileBytes + half * kHalfBytes, tmq, col + half * 64,
                             w.q0 + t * kTileQ, c.bars + BAR_Q_FULL * 8);
-        for (int it = 0; it < 2 * nkv; it++, issued++, r.next()) {
+        for (int it = 0; it < 2 * w.nj; it++, issued++, r.next()) {
             /* A slot is refilled once the MMAs that read its previous content are done. */
             if (issued >= kStages && !mbar_wait(c, BAR_KV_EMPTY + r.slot, r.phase ^ 1u, 100 + r.slot)) {
                 ok = false;
@@ -371,7 +384,7 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
             const CUtensorMap *map = (it & 1) ? tmv : tmk;
             for (int half = 0; half < 2; half++)
                 tma_load_2d(smem + kSmemKV + r.slot * kTileBytes + half * kHalfBytes, map, col + half * 64,
-                            (it >> 1) * kTileK, full);
+                            (w.j0 + (it >> 1)) * kTileK, full);
         }
     }
     if (*c.abort_flag) {
@@ -382,7 +395,7 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
 }
 
 template <bool DEBUG>
-__device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem, int nkv) {
+__device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem) {
     /* Descriptor words that never change: the high word (stride offset,
      * version, swizzle mode) per operand kind, and the low word of each
      * tile base (start address and leading offset, 16-byte units). A k-step
@@ -426,7 +439,8 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
     Ring r = {0, 0u};
     uint32_t seen[2] = {0u, 0u};            /* key tiles of query tile t so far, over all items */
     for (int item = blockIdx.x, n = 0; ok && item < p.items; item += gridDim.x, n++) {
-        const int ntq = item_of(p, item).ntq;
+        const Item w = item_of(p, item);
+        const int ntq = w.ntq, nkv = w.nj;
         const int js = n == 0 ? 0 : 16;     /* timestamps cover the first item only */
         ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_Q_FULL, n & 1, 200) && mbar_wait(c, BAR_KV_FULL + r.slot, r.phase, 201));
         if (!ok) break;
@@ -525,11 +539,53 @@ __device__ __forceinline__ void exp_half(const uint32_t *s, float sl2, float neg
     }
 }
 
+/* fp32 rows of a warp through its staging area. A thread owns one row of
+ * the accumulator; memory wants eight threads per 128 contiguous bytes of a
+ * row. Both helpers move 32 columns (128 bytes) of the warp's 32 rows, of
+ * which the first `nvalid` exist; `base` points at row 0, rows are `ld`
+ * floats apart. The staging rows are 128 bytes with their 16-byte chunks
+ * XOR-swizzled by the row, free of bank conflicts on either side. */
+__device__ __forceinline__ void rows_load_f32(uint32_t *dst, const float *base, size_t ld, int nvalid,
+                                              unsigned char *stage_w, int lane) {
+    const int ch = lane & 7;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int r = k * 4 + (lane >> 3);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < nvalid) v = __ldcg(reinterpret_cast<const uint4 *>(base + (size_t)r * ld + ch * 4));
+        *reinterpret_cast<uint4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int c8 = 0; c8 < 8; c8++) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(stage_w + lane * 128 + ((c8 ^ (lane & 7)) << 4));
+        dst[4 * c8] = v.x; dst[4 * c8 + 1] = v.y; dst[4 * c8 + 2] = v.z; dst[4 * c8 + 3] = v.w;
+    }
+    __syncwarp();
+}
+__device__ __forceinline__ void rows_store_f32(const uint32_t *src, float *base, size_t ld, int nvalid,
+                                               unsigned char *stage_w, int lane) {
+#pragma unroll
+    for (int c8 = 0; c8 < 8; c8++)
+        *reinterpret_cast<uint4 *>(stage_w + lane * 128 + ((c8 ^ (lane & 7)) << 4)) =
+            make_uint4(src[4 * c8], src[4 * c8 + 1], src[4 * c8 + 2], src[4 * c8 + 3]);
+    __syncwarp();
+    const int ch = lane & 7;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int r = k * 4 + (lane >> 3);
+        const uint4 v = *reinterpret_cast<const uint4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4));
+        if (r < nvalid) __stcg(reinterpret_cast<uint4 *>(base + (size_t)r * ld + ch * 4), v);
+    }
+    __syncwarp();
+}
+
 /* One work item of query tile t. `cnt`: key tiles this tile has been through
  * before (the barrier phases run on over the items). False when aborting. */
 template <bool DEBUG>
 __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsigned char *stage, uint32_t tmem, int t,
-                                             int item, int head, int q0, int nkv, uint32_t cnt, int js) {
+                                             int item, const Item &w, uint32_t cnt, int js) {
+    const int head = w.head, q0 = w.q0, nkv = w.nj;
     const int row = threadIdx.x & 127;                     /* row of the tile == TMEM lane */
     const uint32_t lane_base = (uint32_t)(row & ~31) << 16;
     const uint32_t tS = tmem + lane_base + t * 128;
@@ -553,9 +609,9 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
             continue;
         }
 
-        const bool partial = (j == nkv - 1 && (p.seq_k & (kTileK - 1)) != 0) || p.mask_bits != nullptr;
+        const bool partial = (w.j0 + j == p.nkv - 1 && (p.seq_k & (kTileK - 1)) != 0) || p.mask_bits != nullptr;
         uint32_t bits[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
-        if (partial) tile_bits(p, j, bits);
+        if (partial) tile_bits(p, w.j0 + j, bits);
 
         /* The whole S row of this thread: four loads in flight, one wait. */
         uint32_t s[128];
@@ -639,6 +695,69 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
     if (!ok) return false;
     tc_fence_after();
     if (DEBUG && threadIdx.x == 0 && js == 0) stamp_ns(p, 4);
+    const int lane = threadIdx.x & 31, wrow0 = row & ~31;
+
+    /* Key split: each warp settles with its counterpart of the other half.
+     * The first to arrive leaves its unnormalised rows, maxima and sums in
+     * the scratch of the query block; the second, which only ever waits for a
+     * warp that is already writing, folds them into its own and goes on to
+     * the output as if it had seen every key. */
+    float a_own = 1.0f, a_other = 0.0f;
+    const float *part_rows = nullptr;         /* the warp's 32 rows of the other half's partial */
+    unsigned char *stage_w = stage + (size_t)(t * 4 + (wrow0 >> 5)) * 4096;
+    if (p.nsplit > 1) {
+        unsigned int *tk = p.tickets + ((size_t)w.qitem * 8 + t * 4 + (wrow0 >> 5)) * 2;
+        float *prows = p.part_o + ((size_t)w.qitem * 256 + t * kTileQ + wrow0) * kHeadDim;
+        float2 *pml = p.part_ml + (size_t)w.qitem * 256 + t * kTileQ + row;
+        unsigned int order = 0;
+        if (lane == 0) order = atomicAdd(tk, 1u);
+        order = __shfl_sync(0xffffffffu, order, 0);
+        if (order == 0) {
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                uint32_t o[64];
+                tmem_ld32(tO + half * 64, o);
+                tmem_ld32(tO + half * 64 + 32, o + 32);
+                tc_wait_ld();
+                rows_store_f32(o, prows + half * 64, kHeadDim, 32, stage_w, lane);
+                rows_store_f32(o + 32, prows + half * 64 + 32, kHeadDim, 32, stage_w, lane);
+            }
+            __stcg(pml, make_float2(m_ref, l));
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicExch(tk + 1, 1u);
+            tc_fence_before();
+            return true;
+        }
+        unsigned int ready = 1;
+        if (lane == 0) {
+            unsigned long long t0 = global_ns();
+            while (atomicAdd(tk + 1, 0u) == 0u) {
+                if (*c.abort_flag || global_ns() - t0 > kWaitLimitNs) {
+                    *c.abort_flag = 1u;
+                    if (atomicCAS(c.status, 0u, 1u) == 0u) {
+                        c.status[1] = 320u + t;
+                        c.status[2] = blockIdx.x;
+                        c.status[3] = (unsigned)item;
+                    }
+                    ready = 0;
+                    break;
+                }
+            }
+            tk[0] = 0u;                      /* the next launch finds the pair of words cleared */
+            tk[1] = 0u;
+        }
+        ready = __shfl_sync(0xffffffffu, ready, 0);
+        if (!ready) return false;
+        __threadfence();
+        const float2 ml = __ldcg(pml);
+        const float m_new = fmaxf(m_ref, ml.x);
+        a_own = m_ref == -INFINITY ? 0.0f : ex2(m_ref - m_new);
+        a_other = ml.x == -INFINITY ? 0.0f : ex2(ml.x - m_new);
+        l = a_own * l + a_other * ml.y;
+        m_ref = m_new;
+        part_rows = prows;
+    }
     const bool valid = qrow < p.seq_q;
     float inv = l > 0.0f ? 1.0f / l : 0.0f;
     if (DEBUG && p.debug) {
@@ -649,9 +768,7 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
 
     /* Chunked state: this launch saw only part of the keys. lse = m + log2(l). */
     float w_prev = 0.0f, w_cur = 1.0f;
-    float *acc_row = nullptr;
     if (p.acc_mode != 0 && valid) {
-        acc_row = p.o_acc + (size_t)qrow * ((size_t)p.heads * kHeadDim) + (size_t)head * kHeadDim;
         float *lse_p = p.lse_acc + (size_t)head * p.seq_q + qrow;
         float lse_cur = l > 0.0f ? m_ref + log2f(l) : -INFINITY;
         if (p.acc_mode >= 2) {
@@ -680,9 +797,11 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
      * the row so that neither side has bank conflicts): a thread owns a row
      * of the accumulator, but eight threads writing 128 contiguous bytes of
      * one output row is what the memory system wants. */
-    const int lane = threadIdx.x & 31, wrow0 = row & ~31;
-    unsigned char *stage_w = stage + (size_t)(t * 4 + (wrow0 >> 5)) * 4096;
-    const float f_cur = inv * w_cur;
+    const float f_cur = inv * w_cur * a_own, f_other = inv * w_cur * a_other;
+    const int grow0 = q0 + t * kTileQ + wrow0;                       /* first row of this warp */
+    const int nvalid = p.seq_q - grow0 < 32 ? (p.seq_q - grow0 < 0 ? 0 : p.seq_q - grow0) : 32;
+    const size_t ld_acc = (size_t)p.heads * kHeadDim;
+    float *acc_rows = p.acc_mode != 0 ? p.o_acc + (size_t)grow0 * ld_acc + (size_t)head * kHeadDim : nullptr;
 #pragma unroll
     for (int half = 0; half < 2; half++) {
         uint32_t o[64];
@@ -691,20 +810,29 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
         tc_wait_ld();
 #pragma unroll
         for (int e = 0; e < 64; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * f_cur);
-        if (read_state && valid) {
+        if (part_rows) {
 #pragma unroll
-            for (int e = 0; e < 64; e += 4) {
-                float4 pr = *reinterpret_cast<const float4 *>(acc_row + half * 64 + e);
-                o[e] = __float_as_uint(__uint_as_float(o[e]) + pr.x * w_prev);
-                o[e + 1] = __float_as_uint(__uint_as_float(o[e + 1]) + pr.y * w_prev);
-                o[e + 2] = __float_as_uint(__uint_as_float(o[e + 2]) + pr.z * w_prev);
-                o[e + 3] = __float_as_uint(__uint_as_float(o[e + 3]) + pr.w * w_prev);
+            for (int sub = 0; sub < 2; sub++) {
+                uint32_t pr[32];
+                rows_load_f32(pr, part_rows + half * 64 + sub * 32, kHeadDim, 32, stage_w, lane);
+#pragma unroll
+                for (int e = 0; e < 32; e++)
+                    o[sub * 32 + e] = __float_as_uint(fmaf(__uint_as_float(pr[e]), f_other, __uint_as_float(o[sub * 32 + e])));
             }
         }
-        if (write_state && valid) {
+        if (read_state) {
 #pragma unroll
-            for (int e = 0; e < 64; e += 4)
-                *reinterpret_cast<uint4 *>(acc_row + half * 64 + e) = make_uint4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+            for (int sub = 0; sub < 2; sub++) {
+                uint32_t pr[32];
+                rows_load_f32(pr, acc_rows + half * 64 + sub * 32, ld_acc, nvalid, stage_w, lane);
+#pragma unroll
+                for (int e = 0; e < 32; e++)
+                    o[sub * 32 + e] = __float_as_uint(fmaf(__uint_as_float(pr[e]), w_prev, __uint_as_float(o[sub * 32 + e])));
+            }
+        }
+        if (write_state) {
+            rows_store_f32(o, acc_rows + half * 64, ld_acc, nvalid, stage_w, lane);
+            rows_store_f32(o + 32, acc_rows + half * 64 + 32, ld_acc, nvalid, stage_w, lane);
         }
         if (write_out) {
             uint32_t pkd[32];
@@ -741,14 +869,13 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
 
 /* The softmax warpgroup of query tile t, over the work items of this CTA. */
 template <bool DEBUG>
-__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, unsigned char *stage, uint32_t tmem, int t,
-                                           int nkv) {
+__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, unsigned char *stage, uint32_t tmem, int t) {
     uint32_t cnt = 0;
     for (int item = blockIdx.x, n = 0; item < p.items; item += gridDim.x, n++) {
         const Item w = item_of(p, item);
         if (t >= w.ntq) continue;
-        if (!softmax_item<DEBUG>(c, p, stage, tmem, t, item, w.head, w.q0, nkv, cnt, n == 0 ? 0 : (n == 1 ? 16 : 32))) return;
-        cnt += (uint32_t)nkv;
+        if (!softmax_item<DEBUG>(c, p, stage, tmem, t, item, w, cnt, n == 0 ? 0 : (n == 1 ? 16 : 32))) return;
+        cnt += (uint32_t)w.nj;
     }
 }
 
@@ -768,7 +895,6 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     c.status = p.status;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemTmemPtr);
 
-    const int nkv = (p.seq_k + kTileK - 1) / kTileK;
     if (DEBUG && threadIdx.x == 0) stamp_ns(p, 0);
 
     if (threadIdx.x == 0) {
@@ -804,11 +930,11 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     if (warp < 8) {
         /* The third warpgroup hands most of its registers to the softmax ones. */
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-        softmax_wg<DEBUG>(c, p, smem_gen + kSmemStage, tmem, warp >> 2, nkv);
+        softmax_wg<DEBUG>(c, p, smem_gen + kSmemStage, tmem, warp >> 2);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-        if (warp == 8 && lane == 0) producer(c, p, &tmq, &tmk, &tmv, smem, nkv);
-        if (warp == 9) mma_issuer<DEBUG>(c, p, smem, tmem, nkv);
+        if (warp == 8 && lane == 0) producer(c, p, &tmq, &tmk, &tmv, smem);
+        if (warp == 9) mma_issuer<DEBUG>(c, p, smem, tmem);
     }
 
     tc_fence_before();
@@ -927,11 +1053,63 @@ bool sm100_supported(const void *out, int ldo, const void *q, const void *k, con
 static uint32_t *g_mask_bits = NULL;
 static size_t g_mask_words = 0;
 
+/* Scratch of the key split, one per stream that launches split kernels
+ * (launches on one stream run one after the other; those of different
+ * streams, the head groups of the ring for instance, may overlap). */
+struct SplitScratch {
+    cudaStream_t stream;
+    int in_use;
+    size_t blocks;                 /* query blocks it has room for */
+    float *o;
+    float2 *ml;
+    unsigned int *tickets;
+};
+static SplitScratch g_split[4];
+
+static void split_free(SplitScratch *sc) {
+    if (sc->o) cuda_ok(cudaFree(sc->o), "free");
+    if (sc->ml) cuda_ok(cudaFree(sc->ml), "free");
+    if (sc->tickets) cuda_ok(cudaFree(sc->tickets), "free");
+    sc->o = NULL;
+    sc->ml = NULL;
+    sc->tickets = NULL;
+    sc->blocks = 0;
+}
+
+/* NULL when no scratch can be had: the caller then launches without split. */
+static SplitScratch *split_scratch(cudaStream_t stream, size_t blocks) {
+    SplitScratch *sc = NULL;
+    for (int i = 0; i < 4 && !sc; i++)
+        if (g_split[i].in_use && g_split[i].stream == stream) sc = &g_split[i];
+    for (int i = 0; i < 4 && !sc; i++)
+        if (!g_split[i].in_use) sc = &g_split[i];
+    if (!sc) return NULL;
+    if (sc->in_use && sc->blocks >= blocks) return sc;
+    if (sc->in_use) {
+        cuda_ok(cudaStreamSynchronize(stream), "sync");
+        split_free(sc);
+    }
+    size_t cap = blocks < 64 ? 64 : blocks;
+    if (cudaMalloc((void **)&sc->o, cap * 256 * sm100::kHeadDim * sizeof(float)) != cudaSuccess ||
+        cudaMalloc((void **)&sc->ml, cap * 256 * sizeof(float2)) != cudaSuccess ||
+        cudaMalloc((void **)&sc->tickets, cap * 16 * sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(sc->tickets, 0, cap * 16 * sizeof(unsigned int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        split_free(sc);
+        sc->in_use = 0;
+        return NULL;
+    }
+    sc->in_use = 1;
+    sc->stream = stream;
+    sc->blocks = cap;
+    return sc;
+}
+
 /* acc_mode / o_acc / lse_acc: see sm100::Params. debug: bring-up dump. */
 int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k,
                            const uint16_t *v, int ldkv, int seq_q, int seq_k, int heads, float scale,
                            const int *key_mask, int acc_mode, float *o_acc, float *lse_acc,
-                           float *debug, const uint32_t *desc_override) {
+                           float *debug, const uint32_t *desc_override, int max_split) {
     using namespace sm100;
     const int diag_mode = desc_override ? (int)desc_override[3] : 0;
     static int configured = 0;
@@ -986,6 +1164,8 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, c
     p.heads = heads;
     p.nqblk = (seq_q + 2 * kTileQ - 1) / (2 * kTileQ);
     p.items = p.nqblk * heads;
+    p.nkv = nkv;
+    p.nsplit = 1;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = g.dev_status;
     p.o_acc = o_acc;
@@ -1007,6 +1187,19 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, c
             sm_count = 148;
         }
     }
+    /* Split the keys in two when that shortens the schedule: the CTAs then
+     * run ceil(2 * items / SMs) rounds of half the length. */
+    if (max_split >= 2 && nkv >= 4 && !debug) {
+        const int rounds1 = (p.items + sm_count - 1) / sm_count, rounds2 = (2 * p.items + sm_count - 1) / sm_count;
+        SplitScratch *sc = rounds2 < 2 * rounds1 ? split_scratch(g.stream, (size_t)p.items) : NULL;
+        if (sc) {
+            p.nsplit = 2;
+            p.items *= 2;
+            p.part_o = sc->o;
+            p.part_ml = sc->ml;
+            p.tickets = sc->tickets;
+        }
+    }
     unsigned grid = (unsigned)(p.items < sm_count ? p.items : sm_count);
     if (debug)
         k_attention_sm100<true><<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk, tmv, p);
@@ -1016,6 +1209,10 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, c
 }
 
 void sm100_release(void) {
+    for (int i = 0; i < 4; i++) {
+        split_free(&g_split[i]);
+        g_split[i].in_use = 0;
+    }
     if (g_mask_bits) cuda_ok(cudaFree(g_mask_bits), "free");
     g_mask_bits = NULL;
     g_mask_words = 0;

@@ -15,7 +15,7 @@ bool sm100_supported(const void *out, int ldo, const void *q, const void *k, con
 int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k,
                            const uint16_t *v, int ldkv, int seq_q, int seq_k, int heads, float scale,
                            const int *key_mask, int acc_mode, float *o_acc, float *lse_acc,
-                           float *debug, const uint32_t *desc_override);
+                           float *debug, const uint32_t *desc_override, int max_split = 2);
 
 void sm100_release(void);
 

@@ -88,7 +88,8 @@ extern "C" int iris_b200_attention_noalloc(uint16_t *out, int ldo,
         done = t1;
         int mode = nsplit == 1 ? 0 : (i == 0 ? 1 : (i == nsplit - 1 ? 3 : 2));
         int rc = launch_attention_sm100(out, ldo, q, ldi, k + (size_t)k0 * ldi, v + (size_t)k0 * ldi, ldi, seq_q,
-                                        k1 - k0, heads, scale, NULL, mode, o_state, lse_state, NULL, NULL);
+                                        k1 - k0, heads, scale, NULL, mode, o_state, lse_state, NULL, NULL,
+                                        1 /* no in-kernel key split: its scratch would be allocated */);
         if (rc != IRIS_B200_OK) return rc;
     }
     return IRIS_B200_OK;
