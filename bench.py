@@ -302,6 +302,7 @@ def run_b200(args):
         if entries:
             step(sets[i % nsets], 2 + 3 * i if (i < nmark and len(entries) == 1) else None)
     lib.iris_b200_mark(1)
+    t_enqueued = time.time()
     barrier()
     t_wall1 = time.time()
     ms_total = lib.iris_b200_mark_elapsed_ms(0, 1)
@@ -348,7 +349,7 @@ def run_b200(args):
     # device buffer sets, so the upload of step i + 1 and the download of step
     # i - 1 run under the compute of step i.
     e2e = None
-    if entries:
+    if entries and not args.no_e2e:
         nrep = max(1, min(args.steps, 10))
         host_out = torch.empty((S, width), dtype=torch.bfloat16)
         if torch.cuda.is_available():
@@ -447,6 +448,7 @@ def run_b200(args):
                        "cfg batch x heads, no collective", "l2": "inputs rotate over %d buffer sets (%.0f MB)" %
                        (nsets, nsets * per_set / 1e6)},
             "per_gpu_tflops": round(value / world, 2),
+            "host_enqueue_ms_per_step": round((t_enqueued - t_wall0) * 1e3 / args.steps, 4),
             "pct_bf16_peak": round(100 * value / world / bf16_peak, 2),
             "pct_bf16_sustained": round(100 * value / world / bf16_sust, 2),
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
@@ -617,6 +619,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffer) measurement")
     ap.add_argument("--mode", default="shard", choices=["shard", "ring"],
                     help="N > 1: independent cfg/head shards (default) or ring sequence parallelism")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

@@ -50,6 +50,7 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <stdlib.h>
 #include <math.h>
 
 namespace iris_b200 {
@@ -1189,7 +1190,12 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, c
     }
     /* Split the keys in two when that shortens the schedule: the CTAs then
      * run ceil(2 * items / SMs) rounds of half the length. */
-    if (max_split >= 2 && nkv >= 4 && !debug) {
+    static int split_off = -1;              /* IRIS_B200_NO_SPLIT=1 turns the key split off (tuning aid) */
+    if (split_off < 0) {
+        const char *env = getenv("IRIS_B200_NO_SPLIT");
+        split_off = env && env[0] == '1';
+    }
+    if (max_split >= 2 && nkv >= 4 && !debug && !split_off) {
         const int rounds1 = (p.items + sm_count - 1) / sm_count, rounds2 = (2 * p.items + sm_count - 1) / sm_count;
         SplitScratch *sc = rounds2 < 2 * rounds1 ? split_scratch(g.stream, (size_t)p.items) : NULL;
         if (sc) {

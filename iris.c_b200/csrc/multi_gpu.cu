@@ -73,11 +73,12 @@ extern "C" int iris_b200_ring_source(int rank, int step, int nranks) {
  * Chunked attention with carried state
  * ------------------------------------------------------------------------ */
 
-extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq,
-                                         const uint16_t *k, const uint16_t *v, int ldkv,
-                                         int seq_q, int seq_k, int heads, float scale,
-                                         const int *key_mask, float *o_state, float *lse_state,
-                                         int first, int last) {
+/* max_split: 2 lets a launch that fills the SMs badly split its keys in two. */
+static int attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq,
+                           const uint16_t *k, const uint16_t *v, int ldkv,
+                           int seq_q, int seq_k, int heads, float scale,
+                           const int *key_mask, float *o_state, float *lse_state,
+                           int first, int last, int max_split) {
     if (!require_device("attention_chunk")) return IRIS_B200_ENODEV;
     if (!q || !k || !v || seq_q < 0 || seq_k <= 0 || heads <= 0 || (last && !out) ||
         (!(first && last) && (!o_state || !lse_state))) {
@@ -93,7 +94,16 @@ extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t 
     if (seq_q == 0) return IRIS_B200_OK;
     int mode = first ? (last ? 0 : 1) : (last ? 3 : 2);
     return launch_attention_sm100(out, ldo, q, ldq, k, v, ldkv, seq_q, seq_k, heads, scale, key_mask, mode,
-                                  o_state, lse_state, NULL, NULL);
+                                  o_state, lse_state, NULL, NULL, max_split);
+}
+
+extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq,
+                                         const uint16_t *k, const uint16_t *v, int ldkv,
+                                         int seq_q, int seq_k, int heads, float scale,
+                                         const int *key_mask, float *o_state, float *lse_state,
+                                         int first, int last) {
+    return attention_chunk(out, ldo, q, ldq, k, v, ldkv, seq_q, seq_k, heads, scale, key_mask, o_state, lse_state,
+                           first, last, 2);
 }
 
 /* ------------------------------------------------------------------------
@@ -152,13 +162,17 @@ struct Ring {
      * sequence numbers in device memory that streams wait on. */
     int ce;                               /* 0 not set up, 1 in use, -1 unavailable (NCCL send/recv instead) */
     FnStreamValue32 wait32, write32;
-    char *pool;                           /* kMaxRanks slots of slot_bytes: [0] local chunk, [s] step s */
+    char *pool;                           /* two sets (call parity) of nranks slots of slot_bytes: [s] step s */
     size_t slot_bytes;
-    uint32_t *flags;                      /* arrive[kMaxRanks] | ack[kMaxRanks] | seq_words[8] */
+    uint32_t *flags;                      /* arrive[kMaxRanks] | unused[kMaxRanks] | seq_words[8] */
     char *peer_pool[kMaxRanks];
     uint32_t *peer_flags[kMaxRanks];
     void *xchg;                           /* device staging of the handle exchange */
     uint32_t seq;
+    /* IRIS_B200_RING_TRACE=1: device timeline of the last call, printed by ring_destroy() */
+    int trace;                            /* -1 off, 1 on, 0 not looked up yet */
+    cudaEvent_t t_start, t_push[kMaxRanks], t_step[kMaxRanks][2];
+    int t_steps, t_pushes;
 } ring = {};
 
 enum { kFlagArrive = 0, kFlagAck = kMaxRanks, kFlagSeq = 2 * kMaxRanks, kFlagWords = 2 * kMaxRanks + 8 };
@@ -291,7 +305,7 @@ bool ce_setup(size_t slot_bytes) {
             !cuda_ok(cudaMemset(ring.flags, 0, kFlagWords * 4), "memset"))
             return false;
     }
-    if (cudaMalloc((void **)&ring.pool, slot_bytes * G) != cudaSuccess) {
+    if (cudaMalloc((void **)&ring.pool, slot_bytes * G * 2) != cudaSuccess) {
         (void)cudaGetLastError();
         set_error(IRIS_B200_ENOMEM, "ring slot pool", NULL);
         return false;
@@ -367,6 +381,23 @@ extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
 extern "C" void iris_b200_ring_destroy(void) {
     if (!ring.comm) return;
     cuda_ok(cudaDeviceSynchronize(), "sync");
+    if (ring.trace == 1 && ring.t_steps > 0) {
+        /* Timeline of the last call, milliseconds after its start on the library's stream. */
+        char line[1024];
+        int n = snprintf(line, sizeof(line), "iris_b200 ring trace, rank %d:", ring.rank);
+        float ms = 0.0f;
+        for (int s = 1; s < ring.t_pushes && n < 900; s++)
+            if (cudaEventElapsedTime(&ms, ring.t_start, ring.t_push[s]) == cudaSuccess)
+                n += snprintf(line + n, sizeof(line) - n, " push%d=%.3f", s, ms);
+        for (int i = 0; i < ring.t_steps && n < 900; i++) {
+            float a = 0.0f, b = 0.0f;
+            if (cudaEventElapsedTime(&a, ring.t_start, ring.t_step[i][0]) == cudaSuccess &&
+                cudaEventElapsedTime(&b, ring.t_start, ring.t_step[i][1]) == cudaSuccess)
+                n += snprintf(line + n, sizeof(line) - n, " launch%d=[%.3f,%.3f]", i, a, b);
+        }
+        fprintf(stderr, "%s\n", line);
+        (void)cudaGetLastError();
+    }
     ce_close_peers();
     if (ring.ce == 1) ce_barrier();
     ce_free_pool();
@@ -425,14 +456,22 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         for (int s = 0; s < G; s++)
             if (!grow(&ring.buf[s], &ring.buf_bytes[s], slot_bytes)) return IRIS_B200_ENOMEM;
     }
-    auto chunk = [&](int s) -> char * { return ce ? ring.pool + (size_t)s * ring.slot_bytes : (char *)ring.buf[s]; };
+    const uint32_t seq = ++ring.seq;
+    /* Copy-engine slots come in two sets used by alternate calls. A peer
+     * pushes the rows of call n + 1 only after its own call n, which waited
+     * for this rank's push of call n, itself ordered after this rank's call
+     * n - 1: the set of call n + 1 was last read here in call n - 1, so no
+     * acknowledgement has to travel back. */
+    const size_t set_off = ce ? (size_t)(seq & 1u) * G * ring.slot_bytes : 0;
+    auto chunk = [&](int s) -> char * {
+        return ce ? ring.pool + set_off + (size_t)s * ring.slot_bytes : (char *)ring.buf[s];
+    };
     if (G > 1) {
         for (int i = 0; i < ngroups; i++)
             if (!grow((void **)&ring.o_state[i], &ring.o_bytes[i], (size_t)rows * hg * 128 * 4) ||
                 !grow((void **)&ring.lse_state[i], &ring.lse_bytes[i], (size_t)rows * hg * 4))
                 return IRIS_B200_ENOMEM;
     }
-    const uint32_t seq = ++ring.seq;
     uint32_t *seq_word = ce ? ring.flags + kFlagSeq + (seq & 7u) : NULL;
     const size_t my_bytes = (size_t)rows * 2 * width * 2;
     const size_t row_bytes = width * 2, slot_pitch = 2 * width * 2;      /* a slot row is K | V */
@@ -459,6 +498,23 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record");
     cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
     if (ce) cuda_ok(cudaStreamWaitEvent(ring.comm_stream2, ring.packed, 0), "stream wait");
+    if (ring.trace == 0) {
+        const char *env = getenv("IRIS_B200_RING_TRACE");
+        ring.trace = env && env[0] == '1' ? 1 : -1;
+        if (ring.trace == 1) {
+            cudaEventCreate(&ring.t_start);
+            for (int i = 0; i < kMaxRanks; i++) {
+                cudaEventCreate(&ring.t_push[i]);
+                cudaEventCreate(&ring.t_step[i][0]);
+                cudaEventCreate(&ring.t_step[i][1]);
+            }
+        }
+    }
+    const bool trace = ring.trace == 1 && ce;
+    if (trace) {
+        cudaEventRecord(ring.t_start, g.stream);
+        ring.t_steps = ring.t_pushes = 0;
+    }
 
     /* All transfers, in step order: at step s this rank's rows are wanted by
      * rank me + s, which keeps them in its slot s. Pushes alternate between
@@ -467,17 +523,25 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         const int to = (me + s) % G, from = iris_b200_ring_source(me, s, G);
         if (ce) {
             cudaStream_t cs = (s & 1) ? ring.comm_stream : ring.comm_stream2;
-            char *dst = ring.peer_pool[to] + (size_t)s * ring.slot_bytes;
-            /* `to` has finished reading what the previous call put there. */
-            if (!stream_value(ring.wait32, cs, ring.flags + kFlagAck + to, seq - 1, CU_STREAM_WAIT_VALUE_GEQ,
-                              "wait ack") ||
-                !cuda_ok(cudaMemcpy2DAsync(dst, slot_pitch, k, (size_t)ldi * 2, row_bytes, rows, cudaMemcpyDefault, cs),
-                         "push K") ||
-                !cuda_ok(cudaMemcpy2DAsync(dst + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
-                                           cudaMemcpyDefault, cs), "push V") ||
-                !cuda_ok(cudaMemcpyAsync(ring.peer_flags[to] + kFlagArrive + s, seq_word, 4, cudaMemcpyDefault, cs),
-                         "push flag"))
+            char *dst = ring.peer_pool[to] + set_off + (size_t)s * ring.slot_bytes;
+            bool ok;
+            if (v == k + width) {
+                /* K and V are neighbouring column blocks of one buffer: one copy of K | V rows. */
+                ok = cuda_ok(cudaMemcpy2DAsync(dst, slot_pitch, k, (size_t)ldi * 2, 2 * row_bytes, rows,
+                                               cudaMemcpyDefault, cs), "push K|V");
+            } else {
+                ok = cuda_ok(cudaMemcpy2DAsync(dst, slot_pitch, k, (size_t)ldi * 2, row_bytes, rows, cudaMemcpyDefault,
+                                               cs), "push K") &&
+                     cuda_ok(cudaMemcpy2DAsync(dst + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
+                                               cudaMemcpyDefault, cs), "push V");
+            }
+            if (!ok || !cuda_ok(cudaMemcpyAsync(ring.peer_flags[to] + kFlagArrive + s, seq_word, 4, cudaMemcpyDefault, cs),
+                                "push flag"))
                 return IRIS_B200_ECUDA;
+            if (trace) {
+                cudaEventRecord(ring.t_push[s], cs);
+                ring.t_pushes = s + 1;
+            }
         } else {
             if (!nccl_ok(ring.group_start(), "ncclGroupStart")) return IRIS_B200_ECOMM;
             bool ok = nccl_ok(ring.send(chunk(0), my_bytes, 1, to, ring.comm, ring.comm_stream), "ncclSend") &&
@@ -522,24 +586,17 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
             }
             StreamScope scope(st);
             const size_t col = (size_t)grp * hg * 128;
-            rc = iris_b200_attention_chunk(out + col, ldo, q + col, ldi, kc + col, vc + col, ldc, rows, keys, hg,
-                                           scale, NULL, ring.o_state[grp], ring.lse_state[grp], s == 0,
-                                           s + nsteps == G);
+            if (trace && grp == 0) cudaEventRecord(ring.t_step[ring.t_steps][0], st);
+            /* The head groups fill the SMs between them: no key split inside a launch. */
+            rc = attention_chunk(out + col, ldo, q + col, ldi, kc + col, vc + col, ldc, rows, keys, hg, scale, NULL,
+                                 ring.o_state[grp], ring.lse_state[grp], s == 0, s + nsteps == G, ngroups > 1 ? 1 : 2);
+            if (trace && grp == 0) cudaEventRecord(ring.t_step[ring.t_steps++][1], st);
         }
         s += nsteps;
     }
     if (ngroups > 1) {
         cuda_ok(cudaEventRecord(ring.join, ring.aux_stream), "event record");
         cuda_ok(cudaStreamWaitEvent(g.stream, ring.join, 0), "stream wait");
-    }
-    if (ce) {
-        /* Tell every owner that its chunk has been consumed here. */
-        for (int s = 1; s < G && rc == IRIS_B200_OK; s++) {
-            const int src = iris_b200_ring_source(me, s, G);
-            if (!cuda_ok(cudaMemcpyAsync(ring.peer_flags[src] + kFlagAck + me, seq_word, 4, cudaMemcpyDefault,
-                                         g.stream), "push ack"))
-                rc = IRIS_B200_ECUDA;
-        }
     }
     /* The transfers of the local rows must not outlive the call. */
     cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done, 0), "stream wait");
