@@ -219,6 +219,55 @@ def test_key_mask_and_fully_masked_rows(lib, kernel):
     check_raw(got, want, 2)
 
 
+@pytest.mark.parametrize("seq_q,seq_k,heads", [(700, 1500, 5), (257, 513, 2), (130, 4100, 3)])
+def test_key_split_launches(lib, seq_q, seq_k, heads):
+    """Few query blocks and four or more key tiles: the tcgen05 kernel gives
+    each half of the keys to a CTA of its own and the later one merges."""
+    got, want = attention_raw(lib, seq_q, seq_k, heads, TC, seed=seq_q + 7 * seq_k)
+    check_raw(got, want, heads)
+    # one half of the keys masked out entirely, then a ragged mix
+    for lo, hi in ((0, seq_k // 2 + 64), (seq_k // 2 - 30, seq_k)):
+        m = np.ones(seq_k, np.int32)
+        m[lo:hi] = 0
+        m[5::7] = 0
+        got, want = attention_raw(lib, seq_q, seq_k, heads, TC, mask=m, seed=seq_q + lo)
+        check_raw(got, want, heads)
+
+
+def test_use_stream_runs_calls_side_by_side(lib):
+    """Two independent attention calls on two caller-owned streams, switched
+    without synchronisation, both correct once the streams are drained."""
+    rt = C.CDLL("libcudart.so.12")
+    streams = [C.c_void_p(), C.c_void_p()]
+    for st in streams:
+        assert rt.cudaStreamCreateWithFlags(C.byref(st), 1) == 0           # non-blocking
+    heads = 2
+    jobs = []
+    for i, (sq, sk) in enumerate(((600, 900), (300, 2000))):
+        q, k, v = (ol.to_bf16(ol.randn(50 + 3 * i + j, n, heads * D)) for j, n in enumerate((sq, sk, sk)))
+        dq, dk, dv = lib.to_device(q), lib.to_device(k), lib.to_device(v)
+        dout = lib.alloc(sq * heads * D * 2)
+        jobs.append((q, k, v, dq, dk, dv, dout, sq, sk))
+    lib.iris_dev_sync()
+    for rep in range(3):
+        for st, (q, k, v, dq, dk, dv, dout, sq, sk) in zip(streams, jobs):
+            assert lib.iris_b200_use_stream(st) == 0
+            lib.iris_dev_attention(dout, heads * D, dq, dk, dv, heads * D, sq, sk, heads, heads, D,
+                                   1.0 / np.sqrt(D), 0, None)
+    assert lib.iris_b200_use_stream(None) == 0
+    for st in streams:
+        assert rt.cudaStreamSynchronize(st) == 0
+    for q, k, v, dq, dk, dv, dout, sq, sk in jobs:
+        got = ol.from_bf16(lib.to_host(dout, (sq, heads * D), np.uint16))
+        want = ol.dev_attention(ol.from_bf16(q), ol.from_bf16(k), ol.from_bf16(v), heads)
+        check_raw(got, want, heads)
+        for p in (dq, dk, dv, dout):
+            lib.iris_dev_free(p)
+    for st in streams:
+        rt.cudaStreamDestroy(st)
+    lib.check()
+
+
 def test_empty_sequences(lib):
     got, _ = attention_raw(lib, 0, 50, 2, 0)
     assert got.size == 0
