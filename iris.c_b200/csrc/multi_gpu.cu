@@ -151,8 +151,8 @@ struct Ring {
     FnAllGather all_gather;
     NcclComm comm;
     int rank, nranks;
-    cudaStream_t comm_stream, comm_stream2, aux_stream;   /* the second one only carries copy-engine pushes */
-    cudaEvent_t received[kMaxRanks], packed, comm_done, comm_done2, join;
+    cudaStream_t comm_stream, aux_stream;
+    cudaEvent_t received[kMaxRanks], packed, comm_done, join;
     void *buf[kMaxRanks];                 /* [0] local chunk, [s] chunk of step s */
     size_t buf_bytes[kMaxRanks];
     float *o_state[kHeadGroups], *lse_state[kHeadGroups];
@@ -366,14 +366,12 @@ extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
     ring.rank = rank;
     ring.nranks = nranks;
     if (!cuda_ok(cudaStreamCreateWithFlags(&ring.comm_stream, cudaStreamNonBlocking), "stream create") ||
-        !cuda_ok(cudaStreamCreateWithFlags(&ring.comm_stream2, cudaStreamNonBlocking), "stream create") ||
         !cuda_ok(cudaStreamCreateWithFlags(&ring.aux_stream, cudaStreamNonBlocking), "stream create"))
         return IRIS_B200_ECUDA;
     for (int i = 0; i < kMaxRanks; i++)
         cuda_ok(cudaEventCreateWithFlags(&ring.received[i], cudaEventDisableTiming), "event create");
     cuda_ok(cudaEventCreateWithFlags(&ring.packed, cudaEventDisableTiming), "event create");
     cuda_ok(cudaEventCreateWithFlags(&ring.comm_done, cudaEventDisableTiming), "event create");
-    cuda_ok(cudaEventCreateWithFlags(&ring.comm_done2, cudaEventDisableTiming), "event create");
     cuda_ok(cudaEventCreateWithFlags(&ring.join, cudaEventDisableTiming), "event create");
     return g.last_error;
 }
@@ -423,10 +421,8 @@ extern "C" void iris_b200_ring_destroy(void) {
     }
     cuda_ok(cudaEventDestroy(ring.packed), "event destroy");
     cuda_ok(cudaEventDestroy(ring.comm_done), "event destroy");
-    cuda_ok(cudaEventDestroy(ring.comm_done2), "event destroy");
     cuda_ok(cudaEventDestroy(ring.join), "event destroy");
     cuda_ok(cudaStreamDestroy(ring.comm_stream), "stream destroy");
-    cuda_ok(cudaStreamDestroy(ring.comm_stream2), "stream destroy");
     cuda_ok(cudaStreamDestroy(ring.aux_stream), "stream destroy");
 }
 
@@ -497,7 +493,6 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     }
     cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record");
     cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
-    if (ce) cuda_ok(cudaStreamWaitEvent(ring.comm_stream2, ring.packed, 0), "stream wait");
     if (ring.trace == 0) {
         const char *env = getenv("IRIS_B200_RING_TRACE");
         ring.trace = env && env[0] == '1' ? 1 : -1;
@@ -516,13 +511,15 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         ring.t_steps = ring.t_pushes = 0;
     }
 
-    /* All transfers, in step order: at step s this rank's rows are wanted by
-     * rank me + s, which keeps them in its slot s. Pushes alternate between
-     * two streams so that the flag write of one overlaps the data of the next. */
+    /* All transfers, in step order on one stream: at step s this rank's rows
+     * are wanted by rank me + s, which keeps them in its slot s. (Pushes on
+     * two streams were measured to share one copy engine and run one after
+     * the other anyway, 48 us per 26 MB, only no longer in the order the
+     * steps need them.) */
     for (int s = 1; s < G; s++) {
         const int to = (me + s) % G, from = iris_b200_ring_source(me, s, G);
         if (ce) {
-            cudaStream_t cs = (s & 1) ? ring.comm_stream : ring.comm_stream2;
+            cudaStream_t cs = ring.comm_stream;
             char *dst = ring.peer_pool[to] + set_off + (size_t)s * ring.slot_bytes;
             bool ok;
             if (v == k + width) {
@@ -552,7 +549,6 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         }
     }
     cuda_ok(cudaEventRecord(ring.comm_done, ring.comm_stream), "event record");
-    if (ce) cuda_ok(cudaEventRecord(ring.comm_done2, ring.comm_stream2), "event record");
 
     /* With many ranks a step is a small problem whose fixed costs (pipeline
      * fill, state traffic) weigh: from step 2 on, two steps share a launch
@@ -600,6 +596,5 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     }
     /* The transfers of the local rows must not outlive the call. */
     cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done, 0), "stream wait");
-    if (ce) cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done2, 0), "stream wait");
     return rc != IRIS_B200_OK ? rc : g.last_error;
 }
