@@ -8,17 +8,22 @@
  * [seq, heads*128] views with 16-byte aligned bases and ldi % 8 == 0.
  *
  * Work decomposition
- *   One CTA owns 256 consecutive queries of one head as two 128-row tiles
- *   and walks the keys in tiles of 128. CTAs of the same head are adjacent
- *   in the grid, so the K/V of a head (2.4 MB at 4608 keys) are shared
- *   through L2.
+ *   A work item is 256 consecutive queries of one head, as two 128-row
+ *   tiles, against the keys in tiles of 128. The grid is persistent (one CTA
+ *   per SM at most): CTA b runs items b, b + gridDim.x, ... and overlaps the
+ *   loads and first MMAs of an item with the output of the one before. Items
+ *   are head-major, so the CTAs of a round share the K/V of a head (2.4 MB
+ *   at 4608 keys) through L2. When the query blocks fill the SMs badly the
+ *   keys of every block are split in two items whose results are merged by
+ *   whichever finishes second.
  *
  * Warps (384 threads)
  *   0-3   softmax of query tile 0: thread r owns row r of S / P / O
  *   4-7   softmax of query tile 1
- *   8     TMA producer (one lane): Q once, then K0 V0 K1 V1 ... through a
- *         ring of 32 KB slots guarded by full / empty mbarriers
- *   9     MMA issuer (one lane), owner of the TMEM allocation
+ *   8     TMA producer (one lane): Q per item, then K0 V0 K1 V1 ... through
+ *         a ring of 32 KB slots guarded by full / empty mbarriers
+ *   9     MMA issuer (whole warp, one elected lane issues), owner of the
+ *         TMEM allocation
  *   10-11 idle: they complete the third warpgroup, which gives most of its
  *         registers to the softmax warpgroups (setmaxnreg)
  *
@@ -27,7 +32,8 @@
  *   P_t (bf16, 64 columns) overwrites the first half of S_t: a softmax
  *   thread has read its whole S row before it stores P.
  *
- * MMA issue order per key tile j (all from one thread, executed in order):
+ * MMA issue order per key tile j (all from one thread, executed in order;
+ * each PV in two halves of 64 keys as the softmax hands them over):
  *   PV0(j)  QK0(j+1)  PV1(j)  QK1(j+1)
  *   S_t = Q_t K^T : both operands from shared memory, K-major, 128B swizzle
  *   O_t += P_t V  : P from tensor memory, V from shared memory, MN-major
@@ -42,7 +48,10 @@
  *   kernel does (iris_cuda.cu:819-831). Masked and out-of-range keys score
  *   -inf; a row without any valid key yields zeros (iris_cuda.cu:811, :853).
  *
- * Every wait on an mbarrier is bounded in time: when the limit passes the
+ * Output: accumulator rows go through a per-warp shared-memory staging area
+ * so that global memory sees whole 128-byte segments of a row.
+ *
+ * Every wait (mbarriers, the partner of a key split) is bounded in time: when the limit passes the
  * CTA records where in the device status word, raises a CTA-wide abort flag,
  * drains what it has in flight (again bounded), frees its tensor memory and
  * returns. Loads never use cluster multicast.
