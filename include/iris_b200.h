@@ -133,6 +133,12 @@ int iris_b200_seq_shard(int seq, int nranks, int rank, int *first, int *count);
 /* Rank whose K/V chunk is resident on `rank` at ring step `step`. */
 int iris_b200_ring_source(int rank, int step, int nranks);
 
+/* Launch schedule of one ring call: launch i covers the steps
+ * [first_step[i], first_step[i] + step_count[i]) (arrays of nranks entries).
+ * even_rows: every rank holds the same number of rows. Returns the number of
+ * launches, -1 on bad arguments. Pure host arithmetic. */
+int iris_b200_ring_plan(int nranks, int even_rows, int *first_step, int *step_count);
+
 /* Attention of seq_q queries over ONE chunk of seq_k keys, merged into a
  * state carried between chunks: o_state [seq_q, heads * 128] fp32 (the
  * normalised output over the keys seen so far) and lse_state [heads, seq_q]

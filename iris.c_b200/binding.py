@@ -55,6 +55,7 @@ SIGNATURES = {
     "iris_b200_cfg_shard": (INT, [INT, INT, INT, INT, C.POINTER(INT), C.POINTER(INT), C.POINTER(INT), C.POINTER(INT)]),
     "iris_b200_seq_shard": (INT, [INT, INT, INT, C.POINTER(INT), C.POINTER(INT)]),
     "iris_b200_ring_source": (INT, [INT, INT, INT]),
+    "iris_b200_ring_plan": (INT, [INT, INT, VP, VP]),
     "iris_b200_attention_chunk": (INT, [VP, INT, VP, INT, VP, VP, INT, INT, INT, INT, FLT, VP, VP, VP, INT, INT]),
     "iris_b200_ring_unique_id": (INT, [VP]),
     "iris_b200_ring_init": (INT, [INT, INT, VP]),

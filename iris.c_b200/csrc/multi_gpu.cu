@@ -69,6 +69,24 @@ extern "C" int iris_b200_ring_source(int rank, int step, int nranks) {
     return ((rank - step) % nranks + nranks) % nranks;
 }
 
+extern "C" int iris_b200_ring_plan(int nranks, int even_rows, int *first_step, int *step_count) {
+    if (nranks <= 0 || !first_step || !step_count) return -1;
+    /* With many ranks a step is a small problem whose fixed costs (pipeline
+     * fill, state traffic) weigh: from step 2 on, two steps share a launch
+     * when their chunks have the same size (their slots are then adjacent
+     * rows of one buffer). Steps 0 and 1 stay alone: 0 needs no transfer and
+     * 1 is the first to arrive. */
+    const int pair_from = (even_rows && nranks >= 6) ? 2 : nranks;
+    int n = 0;
+    for (int s = 0; s < nranks; n++) {
+        const int c = (s >= pair_from && s + 1 < nranks) ? 2 : 1;
+        first_step[n] = s;
+        step_count[n] = c;
+        s += c;
+    }
+    return n;
+}
+
 /* ------------------------------------------------------------------------
  * Chunked attention with carried state
  * ------------------------------------------------------------------------ */
@@ -550,24 +568,24 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
     }
     cuda_ok(cudaEventRecord(ring.comm_done, ring.comm_stream), "event record");
 
-    /* With many ranks a step is a small problem whose fixed costs (pipeline
-     * fill, state traffic) weigh: from step 2 on, two steps share a launch
-     * when their slots are adjacent rows of one buffer. */
-    bool even = ce && G >= 6 && ring.slot_bytes == my_bytes;
+    /* Launch schedule: which steps share a launch (only chunks of one size
+     * lying in adjacent slots can). */
+    bool even = ce && ring.slot_bytes == my_bytes;
     for (int r = 0; r < G && even; r++) even = rows_of[r] == rows;
-    const int pair_from = even ? 2 : G;
+    int plan_first[kMaxRanks], plan_count[kMaxRanks];
+    const int nlaunch = iris_b200_ring_plan(G, even ? 1 : 0, plan_first, plan_count);
 
     /* The head groups run side by side: group 0 on the library's stream,
      * group 1 on the auxiliary one, joined again before the call returns. */
     if (ngroups > 1) cuda_ok(cudaStreamWaitEvent(ring.aux_stream, ring.packed, 0), "stream wait");
     int rc = IRIS_B200_OK;
-    for (int s = 0; s < G && rc == IRIS_B200_OK;) {
-        const int nsteps = (s >= pair_from && s + 1 < G) ? 2 : 1;
+    for (int li = 0; li < nlaunch && rc == IRIS_B200_OK; li++) {
+        const int s = plan_first[li], nsteps = plan_count[li];
         const int src = iris_b200_ring_source(me, s, G);
         const uint16_t *kc = s == 0 ? k0 : (const uint16_t *)chunk(s);
         const uint16_t *vc = s == 0 ? v0 : kc + width;
         const int ldc = s == 0 ? ld0 : (int)(2 * width);
-        const int keys = nsteps == 2 ? 2 * rows : rows_of[src];
+        const int keys = nsteps > 1 ? nsteps * rows : rows_of[src];
         for (int grp = 0; grp < ngroups && rc == IRIS_B200_OK; grp++) {
             cudaStream_t st = grp == 0 ? g.stream : ring.aux_stream;
             for (int w = s; w < s + nsteps; w++) {
@@ -588,7 +606,6 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
                                  ring.o_state[grp], ring.lse_state[grp], s == 0, s + nsteps == G, ngroups > 1 ? 1 : 2);
             if (trace && grp == 0) cudaEventRecord(ring.t_step[ring.t_steps++][1], st);
         }
-        s += nsteps;
     }
     if (ngroups > 1) {
         cuda_ok(cudaEventRecord(ring.join, ring.aux_stream), "event record");

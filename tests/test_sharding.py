@@ -9,6 +9,8 @@ import sys
 import numpy as np
 import pytest
 
+import oracle_lib as ol
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -75,6 +77,57 @@ def test_ring_schedule_visits_every_chunk_once(lib):
     assert lib.iris_b200_ring_source(0, 0, 0) == -1
     a, b = C.c_int(), C.c_int()
     assert lib.iris_b200_seq_shard(16896, 8, 3, C.byref(a), C.byref(b)) == 0 and (a.value, b.value) == (6336, 2112)
+
+
+def ring_plan(lib, n, even):
+    first, count = (C.c_int * max(n, 1))(), (C.c_int * max(n, 1))()
+    nl = lib.iris_b200_ring_plan(n, even, first, count)
+    return [(first[i], count[i]) for i in range(max(nl, 0))], nl
+
+
+def test_ring_plan_covers_the_steps_in_order(lib):
+    for n in range(1, 17):
+        for even in (0, 1):
+            plan, nl = ring_plan(lib, n, even)
+            assert nl == len(plan) >= 1
+            steps = [s for f, c in plan for s in range(f, f + c)]
+            assert steps == list(range(n))                       # every step once, in arrival order
+            assert plan[0] == (0, 1)                             # the local rows need no transfer
+            if n > 1:
+                assert plan[1] == (1, 1)                         # the first arrival is not held back
+            if not even or n < 6:
+                assert all(c == 1 for _, c in plan)              # unequal chunks never share a launch
+            else:
+                assert all(c == 2 for _, c in plan[2:-1]) and plan[-1][1] in (1, 2)
+    assert ring_plan(lib, 8, 1)[0] == [(0, 1), (1, 1), (2, 2), (4, 2), (6, 2)]
+    assert ring_plan(lib, 7, 1)[0] == [(0, 1), (1, 1), (2, 2), (4, 2), (6, 1)]
+    assert lib.iris_b200_ring_plan(0, 1, None, None) == -1
+
+
+def test_paired_steps_merge_like_single_steps(lib):
+    """The carried-state merge does not care how the keys are grouped into
+    launches: eight chunks merged one by one and by the 8-rank plan agree."""
+    H, D, S, n = 2, 128, 64, 8
+    q, k, v = (ol.randn(30 + i, S * n if i else S, H * D) for i in range(3))
+    scale = 1 / np.sqrt(D)
+
+    def run(groups):
+        out = np.zeros((S, H, D), np.float32)
+        lse = np.full((S, H), -np.inf, np.float32)
+        for f, c in groups:
+            kc, vc = k[f * S:(f + c) * S], v[f * S:(f + c) * S]
+            o_c = ol.dev_attention(q, kc, vc, H).reshape(S, H, D)
+            sc = np.einsum("qhd,khd->hqk", q.reshape(S, H, D), kc.reshape(-1, H, D)) * scale * np.log2(np.e)
+            lse_c = (np.log2(np.exp2(sc - sc.max(2, keepdims=True)).sum(2)) + sc.max(2)).T
+            new = np.logaddexp2(lse, lse_c)
+            out = out * np.exp2(lse - new)[:, :, None] + o_c * np.exp2(lse_c - new)[:, :, None]
+            lse = new
+        return out.reshape(S, H * D)
+
+    want = ol.dev_attention(q, k, v, H)
+    single = run([(s, 1) for s in range(n)])
+    paired = run(ring_plan(lib, n, 1)[0])
+    assert np.abs(single - want).max() < 2e-5 and np.abs(paired - want).max() < 2e-5
 
 
 WORKER = r'''
