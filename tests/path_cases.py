@@ -202,3 +202,19 @@ def run_case(lib, case, kernel=0, b=0, fused_prologue=True, rows="auto"):
     pro_err = max(np.abs(qg - q_pro).max(), np.abs(kg - k_pro).max())
     return dict(max_abs=float(mx.max()), min_cos=float(cs.min()), per_head_max=mx, per_head_cos=cs,
                 prologue_max_abs=float(pro_err), rows=rows, out=got, want=want)
+
+
+def write_block_input(path, case, b=0):
+    """Input file of the C host program (iris.c_b200/examples/block_attention.c)."""
+    H = case["heads"]
+    q, k, v = qkv_inputs(case, b)
+    cos, sin, mask = rope_tables(case)
+    assert mask is None
+    with open(path, "wb") as f:
+        f.write(np.array([seq_len(case), H], np.int32).tobytes())
+        f.write(np.array([case["eps"]], np.float32).tobytes())
+        f.write(ol.to_bf16(np.concatenate([q, k, v], axis=1)).tobytes())
+        f.write(cos.tobytes())
+        f.write(sin.tobytes())
+        f.write(np.ones(D, np.float32).tobytes())
+        f.write(np.ones(D, np.float32).tobytes())

@@ -3,6 +3,7 @@ headers declare, and refuses to compute without a device (no CPU path)."""
 import glob
 import os
 import re
+import subprocess
 
 import pytest
 
@@ -72,3 +73,19 @@ def test_product_sources_do_not_touch_the_oracle():
         if os.path.isfile(path) and path.endswith((".cu", ".cuh", ".h", ".py", ".c", "Makefile")):
             text = open(path, errors="ignore").read()
             assert "oracle" not in text.lower(), path
+
+
+def test_c_host_program_builds_against_the_headers(tmp_path):
+    """The drop-in boundary is C: a C11 program that includes only
+    include/iris_dev.h compiles with gcc and links against the library. Run
+    without a GPU it reports that there is no device (exit code 2)."""
+    import path_cases as pc
+    pkg = os.path.join(ROOT, "iris.c_b200")
+    subprocess.check_call(["make", "-C", pkg, "example"], stdout=subprocess.DEVNULL)
+    exe = os.path.join(pkg, "build", "block_attention")
+    inp, out = tmp_path / "in.bin", tmp_path / "out.bin"
+    pc.write_block_input(inp, pc.FLUX_SMALL)
+    r = subprocess.run([exe, str(inp), str(out)], capture_output=True, text=True, timeout=120)
+    assert r.returncode in (0, 2), (r.returncode, r.stdout, r.stderr)
+    if r.returncode == 2:
+        assert "no usable device" in r.stderr

@@ -376,3 +376,27 @@ def test_host_softmax_and_rope(lib):
     o.orc_apply_rope(wy.reshape(-1), wf.reshape(-1), 2, pos.size, 3, 64)
     np.testing.assert_allclose(y, wy, rtol=0, atol=2e-6)
     lib.check()
+
+
+def test_c_host_program_matches_the_oracle(lib, tmp_path):
+    """The plain-C program written against include/iris_dev.h (prologue on Q
+    and K, attention on the fused-QKV slices, as the reference's block code
+    calls them) gives the oracle's result within the gate."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pkg = os.path.join(root, "iris.c_b200")
+    exe = os.path.join(pkg, "build", "block_attention")
+    if not os.path.exists(exe):          # normally built by build() / the CPU suite beforehand
+        subprocess.check_call(["make", "-C", pkg, "example"], stdout=subprocess.DEVNULL)
+    case = pc.FLUX_REF_SMALL
+    inp, out = tmp_path / "in.bin", tmp_path / "out.bin"
+    pc.write_block_input(inp, case)
+    r = subprocess.run([exe, str(inp), str(out)],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+    H = case["heads"]
+    got = ol.from_bf16(np.fromfile(out, np.uint16).reshape(pc.seq_len(case), H * D))
+    want, _, _, rows = pc.oracle_case(case)
+    mx, cs = ol.compare_heads(got, want, H, D, rows)
+    assert mx.max() <= MAX_ABS and cs.min() >= MIN_COS, (mx, cs)
