@@ -1223,6 +1223,13 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, c
     return after_launch("attention (tcgen05)") ? IRIS_B200_OK : IRIS_B200_ECUDA;
 }
 
+void sm100_reset_split(void) {
+    cuda_ok(cudaDeviceSynchronize(), "sync");
+    for (int i = 0; i < 4; i++)
+        if (g_split[i].in_use && g_split[i].tickets)
+            cuda_ok(cudaMemset(g_split[i].tickets, 0, g_split[i].blocks * 16 * sizeof(unsigned int)), "ticket clear");
+}
+
 void sm100_release(void) {
     for (int i = 0; i < 4; i++) {
         split_free(&g_split[i]);

@@ -19,4 +19,7 @@ int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, c
 
 void sm100_release(void);
 
+/* Clears the arrival words of the key-split scratch (after a device wait timed out). */
+void sm100_reset_split(void);
+
 }  // namespace iris_b200

@@ -219,6 +219,8 @@ int iris_b200_check_device_status(void) {
         snprintf(msg, sizeof(msg), "wait timed out in kernel (site %u, block %u, aux %u)", st[1], st[2], st[3]);
         set_error(IRIS_B200_ETIMEOUT, "device wait", msg);
         cuda_ok(cudaMemset(g.dev_status, 0, 64), "status clear");
+        /* A kernel that gave up may have left key-split tickets half used. */
+        sm100_reset_split();
     }
     return g.last_error;
 }
