@@ -125,7 +125,7 @@ extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t 
 }
 
 /* ------------------------------------------------------------------------
- * NCCL ring
+ * Ring sequence parallelism
  *
  * Rank r holds the query rows and the K / V rows of its token block. Step s
  * (s = 0 .. G-1) computes the attention of the local queries against the
@@ -134,9 +134,12 @@ extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t 
  * its own chunk to rank r + s and receives from rank r - s (NVSwitch gives
  * every pair full bandwidth, so nothing is relayed and no transfer waits
  * for a computation). All transfers are queued on a communication stream
- * when the call starts; each records an event the attention of its step
- * waits for. A received chunk lies in this GPU's memory before a kernel
- * reads it.
+ * when the call starts. Transport: the copy engines push the rows from the
+ * caller's buffers into the consumer's slot (pools mapped through CUDA IPC)
+ * and then write the call's sequence number into its arrival word, on
+ * which the consumer's streams wait; NCCL send / recv with events when that
+ * cannot be set up. NCCL also carries the set-up exchanges. A received
+ * chunk lies in this GPU's memory before a kernel reads it.
  *
  * The heads are processed as two independent halves on two streams: a ring
  * step is a small problem (its CTAs fill the SMs about one and a half times),
@@ -193,7 +196,7 @@ struct Ring {
     int t_steps, t_pushes;
 } ring = {};
 
-enum { kFlagArrive = 0, kFlagAck = kMaxRanks, kFlagSeq = 2 * kMaxRanks, kFlagWords = 2 * kMaxRanks + 8 };
+enum { kFlagArrive = 0, kFlagSeq = 2 * kMaxRanks, kFlagWords = 2 * kMaxRanks + 8 };
 
 bool nccl_load(void) {
     if (ring.dl) return true;
