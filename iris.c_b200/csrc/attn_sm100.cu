@@ -54,7 +54,7 @@
  * Every wait (mbarriers, the partner of a key split) is bounded in time: when the limit passes the
  * CTA records where in the device status word, raises a CTA-wide abort flag,
  * drains what it has in flight (again bounded), frees its tensor memory and
- * returns. Loads never use cluster multicast.
+ * returns. Every load is a TMA copy issued by and for one CTA.
  */
 #include "common.cuh"
 
