@@ -11,13 +11,22 @@ Metric: attention TFLOP/s, 4*B*H*S^2*128 FLOP per step (QK^T and PV; softmax,
 scaling and prologue not counted), aggregate over all GPUs of the job.
 
 N = 1 runs the Klein-4B 1024^2 block (4608 tokens, 24 heads, bf16). N > 1
-runs the Klein-9B CFG block (batch 2 x 32 heads x 4608 tokens) with the two
-batch entries on disjoint GPU groups and the heads of an entry sharded over
-the GPUs of its group: independent shards, no collective in the data path.
+runs the FLUX.3 multi-reference block (16 896 tokens, 24 heads) with ring
+sequence parallelism: every GPU keeps its token rows, the K/V rows travel
+peer to peer while one attention launch per GPU consumes them. The same
+line carries, as extra keys, that workload on one GPU measured in the same
+run (`speedup_vs_1gpu`), its head-parallel decomposition, and the
+independent-shard runs of the Klein-9B CFG block (cond/uncond x heads) and of
+the Z-Image block (30 heads, uneven split).
 
 Data is synthetic: seeded N(0,1) Q/K/V in bf16, unit norm weights and the
 RoPE tables of the model family; the reference publishes no dataset for this
 path. Inputs rotate through several buffer sets larger than L2 in total.
+
+Parity inside the run: the CPU leg (the reference's own CPU code) consumes
+the very tensors the GPU arm uploaded (the bf16 values widened to fp32) and
+the line reports the worst per-head max-abs error and cosine between the two
+results (`parity`).
 
 --impl reference times the reference's own CPU implementation of the same
 step (oracle/_ref, built from the reference sources; else the CPU port in
@@ -50,9 +59,13 @@ WORKLOADS = {
 }
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_attention_sm100 launch, from the ncu capture
-# summarised in profiles/k_attention_sm100_klein4b-1024.md (algorithmic Q+K+V+O: 113.2 MB).
+# DRAM bytes (read + written) of one attention launch as counted by an ncu capture of this workload
+# (dram__bytes_read.sum + dram__bytes_write.sum); not measured by this script. The algorithmic
+# figure for comparison is Q + K + V + O = 113.2 MB.
 NCU_DRAM_BYTES_PER_LAUNCH = {"klein4b-1024": 91.5e6}
+
+METRIC = "joint-attn TFLOP/s per GPU & % bf16 peak at 1/2/4/8 B200 vs host-CPU ref"
+STEP_WORDS = "qk_norm + rope + attention"
 
 
 def seq_len(w):
@@ -178,23 +191,6 @@ def load_lib():
     return ge.load_package().load()
 
 
-def shard_of(w, rank, world):
-    """(batch entry, first head, head count) of this rank: batch entries on
-    disjoint GPU groups, heads of an entry split evenly over its group (the
-    first heads % group ranks take one more)."""
-    B, H = w["batch"], w["heads"]
-    groups = min(B, world)
-    per = world // groups
-    grp, r = min(rank // per, groups - 1), rank % per
-    if rank >= groups * per:           # leftover ranks when world is not a multiple of the batch
-        return None
-    base, extra = divmod(H, per)
-    h0 = r * base + min(r, extra)
-    nh = base + (1 if r < extra else 0)
-    entries = list(range(grp, B, groups))
-    return entries, h0, nh
-
-
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -203,261 +199,485 @@ def peaks():
     return 1590.0, 1400.0, 6650.0, "fallback"
 
 
-def run_b200(args):
-    rank = int(os.environ.get("RANK", 0))
-    world = int(os.environ.get("WORLD_SIZE", 1))
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    dist = None
-    import torch
-    if world > 1:
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ring = args.mode == "ring"
-    name = args.workload or ("flux3-multiref" if ring else "klein4b-1024" if world == 1 else "klein9b-cfg")
-    w = WORKLOADS[name]
-    lib = load_lib()
-    lib.init(local)
+class Job:
+    """Process-wide state of one bench run: the library, this rank, the
+    process group."""
+
+    def __init__(self):
+        import torch
+        self.torch = torch
+        self.rank = int(os.environ.get("RANK", 0))
+        self.world = int(os.environ.get("WORLD_SIZE", 1))
+        self.local = int(os.environ.get("LOCAL_RANK", 0))
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            torch.cuda.set_device(self.local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.dist = dist
+        self.lib = load_lib()
+        self.lib.init(self.local)
+        self.ring_ready = False
+
+    def barrier(self, group_all=True):
+        if self.dist and group_all:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        if not self.dist:
+            return list(values)
+        t = self.torch.tensor(list(values), device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(x) for x in t.tolist()]
+
+    def ring_init(self):
+        if self.ring_ready:
+            return
+        torch, lib = self.torch, self.lib
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if self.rank == 0:
+            buf = C.create_string_buffer(128)
+            assert lib.iris_b200_ring_unique_id(buf) == 0
+            ident = torch.tensor(list(buf.raw), dtype=torch.uint8, device="cuda")
+        if self.dist:
+            self.dist.broadcast(ident, src=0)
+        assert lib.iris_b200_ring_init(self.rank, self.world, bytes(ident.cpu().tolist())) == 0
+        self.ring_ready = True
+
+
+def plan_of(job, w, mode):
+    """What this rank holds and computes. mode: 'single' (everything on this
+    rank), 'shard' (batch entries on disjoint GPU groups, heads of an entry
+    split over its group: independent shards, nothing exchanged) or 'ring'
+    (this rank's block of token rows, all heads)."""
+    lib, rank, world = job.lib, job.rank, job.world
     S_full, H = seq_len(w), w["heads"]
-    cos, sin = rope_tables(w)
-    assert cos.shape == (S_full, 64)
-    if ring:
-        # Sequence parallel: this rank owns a block of token rows (all heads);
-        # K/V chunks go round the ring inside iris_b200_ring_attention().
+    p = dict(mode=mode, S_full=S_full, S=S_full, row0=0, rows_of=None, entries=list(range(w["batch"])), h0=0, nh=H)
+    a, b, c, d = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+    if mode == "shard":
+        assert lib.iris_b200_cfg_shard(w["batch"], H, world, rank, C.byref(a), C.byref(b), C.byref(c), C.byref(d)) == 0
+        p["entries"] = list(range(a.value, w["batch"], b.value)) if d.value > 0 else []
+        p["h0"], p["nh"] = c.value, d.value
+    elif mode == "ring":
         assert w["batch"] == 1
         rows_of = np.zeros(world, np.int32)
-        a, b = C.c_int(), C.c_int()
-        row0 = 0
         for r in range(world):
             lib.iris_b200_seq_shard(S_full, world, r, C.byref(a), C.byref(b))
             rows_of[r] = b.value
             if r == rank:
-                row0 = a.value
-        S = int(rows_of[rank])
-        cos, sin = np.ascontiguousarray(cos[row0:row0 + S]), np.ascontiguousarray(sin[row0:row0 + S])
-        entries, h0, nh = [0], 0, H
-        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            buf = C.create_string_buffer(128)
-            assert lib.iris_b200_ring_unique_id(buf) == 0
-            ident = torch.tensor(list(buf.raw), dtype=torch.uint8, device="cuda")
-        if dist:
-            dist.broadcast(ident, src=0)
-        assert lib.iris_b200_ring_init(rank, world, bytes(ident.cpu().tolist())) == 0
-    else:
-        S = S_full
-        shard = shard_of(w, rank, world)
-        entries, h0, nh = shard if shard else ([], 0, 0)
-    width = nh * D                                  # this rank's column slice of every tensor
-    d_cos, d_sin = lib.to_device(cos), lib.to_device(sin)
-    d_w = lib.to_device(np.ones(D, np.float32))
+                p["row0"] = a.value
+        p["rows_of"], p["S"] = rows_of, int(rows_of[rank])
+    return p
+
+
+class Buffers:
+    """Device buffer sets of one plan: each set holds, per batch entry of this
+    rank, the fused QKV slice [S, 3 * width] and the output [S, width]; enough
+    sets to exceed L2 (126 MB) several times. The host copies are the pinned
+    tensors every set was uploaded from."""
+
+    def __init__(self, job, w, plan, seed_base=None):
+        lib = job.lib
+        self.job, self.w, self.plan = job, w, plan
+        S, nh = plan["S"], plan["nh"]
+        self.width = nh * D
+        cos, sin = rope_tables(w)
+        self.cos = np.ascontiguousarray(cos[plan["row0"]:plan["row0"] + S])
+        self.sin = np.ascontiguousarray(sin[plan["row0"]:plan["row0"] + S])
+        self.d_cos, self.d_sin = lib.to_device(self.cos), lib.to_device(self.sin)
+        self.d_w = lib.to_device(np.ones(D, np.float32))
+        entries = plan["entries"] if nh > 0 else []
+        self.per_set = len(entries) * S * self.width * 8
+        self.nsets = max(2, min(8, int(np.ceil(512e6 / max(self.per_set, 1))))) if entries else 0
+        seed_base = 1000 * job.rank if seed_base is None else seed_base
+        self.host_qkv = [make_qkv(S, self.width, seed_base + e) for e in entries]
+        self.sets = []
+        for _ in range(self.nsets):
+            bufs = []
+            for hq in self.host_qkv:
+                dq = lib.alloc(hq.numel() * 2)
+                lib.iris_dev_upload(dq, hq.data_ptr(), hq.numel() * 2)
+                bufs.append((dq, lib.alloc(S * self.width * 2)))
+            self.sets.append(bufs)
+        lib.check()
+
+    def free(self):
+        lib = self.job.lib
+        for bufs in self.sets:
+            for dq, dout in bufs:
+                lib.iris_dev_free(dq)
+                lib.iris_dev_free(dout)
+        for p in (self.d_cos, self.d_sin, self.d_w):
+            lib.iris_dev_free(p)
+        self.sets = []
+
+
+def run_step(job, w, plan, B, bufs, cs=None, mark=None):
+    """One step on one buffer set: per batch entry the Q/K prologue, then the
+    attention (plain, or the ring call)."""
+    lib = job.lib
+    S, nh, width = plan["S"], plan["nh"], B.width
     scale = 1.0 / np.sqrt(D)
+    d_cos, d_sin = cs if cs else (B.d_cos, B.d_sin)
+    for dq, dout in bufs:
+        q, k, v = dq, dq + width * 2, dq + 2 * width * 2
+        if mark is not None:
+            lib.iris_b200_mark(mark + 2)
+        lib.iris_b200_qk_norm_rope(q, k, 3 * width, B.d_w, B.d_w, d_cos, d_sin, S, nh, D, w["eps"], 0)
+        if mark is not None:
+            lib.iris_b200_mark(mark)
+        if plan["mode"] == "ring":
+            rc = lib.iris_b200_ring_attention(dout, width, q, k, v, 3 * width, plan["rows_of"].ctypes.data, nh, scale)
+            assert rc == 0, rc
+        else:
+            lib.iris_dev_attention(dout, width, q, k, v, 3 * width, S, S, nh, nh, D, scale, 0, None)
+        if mark is not None:
+            lib.iris_b200_mark(mark + 1)
 
-    # Buffer sets: each holds the fused QKV slice of every batch entry this
-    # rank owns plus its output; enough sets to exceed L2 (126 MB) several times.
-    per_set = len(entries) * S * width * 8
-    nsets = max(2, min(8, int(np.ceil(512e6 / max(per_set, 1))))) if entries else 0
-    host_qkv = [make_qkv(S, width, 1000 * rank + e) for e in entries]
-    sets = []
-    for s in range(nsets):
-        bufs = []
-        for hq in host_qkv:
-            dq = lib.alloc(hq.numel() * 2)
-            lib.iris_dev_upload(dq, hq.data_ptr(), hq.numel() * 2)
-            bufs.append((dq, lib.alloc(S * width * 2)))
-        sets.append(bufs)
-    lib.check()
 
-    def step(bufs, mark=None):
-        for dq, dout in bufs:
-            q, k, v = dq, dq + width * 2, dq + 2 * width * 2
-            if mark is not None:
-                lib.iris_b200_mark(mark + 2)
-            lib.iris_b200_qk_norm_rope(q, k, 3 * width, d_w, d_w, d_cos, d_sin, S, nh, D, w["eps"], 0)
-            if mark is not None:
-                lib.iris_b200_mark(mark)
-            if ring:
-                rc = lib.iris_b200_ring_attention(dout, width, q, k, v, 3 * width, rows_of.ctypes.data, nh, scale)
-                assert rc == 0, rc
-            else:
-                lib.iris_dev_attention(dout, width, q, k, v, 3 * width, S, S, nh, nh, D, scale, 0, None)
-            if mark is not None:
-                lib.iris_b200_mark(mark + 1)
-
-    def barrier():
-        if dist:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for i in range(args.warmup):
-        if entries:
-            step(sets[i % nsets])
-    barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
+def timed_steps(job, w, plan, B, steps, warmup, collective=True, marks=False):
+    """W warm-up steps, then K steps between two marks on the library's
+    stream, bracketed by a barrier + device synchronisation. Returns the time
+    per step in ms (max over the ranks when `collective`), the launches
+    enqueued and, with marks, the durations of the attention and prologue
+    launches of every step."""
+    lib = job.lib
+    active = bool(B.sets)
+    for i in range(warmup):
+        if active:
+            run_step(job, w, plan, B, B.sets[i % B.nsets])
+    job.barrier(collective)
     launches0 = lib.iris_b200_launch_count()
-    t_wall0 = time.time()
+    t0 = time.time()
     lib.iris_b200_mark(0)
-    nmark = min(args.steps, 2500)
-    for i in range(args.steps):
-        if entries:
-            step(sets[i % nsets], 2 + 3 * i if (i < nmark and len(entries) == 1) else None)
+    nmark = min(steps, 2500) if (marks and active and len(B.sets[0]) == 1) else 0
+    for i in range(steps):
+        if active:
+            run_step(job, w, plan, B, B.sets[i % B.nsets], 2 + 3 * i if i < nmark else None)
     lib.iris_b200_mark(1)
-    t_enqueued = time.time()
-    barrier()
-    t_wall1 = time.time()
-    ms_total = lib.iris_b200_mark_elapsed_ms(0, 1)
-    launches = lib.iris_b200_launch_count() - launches0
+    t_enq = time.time()
+    job.barrier(collective)
+    t1 = time.time()
+    ms = lib.iris_b200_mark_elapsed_ms(0, 1) / steps
     lib.check()
-    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
-    if dist:
-        t = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+    if collective:
+        ms = job.max_over_ranks([ms])[0]
+    res = dict(ms=ms, launches=int(lib.iris_b200_launch_count() - launches0), wall=(t0, t1),
+               enqueue_ms=(t_enq - t0) * 1e3 / steps)
+    if nmark:
+        res["attn_ms"] = [d for d in (lib.iris_b200_mark_elapsed_ms(2 + 3 * i, 3 + 3 * i) for i in range(nmark)) if d > 0]
+        res["pro_ms"] = [d for d in (lib.iris_b200_mark_elapsed_ms(4 + 3 * i, 2 + 3 * i) for i in range(nmark)) if d > 0]
+    return res
+
+
+def e2e_steps(job, w, plan, B, steps):
+    """End to end through the C-ABI with host buffers. Every step uploads its
+    inputs (QKV slice and RoPE tables) from page-locked host memory, runs
+    prologue + attention and downloads the result. `serial`: the reference's
+    blocking iris_dev_upload / iris_dev_download around every step.
+    `pipelined` (the reported value): iris_b200_upload_async /
+    iris_b200_download_async on two copy streams of the library's making,
+    ordered against the library's stream by events over three device buffer
+    sets, so the upload of step i + 1 and the download of step i - 1 run under
+    the kernels of step i. Returns ms per step (max over ranks) of both."""
+    lib, torch = job.lib, job.torch
+    S, width = plan["S"], B.width
+    entries = B.host_qkv
+    if not entries:
+        r = job.max_over_ranks([0.0, 0.0])
+        return r[0], r[1], 0, 0
+    in_bytes, out_bytes = S * 3 * width * 2, S * width * 2
+    cs_bytes = B.cos.nbytes
+    nrep = max(1, min(steps, 10))
+    host_out = lib.iris_b200_host_alloc(out_bytes)
+    job.barrier()
+    t0 = time.perf_counter()
+    for i in range(nrep):
+        bufs = B.sets[i % B.nsets]
+        for (dq, dout), hq in zip(bufs, entries):
+            lib.iris_dev_upload(dq, hq.data_ptr(), in_bytes)
+        lib.iris_dev_upload(B.d_cos, B.cos.ctypes.data, cs_bytes)
+        lib.iris_dev_upload(B.d_sin, B.sin.ctypes.data, cs_bytes)
+        run_step(job, w, plan, B, bufs)
+        for dq, dout in bufs:
+            lib.iris_dev_download(host_out, dout, out_bytes)
+    torch.cuda.synchronize()
+    serial_ms = (time.perf_counter() - t0) * 1e3 / nrep
+
+    nbuf, prep = 3, max(3, min(steps, 30))
+    up, down = lib.iris_b200_stream_create(), lib.iris_b200_stream_create()
+    pin_cos, pin_sin = lib.iris_b200_host_alloc(cs_bytes), lib.iris_b200_host_alloc(cs_bytes)
+    C.memmove(pin_cos, B.cos.ctypes.data, cs_bytes)
+    C.memmove(pin_sin, B.sin.ctypes.data, cs_bytes)
+    dev = [[(lib.alloc(in_bytes), lib.alloc(out_bytes)) for _ in entries] for _ in range(nbuf)]
+    dev_cs = [(lib.alloc(cs_bytes), lib.alloc(cs_bytes)) for _ in range(nbuf)]
+    pin_out = [[lib.iris_b200_host_alloc(out_bytes) for _ in entries] for _ in range(nbuf)]
+    ev_up = [lib.iris_b200_event_create() for _ in range(prep)]
+    ev_comp = [lib.iris_b200_event_create() for _ in range(prep)]
+    ev_down = [lib.iris_b200_event_create() for _ in range(prep)]
+    job.barrier()
+    t0 = time.perf_counter()
+    for i in range(prep):
+        b = i % nbuf
+        if i >= nbuf:
+            lib.iris_b200_stream_wait_event(up, ev_comp[i - nbuf])        # the last reader of this input set
+        for (dq, _), hq in zip(dev[b], entries):
+            lib.iris_b200_upload_async(dq, hq.data_ptr(), in_bytes, up)
+        lib.iris_b200_upload_async(dev_cs[b][0], pin_cos, cs_bytes, up)
+        lib.iris_b200_upload_async(dev_cs[b][1], pin_sin, cs_bytes, up)
+        lib.iris_b200_event_record(ev_up[i], up)
+        lib.iris_b200_stream_wait_event(None, ev_up[i])
+        if i >= nbuf:
+            lib.iris_b200_stream_wait_event(None, ev_down[i - nbuf])      # the last download of this output set
+        run_step(job, w, plan, B, dev[b], cs=dev_cs[b])
+        lib.iris_b200_event_record(ev_comp[i], None)
+        lib.iris_b200_stream_wait_event(down, ev_comp[i])
+        for (_, dout), po in zip(dev[b], pin_out[b]):
+            lib.iris_b200_download_async(po, dout, out_bytes, down)
+        lib.iris_b200_event_record(ev_down[i], down)
+    lib.iris_b200_stream_sync(up)
+    lib.iris_b200_stream_sync(down)
+    lib.iris_b200_stream_sync(None)
+    e_ms = (time.perf_counter() - t0) * 1e3 / prep
+    lib.check()
+    for ev in ev_up + ev_comp + ev_down:
+        lib.iris_b200_event_destroy(ev)
+    for st in (up, down):
+        lib.iris_b200_stream_destroy(st)
+    for row in dev:
+        for dq, dout in row:
+            lib.iris_dev_free(dq)
+            lib.iris_dev_free(dout)
+    for a, b in dev_cs:
+        lib.iris_dev_free(a)
+        lib.iris_dev_free(b)
+    for p in [host_out, pin_cos, pin_sin] + [x for row in pin_out for x in row]:
+        lib.iris_b200_host_free(p)
+    e_ms, serial_ms = job.max_over_ranks([e_ms, serial_ms])
+    return e_ms, serial_ms, len(entries) * (in_bytes + 2 * cs_bytes), len(entries) * out_bytes
+
+
+def bf16_to_f32(t):
+    """torch bf16 tensor -> numpy fp32 (exact widening)."""
+    return t.float().numpy()
+
+
+def head_errors(got, want, heads):
+    """Worst per-head max-abs error and cosine between two fp32 [rows, heads * 128] results."""
+    g = got.reshape(got.shape[0], heads, D).astype(np.float64)
+    w = want.reshape(want.shape[0], heads, D).astype(np.float64)
+    mx = np.abs(g - w).max(axis=(0, 2))
+    cs = (g * w).sum(axis=(0, 2)) / np.sqrt((g * g).sum(axis=(0, 2)) * (w * w).sum(axis=(0, 2)) + 1e-300)
+    return float(mx.max()), float(cs.min())
+
+
+def gpu_result(job, w, plan, B):
+    """One step on freshly uploaded inputs of buffer set 0; the output of
+    batch entry 0 as fp32 [S, width]."""
+    lib, torch = job.lib, job.torch
+    if not B.sets:
+        return None
+    dq, dout = B.sets[0][0]
+    hq = B.host_qkv[0]
+    lib.iris_dev_upload(dq, hq.data_ptr(), hq.numel() * 2)
+    run_step(job, w, plan, B, B.sets[0][:1])
+    out = torch.empty((plan["S"], B.width), dtype=torch.bfloat16)
+    lib.iris_dev_download(out.data_ptr(), dout, out.numel() * 2)
+    lib.check()
+    return out
+
+
+def roofline_of(res, name, nh, S, S_full, pk):
+    """Roofline objects of the two kernels of a step from the per-launch marks."""
+    bf16_peak, bf16_sust, hbm_peak, src = pk
+    roof = pro = None
+    durs, pdurs = res.get("attn_ms") or [], res.get("pro_ms") or []
+    if durs:
+        kms = sum(durs) / len(durs)
+        achieved = attn_flops(1, nh, S, S_full) / (kms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "k_attention_sm100", "achieved": round(achieved, 1),
+                "peak": bf16_peak, "peak_source": src + " bf16 burst", "unit": "TFLOP/s",
+                "frac": round(achieved / bf16_peak, 4), "frac_of_sustained": round(achieved / bf16_sust, 4),
+                "kernel_ms": round(kms, 4), "kernel_ms_median": round(float(np.median(durs)), 4),
+                "kernel_ms_min": round(min(durs), 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(name),
+                "traffic_source": "ncu capture of this workload (constant, not measured in this run)"
+                if name in NCU_DRAM_BYTES_PER_LAUNCH else None}
+    if pdurs:
+        pms = sum(pdurs) / len(pdurs)
+        pbytes = 4.0 * S * nh * D * 2 + 2.0 * S * 64 * 4     # Q and K read + written, cos + sin read
+        pro = {"bound": "hbm", "kernel": "k_head_norm_rope_128_tok", "achieved": round(pbytes / pms / 1e6, 1),
+               "peak": hbm_peak, "peak_source": src + " HBM copy", "unit": "GB/s",
+               "frac": round(pbytes / pms / 1e6 / hbm_peak, 4), "kernel_ms": round(pms, 4),
+               "kernel_ms_median": round(float(np.median(pdurs)), 4), "kernel_ms_min": round(min(pdurs), 4),
+               "bytes": pbytes}
+    return roof, pro
+
+
+def extra_run(job, name, mode, steps, warmup, pk):
+    """A further workload / decomposition measured in the same run: ms per
+    step (max over ranks), aggregate TFLOP/s and per-GPU share of the peak."""
+    w = WORKLOADS[name]
+    plan = plan_of(job, w, mode)
+    B = Buffers(job, w, plan)
+    res = timed_steps(job, w, plan, B, steps, warmup)
+    B.free()
+    total = attn_flops(w["batch"], w["heads"], plan["S_full"], plan["S_full"]) / (res["ms"] * 1e-3) / 1e12
+    return {"workload": name, "mode": mode, "ms_per_step": round(res["ms"], 4), "tflops": round(total, 1),
+            "per_gpu_pct_bf16_peak": round(100 * total / job.world / pk[0], 2)}
+
+
+def run_b200(args):
+    job = Job()
+    lib, torch, rank, world = job.lib, job.torch, job.rank, job.world
+    mode = args.mode or ("single" if world == 1 else "ring")
+    name = args.workload or ("klein4b-1024" if world == 1 else "flux3-multiref" if mode == "ring" else "klein9b-cfg")
+    w = WORKLOADS[name]
+    pk = peaks()
+    if mode == "ring":
+        job.ring_init()
+    plan = plan_of(job, w, mode)
+    B = Buffers(job, w, plan)
+    S_full, H = plan["S_full"], w["heads"]
+
+    sampler = ClockSampler(job.local) if rank == 0 else None
+    res = timed_steps(job, w, plan, B, args.steps, args.warmup, marks=(rank == 0))
+    clocks = sampler.stop(*res["wall"]) if sampler else None
+    ms_step = res["ms"]
     total_flops = attn_flops(w["batch"], H, S_full, S_full)
     value = total_flops / (ms_step * 1e-3) / 1e12
+    roof, prologue = roofline_of(res, name, plan["nh"], plan["S"], S_full, pk) if rank == 0 else (None, None)
+    if roof and mode == "ring":
+        roof["kernel"] = "k_attention_sm100 (one launch per ring call; the time includes its waits for arriving chunks)"
 
-    # Dominant kernel alone (rank 0): mean launch duration from the marks.
-    roof = prologue = None
-    bf16_peak, bf16_sust, hbm_peak, src = peaks()
-    if rank == 0 and entries and len(entries) == 1:
-        durs = [lib.iris_b200_mark_elapsed_ms(2 + 3 * i, 3 + 3 * i) for i in range(min(args.steps, nmark))]
-        pdurs = [lib.iris_b200_mark_elapsed_ms(4 + 3 * i, 2 + 3 * i) for i in range(min(args.steps, nmark))]
-        pdurs = [d for d in pdurs if d > 0]
-        durs = [d for d in durs if d > 0]
-        if durs:
-            kms = sum(durs) / len(durs)
-            achieved = attn_flops(1, nh, S, S_full) / (kms * 1e-3) / 1e12
-            roof = {"bound": "tensor", "kernel": "k_attention_sm100", "achieved": round(achieved, 1),
-                    "peak": bf16_peak, "peak_source": src + " bf16 burst", "unit": "TFLOP/s",
-                    "frac": round(achieved / bf16_peak, 4), "frac_of_sustained": round(achieved / bf16_sust, 4),
-                    "kernel_ms": round(kms, 4), "kernel_ms_median": round(float(np.median(durs)), 4),
-                    "kernel_ms_min": round(min(durs), 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(name)}
-            if pdurs and not ring:
-                pms = sum(pdurs) / len(pdurs)
-                pbytes = 4.0 * S * nh * D * 2 + 2.0 * S * 64 * 4     # Q and K read + written, cos + sin read
-                prologue = {"bound": "hbm", "kernel": "k_head_norm_rope_128_tok", "achieved": round(pbytes / pms / 1e6, 1),
-                            "peak": hbm_peak, "peak_source": src + " HBM copy", "unit": "GB/s",
-                            "frac": round(pbytes / pms / 1e6 / hbm_peak, 4), "kernel_ms": round(pms, 4),
-                            "kernel_ms_median": round(float(np.median(pdurs)), 4),
-                            "kernel_ms_min": round(min(pdurs), 4), "bytes": pbytes}
-
-    # End to end through the C-ABI with host buffers: every step uploads its
-    # inputs from pinned memory, runs prologue + attention and downloads the
-    # result. Serial: the reference's own blocking upload / download calls.
-    # Pipelined (the reported value): the same operations on the library's
-    # stream, the copies on two copy streams ordered by events over three
-    # device buffer sets, so the upload of step i + 1 and the download of step
-    # i - 1 run under the compute of step i.
     e2e = None
-    if entries and not args.no_e2e:
-        nrep = max(1, min(args.steps, 10))
-        host_out = torch.empty((S, width), dtype=torch.bfloat16)
-        if torch.cuda.is_available():
-            host_out = host_out.pin_memory()
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(nrep):
-            bufs = sets[i % nsets]
-            for (dq, dout), hq in zip(bufs, host_qkv):
-                lib.iris_dev_upload(dq, hq.data_ptr(), hq.numel() * 2)
-                lib.iris_dev_upload(d_cos, cos.ctypes.data, cos.nbytes)
-                lib.iris_dev_upload(d_sin, sin.ctypes.data, sin.nbytes)
-            step(bufs)
-            for dq, dout in bufs:
-                lib.iris_dev_download(host_out.data_ptr(), dout, S * width * 2)
-        torch.cuda.synchronize()
-        serial_ms = (time.perf_counter() - t0) * 1e3 / nrep
+    if not args.no_e2e:
+        e_ms, serial_ms, h2d, d2h = e2e_steps(job, w, plan, B, args.steps)
+        if e_ms > 0:
+            e2e = {"value": round(total_flops / (e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_step": round(e_ms, 3),
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                   "how": "iris_b200_upload_async / download_async on two copy streams, ordered by events over 3 "
+                          "buffer sets: copies overlap the neighbouring steps",
+                   "serial": {"value": round(total_flops / (serial_ms * 1e-3) / 1e12, 2), "ms_per_step": round(serial_ms, 3),
+                              "how": "blocking iris_dev_upload / iris_dev_download around every step"}}
 
-        nbuf, prep = 3, max(3, min(args.steps, 30))
-        up, down = torch.cuda.Stream(), torch.cuda.Stream()
-        comp = torch.cuda.ExternalStream(int(lib.iris_b200_stream()))
-        h_cos, h_sin = torch.from_numpy(cos).pin_memory(), torch.from_numpy(sin).pin_memory()
-        dev_in = [[torch.empty((S, 3 * width), dtype=torch.bfloat16, device="cuda") for _ in entries] for _ in range(nbuf)]
-        dev_out = [[torch.empty((S, width), dtype=torch.bfloat16, device="cuda") for _ in entries] for _ in range(nbuf)]
-        dev_cs = [(torch.empty_like(h_cos, device="cuda"), torch.empty_like(h_sin, device="cuda")) for _ in range(nbuf)]
-        pin_out = [[torch.empty((S, width), dtype=torch.bfloat16).pin_memory() for _ in entries] for _ in range(nbuf)]
-        ev_up = [torch.cuda.Event() for _ in range(prep)]
-        ev_comp = [torch.cuda.Event() for _ in range(prep)]
-        ev_down = [torch.cuda.Event() for _ in range(prep)]
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(prep):
-            b = i % nbuf
-            if i >= nbuf:
-                up.wait_event(ev_comp[i - nbuf])          # the last reader of this input set
-            with torch.cuda.stream(up):
-                for e, hq in enumerate(host_qkv):
-                    dev_in[b][e].copy_(hq.view(S, 3 * width), non_blocking=True)
-                dev_cs[b][0].copy_(h_cos, non_blocking=True)
-                dev_cs[b][1].copy_(h_sin, non_blocking=True)
-            ev_up[i].record(up)
-            comp.wait_event(ev_up[i])
-            if i >= nbuf:
-                comp.wait_event(ev_down[i - nbuf])        # the last download of this output set
-            for e in range(len(entries)):
-                dq, dout = dev_in[b][e].data_ptr(), dev_out[b][e].data_ptr()
-                q, k, v = dq, dq + width * 2, dq + 2 * width * 2
-                lib.iris_b200_qk_norm_rope(q, k, 3 * width, d_w, d_w, dev_cs[b][0].data_ptr(), dev_cs[b][1].data_ptr(),
-                                           S, nh, D, w["eps"], 0)
-                if ring:
-                    rc = lib.iris_b200_ring_attention(dout, width, q, k, v, 3 * width, rows_of.ctypes.data, nh, scale)
-                    assert rc == 0, rc
-                else:
-                    lib.iris_dev_attention(dout, width, q, k, v, 3 * width, S, S, nh, nh, D, scale, 0, None)
-            ev_comp[i].record(comp)
-            down.wait_event(ev_comp[i])
-            with torch.cuda.stream(down):
-                for e in range(len(entries)):
-                    pin_out[b][e].copy_(dev_out[b][e], non_blocking=True)
-            ev_down[i].record(down)
-        torch.cuda.synchronize()
-        e_ms = (time.perf_counter() - t0) * 1e3 / prep
-        if dist:
-            t = torch.tensor([e_ms, serial_ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e_ms, serial_ms = float(t[0].item()), float(t[1].item())
-        e2e = {"value": round(total_flops / (e_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_step": round(e_ms, 3),
-               "h2d_bytes_per_step": len(entries) * (S * 3 * width * 2 + 2 * cos.nbytes),
-               "d2h_bytes_per_step": len(entries) * S * width * 2,
-               "how": "copies on two copy streams overlap the neighbouring steps (3 buffer sets)",
-               "serial": {"value": round(total_flops / (serial_ms * 1e-3) / 1e12, 2), "ms_per_step": round(serial_ms, 3),
-                          "how": "blocking iris_dev_upload / iris_dev_download around every step"}}
-    elif dist:
-        t = torch.tensor([0.0, 0.0], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    lib.check()
-    if ring:
+    # The GPU result on the uploaded inputs, for the parity check against the CPU leg.
+    got = gpu_result(job, w, plan, B)
+    host_inputs = B.host_qkv[0] if B.host_qkv else None
+    width = B.width
+    B.free()
+
+    # Further decompositions in the same run (N > 1 only).
+    extras, one_gpu, speedup = {}, None, None
+    if world > 1 and not args.no_extras:
+        if mode == "ring":
+            # the same workload on ONE GPU (rank 0 alone; the others wait at the barrier)
+            if rank == 0:
+                p1 = plan_of(job, w, "single")
+                B1 = Buffers(job, w, p1)
+                r1 = timed_steps(job, w, p1, B1, max(5, min(args.steps, 20)), 3, collective=False)
+                B1.free()
+                one_gpu = r1["ms"]
+            job.barrier()
+            one_gpu = job.max_over_ranks([one_gpu or 0.0])[0]
+            speedup = one_gpu / ms_step
+            extras[name + " head-parallel"] = extra_run(job, name, "shard", args.steps, args.warmup, pk)
+        for other in ("klein9b-cfg", "zimage-turbo"):
+            if other != name:
+                extras[other] = extra_run(job, other, "shard", args.steps, args.warmup, pk)
+
+    # CPU leg on the same inputs (rank 0), and the parity of the two results.
+    cpu = parity = ref_gpu = None
+    if not args.no_cpu:
+        cpu, parity = cpu_leg_with_parity(job, w, plan, got, host_inputs, width, budget_s=20.0 if world == 1 else 12.0)
+    if rank == 0 and world == 1 and mode == "single" and not args.no_ref_gpu:
+        plan2 = plan_of(job, w, "single")
+        B2 = Buffers(job, w, plan2)
+        ref_gpu = reference_gpu_kernels(lib, w, B2.sets[0][0], (B2.d_w, B2.d_cos, B2.d_sin), plan2["S"], plan2["nh"],
+                                        1.0 / np.sqrt(D))
+        B2.free()
+    if mode == "ring":
         lib.iris_b200_ring_destroy()
 
-    cpu = ref_gpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        cpu = cpu_reference(w, budget_s=20.0, steps=1, warmup=0)["cpu_baseline"]
-    if rank == 0 and world == 1 and not ring and entries and not args.no_ref_gpu:
-        ref_gpu = reference_gpu_kernels(lib, w, sets[0][0], (d_w, d_cos, d_sin), S, nh, scale)
-
     if rank == 0:
+        sharding = {"single": "none",
+                    "ring": "ring sequence parallel: K/V rows pushed peer to peer by the copy engines, one attention "
+                            "launch per GPU waits for them in the kernel; NCCL for set-up",
+                    "shard": "cfg batch x heads, no collective"}[mode]
         out = {
-            "metric": "joint-attn TFLOP/s per GPU & % bf16 peak at 1/2/4/8 B200 vs host-CPU ref",
-            "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_step, 4), "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic",
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": name, "batch": w["batch"], "heads": H, "head_dim": D, "tokens": S_full,
-                       "step": "qk_norm_rope + attention", "sharding": "none" if world == 1 and not ring else
-                       "ring sequence parallel (K/V rows pushed peer to peer by the copy engines, NCCL for set-up)" if ring else
-                       "cfg batch x heads, no collective", "l2": "inputs rotate over %d buffer sets (%.0f MB)" %
-                       (nsets, nsets * per_set / 1e6)},
+                       "step": STEP_WORDS},
+            "sharding": sharding,
+            "l2": "inputs rotate over %d buffer sets (%.0f MB)" % (B.nsets, B.nsets * B.per_set / 1e6),
             "per_gpu_tflops": round(value / world, 2),
-            "host_enqueue_ms_per_step": round((t_enqueued - t_wall0) * 1e3 / args.steps, 4),
-            "pct_bf16_peak": round(100 * value / world / bf16_peak, 2),
-            "pct_bf16_sustained": round(100 * value / world / bf16_sust, 2),
-            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-            "roofline": roof, "roofline_prologue": prologue, "cpu_baseline": cpu, "reference_gpu": ref_gpu,
+            "host_enqueue_ms_per_step": round(res["enqueue_ms"], 4),
+            "pct_bf16_peak": round(100 * value / world / pk[0], 2),
+            "pct_bf16_sustained": round(100 * value / world / pk[1], 2),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
+            "roofline": roof, "roofline_prologue": prologue, "cpu_baseline": cpu, "parity": parity,
+            "reference_gpu": ref_gpu,
         }
+        if speedup is not None:
+            out["one_gpu_ms_per_step"] = round(one_gpu, 4)
+            out["speedup_vs_1gpu"] = round(speedup, 3)
+        if extras:
+            out["shards"] = extras
         print(json.dumps(out))
-    if dist:
-        dist.destroy_process_group()
+    if job.dist:
+        job.dist.destroy_process_group()
+
+
+def cpu_leg_with_parity(job, w, plan, got, host_inputs, width, budget_s):
+    """Rank 0 times the reference's CPU code on the tensors the GPU arm used
+    (batch entry 0, the first heads, as many as the time budget allows) and
+    compares the two results on every row of those heads."""
+    torch, rank, world = job.torch, job.rank, job.world
+    S_full, H = plan["S_full"], w["heads"]
+    mode = plan["mode"]
+    cpu = parity = None
+    if mode == "shard" and world > 1:
+        return None, None                 # shards of the heads: no parity leg in that mode
+    # Assemble the full-sequence inputs on rank 0. In ring mode the other
+    # ranks' rows are regenerated from their seeds (seed = 1000 * rank).
+    if rank == 0:
+        if mode == "ring" and world > 1:
+            blocks = [host_inputs] + [make_qkv(int(plan["rows_of"][r]), width, 1000 * r) for r in range(1, world)]
+            full = torch.cat([b.cpu() for b in blocks], 0)
+        else:
+            full = host_inputs
+
+        def inputs(hs):
+            n = hs * D
+            return tuple(np.ascontiguousarray(bf16_to_f32(full[:, i * width:i * width + n])) for i in range(3))
+
+        r = cpu_reference(w, budget_s=budget_s, steps=1, warmup=0, inputs=inputs)
+        cpu, hs, want = r["cpu_baseline"], r["heads_sampled"], r["out"]
+    else:
+        hs, want = 0, None
+    if world > 1:
+        t = torch.tensor([hs], device="cuda")
+        job.dist.broadcast(t, src=0)
+        hs = int(t.item())
+        # every rank's rows of the compared heads -> rank 0
+        mine = got[:, :hs * D].contiguous().cuda()
+        rows_max = int(max(plan["rows_of"]))
+        pad = torch.zeros((rows_max, hs * D), dtype=torch.bfloat16, device="cuda")
+        pad[:mine.shape[0]] = mine
+        gathered = [torch.empty_like(pad) for _ in range(world)] if rank == 0 else None
+        job.dist.gather(pad, gathered, dst=0)
+        if rank == 0:
+            got_all = torch.cat([g[:int(plan["rows_of"][r])].cpu() for r, g in enumerate(gathered)], 0)
+    else:
+        got_all = got[:, :hs * D]
+    if rank == 0:
+        mx, cs = head_errors(bf16_to_f32(got_all), want, hs)
+        parity = {"max_abs": round(mx, 5), "min_cos": round(cs, 7), "heads": hs, "rows": int(S_full),
+                  "against": cpu["kind"] + " CPU result on the same bf16-rounded inputs, every row of the compared heads",
+                  "tolerance": {"max_abs": 2e-2, "min_cos": 0.9999}, "ok": bool(mx <= 2e-2 and cs >= 0.9999)}
+    return cpu, parity
 
 
 # ---------------------------------------------------------------------------
@@ -503,11 +723,14 @@ def reference_gpu_kernels(lib, w, bufs, consts, S, nh, scale, reps=20):
     return out
 
 
-def cpu_reference(w, budget_s, steps, warmup):
+def cpu_reference(w, budget_s, steps, warmup, inputs=None):
     """Times the reference's CPU code for one step of workload `w` on the host
     cores: Q/K norm + RoPE, then attention. Uses oracle/_ref (the reference
     sources compiled unmodified: BLAS build if it loads, else generic), else
-    the CPU port. The sample is a subset of heads sized to the time budget."""
+    the CPU port. The sample is a subset of heads sized to the time budget.
+    inputs(hs) -> fp32 (q, k, v) [S, hs * 128] of the first hs heads: the
+    tensors of the GPU arm; without it seeded normal values are drawn. The
+    result of the last pass comes back as `out` for the parity check."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
     os.environ.setdefault("OPENBLAS_NUM_THREADS", "1")
@@ -525,9 +748,14 @@ def cpu_reference(w, budget_s, steps, warmup):
     cos, sin = rope_tables(w)
     cos2, sin2 = np.repeat(cos, 2, axis=1).copy(), np.repeat(sin, 2, axis=1).copy()
 
+    last = {}
+
     def one(hs):
-        rng = np.random.default_rng(7)
-        q, k, v = (rng.standard_normal((S, hs * D), dtype=np.float32) for _ in range(3))
+        if inputs is not None:
+            q, k, v = inputs(hs)
+        else:
+            rng = np.random.default_rng(7)
+            q, k, v = (rng.standard_normal((S, hs * D), dtype=np.float32) for _ in range(3))
         ones = np.ones(D, np.float32)
         out = np.zeros_like(q)
         t0 = time.perf_counter()
@@ -551,7 +779,9 @@ def cpu_reference(w, budget_s, steps, warmup):
             o.orc_head_norm_rope_f32(q.ctypes.data, hs * D, ones, cos, sin, S, hs, D, w["eps"], 0)
             o.orc_head_norm_rope_f32(k.ctypes.data, hs * D, ones, cos, sin, S, hs, D, w["eps"], 0)
             out = ol.dev_attention(q, k, v, hs)
-        return time.perf_counter() - t0
+        dt = time.perf_counter() - t0
+        last["out"] = out
+        return dt
 
     # Head count of the sample. The reference's BLAS build runs one pthread
     # per group of heads (thread count = largest divisor of the head count
@@ -582,7 +812,7 @@ def cpu_reference(w, budget_s, steps, warmup):
     t = sum(times) / len(times)
     flops = attn_flops(1, hs, S, S)
     val = flops / t / 1e12
-    return {"seconds_per_step": t, "value": val, "heads_sampled": hs,
+    return {"seconds_per_step": t, "value": val, "heads_sampled": hs, "out": last["out"],
             "cpu_baseline": {"value": round(val, 5), "unit": "TFLOP/s", "cores": int(threads), "host_cores": ncpu,
                              "kind": kind, "variant": variant,
                              "sample": "%d of %d heads x %d tokens, batch entry 0, fp32, prologue + attention, %.2f s per pass"
@@ -594,18 +824,20 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", 1))
     if rank != 0:
         return
-    name = args.workload or ("klein4b-1024" if world == 1 else "klein9b-cfg")
+    mode = args.mode or ("single" if world == 1 else "ring")
+    name = args.workload or ("klein4b-1024" if world == 1 else "flux3-multiref" if mode == "ring" else "klein9b-cfg")
     w = WORKLOADS[name]
     r = cpu_reference(w, budget_s=150.0, steps=args.steps, warmup=args.warmup)
     S = seq_len(w)
     out = {
         "impl": "reference",
-        "metric": "joint-attn TFLOP/s per GPU & % bf16 peak at 1/2/4/8 B200 vs host-CPU ref",
+        "metric": METRIC,
         "value": round(r["value"], 5), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(r["seconds_per_step"] * 1e3, 2), "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, "batch": w["batch"], "heads": w["heads"], "head_dim": D, "tokens": S,
-                   "step": "qk_norm + rope + attention on the host CPU"},
+                   "step": STEP_WORDS},
+        "where": "host CPU",
         "cpu_baseline": r["cpu_baseline"],
         "e2e": {"value": round(r["value"], 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -621,8 +853,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffer) measurement")
-    ap.add_argument("--mode", default="shard", choices=["shard", "ring"],
-                    help="N > 1: independent cfg/head shards (default) or ring sequence parallelism")
+    ap.add_argument("--mode", default=None, choices=["single", "shard", "ring"],
+                    help="N > 1: ring sequence parallelism (default) or independent cfg/head shards")
+    ap.add_argument("--no-extras", action="store_true", help="N > 1: skip the further workloads of the same run")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference's own CUDA kernels")
     args = ap.parse_args()

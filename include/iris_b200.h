@@ -5,8 +5,9 @@
  * which reference code it stands in for: the reference is single device,
  * single stream and reports errors only on stderr. These entry points add a
  * status word, stream sharing, device-side timing, a one-launch Q+K
- * prologue, kernel selection for tests, and the multi-GPU decompositions of
- * the attention (head shards, CFG split, ring sequence parallelism).
+ * prologue, kernel selection for tests, stream-ordered copies, attention over
+ * key runs that arrive over time, and the multi-GPU decompositions of the
+ * attention (head shards, CFG split, ring sequence parallelism).
  */
 #ifndef IRIS_B200_H
 #define IRIS_B200_H
@@ -28,7 +29,8 @@ enum {
     IRIS_B200_ENODEV = 4,       /* iris_dev_init() has not succeeded */
     IRIS_B200_ENOMEM = 5,       /* device allocation failed */
     IRIS_B200_EUNSUPPORTED = 6, /* no kernel for this argument combination */
-    IRIS_B200_ECOMM = 7         /* collective transport (NCCL) failed */
+    IRIS_B200_ECOMM = 7,        /* collective transport failed, or the ring is unusable after a failure */
+    IRIS_B200_EPROTO = 8        /* ring ranks disagree (row counts, chunk sizes, sequence numbers) */
 };
 
 /* First error since the last clear (0 = none). The void operations of
@@ -43,6 +45,20 @@ const char *iris_b200_strerror(int code);
  * after a time limit instead of spinning forever). Returns the resulting
  * last error. */
 int iris_b200_check_device_status(void);
+
+/* Limit of every wait inside the kernels, in microseconds (0 restores the
+ * default of one second). Applies to the launches that follow. A host that
+ * knows how long a peer may legitimately take (ring steps) sets it to that;
+ * tests set a few milliseconds to make a wait run out. */
+int iris_b200_set_wait_limit_us(unsigned int us);
+
+/* Host-side fault injection for tests of the failure paths (nothing faults or
+ * hangs on the GPU: the affected launch gives up at the wait limit and reports
+ * IRIS_B200_ETIMEOUT). STALE_TICKET: the next launch that splits its keys
+ * finds an arrival ticket nobody took, so the parts of one query block wait
+ * for a partial result that never comes. One shot. */
+enum { IRIS_B200_FAULT_STALE_TICKET = 1 };
+int iris_b200_inject_fault(int what);
 
 /* ---- device and stream ------------------------------------------------- */
 
@@ -77,6 +93,27 @@ float iris_b200_mark_elapsed_ms(int from, int to);
 
 /* Number of kernel launches the library has enqueued since init. */
 unsigned long long iris_b200_launch_count(void);
+
+/* ---- stream-ordered copies ------------------------------------------------ */
+
+/* iris_dev_upload / iris_dev_download (iris_dev.h) block, as the reference's
+ * do (iris_cuda.cu:191-230). These return at once: the copy runs on
+ * `cuda_stream` (NULL: the library's stream) between page-locked host memory
+ * and the device. A host overlaps the upload of step i + 1 and the download
+ * of step i - 1 with the kernels of step i by giving the copies two streams of
+ * their own and ordering them against the library's stream with events; the
+ * helpers below let a plain-C host do that without CUDA headers. */
+int iris_b200_upload_async(void *dst, const void *src, size_t bytes, void *cuda_stream);
+int iris_b200_download_async(void *dst, const void *src, size_t bytes, void *cuda_stream);
+void *iris_b200_host_alloc(size_t bytes);            /* page-locked host memory */
+void iris_b200_host_free(void *p);
+void *iris_b200_stream_create(void);
+void iris_b200_stream_destroy(void *cuda_stream);
+void *iris_b200_event_create(void);
+void iris_b200_event_destroy(void *event);
+int iris_b200_event_record(void *event, void *cuda_stream);        /* NULL stream: the library's */
+int iris_b200_stream_wait_event(void *cuda_stream, void *event);   /* NULL stream: the library's */
+int iris_b200_stream_sync(void *cuda_stream);
 
 /* ---- prologue ----------------------------------------------------------- */
 
@@ -133,11 +170,12 @@ int iris_b200_seq_shard(int seq, int nranks, int rank, int *first, int *count);
 /* Rank whose K/V chunk is resident on `rank` at ring step `step`. */
 int iris_b200_ring_source(int rank, int step, int nranks);
 
-/* Launch schedule of one ring call: launch i covers the steps
- * [first_step[i], first_step[i] + step_count[i]) (arrays of nranks entries).
- * even_rows: every rank holds the same number of rows. Returns the number of
- * launches, -1 on bad arguments. Pure host arithmetic. */
-int iris_b200_ring_plan(int nranks, int even_rows, int *first_step, int *step_count);
+/* Key parts of one ring call: the attention launch of a call orders its work
+ * by groups of ring steps, group i = steps [first_step[i], first_step[i] +
+ * step_count[i]) (arrays of nranks entries), so that chunks are worked on in
+ * the order they arrive. max_parts <= 0: the library's choice (up to four).
+ * Returns the number of groups, -1 on bad arguments. Pure host arithmetic. */
+int iris_b200_ring_plan(int nranks, int max_parts, int *first_step, int *step_count);
 
 /* Attention of seq_q queries over ONE chunk of seq_k keys, merged into a
  * state carried between chunks: o_state [seq_q, heads * 128] fp32 (the
@@ -146,30 +184,78 @@ int iris_b200_ring_plan(int nranks, int even_rows, int *first_step, int *step_co
  * the merged result is written to `out` as bf16 and the state is left as it
  * is. first && last is the plain attention (state may be NULL). q has row
  * stride ldq, k and v share ldkv. tcgen05 kernel domain only (head_dim 128,
- * aligned views); key_mask covers this chunk's keys. Used for split-K on one
- * GPU and for every step of the ring. */
+ * aligned views); key_mask covers this chunk's keys. Split-K over several
+ * launches on one GPU. */
 int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq,
                               const uint16_t *k, const uint16_t *v, int ldkv,
                               int seq_q, int seq_k, int heads, float scale,
                               const int *key_mask, float *o_state, float *lse_state,
                               int first, int last);
 
-/* Ring sequence parallelism over NCCL (loaded at run time). One rank calls
- * ring_unique_id(), the 128-byte id is handed to every rank by the caller's
- * own means, then every rank calls ring_init(). ring_attention(): q, k, v are
- * this rank's token rows (rows_of[rank] of them, row stride ldi), rows_of
- * lists the row count of every rank; out receives the attention of the local
- * queries over the keys of ALL ranks. At step s a rank works on the chunk of
- * rank (rank - s) mod nranks, which its owner sends directly; all transfers
- * are queued on a second stream at the start and overlap the attention of
- * the earlier steps. A received chunk is in this GPU's memory before any
- * kernel reads it. Up to 16 ranks. */
+/* Attention whose keys are runs of rows taken from two K/V buffers
+ * ("views"), in the order given: one launch, as if the runs were one
+ * contiguous sequence. A run may be guarded by an arrival word: 32-bit words
+ * in device memory that somebody else (a copy engine, another GPU, another
+ * stream) advances once the run's rows are in place; the kernel waits, with
+ * the library's wait limit, until (int)(word - arrive_value) >= 0 before it
+ * loads the first row of the run. This is the attention of a ring call (own
+ * rows, then the slots the peers fill) and of any host that streams K/V in.
+ * nparts: 0 lets the library decide how to cut the keys of a query block
+ * into separately scheduled parts, 1 forbids it, 2..8 asks for that many
+ * parts of whole runs. tcgen05 kernel domain only; at most 16 runs; arrival
+ * word indices below 32. */
+typedef struct {
+    int view;       /* 0: (k0, v0, ld0), 1: (k1, v1, ld1) */
+    int row0, rows; /* key rows [row0, row0 + rows) of that view */
+    int arrive;     /* index of the arrival word guarding the run, -1: none */
+} iris_b200_key_run;
+int iris_b200_attention_runs(uint16_t *out, int ldo, const uint16_t *q, int ldq,
+                             int seq_q, int heads, float scale,
+                             const uint16_t *k0, const uint16_t *v0, int ld0,
+                             const uint16_t *k1, const uint16_t *v1, int ld1,
+                             const iris_b200_key_run *runs, int nruns,
+                             const uint32_t *arrive_words, uint32_t arrive_value, int nparts);
+
+/* Ring sequence parallelism. One rank calls ring_unique_id(), the 128-byte id
+ * is handed to every rank by the caller's own means, then every rank calls
+ * ring_init() (NCCL, loaded at run time, carries the set-up exchanges).
+ * ring_attention(): q, k, v are this rank's token rows (rows_of[rank] of
+ * them, row stride ldi), rows_of lists the row count of every rank; out
+ * receives the attention of the local queries over the keys of ALL ranks.
+ * The chunk of step s is that of rank (rank - s) mod nranks; its owner's copy
+ * engines push it straight into this GPU's slot s (pools mapped through CUDA
+ * IPC) and then advance the slot's arrival word. The attention is one launch
+ * over the runs "own rows, slot 1, ..., slot nranks - 1" that waits for each
+ * arrival word inside the kernel, bounded by the wait limit: a peer that
+ * never delivers ends the call with IRIS_B200_ETIMEOUT (reported by
+ * iris_b200_check_device_status) instead of a hang. A received chunk is in
+ * this GPU's memory before any kernel reads it. Without peer access the
+ * chunks travel by ncclSend / ncclRecv and the launch follows them. Up to 16
+ * ranks.
+ * After any failure inside a call (an error return, or ETIMEOUT) the ring is
+ * unusable: further calls return IRIS_B200_ECOMM until ring_destroy() and a
+ * new ring_init() on every rank. Argument errors detected before anything is
+ * enqueued leave it usable.
+ * ring_configure() (before ring_init, same values on every rank): transport 0
+ * = copy engines when possible, 1 = NCCL send/recv; parts = key parts of the
+ * launch (0: the library's choice). ring_transport(): what is in use after the
+ * first call (0 / 1, -1 before). */
 int iris_b200_ring_unique_id(void *id128);
+int iris_b200_ring_configure(int transport, int parts);
 int iris_b200_ring_init(int rank, int nranks, const void *id128);
 int iris_b200_ring_attention(uint16_t *out, int ldo,
                              const uint16_t *q, const uint16_t *k, const uint16_t *v,
                              int ldi, const int *rows_of, int heads, float scale);
+int iris_b200_ring_transport(void);
 void iris_b200_ring_destroy(void);
+
+/* Device timeline of the last ring call, for measurement: with tracing on,
+ * ring_timeline() waits for the device and fills ms[] with the times, in
+ * milliseconds after the call's start on the library's stream, of: the
+ * attention launch's start, its end, then the completion of the push of step
+ * 1, 2, ... (copy-engine transport). Returns the number of entries. */
+int iris_b200_ring_trace(int enable);
+int iris_b200_ring_timeline(float *ms, int cap);
 
 /* ---- attention without any allocation --------------------------------------- */
 
@@ -194,22 +280,6 @@ int iris_b200_attention_noalloc(uint16_t *out, int ldo,
                                 int ldi, int seq_q, int seq_k, int heads, float scale,
                                 int nsplit);
 size_t iris_b200_attention_noalloc_max_elems(void);
-
-/* Diagnostics for kernel bring-up: runs the tcgen05 kernel and dumps, into
- * `debug` (device, fp32), the raw scores S = Q K^T of the first key tile of
- * every CTA ([ctas * 256, 128]) followed by (m, l) per row ([ctas * 256, 2])
- * and 512 words of device timestamps (cycle counts of CTA 0 per key tile,
- * then wall-clock milestones of the first and the last CTA), so `debug`
- * holds ctas * 256 * 130 + 512 floats; ctas = ceil(seq_q / 256) * heads.
- * desc_fields: NULL, or four words: the
- * shared memory descriptor fields {qk_sbo, v_lbo, v_sbo} in 16-byte units
- * and a mode (bit 0 skip the softmax arithmetic, bit 1 skip the PV MMAs,
- * bit 2 skip the QK MMAs; results are then meaningless, only time is; bit 3
- * leave out the S dump). */
-int iris_b200_attention_diag(uint16_t *out, int ldo,
-                             const uint16_t *q, const uint16_t *k, const uint16_t *v,
-                             int ldi, int seq_q, int seq_k, int heads, float scale,
-                             const int *key_mask, float *debug, const uint32_t *desc_fields);
 
 #ifdef __cplusplus
 }

@@ -25,6 +25,9 @@ extern "C" {
 /* Row softmax in place over x[rows, cols]. Replaces iris_kernels.h:158-159
  * (iris_kernels.c:611-646). */
 void iris_softmax(float *x, int rows, int cols);
+/* The same routine under the name the reference's BLAS attention variants
+ * call (iris_kernels.h:159; iris_transformer_flux.c:1512, 1547, 1558). */
+void iris_softmax_cpu(float *x, int rows, int cols);
 
 /* Batched attention, Q/out: [batch, heads, seq_q, head_dim], K/V: [batch,
  * heads, seq_k, head_dim]. Replaces iris_kernels.h:173-175

@@ -34,6 +34,7 @@ SIGNATURES = {
     "iris_flash_attention": (None, [VP, VP, VP, VP, INT, INT, INT, INT, FLT]),
     "iris_apply_rope": (None, [VP, VP, INT, INT, INT, INT]),
     "iris_compute_rope_freqs": (None, [VP, VP, INT, INT, FLT]),
+    "iris_softmax_cpu": (None, [VP, INT, INT]),
     # iris_b200.h
     "iris_b200_last_error": (INT, []),
     "iris_b200_clear_error": (None, []),
@@ -63,10 +64,33 @@ SIGNATURES = {
     "iris_b200_ring_destroy": (None, []),
     "iris_b200_attention_noalloc": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, FLT, INT]),
     "iris_b200_attention_noalloc_max_elems": (SZ, []),
-    "iris_b200_attention_diag": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, FLT, VP, VP, VP]),
+    "iris_b200_attention_runs": (INT, [VP, INT, VP, INT, INT, INT, FLT, VP, VP, INT, VP, VP, INT, VP, INT, VP,
+                                       C.c_uint32, INT]),
+    "iris_b200_set_wait_limit_us": (INT, [C.c_uint]),
+    "iris_b200_inject_fault": (INT, [INT]),
+    "iris_b200_upload_async": (INT, [VP, VP, SZ, VP]),
+    "iris_b200_download_async": (INT, [VP, VP, SZ, VP]),
+    "iris_b200_host_alloc": (VP, [SZ]),
+    "iris_b200_host_free": (None, [VP]),
+    "iris_b200_stream_create": (VP, []),
+    "iris_b200_stream_destroy": (None, [VP]),
+    "iris_b200_event_create": (VP, []),
+    "iris_b200_event_destroy": (None, [VP]),
+    "iris_b200_event_record": (INT, [VP, VP]),
+    "iris_b200_stream_wait_event": (INT, [VP, VP]),
+    "iris_b200_stream_sync": (INT, [VP]),
+    "iris_b200_ring_configure": (INT, [INT, INT]),
+    "iris_b200_ring_transport": (INT, []),
+    "iris_b200_ring_trace": (INT, [INT]),
+    "iris_b200_ring_timeline": (INT, [VP, INT]),
 }
 
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_GENERIC = 0, 1, 2
+
+
+class KeyRun(C.Structure):
+    """iris_b200_key_run of include/iris_b200.h."""
+    _fields_ = [("view", INT), ("row0", INT), ("rows", INT), ("arrive", INT)]
 
 
 class Lib:

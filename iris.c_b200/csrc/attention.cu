@@ -14,15 +14,24 @@
 
 using namespace iris_b200;
 
-static int check_args(const void *out, const void *q, const void *k, const void *v, int ldo, int ldi,
-                      int seq_q, int seq_k, int heads, int kv_heads, int head_dim) {
-    if (!out || !q || !k || !v || seq_q < 0 || seq_k < 0 || heads <= 0 || kv_heads <= 0 ||
-        heads % kv_heads != 0 || head_dim <= 0 || ldo < heads * head_dim || ldi < kv_heads * head_dim) {
-        set_error(IRIS_B200_EINVAL, "attention", "bad argument");
+namespace iris_b200 {
+
+/* Pointers, counts and row strides every attention entry point insists on:
+ * a stride shorter than a row of heads would make rows overlap (inputs) or
+ * let the output run past its buffer. out may be NULL where an entry point
+ * allows it (ldo is then not looked at). */
+int check_attention_args(const char *op, const void *out, const void *q, const void *k, const void *v, int ldo,
+                         int ldq, int ldkv, int seq_q, int seq_k, int heads, int kv_heads, int head_dim) {
+    if (!q || !k || !v || seq_q < 0 || seq_k < 0 || heads <= 0 || kv_heads <= 0 ||
+        heads % kv_heads != 0 || head_dim <= 0 || (out && ldo < heads * head_dim) || ldq < heads * head_dim ||
+        ldkv < kv_heads * head_dim) {
+        set_error(IRIS_B200_EINVAL, op, "bad argument");
         return IRIS_B200_EINVAL;
     }
     return IRIS_B200_OK;
 }
+
+}  // namespace iris_b200
 
 extern "C" int iris_b200_attention_kernel_for(const void *out, int ldo, const void *q, const void *k,
                                               const void *v, int ldi, int heads, int kv_heads,
@@ -37,7 +46,11 @@ extern "C" int iris_b200_attention_ex(uint16_t *out, int ldo,
                                       int head_dim, float scale, int causal,
                                       const int *key_mask, int kernel) {
     if (!require_device("attention")) return IRIS_B200_ENODEV;
-    int rc = check_args(out, q, k, v, ldo, ldi, seq_q, seq_k, heads, kv_heads, head_dim);
+    if (!out) {
+        set_error(IRIS_B200_EINVAL, "attention", "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    int rc = check_attention_args("attention", out, q, k, v, ldo, ldi, ldi, seq_q, seq_k, heads, kv_heads, head_dim);
     if (rc != IRIS_B200_OK) return rc;
     if (seq_q == 0) return IRIS_B200_OK;
     bool fast = sm100_supported(out, ldo, q, k, v, ldi, heads, kv_heads, head_dim, causal, scale);
@@ -47,8 +60,7 @@ extern "C" int iris_b200_attention_ex(uint16_t *out, int ldo,
     }
     if (kernel == IRIS_B200_KERNEL_GENERIC) fast = false;
     if (fast)
-        return launch_attention_sm100(out, ldo, q, ldi, k, v, ldi, seq_q, seq_k, heads, scale, key_mask,
-                                      0, NULL, NULL, NULL, NULL);
+        return launch_attention_sm100(attn_args(out, ldo, q, ldi, k, v, ldi, seq_q, seq_k, heads, scale, key_mask));
     return launch_attention_generic(out, ldo, q, k, v, ldi, seq_q, seq_k, heads, kv_heads, head_dim,
                                     scale, causal, key_mask);
 }
@@ -60,20 +72,4 @@ extern "C" void iris_dev_attention(uint16_t *out, int ldo,
                                    const int *key_mask) {
     iris_b200_attention_ex(out, ldo, q, k, v, ldi, seq_q, seq_k, heads, kv_heads, head_dim, scale,
                            causal, key_mask, IRIS_B200_KERNEL_AUTO);
-}
-
-/* Diagnostics: the tcgen05 kernel with a dump of the raw first-tile scores
- * and the per-row (m, l) into `debug`, and optional descriptor fields. */
-extern "C" int iris_b200_attention_diag(uint16_t *out, int ldo,
-                                        const uint16_t *q, const uint16_t *k, const uint16_t *v,
-                                        int ldi, int seq_q, int seq_k, int heads, float scale,
-                                        const int *key_mask, float *debug,
-                                        const uint32_t *desc_fields) {
-    if (!require_device("attention_diag")) return IRIS_B200_ENODEV;
-    if (!sm100_supported(out, ldo, q, k, v, ldi, heads, heads, 128, 0, scale)) {
-        set_error(IRIS_B200_EUNSUPPORTED, "attention_diag", "arguments outside the tcgen05 kernel's domain");
-        return IRIS_B200_EUNSUPPORTED;
-    }
-    return launch_attention_sm100(out, ldo, q, ldi, k, v, ldi, seq_q, seq_k, heads, scale, key_mask,
-                                  0, NULL, NULL, debug, desc_fields);
 }

@@ -32,7 +32,9 @@ k_attention_generic(uint16_t *__restrict__ out, int ldo, const uint16_t *__restr
     const int kstride = head_dim + 2;                 /* odd word stride: no bank conflicts */
     uint16_t *ks = reinterpret_cast<uint16_t *>(smem_raw);
     uint16_t *vs = ks + kKeysPerTile * kstride;
-    float *qs = reinterpret_cast<float *>(vs + kKeysPerTile * head_dim + (head_dim & 1));
+    /* 32 (head_dim + 2) + 32 head_dim 16-bit elements precede it: a multiple of
+     * four bytes for every head_dim, odd ones included. */
+    float *qs = reinterpret_cast<float *>(vs + kKeysPerTile * head_dim);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y, kvh = h / group;
     const int qi = blockIdx.x * kQPerBlock + warp;
@@ -113,7 +115,7 @@ k_attention_generic(uint16_t *__restrict__ out, int ldo, const uint16_t *__restr
 
 static size_t generic_smem(int head_dim) {
     return (size_t)kKeysPerTile * (head_dim + 2) * 2 + (size_t)kKeysPerTile * head_dim * 2 +
-           (head_dim & 1) * 2 + (size_t)kQPerBlock * head_dim * 4;
+           (size_t)kQPerBlock * head_dim * 4;
 }
 
 int launch_attention_generic(uint16_t *out, int ldo, const uint16_t *q, const uint16_t *k,
@@ -125,12 +127,10 @@ int launch_attention_generic(uint16_t *out, int ldo, const uint16_t *q, const ui
         return IRIS_B200_EUNSUPPORTED;
     }
     size_t smem = generic_smem(head_dim);
-    static size_t opted = 0;
-    if (smem > 48 * 1024 && smem > opted) {
+    if (smem > 48 * 1024) {
         if (!cuda_ok(cudaFuncSetAttribute(k_attention_generic, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)generic_smem(kMaxHeadDim)), "attention smem opt-in"))
             return IRIS_B200_ECUDA;
-        opted = generic_smem(kMaxHeadDim);
     }
     dim3 grid((seq_q + kQPerBlock - 1) / kQPerBlock, heads);
     k_attention_generic<<<grid, kQPerBlock * 32, smem, g.stream>>>(

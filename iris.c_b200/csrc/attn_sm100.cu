@@ -9,19 +9,31 @@
  *
  * Work decomposition
  *   A work item is 256 consecutive queries of one head, as two 128-row
- *   tiles, against the keys in tiles of 128. The grid is persistent (one CTA
- *   per SM at most): CTA b runs items b, b + gridDim.x, ... and overlaps the
- *   loads and first MMAs of an item with the output of the one before. Items
- *   are head-major, so the CTAs of a round share the K/V of a head (2.4 MB
- *   at 4608 keys) through L2. When the query blocks fill the SMs badly the
- *   keys of every block are split in two items whose results are merged by
- *   whichever finishes second.
+ *   tiles, against a run of key tiles of 128. The grid is persistent (one CTA
+ *   per SM at most). The CTAs draw items from one list in order (an atomic
+ *   counter; the producer warp fetches the next index while the current item
+ *   runs and hands it to the other warps through shared memory), so a CTA
+ *   that was held up simply takes fewer items. Items are head-major: the
+ *   CTAs working at the same time share the K/V of a few heads through L2.
+ *   When the query blocks fill the SMs badly, or the keys arrive over time,
+ *   the keys are cut into up to eight parts; the list then holds part 0 of
+ *   every query block, then part 1, ...; the parts of a block leave their
+ *   unnormalised results in scratch and whichever finishes last merges them.
+ *
+ * Keys
+ *   The key rows are a sequence of sources: runs of rows inside one of two
+ *   K/V views (two pairs of tensor maps), e.g. the caller's own rows followed
+ *   by the slots other GPUs have copied their rows into. A source may be
+ *   guarded by arrival words in device memory: before the first load of a
+ *   tile the producer waits (bounded) until the words covering its rows have
+ *   reached the call's sequence number. Every load reads this GPU's memory.
  *
  * Warps (384 threads)
  *   0-3   softmax of query tile 0: thread r owns row r of S / P / O
  *   4-7   softmax of query tile 1
- *   8     TMA producer (one lane): Q per item, then K0 V0 K1 V1 ... through
- *         a ring of 32 KB slots guarded by full / empty mbarriers
+ *   8     scheduler and TMA producer (one lane): Q per item, then K0 V0 K1
+ *         V1 ... through a ring of 32 KB slots guarded by full / empty
+ *         mbarriers
  *   9     MMA issuer (whole warp, one elected lane issues), owner of the
  *         TMEM allocation
  *   10-11 idle: they complete the third warpgroup, which gives most of its
@@ -51,15 +63,20 @@
  * Output: accumulator rows go through a per-warp shared-memory staging area
  * so that global memory sees whole 128-byte segments of a row.
  *
- * Every wait (mbarriers, the partner of a key split) is bounded in time: when the limit passes the
- * CTA records where in the device status word, raises a CTA-wide abort flag,
- * drains what it has in flight (again bounded), frees its tensor memory and
- * returns. Every load is a TMA copy issued by and for one CTA.
+ * Every wait (mbarriers, the other parts of a key split, arrival words) is
+ * bounded in time (a launch parameter, one second unless the host sets
+ * another): when the limit passes the CTA records where in the device status
+ * word, raises a CTA-wide abort flag, drains what it has in flight (again
+ * bounded), frees its tensor memory and returns. Every load is a TMA copy
+ * issued by and for one CTA.
  */
 #include "common.cuh"
 
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
+
+#include "kernels.h"
 #include <math.h>
 
 namespace iris_b200 {
@@ -79,9 +96,13 @@ static constexpr int kSmemStage = kSmemKV + kStages * kTileBytes;   /* output st
 static constexpr int kSmemBar = kSmemStage + 8 * 4096;
 static constexpr int kSmemBytes = kSmemBar + 256 + 1024;   /* + barriers + alignment slack */
 static constexpr float kRescaleThreshold = 8.0f;
-static constexpr bool kPolyExp = false;    /* evaluate one exponential in four on the FMA pipe */
 static constexpr int kRegsSoftmax = 216, kRegsOther = 72;   /* 2 * 224 + 56 <= 512 */
-static constexpr unsigned long long kWaitLimitNs = 1000000000ull;   /* 1 s */
+static constexpr int kMaxSources = AttnArgs::kMaxSources;
+static constexpr int kMaxParts = AttnArgs::kMaxParts;
+/* Shared memory descriptor fields, in 16-byte units */
+static constexpr uint32_t kQkSbo = 1024 / 16;          /* 8 rows of 128 B */
+static constexpr uint32_t kVLbo = kHalfBytes / 16;     /* next 64-dim half */
+static constexpr uint32_t kVSbo = 1024 / 16;           /* next 8 keys */
 
 /* mbarrier slots inside the barrier block (8 bytes each) */
 enum {
@@ -93,36 +114,56 @@ enum {
     BAR_O_DONE = BAR_P_FULL + 4,          /* 2 */
     BAR_Q_EMPTY = BAR_O_DONE + 2,         /* the QK products of a work item are complete */
     BAR_DRAIN,
-    BAR_COUNT
+    BAR_SCHED_FULL,                       /* 2: the index of work item n (slot n & 1) is published */
+    BAR_SCHED_EMPTY = BAR_SCHED_FULL + 2, /* 2: every consumer warp has read it */
+    BAR_COUNT = BAR_SCHED_EMPTY + 2
 };
 static constexpr int kSmemTmemPtr = BAR_COUNT * 8;      /* u32 */
 static constexpr int kSmemAbort = kSmemTmemPtr + 4;     /* u32 */
+static constexpr int kSmemSched = kSmemAbort + 4;       /* int [2] */
+static_assert(kSmemSched + 8 <= 256, "barrier block");
+static constexpr int kSchedConsumers = 9;               /* the MMA warp and the eight softmax warps */
+
+/* A run of key rows inside one of the two K/V views. */
+struct KeySource {
+    int tile0;          /* first key tile (over all sources) */
+    int row0;           /* first row inside the view */
+    int rows;           /* keys */
+    int view;           /* 0 / 1: which pair of tensor maps */
+    int arrive;         /* index of the first arrival word guarding the rows, -1: none */
+    int rows_per_word;  /* rows guarded by one word (consecutive words follow) */
+};
 
 struct Params {
     uint16_t *out;
     int ldo;
-    int seq_q, seq_k, heads;
+    int seq_q, heads;
     int nqblk;                 /* 256-row query blocks per head */
-    int items;                 /* work items: nqblk * heads * nsplit, dealt round-robin to the CTAs */
-    int nkv;                   /* 128-key tiles */
-    /* Key split: the two halves of the keys of a query block are separate
-     * work items; whichever half finishes second merges the other's partial. */
-    int nsplit;                /* 1 or 2 */
-    float *part_o;             /* [nqblk * heads, 256, 128] fp32, unnormalised O of the half that finished first */
-    float2 *part_ml;           /* [nqblk * heads, 256] its (row maximum, row sum) */
-    unsigned int *tickets;     /* [nqblk * heads, 8 warps, 2]: arrivals, partial ready; zero between launches */
+    int nq;                    /* query blocks over all heads */
+    int items;                 /* work items: nq * nparts */
+    int nkv;                   /* 128-key tiles over all sources */
+    /* Key split: part i of a query block covers the tiles [part_tile[i],
+     * part_tile[i + 1]); whichever part finishes last merges the others. */
+    int nparts;
+    int part_tile[kMaxParts + 1];
+    int nsrc;
+    KeySource src[kMaxSources];
+    const uint32_t *arrive;    /* arrival words, or NULL */
+    uint32_t arrive_seq;       /* a word has arrived when (int)(word - arrive_seq) >= 0 */
+    float *part_o;             /* [nq, nparts - 1, 256, 128] fp32 unnormalised O of the parts that finished early */
+    float2 *part_ml;           /* [nq, nparts - 1, 256] their (row maximum, row sum) */
+    unsigned int *tickets;     /* [nq, 8 warps, 2]: arrivals, partials written; zero between launches */
+    unsigned int *sched;       /* [0] next work item, [1] CTAs that are through; zero between launches; NULL: CTA b
+                                  takes the items b, b + gridDim.x, ... */
     float scale_log2;
-    const uint32_t *mask_bits; /* packed key mask, bit j of word j/32, or NULL */
+    const uint32_t *mask_bits; /* packed key mask, bit j of word j/32, or NULL (single source only) */
     unsigned int *status;      /* [0] flag, [1] site, [2] block, [3] aux */
-    /* state carried across key chunks (ring / split-K), or NULL */
+    unsigned long long wait_ns; /* limit of every wait */
+    /* state carried across key chunks (split-K over several launches), or NULL */
     float *o_acc;              /* [seq_q, heads*128] fp32, normalised partial output */
     float *lse_acc;            /* [heads, seq_q] fp32, log2-sum-exp of the keys seen so far */
     int acc_mode;              /* 0: single pass; 1: first chunk (write state); 2: merge into state;
                                   3: merge with the state and write the final bf16 output */
-    /* descriptor fields, in 16-byte units */
-    uint32_t qk_sbo, v_lbo, v_sbo;
-    float *debug;              /* bring-up dump, or NULL */
-    int diag_mode;             /* diagnostics build: 1 skip softmax math, 2 skip PV MMAs, 4 skip QK MMAs, 8 no S dump */
 };
 
 /* ---------------- PTX wrappers ---------------- */
@@ -159,7 +200,19 @@ struct Ctx {
     uint32_t bars;                  /* shared address of the barrier block */
     volatile uint32_t *abort_flag;  /* generic pointer to the CTA abort word */
     unsigned int *status;
+    unsigned long long wait_ns;
 };
+
+/* A wait ran out: raise the CTA's abort flag and record the first such event
+ * of the launch in the device status word. */
+__device__ __forceinline__ void give_up(const Ctx &c, int site, unsigned aux) {
+    *c.abort_flag = 1u;
+    if (atomicCAS(c.status, 0u, 1u) == 0u) {
+        c.status[1] = (unsigned)site;
+        c.status[2] = blockIdx.x;
+        c.status[3] = aux;
+    }
+}
 
 /* Bounded wait. Returns false when the CTA is aborting. `site` identifies
  * the caller in the status word. */
@@ -169,13 +222,8 @@ __device__ __forceinline__ bool mbar_wait_slow(const Ctx &c, uint32_t bar, uint3
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 63u) == 63u) {
             if (*c.abort_flag) return false;
-            if (global_ns() - t0 > kWaitLimitNs || spin > (1u << 26)) {
-                *c.abort_flag = 1u;
-                if (atomicCAS(c.status, 0u, 1u) == 0u) {
-                    c.status[1] = (unsigned)site;
-                    c.status[2] = blockIdx.x;
-                    c.status[3] = parity;
-                }
+            if (global_ns() - t0 > c.wait_ns || spin > (1u << 26)) {
+                give_up(c, site, parity);
                 return false;
             }
         }
@@ -185,6 +233,29 @@ __device__ __forceinline__ bool mbar_wait(const Ctx &c, int idx, uint32_t parity
     uint32_t bar = c.bars + idx * 8;
     if (mbar_try_wait(bar, parity)) return true;
     return mbar_wait_slow(c, bar, parity, site);
+}
+
+/* Bounded wait for a 32-bit word in global memory that somebody else (another
+ * CTA, a copy engine, another GPU) advances to at least `target`. */
+__device__ __forceinline__ bool word_reached(const uint32_t *word, uint32_t target) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+    return (int32_t)(v - target) >= 0;
+}
+__device__ __forceinline__ bool word_wait(const Ctx &c, const uint32_t *word, uint32_t target, int site, unsigned aux) {
+    if (word_reached(word, target)) return true;
+    unsigned long long t0 = global_ns();
+    for (uint32_t spin = 0;; spin++) {
+        if (word_reached(word, target)) return true;
+        if ((spin & 7u) == 7u) {
+            if (*c.abort_flag) return false;
+            if (global_ns() - t0 > c.wait_ns || spin > (1u << 26)) {
+                give_up(c, site, aux);
+                return false;
+            }
+            __nanosleep(100);
+        }
+    }
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
@@ -271,19 +342,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return d;
 }
 
-/* 2^x on the FMA pipe: round x to the nearest integer n with the 1.5 * 2^23
- * trick, cubic minimax polynomial for 2^f on f in [-0.5, 0.5] (relative
- * error 1e-4, below the bf16 rounding of P), n added into the exponent. */
-__device__ __forceinline__ float ex2_poly(float x) {
-    x = fmaxf(x, -125.0f);
-    float t = x + 12582912.0f;
-    float f = x - (t - 12582912.0f);
-    float p = fmaf(f, 0.0555041086f, 0.2402265069f);
-    p = fmaf(p, f, 0.6931471806f);
-    p = fmaf(p, f, 1.0f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -307,31 +365,9 @@ static constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((12
 static constexpr uint32_t kIdescQK = kIdescBase;
 static constexpr uint32_t kIdescPV = kIdescBase | (1u << 16);
 
-/* Timestamps of CTA 0 for the first 16 key tiles (diagnostics build only):
- * slot [who][j][k], who = 0 / 1 softmax warpgroup of tile 0 / 1, 2 = MMA. */
-__device__ __forceinline__ void stamp(const Params &p, int who, int j, int k) {
-    if (p.debug && blockIdx.x == 0 && j < 16 && (threadIdx.x & 31) == 0 && (who == 2 || (threadIdx.x & 127) == 0)) {
-        unsigned long long c;
-        asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
-        float *base = p.debug + (size_t)p.items * 256 * 130;
-        reinterpret_cast<uint32_t *>(base)[(who * 16 + j) * 8 + k] = (uint32_t)c;
-    }
-}
+/* ---------------- work items ---------------- */
 
-/* Wall-clock (ns) milestones of the first and the last CTA (diagnostics build
- * only): slot [3][first / last][k]; k = 0 entry, 1 set-up done, 2 first S of
- * the first item, 3 its last softmax done, 4 its last PV done, 5 its output
- * written, 6 first S of the second item, 7 all warps done. */
-__device__ __forceinline__ void stamp_ns(const Params &p, int k) {
-    if (p.debug && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1)) {
-        float *base = p.debug + (size_t)p.items * 256 * 130;
-        reinterpret_cast<uint32_t *>(base)[(3 * 16 + (blockIdx.x == 0 ? 0 : 1)) * 8 + k] = (uint32_t)global_ns();
-    }
-}
-
-/* ---------------- roles ---------------- */
-
-/* Position in the K/V ring: items are consumed in load order K0 V0 K1 V1 ... */
+/* Position in the K/V ring: tiles are consumed in load order K0 V0 K1 V1 ... */
 struct Ring {
     int slot;
     uint32_t phase;
@@ -343,10 +379,8 @@ struct Ring {
     }
 };
 
-/* A work item is one 256-row query block of one head. CTA b runs items
- * b, b + gridDim.x, ... one after the other: while the softmax warps write
- * the output of one item, the Q / K / V tiles of the next are already in
- * shared memory and its first QK products are in flight. */
+/* A work item is one part of the keys for one 256-row query block of one
+ * head. The list is part-major: item = part * nq + query block. */
 struct Item {
     int qitem;          /* query block index over all heads */
     int head, q0, ntq;
@@ -354,48 +388,130 @@ struct Item {
 };
 __device__ __forceinline__ Item item_of(const Params &p, int item) {
     Item w;
-    w.qitem = p.nsplit == 2 ? item >> 1 : item;
-    const int ks = p.nsplit == 2 ? item & 1 : 0;
+    const int part = item / p.nq;
+    w.qitem = item - part * p.nq;
     w.head = w.qitem / p.nqblk;
     w.q0 = (w.qitem - w.head * p.nqblk) * 2 * kTileQ;
     w.ntq = (p.seq_q - w.q0 > kTileQ) ? 2 : 1;
-    w.j0 = ks * p.nkv / p.nsplit;
-    w.nj = (ks + 1) * p.nkv / p.nsplit - w.j0;
+    w.j0 = p.part_tile[part];
+    w.nj = p.part_tile[part + 1] - w.j0;
     return w;
+}
+
+/* Source that holds key tile j (sources are few: a linear walk). */
+__device__ __forceinline__ int source_of(const Params &p, int j) {
+    int s = 0;
+    while (s + 1 < p.nsrc && p.src[s + 1].tile0 <= j) s++;
+    return s;
+}
+/* Keys of tile j that exist, given its source. */
+__device__ __forceinline__ int tile_keys(const KeySource &s, int j) {
+    const int left = s.rows - (j - s.tile0) * kTileK;
+    return left < kTileK ? left : kTileK;
+}
+
+/* The work list as seen by the warps that do not fetch from it: item n of
+ * this CTA is published in slot n & 1 of a two-entry mailbox. Returns the
+ * item index, -1 at the end of the list, -2 when the CTA is aborting. */
+__device__ __forceinline__ int sched_get(const Ctx &c, const int *mail, int n, int site) {
+    const int slot = n & 1;
+    if (!__all_sync(0xffffffffu, mbar_wait(c, BAR_SCHED_FULL + slot, (n >> 1) & 1u, site))) return -2;
+    const int item = mail[slot];
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(c.bars + (BAR_SCHED_EMPTY + slot) * 8);
+    return item;
 }
 
 __device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
     return ((uint64_t)hi << 32) | lo;
 }
 
-__device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmq, const CUtensorMap *tmk,
-                         const CUtensorMap *tmv, uint32_t smem) {
+/* ---------------- roles ---------------- */
+
+struct Maps {
+    const CUtensorMap *q, *k[2], *v[2];
+};
+
+__device__ __forceinline__ void producer(const Ctx &c, const Params &p, const Maps &m, uint32_t smem, volatile int *mail) {
     int issued = 0;
     Ring r = {0, 0u};
     bool ok = true;
-    for (int item = blockIdx.x, n = 0; ok && item < p.items; item += gridDim.x, n++) {
-        const Item w = item_of(p, item);
+    uint32_t arrived = 0;                   /* arrival words seen at their target value */
+
+    /* Next index of the work list, and its publication as item n of this CTA. */
+    auto take = [&](int n) -> int {
+        const int item = p.sched ? (int)atomicAdd(p.sched, 1u) : (int)(blockIdx.x + (unsigned)n * gridDim.x);
+        return item < p.items ? item : -1;
+    };
+    auto publish = [&](int n, int item) -> bool {
+        const int slot = n & 1;
+        /* The slot held item n - 2, which every consumer has read long ago. */
+        if (n >= 2 && !mbar_wait(c, BAR_SCHED_EMPTY + slot, ((n >> 1) - 1) & 1u, 120 + slot)) return false;
+        mail[slot] = item;
+        mbar_arrive(c.bars + (BAR_SCHED_FULL + slot) * 8);
+        return true;
+    };
+
+    int cur = take(0);
+    ok = publish(0, cur);
+    for (int n = 0; ok && cur >= 0; n++) {
+        const Item w = item_of(p, cur);
         const int col = w.head * kHeadDim;
         /* The Q tiles are replaced once every QK product of the previous item is done. */
         if (n > 0 && !mbar_wait(c, BAR_Q_EMPTY, (n - 1) & 1, 110)) break;
         mbar_expect_tx(c.bars + BAR_Q_FULL * 8, w.ntq * kTileBytes);
         for (int t = 0; t < w.ntq; t++)
             for (int half = 0; half < 2; half++)
-                tma_load_2d(smem + kSmemQ + t * kTileBytes + half * kHalfBytes, tmq, col + half * 64,
+                tma_load_2d(smem + kSmemQ + t * kTileBytes + half * kHalfBytes, m.q, col + half * 64,
                             w.q0 + t * kTileQ, c.bars + BAR_Q_FULL * 8);
+        int si = source_of(p, w.j0);
+        int next = -1;
+        bool fetched = false;
         for (int it = 0; it < 2 * w.nj; it++, issued++, r.next()) {
+            /* The next item is fetched once the first tiles of this one are on
+             * their way: the round trip of the atomic hides behind them. */
+            if (!fetched && it >= 4) {
+                next = take(n + 1);
+                fetched = true;
+                if (!(ok = publish(n + 1, next))) break;
+            }
+            const int j = w.j0 + (it >> 1);
+            if (!(it & 1)) {
+                while (si + 1 < p.nsrc && p.src[si + 1].tile0 <= j) si++;
+                const KeySource &s = p.src[si];
+                if (s.arrive >= 0) {
+                    /* Rows of this tile inside the source, and the words that guard them. */
+                    const int a = (j - s.tile0) * kTileK;
+                    const int b = (a + kTileK < s.rows ? a + kTileK : s.rows) - 1;
+                    for (int wd = s.arrive + a / s.rows_per_word; ok && wd <= s.arrive + b / s.rows_per_word; wd++) {
+                        if ((arrived >> (wd & 31)) & 1u) continue;
+                        ok = word_wait(c, p.arrive + wd, p.arrive_seq, 130, (unsigned)wd);
+                        arrived |= 1u << (wd & 31);
+                        /* The rows were written by a copy engine or another GPU; the
+                         * loads below go through the asynchronous proxy. */
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                    }
+                    if (!ok) break;
+                }
+            }
             /* A slot is refilled once the MMAs that read its previous content are done. */
             if (issued >= kStages && !mbar_wait(c, BAR_KV_EMPTY + r.slot, r.phase ^ 1u, 100 + r.slot)) {
                 ok = false;
                 break;
             }
+            const KeySource &s = p.src[si];
             uint32_t full = c.bars + (BAR_KV_FULL + r.slot) * 8;
             mbar_expect_tx(full, kTileBytes);
-            const CUtensorMap *map = (it & 1) ? tmv : tmk;
+            const CUtensorMap *map = (it & 1) ? m.v[s.view] : m.k[s.view];
             for (int half = 0; half < 2; half++)
                 tma_load_2d(smem + kSmemKV + r.slot * kTileBytes + half * kHalfBytes, map, col + half * 64,
-                            (w.j0 + (it >> 1)) * kTileK, full);
+                            s.row0 + (j - s.tile0) * kTileK, full);
         }
+        if (ok && !fetched) {
+            next = take(n + 1);
+            ok = publish(n + 1, next);
+        }
+        cur = next;
     }
     if (*c.abort_flag) {
         /* Nobody may be consuming any more: wait for the copies still in flight. */
@@ -404,17 +520,16 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
     }
 }
 
-template <bool DEBUG>
-__device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem) {
+__device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem, const int *mail) {
     /* Descriptor words that never change: the high word (stride offset,
      * version, swizzle mode) per operand kind, and the low word of each
      * tile base (start address and leading offset, 16-byte units). A k-step
      * only adds a constant to the low word. */
-    const uint32_t hi_qk = (uint32_t)(make_desc(0, 0, p.qk_sbo) >> 32);
-    const uint32_t hi_v = (uint32_t)(make_desc(0, 0, p.v_sbo) >> 32);
+    const uint32_t hi_qk = (uint32_t)(make_desc(0, 0, kQkSbo) >> 32);
+    const uint32_t hi_v = (uint32_t)(make_desc(0, 0, kVSbo) >> 32);
     const uint32_t lo_q0 = (uint32_t)make_desc(smem + kSmemQ, 1, 0);
     const uint32_t lo_k0 = (uint32_t)make_desc(smem + kSmemKV, 1, 0);
-    const uint32_t lo_v0 = (uint32_t)make_desc(smem + kSmemKV, p.v_lbo, 0);
+    const uint32_t lo_v0 = (uint32_t)make_desc(smem + kSmemKV, kVLbo, 0);
     const bool leader = elect_one();        /* the whole warp runs this code, one lane issues */
     bool ok = true;
 
@@ -422,7 +537,6 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
         const uint32_t lo_q = lo_q0 + t * (kTileBytes >> 4), lo_k = lo_k0 + slot * (kTileBytes >> 4);
 #pragma unroll
         for (int ks = 0; ks < kHeadDim / 16; ks++) {
-            if (DEBUG && (p.diag_mode & 4)) break;
             const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
             if (leader)
                 mma_ss(tmem + t * 128, desc64(lo_q + off, hi_qk), desc64(lo_k + off, hi_qk), kIdescQK, ks > 0);
@@ -433,8 +547,7 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
     auto issue_pv = [&](int t, int h, int slot, bool first) {
         const uint32_t lo_v = lo_v0 + slot * (kTileBytes >> 4) + h * (64 * 128 >> 4);
         const uint32_t tp = tmem + t * 128 + h * 32, to = tmem + 256 + t * 128;
-        if (DEBUG && (p.diag_mode & 2)) {
-        } else if (first && h == 0) {
+        if (first && h == 0) {
 #pragma unroll
             for (int ks = 0; ks < 4; ks++)
                 if (leader) mma_ts(to, tp + ks * 8, desc64(lo_v + ks * (16 * 128 >> 4), hi_v), kIdescPV, ks > 0);
@@ -448,10 +561,14 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
 
     Ring r = {0, 0u};
     uint32_t seen[2] = {0u, 0u};            /* key tiles of query tile t so far, over all items */
-    for (int item = blockIdx.x, n = 0; ok && item < p.items; item += gridDim.x, n++) {
+    for (int n = 0; ok; n++) {
+        const int item = sched_get(c, mail, n, 240);
+        if (item < 0) {
+            ok = item == -1;
+            break;
+        }
         const Item w = item_of(p, item);
         const int ntq = w.ntq, nkv = w.nj;
-        const int js = n == 0 ? 0 : 16;     /* timestamps cover the first item only */
         ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_Q_FULL, n & 1, 200) && mbar_wait(c, BAR_KV_FULL + r.slot, r.phase, 201));
         if (!ok) break;
         tc_fence_after();
@@ -472,7 +589,6 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
             if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rv.slot, rv.phase, 210)))) break;
             for (int t = 0; t < ntq; t++) {
                 const uint32_t par = (seen[t] + j) & 1u;
-                if (DEBUG) stamp(p, 2, j + js, 4 * t);
                 /* The first 64 keys' P arrives while the softmax is still busy
                  * with the other 64: their PV runs under it. (With j == 0 the
                  * softmax warps have also read the previous item's O by now.) */
@@ -481,20 +597,17 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
                 issue_pv(t, 0, rv.slot, j == 0);
                 if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_P_FULL + 2 * t + 1, par, 224 + t)))) break;
                 tc_fence_after();
-                if (DEBUG) stamp(p, 2, j + js, 4 * t + 1);
                 issue_pv(t, 1, rv.slot, j == 0);
                 if (t == ntq - 1 && leader) tc_commit(c.bars + (BAR_KV_EMPTY + rv.slot) * 8);
                 if (more) {
                     if (t == 0 && !(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_KV_FULL + rk.slot, rk.phase, 230)))) break;
                     tc_fence_after();
-                    if (DEBUG) stamp(p, 2, j + js, 4 * t + 2);
                     issue_qk(t, rk.slot);
                     if (t == ntq - 1 && leader) {
                         tc_commit(c.bars + (BAR_KV_EMPTY + rk.slot) * 8);
                         /* That was the last read of this item's Q tiles. */
                         if (j + 2 == nkv) tc_commit(c.bars + BAR_Q_EMPTY * 8);
                     }
-                    if (DEBUG) stamp(p, 2, j + js, 4 * t + 3);
                 }
             }
         }
@@ -505,16 +618,16 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
         if (leader) tc_commit(c.bars + BAR_DRAIN * 8);
         uint32_t bar = c.bars + BAR_DRAIN * 8;
         unsigned long long t0 = global_ns();
-        while (!mbar_try_wait(bar, 0) && global_ns() - t0 < kWaitLimitNs) {}
+        while (!mbar_try_wait(bar, 0) && global_ns() - t0 < c.wait_ns) {}
     }
 }
 
-/* Valid-key bits of key tile j (bit b of word w = key j*128 + 32w + b). */
-__device__ __forceinline__ void tile_bits(const Params &p, int j, uint32_t bits[4]) {
-    int n = p.seq_k - j * kTileK;                 /* keys left, >= 1 */
+/* Valid-key bits of key tile j holding `nkeys` keys (bit b of word w = key
+ * 32 w + b of the tile). */
+__device__ __forceinline__ void tile_bits(const Params &p, int j, int nkeys, uint32_t bits[4]) {
 #pragma unroll
     for (int w = 0; w < 4; w++) {
-        int left = n - 32 * w;
+        int left = nkeys - 32 * w;
         uint32_t b = left >= 32 ? 0xFFFFFFFFu : (left <= 0 ? 0u : ((1u << left) - 1u));
         if (p.mask_bits) b &= p.mask_bits[j * 4 + w];    /* padded to whole tiles by the packer */
         bits[w] = b;
@@ -529,8 +642,7 @@ __device__ __forceinline__ void mask_chunk(uint32_t *v, uint32_t bits) {
 }
 
 /* Half an S row (64 scores) -> P (bf16 pairs into 32 columns at tP) and the
- * four partial row sums. POLY: one exponential in four runs on the FMA pipe. */
-template <bool POLY>
+ * four partial row sums. */
 __device__ __forceinline__ void exp_half(const uint32_t *s, float sl2, float neg_ref, float *sum4, uint32_t tP) {
 #pragma unroll
     for (int ch = 0; ch < 2; ch++) {
@@ -540,7 +652,7 @@ __device__ __forceinline__ void exp_half(const uint32_t *s, float sl2, float neg
             float x0 = fmaf(__uint_as_float(s[ch * 32 + 2 * i]), sl2, neg_ref);
             float x1 = fmaf(__uint_as_float(s[ch * 32 + 2 * i + 1]), sl2, neg_ref);
             float p0 = ex2(x0);
-            float p1 = (POLY && (i & 1)) ? ex2_poly(x1) : ex2(x1);
+            float p1 = ex2(x1);
             sum4[(2 * i) & 3] += p0;
             sum4[(2 * i + 1) & 3] += p1;
             pk[i] = cvt_bf16x2(p0, p1);
@@ -592,9 +704,8 @@ __device__ __forceinline__ void rows_store_f32(const uint32_t *src, float *base,
 
 /* One work item of query tile t. `cnt`: key tiles this tile has been through
  * before (the barrier phases run on over the items). False when aborting. */
-template <bool DEBUG>
 __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsigned char *stage, uint32_t tmem, int t,
-                                             int item, const Item &w, uint32_t cnt, int js) {
+                                             int item, const Item &w, uint32_t cnt) {
     const int head = w.head, q0 = w.q0, nkv = w.nj;
     const int row = threadIdx.x & 127;                     /* row of the tile == TMEM lane */
     const uint32_t lane_base = (uint32_t)(row & ~31) << 16;
@@ -605,35 +716,31 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
     float m_ref = -INFINITY;     /* reference of the exponentials, in scaled log2 units */
     float l = 0.0f;
     bool ok = true;
+    int si = source_of(p, w.j0);
+    int src_last = (si + 1 < p.nsrc ? p.src[si + 1].tile0 : p.nkv) - 1;     /* last tile of the current source */
 
     for (int j = 0; j < nkv; j++) {
         /* One decision per warp: the TMEM accesses below are warp-collective. */
         if (!(ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_S_FULL + t, (cnt + j) & 1u, 300 + t)))) break;
         tc_fence_after();
-        if (DEBUG) stamp(p, t, j + js, 0);
-        if (DEBUG && j == 0 && threadIdx.x == 0 && js <= 16) stamp_ns(p, js == 0 ? 2 : 6);
-        if (DEBUG && (p.diag_mode & 1)) {
-            tc_fence_before();
-            mbar_arrive(c.bars + (BAR_P_FULL + 2 * t) * 8);
-            mbar_arrive(c.bars + (BAR_P_FULL + 2 * t + 1) * 8);
-            continue;
-        }
 
-        const bool partial = (w.j0 + j == p.nkv - 1 && (p.seq_k & (kTileK - 1)) != 0) || p.mask_bits != nullptr;
+        /* Only the last tile of a source can hold fewer than 128 keys. */
+        const int jg = w.j0 + j;
+        if (jg > src_last) {
+            si++;
+            src_last = (si + 1 < p.nsrc ? p.src[si + 1].tile0 : p.nkv) - 1;
+        }
+        int nkeys = kTileK;
+        if (jg == src_last) nkeys = tile_keys(p.src[si], jg);
+        const bool partial = nkeys < kTileK || p.mask_bits != nullptr;
         uint32_t bits[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
-        if (partial) tile_bits(p, w.j0 + j, bits);
+        if (partial) tile_bits(p, jg, nkeys, bits);
 
         /* The whole S row of this thread: four loads in flight, one wait. */
         uint32_t s[128];
 #pragma unroll
         for (int ch = 0; ch < 4; ch++) tmem_ld32(tS + ch * 32, s + ch * 32);
         tc_wait_ld();
-        if (DEBUG) stamp(p, t, j + js, 1);
-        if (DEBUG && p.debug && j == 0 && !(p.diag_mode & 8)) {
-            float *dst = p.debug + ((size_t)item * 256 + t * 128 + row) * 128;
-#pragma unroll
-            for (int i = 0; i < 128; i++) dst[i] = __uint_as_float(s[i]);
-        }
         if (partial) {
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) mask_chunk(s + ch * 32, bits[ch]);
@@ -677,104 +784,89 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
         }
 
         /* P = 2^(s * scale_log2 - m_ref) as bf16 pairs over the first 64
-         * columns of S (the row is in registers, so nothing is lost). One
-         * exponential in four is evaluated on the FMA pipe instead of the
-         * special-function unit, which is the scarcer of the two here. */
+         * columns of S (the row is in registers, so nothing is lost). A
+         * masked (-inf) score gives an exact 0. */
         const float neg_ref = m_ref == -INFINITY ? 0.0f : -m_ref;
         float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (DEBUG) stamp(p, t, j + js, 2);
-        /* Tiles with masked (-inf) scores keep every exponential on the
-         * special-function unit, which returns an exact 0 for them. */
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            if (partial) exp_half<false>(s + 64 * h, sl2, neg_ref, sum4, tS + 32 * h);
-            else exp_half<kPolyExp>(s + 64 * h, sl2, neg_ref, sum4, tS + 32 * h);
+            exp_half(s + 64 * h, sl2, neg_ref, sum4, tS + 32 * h);
             /* Hand each half of P to the MMA issuer as soon as it is stored. */
             tc_wait_st();
             tc_fence_before();
             mbar_arrive(c.bars + (BAR_P_FULL + 2 * t + h) * 8);
-            if (DEBUG && h == 0) stamp(p, t, j + js, 3);
         }
         l += (sum4[0] + sum4[2]) + (sum4[1] + sum4[3]);
-        if (DEBUG) stamp(p, t, j + js, 4);
     }
 
     /* Epilogue: O / l -> bf16 rows of the output slice of this head. */
-    if (DEBUG && threadIdx.x == 0 && js == 0) stamp_ns(p, 3);
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_O_DONE + t, (cnt + nkv - 1) & 1u, 310 + t));
     if (!ok) return false;
     tc_fence_after();
-    if (DEBUG && threadIdx.x == 0 && js == 0) stamp_ns(p, 4);
     const int lane = threadIdx.x & 31, wrow0 = row & ~31;
 
-    /* Key split: each warp settles with its counterpart of the other half.
-     * The first to arrive leaves its unnormalised rows, maxima and sums in
-     * the scratch of the query block; the second, which only ever waits for a
-     * warp that is already writing, folds them into its own and goes on to
-     * the output as if it had seen every key. */
-    float a_own = 1.0f, a_other = 0.0f;
-    const float *part_rows = nullptr;         /* the warp's 32 rows of the other half's partial */
+    /* Key split: each warp settles with its counterparts of the other parts
+     * through a ticket. All but the last to arrive leave their unnormalised
+     * rows, maxima and sums in the scratch of the query block and move on;
+     * the last, which only ever waits for warps that are already writing,
+     * folds them into its own and goes on to the output as if it had seen
+     * every key. */
+    float a_own = 1.0f;
+    int nmerge = 0;
+    const float *part_rows = nullptr;         /* the warp's 32 rows of the first partial */
+    const float2 *part_ml_row = nullptr;      /* this row's (m, l) of the first partial */
     unsigned char *stage_w = stage + (size_t)(t * 4 + (wrow0 >> 5)) * 4096;
-    if (p.nsplit > 1) {
+    if (p.nparts > 1) {
+        const int others = p.nparts - 1;
         unsigned int *tk = p.tickets + ((size_t)w.qitem * 8 + t * 4 + (wrow0 >> 5)) * 2;
-        float *prows = p.part_o + ((size_t)w.qitem * 256 + t * kTileQ + wrow0) * kHeadDim;
-        float2 *pml = p.part_ml + (size_t)w.qitem * 256 + t * kTileQ + row;
+        float *prows = p.part_o + (((size_t)w.qitem * others) * 256 + t * kTileQ + wrow0) * kHeadDim;
+        float2 *pml = p.part_ml + ((size_t)w.qitem * others) * 256 + t * kTileQ + row;
         unsigned int order = 0;
         if (lane == 0) order = atomicAdd(tk, 1u);
         order = __shfl_sync(0xffffffffu, order, 0);
-        if (order == 0) {
+        if (order < (unsigned)others) {
+            float *mine = prows + (size_t)order * 256 * kHeadDim;
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 uint32_t o[64];
                 tmem_ld32(tO + half * 64, o);
                 tmem_ld32(tO + half * 64 + 32, o + 32);
                 tc_wait_ld();
-                rows_store_f32(o, prows + half * 64, kHeadDim, 32, stage_w, lane);
-                rows_store_f32(o + 32, prows + half * 64 + 32, kHeadDim, 32, stage_w, lane);
+                rows_store_f32(o, mine + half * 64, kHeadDim, 32, stage_w, lane);
+                rows_store_f32(o + 32, mine + half * 64 + 32, kHeadDim, 32, stage_w, lane);
             }
-            __stcg(pml, make_float2(m_ref, l));
+            __stcg(pml + (size_t)order * 256, make_float2(m_ref, l));
             __threadfence();
             __syncwarp();
-            if (lane == 0) atomicExch(tk + 1, 1u);
+            if (lane == 0) atomicAdd(tk + 1, 1u);
             tc_fence_before();
             return true;
         }
         unsigned int ready = 1;
         if (lane == 0) {
-            unsigned long long t0 = global_ns();
-            while (atomicAdd(tk + 1, 0u) == 0u) {
-                if (*c.abort_flag || global_ns() - t0 > kWaitLimitNs) {
-                    *c.abort_flag = 1u;
-                    if (atomicCAS(c.status, 0u, 1u) == 0u) {
-                        c.status[1] = 320u + t;
-                        c.status[2] = blockIdx.x;
-                        c.status[3] = (unsigned)item;
-                    }
-                    ready = 0;
-                    break;
-                }
-            }
+            ready = word_wait(c, tk + 1, (uint32_t)others, 320 + t, (unsigned)item) ? 1u : 0u;
             tk[0] = 0u;                      /* the next launch finds the pair of words cleared */
             tk[1] = 0u;
         }
         ready = __shfl_sync(0xffffffffu, ready, 0);
         if (!ready) return false;
         __threadfence();
-        const float2 ml = __ldcg(pml);
-        const float m_new = fmaxf(m_ref, ml.x);
+        float m_new = m_ref, l_new;
+        for (int i = 0; i < others; i++) m_new = fmaxf(m_new, __ldcg(pml + (size_t)i * 256).x);
         a_own = m_ref == -INFINITY ? 0.0f : ex2(m_ref - m_new);
-        a_other = ml.x == -INFINITY ? 0.0f : ex2(ml.x - m_new);
-        l = a_own * l + a_other * ml.y;
+        l_new = a_own * l;
+        for (int i = 0; i < others; i++) {
+            const float2 ml = __ldcg(pml + (size_t)i * 256);
+            l_new += ml.x == -INFINITY ? 0.0f : ex2(ml.x - m_new) * ml.y;
+        }
+        l = l_new;
         m_ref = m_new;
+        nmerge = others;
         part_rows = prows;
+        part_ml_row = pml;
     }
     const bool valid = qrow < p.seq_q;
     float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    if (DEBUG && p.debug) {
-        float *dst = p.debug + (size_t)p.items * 256 * 128 + ((size_t)item * 256 + t * 128 + row) * 2;
-        dst[0] = m_ref;
-        dst[1] = l;
-    }
 
     /* Chunked state: this launch saw only part of the keys. lse = m + log2(l). */
     float w_prev = 0.0f, w_cur = 1.0f;
@@ -807,7 +899,7 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
      * the row so that neither side has bank conflicts): a thread owns a row
      * of the accumulator, but eight threads writing 128 contiguous bytes of
      * one output row is what the memory system wants. */
-    const float f_cur = inv * w_cur * a_own, f_other = inv * w_cur * a_other;
+    const float f_all = inv * w_cur, f_cur = f_all * a_own;
     const int grow0 = q0 + t * kTileQ + wrow0;                       /* first row of this warp */
     const int nvalid = p.seq_q - grow0 < 32 ? (p.seq_q - grow0 < 0 ? 0 : p.seq_q - grow0) : 32;
     const size_t ld_acc = (size_t)p.heads * kHeadDim;
@@ -820,14 +912,18 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
         tc_wait_ld();
 #pragma unroll
         for (int e = 0; e < 64; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * f_cur);
-        if (part_rows) {
+#pragma unroll 1
+        for (int i = 0; i < nmerge; i++) {
+            const float2 ml = __ldcg(part_ml_row + (size_t)i * 256);
+            const float f_i = ml.x == -INFINITY ? 0.0f : f_all * ex2(ml.x - m_ref);
+            const float *rows_i = part_rows + (size_t)i * 256 * kHeadDim;
 #pragma unroll
             for (int sub = 0; sub < 2; sub++) {
                 uint32_t pr[32];
-                rows_load_f32(pr, part_rows + half * 64 + sub * 32, kHeadDim, 32, stage_w, lane);
+                rows_load_f32(pr, rows_i + half * 64 + sub * 32, kHeadDim, 32, stage_w, lane);
 #pragma unroll
                 for (int e = 0; e < 32; e++)
-                    o[sub * 32 + e] = __float_as_uint(fmaf(__uint_as_float(pr[e]), f_other, __uint_as_float(o[sub * 32 + e])));
+                    o[sub * 32 + e] = __float_as_uint(fmaf(__uint_as_float(pr[e]), f_i, __uint_as_float(o[sub * 32 + e])));
             }
         }
         if (read_state) {
@@ -870,7 +966,6 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
             }
         }
     }
-    if (DEBUG && threadIdx.x == 0 && js == 0) stamp_ns(p, 5);
     /* The reads of O above are complete (each was waited for); the fence
      * orders them before the arrival that lets the next item's PV start. */
     tc_fence_before();
@@ -878,21 +973,23 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
 }
 
 /* The softmax warpgroup of query tile t, over the work items of this CTA. */
-template <bool DEBUG>
-__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, unsigned char *stage, uint32_t tmem, int t) {
+__device__ __forceinline__ void softmax_wg(const Ctx &c, const Params &p, unsigned char *stage, uint32_t tmem, int t,
+                                           const int *mail) {
     uint32_t cnt = 0;
-    for (int item = blockIdx.x, n = 0; item < p.items; item += gridDim.x, n++) {
+    for (int n = 0;; n++) {
+        const int item = sched_get(c, mail, n, 340 + t);
+        if (item < 0) return;
         const Item w = item_of(p, item);
         if (t >= w.ntq) continue;
-        if (!softmax_item<DEBUG>(c, p, stage, tmem, t, item, w, cnt, n == 0 ? 0 : (n == 1 ? 16 : 32))) return;
+        if (!softmax_item(c, p, stage, tmem, t, item, w, cnt)) return;
         cnt += (uint32_t)w.nj;
     }
 }
 
-template <bool DEBUG>
 __global__ void __launch_bounds__(kThreads, 1)
-k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk,
-                  const __grid_constant__ CUtensorMap tmv, const Params p) {
+k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmk0,
+                  const __grid_constant__ CUtensorMap tmv0, const __grid_constant__ CUtensorMap tmk1,
+                  const __grid_constant__ CUtensorMap tmv1, const __grid_constant__ Params p) {
     extern __shared__ unsigned char smem_raw[];
     /* The swizzled operand tiles need 1024-byte alignment. */
     const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -903,9 +1000,9 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     c.bars = smem + kSmemBar;
     c.abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemAbort);
     c.status = p.status;
+    c.wait_ns = p.wait_ns;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemTmemPtr);
-
-    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 0);
+    int *mail = reinterpret_cast<int *>(smem_gen + kSmemBar + kSmemSched);
 
     if (threadIdx.x == 0) {
         mbar_init(c.bars + BAR_Q_FULL * 8, 1);
@@ -918,6 +1015,8 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
             mbar_init(c.bars + (BAR_P_FULL + 2 * t) * 8, 128);
             mbar_init(c.bars + (BAR_P_FULL + 2 * t + 1) * 8, 128);
             mbar_init(c.bars + (BAR_O_DONE + t) * 8, 1);
+            mbar_init(c.bars + (BAR_SCHED_FULL + t) * 8, 1);
+            mbar_init(c.bars + (BAR_SCHED_EMPTY + t) * 8, kSchedConsumers);
         }
         mbar_init(c.bars + BAR_Q_EMPTY * 8, 1);
         mbar_init(c.bars + BAR_DRAIN * 8, 1);
@@ -935,25 +1034,38 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 1);
 
     if (warp < 8) {
         /* The third warpgroup hands most of its registers to the softmax ones. */
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-        softmax_wg<DEBUG>(c, p, smem_gen + kSmemStage, tmem, warp >> 2);
+        softmax_wg(c, p, smem_gen + kSmemStage, tmem, warp >> 2, mail);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsOther));
-        if (warp == 8 && lane == 0) producer(c, p, &tmq, &tmk, &tmv, smem);
-        if (warp == 9) mma_issuer<DEBUG>(c, p, smem, tmem);
+        if (warp == 8 && lane == 0) {
+            Maps m;
+            m.q = &tmq;
+            m.k[0] = &tmk0; m.v[0] = &tmv0;
+            m.k[1] = &tmk1; m.v[1] = &tmv1;
+            producer(c, p, m, smem, mail);
+        }
+        if (warp == 9) mma_issuer(c, p, smem, tmem, mail);
     }
 
     tc_fence_before();
     __syncthreads();
-    if (DEBUG && threadIdx.x == 0) stamp_ns(p, 7);
     if (warp == 9) {
         tc_fence_after();
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+    /* The last CTA through leaves the work-list counters at zero for the
+     * next launch (no CTA fetches after it has counted itself out). */
+    if (threadIdx.x == 0 && p.sched) {
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+            p.sched[0] = 0u;
+            p.sched[1] = 0u;
+        }
     }
 }
 
@@ -1060,184 +1172,335 @@ bool sm100_supported(const void *out, int ldo, const void *q, const void *k, con
            ldi % 8 == 0 && ldo % 2 == 0 && (bits & 15) == 0 && (ldo % 8 == 0 || ((uintptr_t)out & 3) == 0);
 }
 
-static uint32_t *g_mask_bits = NULL;
-static size_t g_mask_words = 0;
-
-/* Scratch of the key split, one per stream that launches split kernels
- * (launches on one stream run one after the other; those of different
- * streams, the head groups of the ring for instance, may overlap). */
-struct SplitScratch {
+/* Library-owned device memory a launch needs besides its operands: the
+ * work-list counters, the scratch of the key split and the packed key mask.
+ * One set per stream that launches (launches on one stream run one after the
+ * other; those of different streams may overlap, so they must not share).
+ * Sets are recycled least recently used; before a set changes hands the
+ * device is brought to rest. */
+struct StreamScratch {
     cudaStream_t stream;
     int in_use;
-    size_t blocks;                 /* query blocks it has room for */
+    unsigned long long used;
+    unsigned int *sched;           /* [16] words, two in use */
+    size_t part_blocks;            /* 256-row partials the split scratch has room for */
     float *o;
     float2 *ml;
+    size_t ticket_blocks;          /* query blocks the ticket array has room for */
     unsigned int *tickets;
+    uint32_t *mask_bits;
+    size_t mask_words;
 };
-static SplitScratch g_split[4];
+static const int kScratchSets = 8;
+static StreamScratch g_scratch[kScratchSets];
+static unsigned long long g_scratch_clock = 0;
 
-static void split_free(SplitScratch *sc) {
-    if (sc->o) cuda_ok(cudaFree(sc->o), "free");
-    if (sc->ml) cuda_ok(cudaFree(sc->ml), "free");
-    if (sc->tickets) cuda_ok(cudaFree(sc->tickets), "free");
-    sc->o = NULL;
-    sc->ml = NULL;
-    sc->tickets = NULL;
-    sc->blocks = 0;
+static void dev_free(void *p) {
+    if (p) cuda_ok(cudaFree(p), "free");
 }
 
-/* NULL when no scratch can be had: the caller then launches without split. */
-static SplitScratch *split_scratch(cudaStream_t stream, size_t blocks) {
-    SplitScratch *sc = NULL;
-    for (int i = 0; i < 4 && !sc; i++)
-        if (g_split[i].in_use && g_split[i].stream == stream) sc = &g_split[i];
-    for (int i = 0; i < 4 && !sc; i++)
-        if (!g_split[i].in_use) sc = &g_split[i];
-    if (!sc) return NULL;
-    if (sc->in_use && sc->blocks >= blocks) return sc;
-    if (sc->in_use) {
-        cuda_ok(cudaStreamSynchronize(stream), "sync");
-        split_free(sc);
+static void scratch_free(StreamScratch *sc) {
+    dev_free(sc->sched);
+    dev_free(sc->o);
+    dev_free(sc->ml);
+    dev_free(sc->tickets);
+    dev_free(sc->mask_bits);
+    memset(sc, 0, sizeof(*sc));
+}
+
+/* NULL when nothing can be allocated: the launch then runs with the static
+ * work list, without key split, and refuses key masks. */
+static StreamScratch *scratch_of(cudaStream_t stream) {
+    StreamScratch *sc = NULL, *lru = &g_scratch[0];
+    for (int i = 0; i < kScratchSets; i++) {
+        if (g_scratch[i].in_use && g_scratch[i].stream == stream) sc = &g_scratch[i];
+        if (!g_scratch[i].in_use) {
+            if (lru->in_use) lru = &g_scratch[i];
+        } else if (lru->in_use && g_scratch[i].used < lru->used) {
+            lru = &g_scratch[i];
+        }
     }
-    size_t cap = blocks < 64 ? 64 : blocks;
-    if (cudaMalloc((void **)&sc->o, cap * 256 * sm100::kHeadDim * sizeof(float)) != cudaSuccess ||
-        cudaMalloc((void **)&sc->ml, cap * 256 * sizeof(float2)) != cudaSuccess ||
-        cudaMalloc((void **)&sc->tickets, cap * 16 * sizeof(unsigned int)) != cudaSuccess ||
-        cudaMemset(sc->tickets, 0, cap * 16 * sizeof(unsigned int)) != cudaSuccess) {
-        (void)cudaGetLastError();
-        split_free(sc);
-        sc->in_use = 0;
-        return NULL;
+    if (!sc) {
+        sc = lru;
+        if (sc->in_use) {
+            /* Its last launches may still be running on a stream this code
+             * knows nothing about any more. */
+            cuda_ok(cudaDeviceSynchronize(), "sync");
+            scratch_free(sc);
+        }
+        if (cudaMalloc((void **)&sc->sched, 64) != cudaSuccess || cudaMemset(sc->sched, 0, 64) != cudaSuccess) {
+            (void)cudaGetLastError();
+            scratch_free(sc);
+            return NULL;
+        }
+        sc->in_use = 1;
+        sc->stream = stream;
     }
-    sc->in_use = 1;
-    sc->stream = stream;
-    sc->blocks = cap;
+    sc->used = ++g_scratch_clock;
     return sc;
 }
 
-/* acc_mode / o_acc / lse_acc: see sm100::Params. debug: bring-up dump. */
-int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k,
-                           const uint16_t *v, int ldkv, int seq_q, int seq_k, int heads, float scale,
-                           const int *key_mask, int acc_mode, float *o_acc, float *lse_acc,
-                           float *debug, const uint32_t *desc_override, int max_split) {
-    using namespace sm100;
-    const int diag_mode = desc_override ? (int)desc_override[3] : 0;
-    static int configured = 0;
-    if (!configured) {
-        if (!cuda_ok(cudaFuncSetAttribute(k_attention_sm100<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          kSmemBytes), "attention smem opt-in") ||
-            !cuda_ok(cudaFuncSetAttribute(k_attention_sm100<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          kSmemBytes), "attention smem opt-in"))
-            return IRIS_B200_ECUDA;
-        configured = 1;
+/* Room for the partials and tickets of `nq` query blocks cut in `nparts`. */
+static bool scratch_parts(StreamScratch *sc, size_t nq, int nparts) {
+    const size_t blocks = nq * (size_t)(nparts - 1);
+    if (blocks > sc->part_blocks || nq > sc->ticket_blocks) {
+        cuda_ok(cudaStreamSynchronize(sc->stream), "sync");
+        dev_free(sc->o);
+        dev_free(sc->ml);
+        dev_free(sc->tickets);
+        sc->o = NULL;
+        sc->ml = NULL;
+        sc->tickets = NULL;
+        sc->part_blocks = sc->ticket_blocks = 0;
+        const size_t cap = blocks < 64 ? 64 : blocks, tcap = nq < 64 ? 64 : nq;
+        if (cudaMalloc((void **)&sc->o, cap * 256 * sm100::kHeadDim * sizeof(float)) != cudaSuccess ||
+            cudaMalloc((void **)&sc->ml, cap * 256 * sizeof(float2)) != cudaSuccess ||
+            cudaMalloc((void **)&sc->tickets, tcap * 16 * sizeof(unsigned int)) != cudaSuccess ||
+            cudaMemset(sc->tickets, 0, tcap * 16 * sizeof(unsigned int)) != cudaSuccess) {
+            (void)cudaGetLastError();
+            dev_free(sc->o);
+            dev_free(sc->ml);
+            dev_free(sc->tickets);
+            sc->o = NULL;
+            sc->ml = NULL;
+            sc->tickets = NULL;
+            return false;
+        }
+        sc->part_blocks = cap;
+        sc->ticket_blocks = tcap;
     }
-    if (seq_k <= 0) {
-        if (acc_mode == 0) {
+    return true;
+}
+
+static bool scratch_mask(StreamScratch *sc, size_t words) {
+    if (words <= sc->mask_words) return true;
+    cuda_ok(cudaStreamSynchronize(sc->stream), "sync");
+    dev_free(sc->mask_bits);
+    sc->mask_bits = NULL;
+    sc->mask_words = 0;
+    const size_t cap = words < 1024 ? 1024 : words * 2;
+    if (cudaMalloc((void **)&sc->mask_bits, cap * 4) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    sc->mask_words = cap;
+    return true;
+}
+
+static unsigned long long g_wait_ns = 1000000000ull;    /* 1 s */
+static int g_inject_ticket = 0;                         /* host-side fault injection, one shot */
+static int g_configured = 0, g_sm_count = 0;
+
+void sm100_set_wait_limit_ns(unsigned long long ns) { g_wait_ns = ns ? ns : 1000000000ull; }
+void sm100_inject_stale_ticket(void) { g_inject_ticket = 1; }
+
+/* Number of key parts that shortens the schedule most, by a model in units
+ * of one key-tile iteration: the CTAs run ceil(items / CTAs) rounds of items
+ * that each cost their tiles plus a fixed part (pipeline fill, output or
+ * partial traffic, and the merge when there are parts). */
+static int choose_parts(int nq, int nkv, int sms, int max_parts) {
+    int best = 1;
+    double best_cost = 0.0;
+    for (int n = 1; n <= max_parts && n <= sm100::kMaxParts && (n == 1 || n <= nkv / 3); n++) {
+        const long long items = (long long)nq * n;
+        const long long ctas = items < sms ? items : sms;
+        const double rounds = (double)((items + ctas - 1) / ctas);
+        const double cost = rounds * ((double)nkv / n + 1.5 + (n > 1 ? 1.0 : 0.0));
+        if (n == 1 || cost < best_cost * 0.97) {
+            best = n;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
+AttnArgs attn_args(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k, const uint16_t *v,
+                   int ldkv, int seq_q, int seq_k, int heads, float scale, const int *key_mask) {
+    AttnArgs a = {};
+    a.out = out;
+    a.ldo = ldo;
+    a.q = q;
+    a.ldq = ldq;
+    a.seq_q = seq_q;
+    a.heads = heads;
+    a.scale = scale;
+    a.k[0] = k;
+    a.v[0] = v;
+    a.ldkv[0] = ldkv;
+    a.nsrc = seq_k > 0 ? 1 : 0;
+    a.src[0].view = 0;
+    a.src[0].row0 = 0;
+    a.src[0].rows = seq_k;
+    a.src[0].arrive = -1;
+    a.src[0].rows_per_word = 1;
+    a.key_mask = key_mask;
+    a.max_parts = AttnArgs::kMaxParts;
+    return a;
+}
+
+int launch_attention_sm100(const AttnArgs &a) {
+    using namespace sm100;
+    if (!g_configured) {
+        if (!cuda_ok(cudaFuncSetAttribute(k_attention_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                     "attention smem opt-in"))
+            return IRIS_B200_ECUDA;
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sm_count <= 0) {
+            (void)cudaGetLastError();
+            g_sm_count = 148;
+        }
+        g_configured = 1;
+    }
+    const int heads = a.heads, seq_q = a.seq_q;
+    if (a.nsrc <= 0) {
+        if (a.acc_mode == 0) {
             size_t n = (size_t)seq_q * heads * kHeadDim;
-            k_zero_rows<<<(unsigned)((n + 255) / 256), 256, 0, g.stream>>>(out, ldo, seq_q, heads * kHeadDim);
+            k_zero_rows<<<(unsigned)((n + 255) / 256), 256, 0, g.stream>>>(a.out, a.ldo, seq_q, heads * kHeadDim);
             return after_launch("attention (zero)") ? IRIS_B200_OK : IRIS_B200_ECUDA;
         }
         set_error(IRIS_B200_EINVAL, "attention", "empty key chunk");
         return IRIS_B200_EINVAL;
     }
     Params p = {};
-    int nkv = (seq_k + kTileK - 1) / kTileK;
-    if (key_mask) {
-        size_t words = (size_t)nkv * 4;
-        if (words > g_mask_words) {
-            if (g_mask_bits) {
-                cuda_ok(cudaStreamSynchronize(g.stream), "sync");
-                cuda_ok(cudaFree(g_mask_bits), "free");
-            }
-            g_mask_bits = NULL;
-            g_mask_words = 0;
-            size_t cap = words < 1024 ? 1024 : words * 2;
-            if (cudaMalloc((void **)&g_mask_bits, cap * 4) != cudaSuccess) {
-                (void)cudaGetLastError();
-                set_error(IRIS_B200_ENOMEM, "mask scratch", NULL);
-                return IRIS_B200_ENOMEM;
-            }
-            g_mask_words = cap;
-        }
-        k_pack_mask<<<(unsigned)((words + 127) / 128), 128, 0, g.stream>>>(g_mask_bits, key_mask, seq_k, (int)words);
-        if (!after_launch("attention (mask pack)")) return IRIS_B200_ECUDA;
-        p.mask_bits = g_mask_bits;
+    /* Sources -> tiles. */
+    if (a.nsrc > kMaxSources || (a.key_mask && a.nsrc != 1)) {
+        set_error(IRIS_B200_EINVAL, "attention", "too many key runs, or a key mask over more than one run");
+        return IRIS_B200_EINVAL;
     }
-    CUtensorMap tmq, tmk, tmv;
-    if (!make_map(&tmq, q, seq_q, heads * kHeadDim, ldq) || !make_map(&tmk, k, seq_k, heads * kHeadDim, ldkv) ||
-        !make_map(&tmv, v, seq_k, heads * kHeadDim, ldkv))
-        return IRIS_B200_ECUDA;
-    p.out = out;
-    p.ldo = ldo;
+    int view_rows[2] = {0, 0};
+    int nkv = 0;
+    for (int s = 0; s < a.nsrc; s++) {
+        const AttnArgs::Source &in = a.src[s];
+        if (in.rows <= 0 || in.row0 < 0 || in.view < 0 || in.view > 1 || !a.k[in.view] || !a.v[in.view] ||
+            (in.arrive >= 0 && (!a.arrive || in.rows_per_word <= 0 ||
+                                in.arrive + (in.rows - 1) / in.rows_per_word >= 32))) {
+            set_error(IRIS_B200_EINVAL, "attention", "bad key run");
+            return IRIS_B200_EINVAL;
+        }
+        KeySource &ks = p.src[s];
+        ks.tile0 = nkv;
+        ks.row0 = in.row0;
+        ks.rows = in.rows;
+        ks.view = in.view;
+        ks.arrive = in.arrive;
+        ks.rows_per_word = in.arrive >= 0 ? in.rows_per_word : 1;
+        nkv += (in.rows + kTileK - 1) / kTileK;
+        if (in.row0 + in.rows > view_rows[in.view]) view_rows[in.view] = in.row0 + in.rows;
+    }
+    p.nsrc = a.nsrc;
+    p.nkv = nkv;
+    p.arrive = a.arrive;
+    p.arrive_seq = a.arrive_seq;
+
+    StreamScratch *sc = a.no_scratch ? NULL : scratch_of(g.stream);
+    if (a.key_mask) {
+        const size_t words = (size_t)nkv * 4;
+        if (!sc || !scratch_mask(sc, words)) {
+            set_error(IRIS_B200_ENOMEM, "mask scratch", NULL);
+            return IRIS_B200_ENOMEM;
+        }
+        k_pack_mask<<<(unsigned)((words + 127) / 128), 128, 0, g.stream>>>(sc->mask_bits, a.key_mask, a.src[0].rows,
+                                                                           (int)words);
+        if (!after_launch("attention (mask pack)")) return IRIS_B200_ECUDA;
+        p.mask_bits = sc->mask_bits;
+    }
+    CUtensorMap tmq, tmk[2] = {}, tmv[2] = {};
+    const int width = heads * kHeadDim;
+    if (!make_map(&tmq, a.q, seq_q, width, a.ldq)) return IRIS_B200_ECUDA;
+    for (int vw = 0; vw < 2; vw++) {
+        if (view_rows[vw] == 0) {
+            tmk[vw] = tmk[0];           /* never dereferenced */
+            tmv[vw] = tmv[0];
+        } else if (!make_map(&tmk[vw], a.k[vw], view_rows[vw], width, a.ldkv[vw]) ||
+                   !make_map(&tmv[vw], a.v[vw], view_rows[vw], width, a.ldkv[vw])) {
+            return IRIS_B200_ECUDA;
+        }
+    }
+    p.out = a.out;
+    p.ldo = a.ldo;
     p.seq_q = seq_q;
-    p.seq_k = seq_k;
     p.heads = heads;
     p.nqblk = (seq_q + 2 * kTileQ - 1) / (2 * kTileQ);
-    p.items = p.nqblk * heads;
-    p.nkv = nkv;
-    p.nsplit = 1;
-    p.scale_log2 = scale * 1.4426950408889634f;
+    p.nq = p.nqblk * heads;
+    p.scale_log2 = a.scale * 1.4426950408889634f;
     p.status = g.dev_status;
-    p.o_acc = o_acc;
-    p.lse_acc = lse_acc;
-    p.acc_mode = acc_mode;
-    p.qk_sbo = desc_override ? desc_override[0] : 1024 / 16;        /* 8 rows of 128 B */
-    p.v_lbo = desc_override ? desc_override[1] : kHalfBytes / 16;   /* next 64-dim half */
-    p.v_sbo = desc_override ? desc_override[2] : 1024 / 16;         /* next 8 keys */
-    p.debug = debug;
-    p.diag_mode = diag_mode;
-    /* One CTA per SM at most (shared and tensor memory allow no more); each
-     * walks its share of the work items. */
-    static int sm_count = 0;
-    if (!sm_count) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0) {
-            (void)cudaGetLastError();
-            sm_count = 148;
+    p.wait_ns = g_wait_ns;
+    p.o_acc = a.o_acc;
+    p.lse_acc = a.lse_acc;
+    p.acc_mode = a.acc_mode;
+    p.sched = sc ? sc->sched : NULL;
+
+    /* Key parts: the caller's (boundaries given as key rows, moved down to a
+     * tile boundary) or the model's (equal numbers of tiles); none without
+     * scratch to merge through. */
+    int nparts = 1;
+    if (sc && a.nparts > 1)
+        nparts = a.nparts > kMaxParts ? kMaxParts : a.nparts;
+    else if (sc && a.max_parts > 1)
+        nparts = choose_parts(p.nq, nkv, g_sm_count, a.max_parts);
+    if (nparts > 1 && !scratch_parts(sc, (size_t)p.nq, nparts)) nparts = 1;
+    p.nparts = nparts;
+    for (int i = 0; i <= nparts; i++) {
+        if (a.nparts > 1 && nparts > 1 && i < nparts) {
+            long long row = a.part_row[i], before = 0;
+            int tile = nkv;
+            for (int sidx = 0; sidx < a.nsrc; sidx++) {
+                if (row < before + a.src[sidx].rows) {
+                    tile = p.src[sidx].tile0 + (int)((row - before) / kTileK);
+                    break;
+                }
+                before += a.src[sidx].rows;
+            }
+            p.part_tile[i] = tile;
+        } else {
+            p.part_tile[i] = (int)((long long)nkv * i / nparts);
         }
     }
-    /* Split the keys in two when that shortens the schedule: the CTAs then
-     * run ceil(2 * items / SMs) rounds of half the length. */
-    static int split_off = -1;              /* IRIS_B200_NO_SPLIT=1 turns the key split off (tuning aid) */
-    if (split_off < 0) {
-        const char *env = getenv("IRIS_B200_NO_SPLIT");
-        split_off = env && env[0] == '1';
-    }
-    if (max_split >= 2 && nkv >= 4 && !debug && !split_off) {
-        const int rounds1 = (p.items + sm_count - 1) / sm_count, rounds2 = (2 * p.items + sm_count - 1) / sm_count;
-        SplitScratch *sc = rounds2 < 2 * rounds1 ? split_scratch(g.stream, (size_t)p.items) : NULL;
-        if (sc) {
-            p.nsplit = 2;
-            p.items *= 2;
-            p.part_o = sc->o;
-            p.part_ml = sc->ml;
-            p.tickets = sc->tickets;
+    p.part_tile[0] = 0;
+    for (int i = 0; i < nparts; i++) {
+        if (p.part_tile[i + 1] <= p.part_tile[i]) {
+            set_error(IRIS_B200_EINVAL, "attention", "empty key part");
+            return IRIS_B200_EINVAL;
         }
     }
-    unsigned grid = (unsigned)(p.items < sm_count ? p.items : sm_count);
-    if (debug)
-        k_attention_sm100<true><<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk, tmv, p);
-    else
-        k_attention_sm100<false><<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk, tmv, p);
+    if (nparts > 1) {
+        p.part_o = sc->o;
+        p.part_ml = sc->ml;
+        p.tickets = sc->tickets;
+        if (g_inject_ticket) {
+            /* Fault injection (tests): an arrival nobody made. Every part of
+             * query block 0 then believes it is the last and waits for
+             * partials that never come, until the wait limit ends the launch. */
+            g_inject_ticket = 0;
+            cuda_ok(cudaMemsetAsync(sc->tickets, 1, 1, g.stream), "ticket injection");
+        }
+    }
+    p.items = p.nq * nparts;
+    /* One CTA per SM at most (shared and tensor memory allow no more). */
+    unsigned grid = (unsigned)(p.items < g_sm_count ? p.items : g_sm_count);
+    k_attention_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk[0], tmv[0], tmk[1], tmv[1], p);
     return after_launch("attention (tcgen05)") ? IRIS_B200_OK : IRIS_B200_ECUDA;
 }
 
+/* After a launch gave up on a wait: tickets and work-list counters may be
+ * left half used. */
 void sm100_reset_split(void) {
     cuda_ok(cudaDeviceSynchronize(), "sync");
-    for (int i = 0; i < 4; i++)
-        if (g_split[i].in_use && g_split[i].tickets)
-            cuda_ok(cudaMemset(g_split[i].tickets, 0, g_split[i].blocks * 16 * sizeof(unsigned int)), "ticket clear");
+    for (int i = 0; i < kScratchSets; i++) {
+        StreamScratch *sc = &g_scratch[i];
+        if (!sc->in_use) continue;
+        if (sc->tickets) cuda_ok(cudaMemset(sc->tickets, 0, sc->ticket_blocks * 16 * sizeof(unsigned int)), "ticket clear");
+        if (sc->sched) cuda_ok(cudaMemset(sc->sched, 0, 64), "work list clear");
+    }
 }
 
 void sm100_release(void) {
-    for (int i = 0; i < 4; i++) {
-        split_free(&g_split[i]);
-        g_split[i].in_use = 0;
-    }
-    if (g_mask_bits) cuda_ok(cudaFree(g_mask_bits), "free");
-    g_mask_bits = NULL;
-    g_mask_words = 0;
+    for (int i = 0; i < kScratchSets; i++)
+        if (g_scratch[i].in_use) scratch_free(&g_scratch[i]);
+    memset(g_maps, 0, sizeof(g_maps));
+    g_configured = 0;              /* the next device needs its own opt-in */
+    g_sm_count = 0;
 }
 
 }  // namespace iris_b200

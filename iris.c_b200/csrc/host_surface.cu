@@ -175,6 +175,10 @@ void iris_softmax(float *x, int rows, int cols) {
     iris_dev_download(x, d, bytes);
 }
 
+/* The reference exports the same routine under a second name that its BLAS
+ * attention variants call (iris_kernels.h:159). */
+void iris_softmax_cpu(float *x, int rows, int cols) { iris_softmax(x, rows, cols); }
+
 void iris_apply_rope(float *x, const float *freqs, int batch, int seq, int heads, int head_dim) {
     if (!require_device("iris_apply_rope") || batch <= 0 || seq <= 0 || heads <= 0 || head_dim <= 0) return;
     size_t n = (size_t)batch * seq * heads * head_dim, nf = (size_t)seq * head_dim;

@@ -12,14 +12,60 @@ int launch_attention_generic(uint16_t *out, int ldo, const uint16_t *q, const ui
 bool sm100_supported(const void *out, int ldo, const void *q, const void *k, const void *v, int ldi,
                      int heads, int kv_heads, int head_dim, int causal, float scale);
 
-int launch_attention_sm100(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k,
-                           const uint16_t *v, int ldkv, int seq_q, int seq_k, int heads, float scale,
-                           const int *key_mask, int acc_mode, float *o_acc, float *lse_acc,
-                           float *debug, const uint32_t *desc_override, int max_split = 2);
+/* One launch of the tcgen05 attention kernel. The keys are a sequence of
+ * runs of rows taken from up to two K/V buffers ("views"); a run may be
+ * guarded by arrival words that the kernel waits for before it loads the
+ * run's rows. */
+struct AttnArgs {
+    enum { kMaxSources = 16, kMaxParts = 8 };
+    uint16_t *out;
+    int ldo;
+    const uint16_t *q;
+    int ldq, seq_q, heads;
+    float scale;
+    const uint16_t *k[2], *v[2];        /* view 0 / 1 */
+    int ldkv[2];
+    int nsrc;
+    struct Source {
+        int view, row0, rows;
+        int arrive;                     /* first arrival word of the run, -1: none */
+        int rows_per_word;              /* rows per arrival word */
+    } src[kMaxSources];
+    const uint32_t *arrive;             /* device words; arrived when (int)(word - arrive_seq) >= 0 */
+    uint32_t arrive_seq;
+    const int *key_mask;                /* single run only */
+    int acc_mode;                       /* 0 plain; 1 / 2 / 3: first / middle / last chunk of a carried state */
+    float *o_acc, *lse_acc;
+    int max_parts;                      /* 1: never split the keys of a query block */
+    int nparts;                         /* > 1: exactly these parts; part i starts at key row part_row[i],
+                                           counted over the runs in order (moved down to a tile boundary) */
+    long long part_row[kMaxParts + 1];
+    bool no_scratch;                    /* use no library scratch: static work list, no key split, no mask */
+};
+
+/* Arguments of the plain case: one run of seq_k rows, split chosen by the library. */
+AttnArgs attn_args(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k, const uint16_t *v,
+                   int ldkv, int seq_q, int seq_k, int heads, float scale, const int *key_mask);
+
+int launch_attention_sm100(const AttnArgs &a);
 
 void sm100_release(void);
 
-/* Clears the arrival words of the key-split scratch (after a device wait timed out). */
+/* Clears the tickets and work-list counters (after a device wait timed out). */
 void sm100_reset_split(void);
+
+/* Limit of every wait inside the kernel (0 restores the default of 1 s). */
+void sm100_set_wait_limit_ns(unsigned long long ns);
+
+/* Host-side fault injection: the next launch that splits its keys finds a
+ * ticket that nobody took. */
+void sm100_inject_stale_ticket(void);
+
+/* A device wait ran out: a ring that was in use cannot go on (multi_gpu.cu). */
+void ring_mark_failed(void);
+
+/* Shared argument checks of the device-pointer attention entry points. */
+int check_attention_args(const char *op, const void *out, const void *q, const void *k, const void *v, int ldo,
+                         int ldq, int ldkv, int seq_q, int seq_k, int heads, int kv_heads, int head_dim);
 
 }  // namespace iris_b200

@@ -6,11 +6,15 @@
  *  - chunked attention: one launch sees a chunk of the keys and merges its
  *    result into a carried state (normalised fp32 output + log2-sum-exp per
  *    row), the building block of split-K and of the ring;
- *  - ring sequence parallelism: every rank keeps its query rows and walks the
- *    K/V chunks of the other ranks in ring order; the chunks arrive through
- *    NCCL send/recv on a second stream while the attention of earlier chunks
- *    runs. A received chunk lands in this GPU's own memory and is read from
- *    there by ordinary TMA loads.
+ *  - attention over key runs: the keys of one launch are runs of rows taken
+ *    from two buffers, each run optionally guarded by an arrival word that the
+ *    kernel waits for (bounded) before it loads the run's rows;
+ *  - ring sequence parallelism: every rank keeps its query rows; the K/V rows
+ *    of the other ranks are pushed into this GPU's slot pool by their owners'
+ *    copy engines while ONE attention launch works through the runs (own
+ *    rows, then the slots in ring order) as they arrive. A received chunk
+ *    lies in this GPU's own memory before a TMA load reads it. NCCL carries
+ *    the set-up exchanges and is the fallback transport.
  *
  * The reference has no multi-GPU code (iris_cuda.cu:122 always uses device
  * 0); these entry points are additions with no counterpart there.
@@ -24,10 +28,19 @@
 #include <dlfcn.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
+#include <unistd.h>
 
 #include "kernels.h"
 
 using namespace iris_b200;
+
+static unsigned long long host_now_ns(void) {
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (unsigned long long)ts.tv_sec * 1000000000ull + (unsigned long long)ts.tv_nsec;
+}
+static void host_pause(void) { usleep(20); }
 
 /* ------------------------------------------------------------------------
  * Index arithmetic (no device needed)
@@ -69,20 +82,18 @@ extern "C" int iris_b200_ring_source(int rank, int step, int nranks) {
     return ((rank - step) % nranks + nranks) % nranks;
 }
 
-extern "C" int iris_b200_ring_plan(int nranks, int even_rows, int *first_step, int *step_count) {
+extern "C" int iris_b200_ring_plan(int nranks, int max_parts, int *first_step, int *step_count) {
     if (nranks <= 0 || !first_step || !step_count) return -1;
-    /* With many ranks a step is a small problem whose fixed costs (pipeline
-     * fill, state traffic) weigh: from step 2 on, two steps share a launch
-     * when their chunks have the same size (their slots are then adjacent
-     * rows of one buffer). Steps 0 and 1 stay alone: 0 needs no transfer and
-     * 1 is the first to arrive. */
-    const int pair_from = (even_rows && nranks >= 6) ? 2 : nranks;
-    int n = 0;
-    for (int s = 0; s < nranks; n++) {
-        const int c = (s >= pair_from && s + 1 < nranks) ? 2 : 1;
-        first_step[n] = s;
-        step_count[n] = c;
-        s += c;
+    /* The ring steps of a call are grouped into key parts of the one
+     * attention launch: part i covers the steps [first_step[i], first_step[i]
+     * + step_count[i]). Parts are what the work list is ordered by, so the
+     * chunks that arrive first are worked on first; more than four parts buy
+     * nothing (every part costs a partial result per query block). */
+    int n = nranks < 4 ? nranks : 4;
+    if (max_parts > 0 && n > max_parts) n = max_parts;
+    for (int i = 0; i < n; i++) {
+        first_step[i] = (int)((long long)nranks * i / n);
+        step_count[i] = (int)((long long)nranks * (i + 1) / n) - first_step[i];
     }
     return n;
 }
@@ -91,18 +102,18 @@ extern "C" int iris_b200_ring_plan(int nranks, int even_rows, int *first_step, i
  * Chunked attention with carried state
  * ------------------------------------------------------------------------ */
 
-/* max_split: 2 lets a launch that fills the SMs badly split its keys in two. */
 static int attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq,
                            const uint16_t *k, const uint16_t *v, int ldkv,
                            int seq_q, int seq_k, int heads, float scale,
                            const int *key_mask, float *o_state, float *lse_state,
-                           int first, int last, int max_split) {
+                           int first, int last) {
     if (!require_device("attention_chunk")) return IRIS_B200_ENODEV;
-    if (!q || !k || !v || seq_q < 0 || seq_k <= 0 || heads <= 0 || (last && !out) ||
-        (!(first && last) && (!o_state || !lse_state))) {
+    if (seq_k <= 0 || (last && !out) || (!(first && last) && (!o_state || !lse_state))) {
         set_error(IRIS_B200_EINVAL, "attention_chunk", "bad argument");
         return IRIS_B200_EINVAL;
     }
+    int rc = check_attention_args("attention_chunk", out, q, k, v, ldo, ldq, ldkv, seq_q, seq_k, heads, heads, 128);
+    if (rc != IRIS_B200_OK) return rc;
     const void *o = out ? (const void *)out : (const void *)q;
     if (!sm100_supported(o, out ? ldo : 8, q, k, v, ldkv, heads, heads, 128, 0, scale) || ldq % 8 != 0 ||
         ((uintptr_t)o_state & 15) != 0) {
@@ -110,9 +121,11 @@ static int attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq,
         return IRIS_B200_EUNSUPPORTED;
     }
     if (seq_q == 0) return IRIS_B200_OK;
-    int mode = first ? (last ? 0 : 1) : (last ? 3 : 2);
-    return launch_attention_sm100(out, ldo, q, ldq, k, v, ldkv, seq_q, seq_k, heads, scale, key_mask, mode,
-                                  o_state, lse_state, NULL, NULL, max_split);
+    AttnArgs a = attn_args(out, ldo, q, ldq, k, v, ldkv, seq_q, seq_k, heads, scale, key_mask);
+    a.acc_mode = first ? (last ? 0 : 1) : (last ? 3 : 2);
+    a.o_acc = o_state;
+    a.lse_acc = lse_state;
+    return launch_attention_sm100(a);
 }
 
 extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq,
@@ -121,29 +134,117 @@ extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t 
                                          const int *key_mask, float *o_state, float *lse_state,
                                          int first, int last) {
     return attention_chunk(out, ldo, q, ldq, k, v, ldkv, seq_q, seq_k, heads, scale, key_mask, o_state, lse_state,
-                           first, last, 2);
+                           first, last);
+}
+
+/* ------------------------------------------------------------------------
+ * Attention over key runs
+ * ------------------------------------------------------------------------ */
+
+extern "C" int iris_b200_attention_runs(uint16_t *out, int ldo, const uint16_t *q, int ldq,
+                                        int seq_q, int heads, float scale,
+                                        const uint16_t *k0, const uint16_t *v0, int ld0,
+                                        const uint16_t *k1, const uint16_t *v1, int ld1,
+                                        const iris_b200_key_run *runs, int nruns,
+                                        const uint32_t *arrive_words, uint32_t arrive_value, int nparts) {
+    if (!require_device("attention_runs")) return IRIS_B200_ENODEV;
+    if (!out || !q || !runs || nruns <= 0 || nruns > AttnArgs::kMaxSources || seq_q < 0 || heads <= 0 ||
+        nparts < 0 || nparts > AttnArgs::kMaxParts) {
+        set_error(IRIS_B200_EINVAL, "attention_runs", "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    AttnArgs a = {};
+    a.out = out;
+    a.ldo = ldo;
+    a.q = q;
+    a.ldq = ldq;
+    a.seq_q = seq_q;
+    a.heads = heads;
+    a.scale = scale;
+    a.k[0] = k0; a.v[0] = v0; a.ldkv[0] = ld0;
+    a.k[1] = k1; a.v[1] = v1; a.ldkv[1] = ld1;
+    a.nsrc = nruns;
+    a.arrive = arrive_words;
+    a.arrive_seq = arrive_value;
+    a.max_parts = AttnArgs::kMaxParts;
+    long long total = 0;
+    for (int i = 0; i < nruns; i++) {
+        const iris_b200_key_run &r = runs[i];
+        const uint16_t *kb = r.view == 0 ? k0 : k1, *vb = r.view == 0 ? v0 : v1;
+        const int ld = r.view == 0 ? ld0 : ld1;
+        if ((r.view != 0 && r.view != 1) || r.rows <= 0 || r.row0 < 0 || (r.arrive >= 0 && !arrive_words) ||
+            check_attention_args("attention_runs", out, q, kb, vb, ldo, ldq, ld, seq_q, r.rows, heads, heads, 128) !=
+                IRIS_B200_OK) {
+            set_error(IRIS_B200_EINVAL, "attention_runs", "bad key run");
+            return IRIS_B200_EINVAL;
+        }
+        if (!sm100_supported(out, ldo, q, kb, vb, ld, heads, heads, 128, 0, scale) || ldq % 8 != 0) {
+            set_error(IRIS_B200_EUNSUPPORTED, "attention_runs", "arguments outside the tcgen05 kernel's domain");
+            return IRIS_B200_EUNSUPPORTED;
+        }
+        a.src[i].view = r.view;
+        a.src[i].row0 = r.row0;
+        a.src[i].rows = r.rows;
+        a.src[i].arrive = r.arrive;
+        a.src[i].rows_per_word = r.rows;
+        total += r.rows;
+    }
+    if (nparts > 1) {
+        /* Parts of whole runs, as even in rows as the runs allow: a cut
+         * before run i once the rows so far reach the part's share, or when
+         * only as many runs are left as parts. */
+        if (nparts > nruns) nparts = nruns;
+        long long before = 0;
+        int part = 1;
+        a.part_row[0] = 0;
+        for (int i = 1; i < nruns && part < nparts; i++) {
+            before += runs[i - 1].rows;
+            if (before * nparts >= total * part || nruns - i <= nparts - part) a.part_row[part++] = before;
+        }
+        a.nparts = part;
+    } else if (nparts == 1) {
+        a.max_parts = 1;
+    }
+    if (seq_q == 0) return IRIS_B200_OK;
+    return launch_attention_sm100(a);
+}
+
+extern "C" int iris_b200_set_wait_limit_us(unsigned int us) {
+    sm100_set_wait_limit_ns((unsigned long long)us * 1000ull);
+    return IRIS_B200_OK;
+}
+
+extern "C" int iris_b200_inject_fault(int what) {
+    if (what != IRIS_B200_FAULT_STALE_TICKET) return IRIS_B200_EINVAL;
+    sm100_inject_stale_ticket();
+    return IRIS_B200_OK;
 }
 
 /* ------------------------------------------------------------------------
  * Ring sequence parallelism
  *
- * Rank r holds the query rows and the K / V rows of its token block. Step s
- * (s = 0 .. G-1) computes the attention of the local queries against the
- * chunk of rank (r - s) mod G and merges it into the carried state. The
- * chunk of step s is sent by its owner directly: at step s every rank sends
- * its own chunk to rank r + s and receives from rank r - s (NVSwitch gives
- * every pair full bandwidth, so nothing is relayed and no transfer waits
- * for a computation). All transfers are queued on a communication stream
- * when the call starts. Transport: the copy engines push the rows from the
- * caller's buffers into the consumer's slot (pools mapped through CUDA IPC)
- * and then write the call's sequence number into its arrival word, on
- * which the consumer's streams wait; NCCL send / recv with events when that
- * cannot be set up. NCCL also carries the set-up exchanges. A received
- * chunk lies in this GPU's memory before a kernel reads it.
+ * Rank r holds the query rows and the K / V rows of its token block. The
+ * chunk of step s (s = 0 .. G-1) is that of rank (r - s) mod G; its owner
+ * sends it directly: at step s every rank sends its own rows to rank r + s
+ * (NVSwitch gives every pair full bandwidth, so nothing is relayed and no
+ * transfer waits for a computation). All transfers are queued on a
+ * communication stream, in step order, when the call starts. Transport: the
+ * copy engines push the rows from the caller's buffers into the consumer's
+ * slot s (pools mapped through CUDA IPC) and then write the call's sequence
+ * number into its arrival word s. No SM is spent on communication.
  *
- * The heads are processed as two independent halves on two streams: a ring
- * step is a small problem (its CTAs fill the SMs about one and a half times),
- * and the CTAs of one half fill the SMs the tail of the other leaves idle.
+ * The attention of a call is ONE launch whose keys are the runs "own rows,
+ * slot 1, ..., slot G-1". The kernel's producer warps wait (bounded) for the
+ * arrival word of a slot before its first load, the work list is ordered by
+ * groups of steps, and the groups of a query block are merged inside the
+ * launch: no per-step launches, no carried state in memory, and a chunk that
+ * is late holds up only the CTAs that have nothing else left to do.
+ *
+ * When the pools cannot be mapped (no peer access), NCCL send / recv moves the
+ * chunks instead. NCCL's kernels need SMs, which the persistent attention
+ * launch does not give back while it waits, so in that mode all chunks are
+ * received first and the attention launch follows on the stream: correct,
+ * without overlap.
  * ------------------------------------------------------------------------ */
 
 namespace {
@@ -157,9 +258,10 @@ typedef int (*FnSendRecv)(void *, size_t, int, int, NcclComm, cudaStream_t);
 typedef int (*FnGroup)(void);
 typedef const char *(*FnErrStr)(int);
 typedef int (*FnAllGather)(const void *, void *, size_t, int, NcclComm, cudaStream_t);
+typedef int (*FnAsyncError)(NcclComm, int *);
 typedef CUresult (*FnStreamValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
 
-enum { kMaxRanks = 16, kHeadGroups = 2 };
+enum { kMaxRanks = 16 };
 
 struct Ring {
     void *dl;
@@ -170,33 +272,32 @@ struct Ring {
     FnGroup group_start, group_end;
     FnErrStr err_str;
     FnAllGather all_gather;
+    FnAsyncError async_error;
     NcclComm comm;
     int rank, nranks;
-    cudaStream_t comm_stream, aux_stream;
-    cudaEvent_t received[kMaxRanks], packed, comm_done, join;
-    void *buf[kMaxRanks];                 /* [0] local chunk, [s] chunk of step s */
-    size_t buf_bytes[kMaxRanks];
-    float *o_state[kHeadGroups], *lse_state[kHeadGroups];
-    size_t o_bytes[kHeadGroups], lse_bytes[kHeadGroups];
-    /* Copy-engine transport: chunks are pushed into the peers' slot pools
-     * (mapped through CUDA IPC) by cudaMemcpyAsync, flow-controlled by
-     * sequence numbers in device memory that streams wait on. */
-    int ce;                               /* 0 not set up, 1 in use, -1 unavailable (NCCL send/recv instead) */
-    FnStreamValue32 wait32, write32;
-    char *pool;                           /* two sets (call parity) of nranks slots of slot_bytes: [s] step s */
+    int failed;                           /* a call failed half way: the ring is unusable until destroy + init */
+    int parts;                            /* key parts of the attention launch, 0: chosen from the rank count */
+    cudaStream_t comm_stream;
+    cudaEvent_t packed, comm_done;
+    /* Slot pool: two sets (used by alternate calls) of nranks slots of
+     * slot_rows rows of K | V; slot s of a set receives the chunk of step s
+     * (slot 0 holds the packed own rows in the NCCL mode). */
+    char *pool;
     size_t slot_bytes;
-    uint32_t *flags;                      /* arrive[kMaxRanks] | unused[kMaxRanks] | seq_words[8] */
+    int ce;                               /* 0 not decided, 1 copy engines + IPC, -1 NCCL send/recv */
+    FnStreamValue32 write32;
+    uint32_t *flags;                      /* arrive[kMaxRanks] | seq_words[8] */
     char *peer_pool[kMaxRanks];
     uint32_t *peer_flags[kMaxRanks];
     void *xchg;                           /* device staging of the handle exchange */
     uint32_t seq;
-    /* IRIS_B200_RING_TRACE=1: device timeline of the last call, printed by ring_destroy() */
-    int trace;                            /* -1 off, 1 on, 0 not looked up yet */
-    cudaEvent_t t_start, t_push[kMaxRanks], t_step[kMaxRanks][2];
-    int t_steps, t_pushes;
+    /* Timeline of the last call (iris_b200_ring_trace) */
+    int trace;
+    cudaEvent_t t_start, t_push[kMaxRanks], t_kernel[2];
+    int t_pushes;
 } ring = {};
 
-enum { kFlagArrive = 0, kFlagSeq = 2 * kMaxRanks, kFlagWords = 2 * kMaxRanks + 8 };
+enum { kFlagArrive = 0, kFlagSeq = kMaxRanks, kFlagWords = kMaxRanks + 8 };
 
 bool nccl_load(void) {
     if (ring.dl) return true;
@@ -215,8 +316,9 @@ bool nccl_load(void) {
     ring.group_end = (FnGroup)dlsym(ring.dl, "ncclGroupEnd");
     ring.err_str = (FnErrStr)dlsym(ring.dl, "ncclGetErrorString");
     ring.all_gather = (FnAllGather)dlsym(ring.dl, "ncclAllGather");
+    ring.async_error = (FnAsyncError)dlsym(ring.dl, "ncclCommGetAsyncError");
     if (!ring.get_id || !ring.init_rank || !ring.destroy || !ring.send || !ring.recv || !ring.group_start ||
-        !ring.group_end) {
+        !ring.group_end || !ring.all_gather) {
         set_error(IRIS_B200_ECOMM, "dlsym nccl", "symbol missing");
         return false;
     }
@@ -229,34 +331,28 @@ bool nccl_ok(int rc, const char *what) {
     return false;
 }
 
-bool grow(void **p, size_t *have, size_t need) {
-    if (need <= *have) return true;
-    if (*p) {
-        cuda_ok(cudaDeviceSynchronize(), "sync");
-        cuda_ok(cudaFree(*p), "free");
+/* Waits for the library's stream while watching the communicator: an NCCL
+ * collective whose peer never joins does not return by itself, but the
+ * communicator reports an asynchronous error (or the deadline passes) and
+ * the caller gets IRIS_B200_ECOMM instead of a hang on the host. */
+bool nccl_wait(cudaStream_t st, double deadline_s, const char *what) {
+    cudaEvent_t ev = ring.comm_done;
+    if (!cuda_ok(cudaEventRecord(ev, st), "event record")) return false;
+    const unsigned long long t0 = host_now_ns();
+    for (;;) {
+        cudaError_t e = cudaEventQuery(ev);
+        if (e == cudaSuccess) return true;
+        if (e != cudaErrorNotReady) return cuda_ok(e, what);
+        int async = 0;
+        if (ring.async_error && ring.async_error(ring.comm, &async) == 0 && async != 0)
+            return nccl_ok(async, what);
+        if ((double)(host_now_ns() - t0) * 1e-9 > deadline_s) {
+            set_error(IRIS_B200_ECOMM, what, "collective did not finish before the deadline");
+            return false;
+        }
+        host_pause();
     }
-    *p = NULL;
-    *have = 0;
-    if (cudaMalloc(p, need) != cudaSuccess) {
-        (void)cudaGetLastError();
-        set_error(IRIS_B200_ENOMEM, "ring buffers", NULL);
-        return false;
-    }
-    *have = need;
-    return true;
 }
-
-/* Launches of the library go to g.stream; this redirects them for a scope. */
-struct StreamScope {
-    cudaStream_t saved;
-    explicit StreamScope(cudaStream_t s) : saved(g.stream) { g.stream = s; }
-    ~StreamScope() { g.stream = saved; }
-};
-
-}  // namespace
-
-
-namespace {
 
 struct IpcPair {
     cudaIpcMemHandle_t pool, flags;
@@ -273,54 +369,51 @@ void ce_close_peers(void) {
     (void)cudaGetLastError();
 }
 
-void ce_free_pool(void) {
-    if (ring.pool) cuda_ok(cudaFree(ring.pool), "free");
-    ring.pool = NULL;
-    ring.slot_bytes = 0;
-}
-
-/* All ranks have reached this point (an all-gather of a few bytes). */
-bool ce_barrier(void) {
-    if (!ring.xchg || !ring.all_gather) return false;
+/* All-gather of one word per rank (the set-up barrier and the vote on the
+ * transport). all[r] receives rank r's word. */
+bool exchange_word(uint32_t mine, uint32_t *all) {
     char *dev = (char *)ring.xchg;
-    return nccl_ok(ring.all_gather(dev + sizeof(IpcPair) * kMaxRanks, dev, 4, 1, ring.comm, g.stream), "ncclAllGather") &&
-           cuda_ok(cudaStreamSynchronize(g.stream), "sync");
+    uint32_t *send = (uint32_t *)(dev + sizeof(IpcPair) * (kMaxRanks + 1)), *recv = send + 1;
+    return cuda_ok(cudaMemcpyAsync(send, &mine, 4, cudaMemcpyHostToDevice, g.stream), "memcpy") &&
+           nccl_ok(ring.all_gather(send, recv, 4, 1, ring.comm, g.stream), "ncclAllGather") &&
+           nccl_wait(g.stream, 30.0, "ncclAllGather") &&
+           cuda_ok(cudaMemcpy(all, recv, 4 * ring.nranks, cudaMemcpyDeviceToHost), "memcpy");
+}
+bool ring_barrier(void) {
+    uint32_t all[kMaxRanks];
+    return exchange_word(1u, all);
 }
 
 /* Collective: every rank calls it with the same slot size. Allocates (or
- * grows) the slot pool, exchanges the IPC handles through an NCCL all-gather
- * and maps the peers' pools and flag words. Returns false, with the NCCL
- * send/recv transport selected, when anything on the way is unavailable. */
-bool ce_setup(size_t slot_bytes) {
-    if (ring.ce < 0) return false;
-    if (ring.ce == 1 && slot_bytes <= ring.slot_bytes) return true;
-    const char *env = getenv("IRIS_B200_RING_TRANSPORT");
+ * grows) the slot pool and, for the copy-engine transport, exchanges the IPC
+ * handles through an NCCL all-gather and maps the peers' pools and arrival
+ * words. The ranks then vote: one rank that could not map a peer puts every
+ * rank on the NCCL transport, so nobody waits for a push that never comes.
+ * Returns false only when the pool itself cannot be had. */
+bool ring_pool(size_t slot_bytes) {
     const int G = ring.nranks;
-    bool want = !(env && strcmp(env, "nccl") == 0) && ring.all_gather != NULL;
-    if (want && !ring.wait32) {
-        void *w = NULL, *wr = NULL;
-        cudaDriverEntryPointQueryResult q1, q2;
-        if (cudaGetDriverEntryPoint("cuStreamWaitValue32", &w, cudaEnableDefault, &q1) != cudaSuccess ||
-            cudaGetDriverEntryPoint("cuStreamWriteValue32", &wr, cudaEnableDefault, &q2) != cudaSuccess ||
-            q1 != cudaDriverEntryPointSuccess || q2 != cudaDriverEntryPointSuccess) {
+    if (ring.pool && slot_bytes <= ring.slot_bytes) return true;
+    if (!ring.xchg && !cuda_ok(cudaMalloc(&ring.xchg, sizeof(IpcPair) * (kMaxRanks + 1) + 4 * (kMaxRanks + 1)), "malloc"))
+        return false;
+    bool want = ring.ce >= 0 && G > 1;
+    if (want && !ring.write32) {
+        void *wr = NULL;
+        cudaDriverEntryPointQueryResult q2;
+        if (cudaGetDriverEntryPoint("cuStreamWriteValue32", &wr, cudaEnableDefault, &q2) != cudaSuccess ||
+            q2 != cudaDriverEntryPointSuccess) {
             (void)cudaGetLastError();
             want = false;
         }
-        ring.wait32 = (FnStreamValue32)w;
         ring.write32 = (FnStreamValue32)wr;
-    }
-    if (!want) {
-        ring.ce = -1;
-        return false;
     }
     /* Nobody may still be pushing into a pool that is about to go away. */
     cuda_ok(cudaDeviceSynchronize(), "sync");
-    if (!ring.xchg && !cuda_ok(cudaMalloc(&ring.xchg, sizeof(IpcPair) * (kMaxRanks + 1)), "malloc")) return false;
-    IpcPair *dev = (IpcPair *)ring.xchg;
-    if (!ce_barrier()) return false;                /* every rank's pushes are complete */
+    if (G > 1 && !ring_barrier()) return false;          /* every rank's pushes are complete */
     ce_close_peers();
-    if (!ce_barrier()) return false;                /* every mapping of the old pools is gone */
-    ce_free_pool();
+    if (G > 1 && !ring_barrier()) return false;          /* every mapping of the old pools is gone */
+    if (ring.pool) cuda_ok(cudaFree(ring.pool), "free");
+    ring.pool = NULL;
+    ring.slot_bytes = 0;
     if (!ring.flags) {
         if (!cuda_ok(cudaMalloc((void **)&ring.flags, kFlagWords * 4), "malloc") ||
             !cuda_ok(cudaMemset(ring.flags, 0, kFlagWords * 4), "memset"))
@@ -332,24 +425,40 @@ bool ce_setup(size_t slot_bytes) {
         return false;
     }
     ring.slot_bytes = slot_bytes;
-    IpcPair mine, all[kMaxRanks];
-    if (!cuda_ok(cudaIpcGetMemHandle(&mine.pool, ring.pool), "cudaIpcGetMemHandle") ||
-        !cuda_ok(cudaIpcGetMemHandle(&mine.flags, ring.flags), "cudaIpcGetMemHandle") ||
-        !cuda_ok(cudaMemcpy(dev + kMaxRanks, &mine, sizeof(mine), cudaMemcpyHostToDevice), "memcpy") ||
-        !nccl_ok(ring.all_gather(dev + kMaxRanks, dev, sizeof(IpcPair), 1, ring.comm, g.stream), "ncclAllGather") ||
-        !cuda_ok(cudaStreamSynchronize(g.stream), "sync") ||
-        !cuda_ok(cudaMemcpy(all, dev, sizeof(IpcPair) * G, cudaMemcpyDeviceToHost), "memcpy"))
-        return false;
-    for (int r = 0; r < G; r++) {
-        if (r == ring.rank) continue;
-        void *pp = NULL, *pf = NULL;
-        if (!cuda_ok(cudaIpcOpenMemHandle(&pp, all[r].pool, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle") ||
-            !cuda_ok(cudaIpcOpenMemHandle(&pf, all[r].flags, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle"))
+    if (G == 1) return true;
+    bool mapped = want;
+    if (want) {
+        IpcPair *dev = (IpcPair *)ring.xchg;
+        IpcPair mine, all[kMaxRanks];
+        mapped = cudaIpcGetMemHandle(&mine.pool, ring.pool) == cudaSuccess &&
+                 cudaIpcGetMemHandle(&mine.flags, ring.flags) == cudaSuccess;
+        if (!mapped) memset(&mine, 0, sizeof(mine));
+        /* The exchange itself is collective: a rank that failed above still takes part. */
+        if (!cuda_ok(cudaMemcpy(dev + kMaxRanks, &mine, sizeof(mine), cudaMemcpyHostToDevice), "memcpy") ||
+            !nccl_ok(ring.all_gather(dev + kMaxRanks, dev, sizeof(IpcPair), 1, ring.comm, g.stream), "ncclAllGather") ||
+            !nccl_wait(g.stream, 30.0, "ncclAllGather") ||
+            !cuda_ok(cudaMemcpy(all, dev, sizeof(IpcPair) * G, cudaMemcpyDeviceToHost), "memcpy"))
             return false;
-        ring.peer_pool[r] = (char *)pp;
-        ring.peer_flags[r] = (uint32_t *)pf;
+        for (int r = 0; r < G && mapped; r++) {
+            if (r == ring.rank) continue;
+            void *pp = NULL, *pf = NULL;
+            if (cudaIpcOpenMemHandle(&pp, all[r].pool, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
+                cudaIpcOpenMemHandle(&pf, all[r].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+                mapped = false;
+            ring.peer_pool[r] = (char *)pp;
+            ring.peer_flags[r] = (uint32_t *)pf;
+        }
+        (void)cudaGetLastError();
     }
-    ring.ce = 1;
+    uint32_t votes[kMaxRanks];
+    if (!exchange_word(mapped ? 1u : 0u, votes)) return false;
+    bool all_mapped = true;
+    for (int r = 0; r < G; r++) all_mapped = all_mapped && votes[r] == 1u;
+    if (!all_mapped) {
+        ce_close_peers();
+        if (!ring_barrier()) return false;
+    }
+    ring.ce = all_mapped ? 1 : -1;
     return true;
 }
 
@@ -386,69 +495,75 @@ extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
     }
     ring.rank = rank;
     ring.nranks = nranks;
-    if (!cuda_ok(cudaStreamCreateWithFlags(&ring.comm_stream, cudaStreamNonBlocking), "stream create") ||
-        !cuda_ok(cudaStreamCreateWithFlags(&ring.aux_stream, cudaStreamNonBlocking), "stream create"))
+    ring.failed = 0;
+    if (ring.ce > 0) ring.ce = 0;
+    if (!cuda_ok(cudaStreamCreateWithFlags(&ring.comm_stream, cudaStreamNonBlocking), "stream create"))
         return IRIS_B200_ECUDA;
-    for (int i = 0; i < kMaxRanks; i++)
-        cuda_ok(cudaEventCreateWithFlags(&ring.received[i], cudaEventDisableTiming), "event create");
     cuda_ok(cudaEventCreateWithFlags(&ring.packed, cudaEventDisableTiming), "event create");
     cuda_ok(cudaEventCreateWithFlags(&ring.comm_done, cudaEventDisableTiming), "event create");
-    cuda_ok(cudaEventCreateWithFlags(&ring.join, cudaEventDisableTiming), "event create");
+    cuda_ok(cudaEventCreate(&ring.t_start), "event create");
+    cuda_ok(cudaEventCreate(&ring.t_kernel[0]), "event create");
+    cuda_ok(cudaEventCreate(&ring.t_kernel[1]), "event create");
+    for (int i = 0; i < kMaxRanks; i++) cuda_ok(cudaEventCreate(&ring.t_push[i]), "event create");
     return g.last_error;
+}
+
+extern "C" int iris_b200_ring_configure(int transport, int parts) {
+    if (ring.comm || transport < 0 || transport > 1 || parts < 0 || parts > AttnArgs::kMaxParts) return IRIS_B200_EINVAL;
+    ring.ce = transport == 1 ? -1 : 0;
+    ring.parts = parts;
+    return IRIS_B200_OK;
+}
+
+extern "C" int iris_b200_ring_transport(void) { return ring.comm ? (ring.ce == 1 ? 0 : 1) : -1; }
+
+extern "C" int iris_b200_ring_trace(int enable) {
+    ring.trace = enable ? 1 : 0;
+    ring.t_pushes = 0;
+    return IRIS_B200_OK;
+}
+
+extern "C" int iris_b200_ring_timeline(float *ms, int cap) {
+    if (!ring.comm || !ring.trace || !ms || cap < 2) return -1;
+    if (!cuda_ok(cudaDeviceSynchronize(), "sync")) return -1;
+    int n = 0;
+    for (int i = 0; i < 2; i++)
+        if (cudaEventElapsedTime(&ms[n], ring.t_start, ring.t_kernel[i]) == cudaSuccess) n++;
+    for (int s = 1; s < ring.t_pushes && n < cap; s++)
+        if (cudaEventElapsedTime(&ms[n], ring.t_start, ring.t_push[s]) == cudaSuccess) n++;
+    (void)cudaGetLastError();
+    return n;
 }
 
 extern "C" void iris_b200_ring_destroy(void) {
     if (!ring.comm) return;
     cuda_ok(cudaDeviceSynchronize(), "sync");
-    if (ring.trace == 1 && ring.t_steps > 0) {
-        /* Timeline of the last call, milliseconds after its start on the library's stream. */
-        char line[1024];
-        int n = snprintf(line, sizeof(line), "iris_b200 ring trace, rank %d:", ring.rank);
-        float ms = 0.0f;
-        for (int s = 1; s < ring.t_pushes && n < 900; s++)
-            if (cudaEventElapsedTime(&ms, ring.t_start, ring.t_push[s]) == cudaSuccess)
-                n += snprintf(line + n, sizeof(line) - n, " push%d=%.3f", s, ms);
-        for (int i = 0; i < ring.t_steps && n < 900; i++) {
-            float a = 0.0f, b = 0.0f;
-            if (cudaEventElapsedTime(&a, ring.t_start, ring.t_step[i][0]) == cudaSuccess &&
-                cudaEventElapsedTime(&b, ring.t_start, ring.t_step[i][1]) == cudaSuccess)
-                n += snprintf(line + n, sizeof(line) - n, " launch%d=[%.3f,%.3f]", i, a, b);
-        }
-        fprintf(stderr, "%s\n", line);
-        (void)cudaGetLastError();
-    }
     ce_close_peers();
-    if (ring.ce == 1) ce_barrier();
-    ce_free_pool();
+    /* Every importer has unmapped before any exporter frees. A ring that
+     * failed may have lost a peer: no collective is attempted on it. */
+    if (ring.nranks > 1 && ring.xchg && !ring.failed) ring_barrier();
+    if (ring.pool) cuda_ok(cudaFree(ring.pool), "free");
     if (ring.flags) cuda_ok(cudaFree(ring.flags), "free");
     if (ring.xchg) cuda_ok(cudaFree(ring.xchg), "free");
+    ring.pool = NULL;
+    ring.slot_bytes = 0;
     ring.flags = NULL;
     ring.xchg = NULL;
-    ring.ce = 0;
+    if (ring.ce > 0) ring.ce = 0;
     ring.seq = 0;
     ring.destroy(ring.comm);
     ring.comm = NULL;
-    for (int i = 0; i < kMaxRanks; i++) {
-        if (ring.buf[i]) cuda_ok(cudaFree(ring.buf[i]), "free");
-        ring.buf[i] = NULL;
-        ring.buf_bytes[i] = 0;
-        cuda_ok(cudaEventDestroy(ring.received[i]), "event destroy");
-    }
-    for (int i = 0; i < kHeadGroups; i++) {
-        if (ring.o_state[i]) cuda_ok(cudaFree(ring.o_state[i]), "free");
-        if (ring.lse_state[i]) cuda_ok(cudaFree(ring.lse_state[i]), "free");
-        ring.o_state[i] = ring.lse_state[i] = NULL;
-        ring.o_bytes[i] = ring.lse_bytes[i] = 0;
-    }
     cuda_ok(cudaEventDestroy(ring.packed), "event destroy");
     cuda_ok(cudaEventDestroy(ring.comm_done), "event destroy");
-    cuda_ok(cudaEventDestroy(ring.join), "event destroy");
+    cuda_ok(cudaEventDestroy(ring.t_start), "event destroy");
+    cuda_ok(cudaEventDestroy(ring.t_kernel[0]), "event destroy");
+    cuda_ok(cudaEventDestroy(ring.t_kernel[1]), "event destroy");
+    for (int i = 0; i < kMaxRanks; i++) cuda_ok(cudaEventDestroy(ring.t_push[i]), "event destroy");
     cuda_ok(cudaStreamDestroy(ring.comm_stream), "stream destroy");
-    cuda_ok(cudaStreamDestroy(ring.aux_stream), "stream destroy");
 }
 
 /* rows_of[r]: token rows of rank r. q, k, v: this rank's rows, row stride
- * ldi. Chunk layout in the buffers: [rows, 2 * heads * 128] (K | V). */
+ * ldi. Slot layout: [slot_rows, 2 * heads * 128] (K | V). */
 extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
                                         const uint16_t *q, const uint16_t *k, const uint16_t *v,
                                         int ldi, const int *rows_of, int heads, float scale) {
@@ -457,92 +572,77 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         set_error(IRIS_B200_EINVAL, "ring_attention", "ring not initialised or bad argument");
         return IRIS_B200_EINVAL;
     }
+    if (ring.failed) {
+        set_error(IRIS_B200_ECOMM, "ring_attention", "an earlier call failed: destroy and re-initialise the ring");
+        return IRIS_B200_ECOMM;
+    }
     const int G = ring.nranks, me = ring.rank;
     const int rows = rows_of[me];
     const size_t width = (size_t)heads * 128;
-    const int ngroups = (G > 1 && heads % kHeadGroups == 0) ? kHeadGroups : 1;
-    const int hg = heads / ngroups;                         /* heads of one group */
     int max_rows = 0;
-    for (int r = 0; r < G; r++) max_rows = rows_of[r] > max_rows ? rows_of[r] : max_rows;
-    const size_t slot_bytes = ((size_t)max_rows * 2 * width * 2 + 255) & ~(size_t)255;
-
-    /* Transport: pushes by the copy engines into IPC-mapped slot pools when
-     * that can be set up, NCCL send/recv into private buffers otherwise. */
-    const bool ce = G > 1 && ce_setup(slot_bytes);
-    if (!ce && G > 1) {
-        for (int s = 0; s < G; s++)
-            if (!grow(&ring.buf[s], &ring.buf_bytes[s], slot_bytes)) return IRIS_B200_ENOMEM;
-    }
-    const uint32_t seq = ++ring.seq;
-    /* Copy-engine slots come in two sets used by alternate calls. A peer
-     * pushes the rows of call n + 1 only after its own call n, which waited
-     * for this rank's push of call n, itself ordered after this rank's call
-     * n - 1: the set of call n + 1 was last read here in call n - 1, so no
-     * acknowledgement has to travel back. */
-    const size_t set_off = ce ? (size_t)(seq & 1u) * G * ring.slot_bytes : 0;
-    auto chunk = [&](int s) -> char * {
-        return ce ? ring.pool + set_off + (size_t)s * ring.slot_bytes : (char *)ring.buf[s];
-    };
-    if (G > 1) {
-        for (int i = 0; i < ngroups; i++)
-            if (!grow((void **)&ring.o_state[i], &ring.o_bytes[i], (size_t)rows * hg * 128 * 4) ||
-                !grow((void **)&ring.lse_state[i], &ring.lse_bytes[i], (size_t)rows * hg * 4))
-                return IRIS_B200_ENOMEM;
-    }
-    uint32_t *seq_word = ce ? ring.flags + kFlagSeq + (seq & 7u) : NULL;
-    const size_t my_bytes = (size_t)rows * 2 * width * 2;
-    const size_t row_bytes = width * 2, slot_pitch = 2 * width * 2;      /* a slot row is K | V */
-
-    /* Step 0 reads the local rows. The copy engines take them from the
-     * caller's buffers as they are; NCCL wants them contiguous in slot 0. */
-    const uint16_t *k0 = k, *v0 = v;
-    int ld0 = ldi;
-    if (ce) {
-        /* Every earlier use of the sequence word is ordered before this
-         * point on the library's stream. */
-        if (!stream_value(ring.write32, g.stream, seq_word, seq, CU_STREAM_WRITE_VALUE_DEFAULT, "write seq"))
-            return IRIS_B200_ECUDA;
-    } else if (G > 1) {
-        if (!cuda_ok(cudaMemcpy2DAsync(chunk(0), slot_pitch, k, (size_t)ldi * 2, row_bytes, rows,
-                                       cudaMemcpyDeviceToDevice, g.stream), "pack K") ||
-            !cuda_ok(cudaMemcpy2DAsync(chunk(0) + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
-                                       cudaMemcpyDeviceToDevice, g.stream), "pack V"))
-            return IRIS_B200_ECUDA;
-        k0 = (const uint16_t *)chunk(0);
-        v0 = k0 + width;
-        ld0 = (int)(2 * width);
-    }
-    cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record");
-    cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
-    if (ring.trace == 0) {
-        const char *env = getenv("IRIS_B200_RING_TRACE");
-        ring.trace = env && env[0] == '1' ? 1 : -1;
-        if (ring.trace == 1) {
-            cudaEventCreate(&ring.t_start);
-            for (int i = 0; i < kMaxRanks; i++) {
-                cudaEventCreate(&ring.t_push[i]);
-                cudaEventCreate(&ring.t_step[i][0]);
-                cudaEventCreate(&ring.t_step[i][1]);
-            }
+    bool even = true;
+    for (int r = 0; r < G; r++) {
+        if (rows_of[r] <= 0) {
+            set_error(IRIS_B200_EINVAL, "ring_attention", "every rank needs at least one row");
+            return IRIS_B200_EINVAL;
         }
+        max_rows = rows_of[r] > max_rows ? rows_of[r] : max_rows;
+        even = even && rows_of[r] == rows;
     }
-    const bool trace = ring.trace == 1 && ce;
-    if (trace) {
-        cudaEventRecord(ring.t_start, g.stream);
-        ring.t_steps = ring.t_pushes = 0;
+    if (check_attention_args("ring_attention", out, q, k, v, ldo, ldi, ldi, rows, rows, heads, heads, 128) != IRIS_B200_OK)
+        return IRIS_B200_EINVAL;
+    if (!sm100_supported(out, ldo, q, k, v, ldi, heads, heads, 128, 0, scale)) {
+        set_error(IRIS_B200_EUNSUPPORTED, "ring_attention", "arguments outside the tcgen05 kernel's domain");
+        return IRIS_B200_EUNSUPPORTED;
     }
+    const size_t row_bytes = width * 2, slot_pitch = 2 * row_bytes;      /* a slot row is K | V */
+    const size_t slot_bytes = (size_t)max_rows * slot_pitch;
+    /* Everything that can fail without having enqueued anything comes first:
+     * an error return up to here leaves the ring usable. */
+    if (G > 1 && !ring_pool(slot_bytes)) {
+        ring.failed = 1;                 /* the ranks may no longer agree on the pools */
+        return g.last_error ? g.last_error : IRIS_B200_ECOMM;
+    }
+    const bool ce = G > 1 && ring.ce == 1;
+    const int slot_rows = G > 1 ? (int)(ring.slot_bytes / slot_pitch) : 0;
+    const uint32_t seq = ++ring.seq;
+    /* Slots come in two sets used by alternate calls. A peer pushes the rows
+     * of call n + 1 only after its own call n, whose launch ended only after
+     * this rank's push of call n had arrived there, and that push was ordered
+     * after this rank's call n - 1: the set of call n + 1 was last read here
+     * in call n - 1, so no acknowledgement has to travel back. */
+    char *set = G > 1 ? ring.pool + (size_t)(seq & 1u) * G * ring.slot_bytes : NULL;
+    const size_t set_off = G > 1 ? (size_t)(set - ring.pool) : 0;
+    uint32_t *seq_word = G > 1 ? ring.flags + kFlagSeq + (seq & 7u) : NULL;
+    const bool trace = ring.trace == 1;
+    bool ok = true;
 
+    /* From here on work is enqueued; a failure marks the ring as failed. */
+    if (trace) cudaEventRecord(ring.t_start, g.stream);
+    if (G > 1) {
+        if (ce) {
+            /* Every earlier use of the sequence word is ordered before this
+             * point on the library's stream. */
+            ok = stream_value(ring.write32, g.stream, seq_word, seq, CU_STREAM_WRITE_VALUE_DEFAULT, "write seq");
+        } else {
+            /* NCCL wants the rows contiguous: K | V into slot 0. */
+            ok = cuda_ok(cudaMemcpy2DAsync(set, slot_pitch, k, (size_t)ldi * 2, row_bytes, rows,
+                                           cudaMemcpyDeviceToDevice, g.stream), "pack K") &&
+                 cuda_ok(cudaMemcpy2DAsync(set + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
+                                           cudaMemcpyDeviceToDevice, g.stream), "pack V");
+        }
+        ok = ok && cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record") &&
+             cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
+    }
     /* All transfers, in step order on one stream: at step s this rank's rows
      * are wanted by rank me + s, which keeps them in its slot s. (Pushes on
      * two streams were measured to share one copy engine and run one after
-     * the other anyway, 48 us per 26 MB, only no longer in the order the
-     * steps need them.) */
-    for (int s = 1; s < G; s++) {
+     * the other anyway, only no longer in the order the steps need them.) */
+    for (int s = 1; s < G && ok; s++) {
         const int to = (me + s) % G, from = iris_b200_ring_source(me, s, G);
+        cudaStream_t cs = ring.comm_stream;
         if (ce) {
-            cudaStream_t cs = ring.comm_stream;
             char *dst = ring.peer_pool[to] + set_off + (size_t)s * ring.slot_bytes;
-            bool ok;
             if (v == k + width) {
                 /* K and V are neighbouring column blocks of one buffer: one copy of K | V rows. */
                 ok = cuda_ok(cudaMemcpy2DAsync(dst, slot_pitch, k, (size_t)ldi * 2, 2 * row_bytes, rows,
@@ -553,68 +653,88 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
                      cuda_ok(cudaMemcpy2DAsync(dst + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
                                                cudaMemcpyDefault, cs), "push V");
             }
-            if (!ok || !cuda_ok(cudaMemcpyAsync(ring.peer_flags[to] + kFlagArrive + s, seq_word, 4, cudaMemcpyDefault, cs),
-                                "push flag"))
-                return IRIS_B200_ECUDA;
+            ok = ok && cuda_ok(cudaMemcpyAsync(ring.peer_flags[to] + kFlagArrive + s, seq_word, 4, cudaMemcpyDefault, cs),
+                               "push flag");
             if (trace) {
                 cudaEventRecord(ring.t_push[s], cs);
                 ring.t_pushes = s + 1;
             }
         } else {
-            if (!nccl_ok(ring.group_start(), "ncclGroupStart")) return IRIS_B200_ECOMM;
-            bool ok = nccl_ok(ring.send(chunk(0), my_bytes, 1, to, ring.comm, ring.comm_stream), "ncclSend") &&
-                      nccl_ok(ring.recv(chunk(s), (size_t)rows_of[from] * 2 * width * 2, 1, from, ring.comm,
-                                        ring.comm_stream), "ncclRecv");
-            if (!nccl_ok(ring.group_end(), "ncclGroupEnd") || !ok) return IRIS_B200_ECOMM;
-            cuda_ok(cudaEventRecord(ring.received[s], ring.comm_stream), "event record");
+            ok = nccl_ok(ring.group_start(), "ncclGroupStart");
+            bool sent = ok && nccl_ok(ring.send(set, (size_t)rows * slot_pitch, 1, to, ring.comm, cs), "ncclSend") &&
+                        nccl_ok(ring.recv(set + (size_t)s * ring.slot_bytes, (size_t)rows_of[from] * slot_pitch, 1, from,
+                                          ring.comm, cs), "ncclRecv");
+            ok = ok && nccl_ok(ring.group_end(), "ncclGroupEnd") && sent;
         }
     }
-    cuda_ok(cudaEventRecord(ring.comm_done, ring.comm_stream), "event record");
+    if (G > 1 && ok) ok = cuda_ok(cudaEventRecord(ring.comm_done, ring.comm_stream), "event record");
+    if (G > 1 && ok && !ce) ok = cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done, 0), "stream wait");
 
-    /* Launch schedule: which steps share a launch (only chunks of one size
-     * lying in adjacent slots can). */
-    bool even = ce && ring.slot_bytes == my_bytes;
-    for (int r = 0; r < G && even; r++) even = rows_of[r] == rows;
-    int plan_first[kMaxRanks], plan_count[kMaxRanks];
-    const int nlaunch = iris_b200_ring_plan(G, even ? 1 : 0, plan_first, plan_count);
-
-    /* The head groups run side by side: group 0 on the library's stream,
-     * group 1 on the auxiliary one, joined again before the call returns. */
-    if (ngroups > 1) cuda_ok(cudaStreamWaitEvent(ring.aux_stream, ring.packed, 0), "stream wait");
+    /* The one attention launch: own rows, then the slots in ring order. With
+     * equal row counts the slots 1 .. G-1 are one run of adjacent rows (no
+     * half-empty tile at every slot boundary), guarded by one word per slot. */
+    AttnArgs a = {};
     int rc = IRIS_B200_OK;
-    for (int li = 0; li < nlaunch && rc == IRIS_B200_OK; li++) {
-        const int s = plan_first[li], nsteps = plan_count[li];
-        const int src = iris_b200_ring_source(me, s, G);
-        const uint16_t *kc = s == 0 ? k0 : (const uint16_t *)chunk(s);
-        const uint16_t *vc = s == 0 ? v0 : kc + width;
-        const int ldc = s == 0 ? ld0 : (int)(2 * width);
-        const int keys = nsteps > 1 ? nsteps * rows : rows_of[src];
-        for (int grp = 0; grp < ngroups && rc == IRIS_B200_OK; grp++) {
-            cudaStream_t st = grp == 0 ? g.stream : ring.aux_stream;
-            for (int w = s; w < s + nsteps; w++) {
-                if (w == 0) continue;
-                if (ce) {
-                    if (!stream_value(ring.wait32, st, ring.flags + kFlagArrive + w, seq, CU_STREAM_WAIT_VALUE_GEQ,
-                                      "wait chunk"))
-                        return IRIS_B200_ECUDA;
-                } else {
-                    cuda_ok(cudaStreamWaitEvent(st, ring.received[w], 0), "stream wait");
-                }
-            }
-            StreamScope scope(st);
-            const size_t col = (size_t)grp * hg * 128;
-            if (trace && grp == 0) cudaEventRecord(ring.t_step[ring.t_steps][0], st);
-            /* The head groups fill the SMs between them: no key split inside a launch. */
-            rc = attention_chunk(out + col, ldo, q + col, ldi, kc + col, vc + col, ldc, rows, keys, hg, scale, NULL,
-                                 ring.o_state[grp], ring.lse_state[grp], s == 0, s + nsteps == G, ngroups > 1 ? 1 : 2);
-            if (trace && grp == 0) cudaEventRecord(ring.t_step[ring.t_steps++][1], st);
+    if (ok) {
+        a.out = out;
+        a.ldo = ldo;
+        a.q = q;
+        a.ldq = ldi;
+        a.seq_q = rows;
+        a.heads = heads;
+        a.scale = scale;
+        a.max_parts = AttnArgs::kMaxParts;
+        a.k[0] = k; a.v[0] = v; a.ldkv[0] = ldi;
+        if (G > 1) {
+            a.k[1] = (const uint16_t *)set;
+            a.v[1] = a.k[1] + width;
+            a.ldkv[1] = (int)(2 * width);
+            a.arrive = ce ? ring.flags + kFlagArrive : NULL;
+            a.arrive_seq = seq;
         }
-    }
-    if (ngroups > 1) {
-        cuda_ok(cudaEventRecord(ring.join, ring.aux_stream), "event record");
-        cuda_ok(cudaStreamWaitEvent(g.stream, ring.join, 0), "stream wait");
+        int n = 0;
+        long long step_row[kMaxRanks + 1];         /* first key row of step s over the runs */
+        step_row[0] = 0;
+        if (ce || G == 1) {
+            a.src[n++] = AttnArgs::Source{0, 0, rows, -1, 1};
+        } else {
+            a.src[n++] = AttnArgs::Source{1, 0, rows, -1, 1};
+        }
+        for (int s = 1; s < G; s++) step_row[s] = step_row[s - 1] + rows_of[iris_b200_ring_source(me, s - 1, G)];
+        step_row[G] = step_row[G - 1] + rows_of[iris_b200_ring_source(me, G - 1, G)];
+        if (G > 1 && even && slot_rows == rows) {
+            a.src[n++] = AttnArgs::Source{1, slot_rows, (G - 1) * rows, ce ? 1 : -1, rows};
+        } else {
+            for (int s = 1; s < G; s++)
+                a.src[n++] = AttnArgs::Source{1, s * slot_rows, rows_of[iris_b200_ring_source(me, s, G)], ce ? s : -1,
+                                              rows_of[iris_b200_ring_source(me, s, G)]};
+        }
+        a.nsrc = n;
+        if (ce) {
+            /* Parts by groups of steps, so that the work list follows the arrivals. */
+            int first[kMaxRanks], count[kMaxRanks];
+            const int np = iris_b200_ring_plan(G, ring.parts, first, count);
+            if (np > 1) {
+                a.nparts = np;
+                for (int i = 0; i < np; i++) a.part_row[i] = step_row[first[i]];
+            }
+        }
+        if (trace) cudaEventRecord(ring.t_kernel[0], g.stream);
+        rc = launch_attention_sm100(a);
+        if (trace) cudaEventRecord(ring.t_kernel[1], g.stream);
     }
     /* The transfers of the local rows must not outlive the call. */
-    cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done, 0), "stream wait");
-    return rc != IRIS_B200_OK ? rc : g.last_error;
+    if (G > 1 && ok && ce) ok = cuda_ok(cudaStreamWaitEvent(g.stream, ring.comm_done, 0), "stream wait");
+    if (!ok || rc != IRIS_B200_OK) {
+        ring.failed = 1;
+        return rc != IRIS_B200_OK ? rc : (g.last_error ? g.last_error : IRIS_B200_ECOMM);
+    }
+    return IRIS_B200_OK;
+}
+
+/* A device wait ran out inside a ring call (iris_b200_check_device_status
+ * reported IRIS_B200_ETIMEOUT): the peers' pushes and this rank's sets are no
+ * longer in step. */
+void iris_b200::ring_mark_failed(void) {
+    if (ring.comm) ring.failed = 1;
 }

@@ -59,10 +59,12 @@ extern "C" int iris_b200_attention_noalloc(uint16_t *out, int ldo,
                                            int ldi, int seq_q, int seq_k, int heads, float scale,
                                            int nsplit) {
     if (!require_device("attention_noalloc")) return IRIS_B200_ENODEV;
-    if (!out || !q || !k || !v || seq_q < 0 || seq_k <= 0 || heads <= 0 || nsplit < 1) {
+    if (!out || seq_k <= 0 || nsplit < 1) {
         set_error(IRIS_B200_EINVAL, "attention_noalloc", "bad argument");
         return IRIS_B200_EINVAL;
     }
+    int rc = check_attention_args("attention_noalloc", out, q, k, v, ldo, ldi, ldi, seq_q, seq_k, heads, heads, 128);
+    if (rc != IRIS_B200_OK) return rc;
     if ((size_t)seq_q * heads * 128 > kMaxOutFloats) {
         char msg[160];
         snprintf(msg, sizeof(msg), "seq_q * heads * 128 = %zu exceeds the built-in scratch of %zu elements",
@@ -87,9 +89,14 @@ extern "C" int iris_b200_attention_noalloc(uint16_t *out, int ldo,
         int k0 = done * 128, k1 = t1 * 128 < seq_k ? t1 * 128 : seq_k;
         done = t1;
         int mode = nsplit == 1 ? 0 : (i == 0 ? 1 : (i == nsplit - 1 ? 3 : 2));
-        int rc = launch_attention_sm100(out, ldo, q, ldi, k + (size_t)k0 * ldi, v + (size_t)k0 * ldi, ldi, seq_q,
-                                        k1 - k0, heads, scale, NULL, mode, o_state, lse_state, NULL, NULL,
-                                        1 /* no in-kernel key split: its scratch would be allocated */);
+        AttnArgs a = attn_args(out, ldo, q, ldi, k + (size_t)k0 * ldi, v + (size_t)k0 * ldi, ldi, seq_q, k1 - k0,
+                               heads, scale, NULL);
+        a.acc_mode = mode;
+        a.o_acc = o_state;
+        a.lse_acc = lse_state;
+        a.max_parts = 1;
+        a.no_scratch = true;        /* the library's own scratch would have to be allocated */
+        rc = launch_attention_sm100(a);
         if (rc != IRIS_B200_OK) return rc;
     }
     return IRIS_B200_OK;

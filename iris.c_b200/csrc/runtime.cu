@@ -219,8 +219,10 @@ int iris_b200_check_device_status(void) {
         snprintf(msg, sizeof(msg), "wait timed out in kernel (site %u, block %u, aux %u)", st[1], st[2], st[3]);
         set_error(IRIS_B200_ETIMEOUT, "device wait", msg);
         cuda_ok(cudaMemset(g.dev_status, 0, 64), "status clear");
-        /* A kernel that gave up may have left key-split tickets half used. */
+        /* A kernel that gave up may have left key-split tickets and work-list
+         * counters half used, and a ring call its peers out of step. */
         sm100_reset_split();
+        ring_mark_failed();
     }
     return g.last_error;
 }
@@ -237,39 +239,11 @@ void *iris_dev_alloc(size_t bytes) {
 
 void iris_dev_free(void *p) {
     if (!p) return;
-    /* Pending work may still use the buffer. */
-    cuda_ok(cudaStreamSynchronize(g.stream), "sync");
+    /* Kernels enqueued earlier may still read or write the buffer: the
+     * reference's contract (iris_cuda.cu:181-186) is that free() is safe
+     * right after the last launch that used it. */
+    if (g.ready) cuda_ok(cudaStreamSynchronize(g.stream), "sync");
     cuda_ok(cudaFree(p), "free");
-}
-
-/* Rows are packed into the pinned buffers by the CPU while the copy engine
- * drains the other buffer; a row wider than a buffer goes in pieces. */
-void iris_dev_upload_2d(void *dst, size_t dst_stride, const void *src, size_t src_stride,
-                        size_t row_bytes, size_t rows) {
-    if (!require_device("upload") || row_bytes == 0 || rows == 0) return;
-    size_t piece = row_bytes < kStageBytes ? row_bytes : kStageBytes;
-    size_t rows_per_chunk = row_bytes <= kStageBytes ? kStageBytes / row_bytes : 1;
-    int buf = 0;
-    for (size_t r0 = 0; r0 < rows; r0 += rows_per_chunk) {
-        size_t nr = rows - r0 < rows_per_chunk ? rows - r0 : rows_per_chunk;
-        for (size_t off = 0; off < row_bytes; off += piece) {
-            size_t len = row_bytes - off < piece ? row_bytes - off : piece;
-            if (!cuda_ok(cudaEventSynchronize(g.stage_done[buf]), "event sync")) return;
-            char *stage = (char *)g.stage[buf];
-            if (src_stride == len && nr > 1 && off == 0 && row_bytes == len) {
-                memcpy(stage, (const char *)src + r0 * src_stride, nr * len);
-            } else {
-                for (size_t r = 0; r < nr; r++)
-                    memcpy(stage + r * len, (const char *)src + (r0 + r) * src_stride + off, len);
-            }
-            if (!cuda_ok(cudaMemcpy2DAsync((char *)dst + r0 * dst_stride + off, dst_stride, stage, len,
-                                           len, nr, cudaMemcpyHostToDevice, g.stream), "upload"))
-                return;
-            cuda_ok(cudaEventRecord(g.stage_done[buf], g.stream), "event record");
-            buf ^= 1;
-        }
-    }
-    cuda_ok(cudaStreamSynchronize(g.stream), "sync");
 }
 
 /* Page-locked host memory is copied by the DMA engine directly; pageable
@@ -283,14 +257,132 @@ static bool host_is_pinned(const void *p) {
     return a.type == cudaMemoryTypeHost;
 }
 
-void iris_dev_upload(void *dst, const void *src, size_t bytes) {
-    if (!bytes) return;
-    if (g.ready && host_is_pinned(src)) {
-        if (cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, g.stream), "upload"))
+/* One tile of a pageable host matrix -> device through a pinned buffer:
+ * `nrows` rows of `nbytes` starting at column byte `col`. The CPU packs the
+ * tile while the copy engine still drains the other buffer. */
+static bool stage_tile(int which, char *dst, size_t dst_stride, const char *src, size_t src_stride, size_t col,
+                       size_t nbytes, size_t nrows) {
+    if (!cuda_ok(cudaEventSynchronize(g.stage_done[which]), "event sync")) return false;
+    char *pin = (char *)g.stage[which];
+    if (src_stride == nbytes && col == 0) {
+        memcpy(pin, src, nrows * nbytes);                   /* the rows are contiguous on the host */
+    } else {
+        for (size_t r = 0; r < nrows; r++) memcpy(pin + r * nbytes, src + r * src_stride + col, nbytes);
+    }
+    if (!cuda_ok(cudaMemcpy2DAsync(dst + col, dst_stride, pin, nbytes, nbytes, nrows, cudaMemcpyHostToDevice, g.stream),
+                 "upload"))
+        return false;
+    return cuda_ok(cudaEventRecord(g.stage_done[which], g.stream), "event record");
+}
+
+/* Blocking strided upload (iris_dev.h: iris_dev_upload_2d). Pinned sources
+ * are one 2-D DMA; pageable ones are cut into tiles that fit a staging
+ * buffer (whole rows when a row fits, else column pieces of single rows). */
+void iris_dev_upload_2d(void *dst, size_t dst_stride, const void *src, size_t src_stride,
+                        size_t row_bytes, size_t rows) {
+    if (!require_device("upload") || row_bytes == 0 || rows == 0) return;
+    if (host_is_pinned(src)) {
+        if (cuda_ok(cudaMemcpy2DAsync(dst, dst_stride, src, src_stride, row_bytes, rows, cudaMemcpyHostToDevice,
+                                      g.stream), "upload"))
             cuda_ok(cudaStreamSynchronize(g.stream), "sync");
         return;
     }
+    const size_t tile_cols = row_bytes < kStageBytes ? row_bytes : kStageBytes;
+    const size_t tile_rows = kStageBytes / tile_cols;         /* >= 1 */
+    int which = 0;
+    bool ok = true;
+    for (size_t r = 0; r < rows && ok; r += tile_rows) {
+        const size_t nrows = rows - r < tile_rows ? rows - r : tile_rows;
+        for (size_t col = 0; col < row_bytes && ok; col += tile_cols, which ^= 1) {
+            const size_t nbytes = row_bytes - col < tile_cols ? row_bytes - col : tile_cols;
+            ok = stage_tile(which, (char *)dst + r * dst_stride, dst_stride, (const char *)src + r * src_stride,
+                            src_stride, col, nbytes, nrows);
+        }
+    }
+    cuda_ok(cudaStreamSynchronize(g.stream), "sync");
+}
+
+void iris_dev_upload(void *dst, const void *src, size_t bytes) {
+    if (!bytes) return;
     iris_dev_upload_2d(dst, bytes, src, bytes, bytes, 1);
+}
+
+/* Stream-ordered copies between page-locked host memory and the device, on a
+ * stream of the caller's (NULL: the library's): they return at once, and the
+ * caller orders them against the operations with events or by sharing the
+ * stream. With three buffer sets this is what overlaps the upload of step
+ * i + 1 and the download of step i - 1 with the kernels of step i. */
+int iris_b200_upload_async(void *dst, const void *src, size_t bytes, void *cuda_stream) {
+    if (!require_device("upload_async")) return IRIS_B200_ENODEV;
+    if (!bytes) return IRIS_B200_OK;
+    if (!dst || !src || !host_is_pinned(src)) {
+        set_error(IRIS_B200_EINVAL, "upload_async", "source must be page-locked host memory");
+        return IRIS_B200_EINVAL;
+    }
+    cudaStream_t st = cuda_stream ? (cudaStream_t)cuda_stream : g.stream;
+    return cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, st), "upload_async") ? IRIS_B200_OK
+                                                                                                 : IRIS_B200_ECUDA;
+}
+
+int iris_b200_download_async(void *dst, const void *src, size_t bytes, void *cuda_stream) {
+    if (!require_device("download_async")) return IRIS_B200_ENODEV;
+    if (!bytes) return IRIS_B200_OK;
+    if (!dst || !src || !host_is_pinned(dst)) {
+        set_error(IRIS_B200_EINVAL, "download_async", "destination must be page-locked host memory");
+        return IRIS_B200_EINVAL;
+    }
+    cudaStream_t st = cuda_stream ? (cudaStream_t)cuda_stream : g.stream;
+    return cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, st), "download_async") ? IRIS_B200_OK
+                                                                                                   : IRIS_B200_ECUDA;
+}
+
+/* Page-locked host memory for the asynchronous copies. */
+void *iris_b200_host_alloc(size_t bytes) {
+    void *p = NULL;
+    if (!g.ready) return NULL;
+    if (cudaMallocHost(&p, bytes ? bytes : 1) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return NULL;
+    }
+    return p;
+}
+void iris_b200_host_free(void *p) {
+    if (p) cuda_ok(cudaFreeHost(p), "free host");
+}
+
+/* Streams and events for callers that have no CUDA headers of their own
+ * (plain-C hosts): what the pipelined copies above are ordered with. */
+void *iris_b200_stream_create(void) {
+    cudaStream_t st = NULL;
+    if (!g.ready || !cuda_ok(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "stream create")) return NULL;
+    return (void *)st;
+}
+void iris_b200_stream_destroy(void *cuda_stream) {
+    if (cuda_stream) cuda_ok(cudaStreamDestroy((cudaStream_t)cuda_stream), "stream destroy");
+}
+void *iris_b200_event_create(void) {
+    cudaEvent_t ev = NULL;
+    if (!g.ready || !cuda_ok(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), "event create")) return NULL;
+    return (void *)ev;
+}
+void iris_b200_event_destroy(void *event) {
+    if (event) cuda_ok(cudaEventDestroy((cudaEvent_t)event), "event destroy");
+}
+/* record: NULL stream = the library's. wait: the stream waits for the event. */
+int iris_b200_event_record(void *event, void *cuda_stream) {
+    if (!require_device("event_record") || !event) return IRIS_B200_EINVAL;
+    return cuda_ok(cudaEventRecord((cudaEvent_t)event, cuda_stream ? (cudaStream_t)cuda_stream : g.stream), "event record")
+               ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+int iris_b200_stream_wait_event(void *cuda_stream, void *event) {
+    if (!require_device("stream_wait_event") || !event) return IRIS_B200_EINVAL;
+    return cuda_ok(cudaStreamWaitEvent(cuda_stream ? (cudaStream_t)cuda_stream : g.stream, (cudaEvent_t)event, 0),
+                   "stream wait") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+int iris_b200_stream_sync(void *cuda_stream) {
+    if (!require_device("stream_sync")) return IRIS_B200_ENODEV;
+    return cuda_ok(cudaStreamSynchronize(cuda_stream ? (cudaStream_t)cuda_stream : g.stream), "sync") ? IRIS_B200_OK
+                                                                                                      : IRIS_B200_ECUDA;
 }
 
 void iris_dev_download(void *dst, const void *src, size_t bytes) {

@@ -1,6 +1,12 @@
-"""One rank of the NCCL ring test (launched by test_gpu_chunks.py through
-torch.distributed.run): local rows through the prologue and the ring
-attention, result checked against the CPU oracle over the full sequence."""
+"""One rank of the multi-GPU ring test (launched by test_gpu_chunks.py through
+torch.distributed.run): local rows through the ring attention, result
+checked against the CPU oracle over the full sequence.
+
+    ring_gpu_worker.py toy       small shapes, even and uneven rows, all rows checked
+    ring_gpu_worker.py config5   24 heads x 16 896 tokens (the FLUX.3 multi-reference
+                                 shape), sampled query rows of every rank checked
+
+RING_TEST_TRANSPORT=nccl selects the send/recv transport."""
 import ctypes as C
 import os
 import sys
@@ -29,23 +35,32 @@ def main():
         assert lib.iris_b200_ring_unique_id(buf) == 0
         ident = [buf.raw]
     dist.broadcast_object_list(ident, src=0)
+    nccl = os.environ.get("RING_TEST_TRANSPORT", "auto") == "nccl"
+    assert lib.iris_b200_ring_configure(1 if nccl else 0, 0) == 0
     assert lib.iris_b200_ring_init(rank, world, ident[0]) == 0
 
     worst = torch.tensor([0.0, -1.0])
-    # equal rows per rank (with six or more ranks two steps then share a launch), then
-    # uneven rows, which also makes the slot pool grow between calls
-    for H, S in ((2, 384 * world), (4, 2000 + 37)):
-        res = one_case(lib, rank, world, H, S)
+    mode = sys.argv[1] if len(sys.argv) > 1 else "toy"
+    if mode == "config5":
+        cases = ((24, 16896, 24),)
+    else:
+        # equal rows per rank (the slots then form one run of rows), a length that leaves
+        # a partial tile in every slot, then uneven rows, which also makes the pool grow
+        cases = ((2, 384 * world, None), (3, 200 * world, None), (4, 2000 + 37, None))
+    for H, S, nsample in cases:
+        res = one_case(lib, rank, world, H, S, nsample)
         worst = torch.maximum(worst, res)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    transport = lib.iris_b200_ring_transport()
     lib.iris_b200_ring_destroy()
     if rank == 0:
         ok = worst[0].item() <= 2e-2 and -worst[1].item() >= 0.9999
-        print("RING_%s max_abs %.4g min_cos %.6f" % ("OK" if ok else "FAIL", worst[0].item(), -worst[1].item()))
+        print("RING_%s max_abs %.4g min_cos %.6f transport %s" % (
+            "OK" if ok else "FAIL", worst[0].item(), -worst[1].item(), "nccl" if transport == 1 else "copy-engine"))
     dist.destroy_process_group()
 
 
-def one_case(lib, rank, world, H, S):
+def one_case(lib, rank, world, H, S, nsample):
     q, k, v = (ol.to_bf16(ol.randn(70 + i, S, H * D)) for i in range(3))
     a, b = C.c_int(), C.c_int()
     rows = []
@@ -64,9 +79,17 @@ def one_case(lib, rank, world, H, S):
         assert rc == 0, rc
     got = ol.from_bf16(lib.to_host(dout, (n, H * D), np.uint16))
     lib.check()
-    want = ol.dev_attention(ol.from_bf16(q), ol.from_bf16(k), ol.from_bf16(v), H,
-                            rows=np.arange(r0, r0 + n, dtype=np.int32))[r0:r0 + n]
-    mx, cs = ol.compare_heads(got, want, H)
+    for p in (dqkv, dout):
+        lib.iris_dev_free(p)
+    if nsample is None:
+        rows = np.arange(r0, r0 + n, dtype=np.int32)
+    else:                                     # the block's edges and a seeded sample in between
+        rng = np.random.default_rng(11 + rank)
+        rows = np.unique(np.concatenate([[r0, r0 + 127, r0 + 128, r0 + n - 1], r0 + rng.integers(0, n, nsample)]))
+        rows = rows.astype(np.int32)
+    want = ol.dev_attention(ol.from_bf16(q), ol.from_bf16(k), ol.from_bf16(v), H, rows=rows)
+    mx, cs = ol.compare_heads(got[rows - r0], want[rows], H)
+    assert np.isfinite(got).all()
     return torch.tensor([float(mx.max()), -float(cs.min())])
 
 

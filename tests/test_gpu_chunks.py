@@ -1,5 +1,5 @@
-"""Chunked attention with carried state (split-K, ring steps) on one GPU, and
-the NCCL ring on two GPUs when the box has them."""
+"""Chunked attention with carried state (split-K over several launches) on one
+GPU, and the ring across GPUs when the box has them."""
 import ctypes as C
 import os
 import subprocess
@@ -106,17 +106,31 @@ def test_chunk_argument_checks(lib):
     lib.iris_b200_clear_error()
 
 
-@pytest.mark.parametrize("nproc,transport", [(2, "auto"), (2, "nccl"), (8, "auto")])
-def test_ring_across_gpus(nproc, transport):
-    """One process per GPU; `auto` pushes the chunks with the copy engines,
-    `nccl` forces the send/recv transport."""
+def run_ring_worker(nproc, transport, mode, port):
     import torch
     if torch.cuda.device_count() < nproc:
         pytest.skip("needs %d GPUs" % nproc)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", IRIS_B200_RING_TRANSPORT=transport)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", RING_TEST_TRANSPORT=transport)
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % nproc,
-                          "--master-addr", "127.0.0.1", "--master-port", "29437",
-                          os.path.join(ROOT, "tests", "ring_gpu_worker.py")],
-                         capture_output=True, text=True, env=env, timeout=600)
+                          "--master-addr", "127.0.0.1", "--master-port", str(port),
+                          os.path.join(ROOT, "tests", "ring_gpu_worker.py"), mode],
+                         capture_output=True, text=True, env=env, timeout=900)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "RING_OK" in out.stdout, out.stdout[-3000:]
+    if transport == "nccl":
+        assert "transport nccl" in out.stdout, out.stdout[-3000:]
+
+
+@pytest.mark.parametrize("nproc,transport", [(2, "auto"), (2, "nccl"), (4, "auto"), (8, "auto")])
+def test_ring_across_gpus(nproc, transport):
+    """One process per GPU; `auto` pushes the chunks with the copy engines
+    while one attention launch waits for them inside the kernel, `nccl`
+    forces the send/recv transport (all chunks first, then the launch)."""
+    run_ring_worker(nproc, transport, "toy", 29437)
+
+
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_ring_at_the_multi_reference_shape(nproc):
+    """24 heads x 16 896 tokens split over the ranks, sampled rows of every
+    rank against the CPU oracle."""
+    run_ring_worker(nproc, "auto", "config5", 29439)

@@ -79,34 +79,32 @@ def test_ring_schedule_visits_every_chunk_once(lib):
     assert lib.iris_b200_seq_shard(16896, 8, 3, C.byref(a), C.byref(b)) == 0 and (a.value, b.value) == (6336, 2112)
 
 
-def ring_plan(lib, n, even):
+def ring_plan(lib, n, max_parts=0):
     first, count = (C.c_int * max(n, 1))(), (C.c_int * max(n, 1))()
-    nl = lib.iris_b200_ring_plan(n, even, first, count)
+    nl = lib.iris_b200_ring_plan(n, max_parts, first, count)
     return [(first[i], count[i]) for i in range(max(nl, 0))], nl
 
 
 def test_ring_plan_covers_the_steps_in_order(lib):
     for n in range(1, 17):
-        for even in (0, 1):
-            plan, nl = ring_plan(lib, n, even)
+        for max_parts in (0, 1, 2, 3, 8):
+            plan, nl = ring_plan(lib, n, max_parts)
             assert nl == len(plan) >= 1
             steps = [s for f, c in plan for s in range(f, f + c)]
             assert steps == list(range(n))                       # every step once, in arrival order
-            assert plan[0] == (0, 1)                             # the local rows need no transfer
-            if n > 1:
-                assert plan[1] == (1, 1)                         # the first arrival is not held back
-            if not even or n < 6:
-                assert all(c == 1 for _, c in plan)              # unequal chunks never share a launch
-            else:
-                assert all(c == 2 for _, c in plan[2:-1]) and plan[-1][1] in (1, 2)
-    assert ring_plan(lib, 8, 1)[0] == [(0, 1), (1, 1), (2, 2), (4, 2), (6, 2)]
-    assert ring_plan(lib, 7, 1)[0] == [(0, 1), (1, 1), (2, 2), (4, 2), (6, 1)]
+            assert all(c >= 1 for _, c in plan)
+            assert nl <= min(n, 4) and (max_parts == 0 or nl <= max_parts)
+            sizes = [c for _, c in plan]
+            assert max(sizes) - min(sizes) <= 1                  # groups as even as they come
+    assert ring_plan(lib, 8)[0] == [(0, 2), (2, 2), (4, 2), (6, 2)]
+    assert ring_plan(lib, 2)[0] == [(0, 1), (1, 1)]
+    assert ring_plan(lib, 7, 2)[0] == [(0, 3), (3, 4)]
     assert lib.iris_b200_ring_plan(0, 1, None, None) == -1
 
 
-def test_paired_steps_merge_like_single_steps(lib):
-    """The carried-state merge does not care how the keys are grouped into
-    launches: eight chunks merged one by one and by the 8-rank plan agree."""
+def test_grouped_steps_merge_like_single_steps(lib):
+    """The merge of partial results does not care how the keys are grouped:
+    eight chunks merged one by one and by the 8-rank plan agree."""
     H, D, S, n = 2, 128, 64, 8
     q, k, v = (ol.randn(30 + i, S * n if i else S, H * D) for i in range(3))
     scale = 1 / np.sqrt(D)
@@ -126,8 +124,8 @@ def test_paired_steps_merge_like_single_steps(lib):
 
     want = ol.dev_attention(q, k, v, H)
     single = run([(s, 1) for s in range(n)])
-    paired = run(ring_plan(lib, n, 1)[0])
-    assert np.abs(single - want).max() < 2e-5 and np.abs(paired - want).max() < 2e-5
+    grouped = run(ring_plan(lib, n)[0])
+    assert np.abs(single - want).max() < 2e-5 and np.abs(grouped - want).max() < 2e-5
 
 
 WORKER = r'''
