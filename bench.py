@@ -231,10 +231,11 @@ class Job:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return [float(x) for x in t.tolist()]
 
-    def ring_init(self):
+    def ring_init(self, parts=0):
         if self.ring_ready:
             return
         torch, lib = self.torch, self.lib
+        assert lib.iris_b200_ring_configure(0, parts) == 0
         ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if self.rank == 0:
             buf = C.create_string_buffer(128)
@@ -354,7 +355,7 @@ def timed_steps(job, w, plan, B, steps, warmup, collective=True, marks=False):
     nmark = min(steps, 2500) if (marks and active and len(B.sets[0]) == 1) else 0
     for i in range(steps):
         if active:
-            run_step(job, w, plan, B, B.sets[i % B.nsets], 2 + 3 * i if i < nmark else None)
+            run_step(job, w, plan, B, B.sets[i % B.nsets], mark=2 + 3 * i if i < nmark else None)
     lib.iris_b200_mark(1)
     t_enq = time.time()
     job.barrier(collective)
@@ -535,7 +536,7 @@ def run_b200(args):
     w = WORKLOADS[name]
     pk = peaks()
     if mode == "ring":
-        job.ring_init()
+        job.ring_init(args.ring_parts)
     plan = plan_of(job, w, mode)
     B = Buffers(job, w, plan)
     S_full, H = plan["S_full"], w["heads"]
@@ -855,6 +856,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffer) measurement")
     ap.add_argument("--mode", default=None, choices=["single", "shard", "ring"],
                     help="N > 1: ring sequence parallelism (default) or independent cfg/head shards")
+    ap.add_argument("--ring-parts", type=int, default=0, help="key parts of a ring call's launch (0: the library's choice)")
     ap.add_argument("--no-extras", action="store_true", help="N > 1: skip the further workloads of the same run")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference's own CUDA kernels")

@@ -102,7 +102,10 @@ def test_ring_order_emulated_on_one_gpu(lib):
 def test_chunk_argument_checks(lib):
     assert lib.iris_b200_attention_chunk(None, 256, 16, 256, 16, 16, 256, 4, 4, 2, 0.1, None, None, None, 1, 0) == 1
     lib.iris_b200_clear_error()
-    assert lib.iris_b200_attention_chunk(16, 256, 16, 250, 16, 16, 256, 4, 4, 2, 0.1, None, None, None, 1, 1) == 6
+    assert lib.iris_b200_attention_chunk(16, 256, 16, 260, 16, 16, 256, 4, 4, 2, 0.1, None, None, None, 1, 1) == 6
+    lib.iris_b200_clear_error()
+    # a query stride shorter than a row of heads
+    assert lib.iris_b200_attention_chunk(16, 256, 16, 248, 16, 16, 256, 4, 4, 2, 0.1, None, None, None, 1, 1) == 1
     lib.iris_b200_clear_error()
 
 

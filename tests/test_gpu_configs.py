@@ -34,6 +34,48 @@ def test_config_parity(lib, case):
         assert res["prologue_max_abs"] <= 11.4 * 2.0 ** -8
 
 
+def test_klein4b_1024_every_row_against_the_reference_cpu_build(lib):
+    """The headline configuration, all 4608 rows of all 24 heads, against the
+    reference's own CPU code (its BLAS build compiled from its sources:
+    qk_norm, its own RoPE tables and rotation, mha_forward) fed the same
+    bf16-rounded inputs. Skipped where that build is absent."""
+    r = ol.ref("blas") or ol.ref("generic")
+    if r is None:
+        pytest.skip("oracle/_ref is not built here")
+    case = pc.FLUX_CFG2
+    H, txt, (ih, iw) = case["heads"], case["txt"], case["img"]
+    img, seq = ih * iw, pc.seq_len(case)
+    dc = pc.DeviceCase(lib, case)
+    try:
+        dc.prologue(True)
+        dc.attention(TC)
+        got = dc.read_out()
+        lib.check()
+    finally:
+        dc.free()
+    q, k, v = pc.qkv_inputs(case)
+    o = ol.oracle()
+    for x in (q, k, v):
+        o.orc_round_bf16(x.reshape(-1), x.size)
+    w = np.ones(D, np.float32)
+    ct = np.zeros((txt, D), np.float32); st = np.zeros_like(ct)
+    ci = np.zeros((img, D), np.float32); si = np.zeros_like(ci)
+    r.ref_flux_rope_text(ct, st, txt, 32, 2000.0)
+    r.ref_flux_rope_2d(ci, si, ih, iw, 32, 2000.0)
+    r.ref_flux_qk_norm(q, k, w, w, seq, H, D, case["eps"])
+    for x in (q, k):
+        r.ref_flux_apply_rope_2d(x[:txt], ct, st, txt, H, D)
+        r.ref_flux_apply_rope_2d(x[txt:], ci, si, img, H, D)
+    want = np.zeros_like(q)
+    if hasattr(r, "openblas_set_num_threads"):
+        r.openblas_set_num_threads(1)
+        assert r.ref_flux_mha(want, q, k, v, seq, H, D) == 0
+    else:
+        r.iris_flash_attention(want, q, k, v, seq, seq, H, D, 1.0 / np.sqrt(D))
+    mx, cs = ol.compare_heads(got, want, H)
+    assert mx.max() <= MAX_ABS and cs.min() >= MIN_COS, (mx, cs)
+
+
 def test_cfg_batch_shares_image_rows():
     """cond / uncond differ in the text rows only (two forward passes over the
     same latent, iris_sample.c:698-712)."""

@@ -268,6 +268,51 @@ def test_use_stream_runs_calls_side_by_side(lib):
     lib.check()
 
 
+def test_masked_calls_on_two_streams_keep_their_own_masks(lib):
+    """Key masks are packed into per-stream scratch: two masked calls that
+    overlap on two streams must not see each other's bits; ten streams in a
+    row exercise the recycling of the scratch sets."""
+    heads = 2
+    streams = [lib.iris_b200_stream_create() for _ in range(2)]
+    jobs = []
+    for i, (sq, sk) in enumerate(((500, 1500), (400, 1400))):
+        q, k, v = (ol.to_bf16(ol.randn(80 + 3 * i + j, n, heads * D)) for j, n in enumerate((sq, sk, sk)))
+        mask = (ol.randn(90 + i, 1, sk)[0] > (0.0 if i else -0.8)).astype(np.int32)      # different patterns
+        mask[:3] = 1
+        jobs.append((q, k, v, mask, lib.to_device(q), lib.to_device(k), lib.to_device(v), lib.to_device(mask),
+                     lib.alloc(sq * heads * D * 2), sq, sk))
+    lib.iris_dev_sync()
+    for rep in range(4):
+        for st, (q, k, v, mask, dq, dk, dv, dm, dout, sq, sk) in zip(streams, jobs):
+            assert lib.iris_b200_use_stream(st) == 0
+            lib.iris_dev_attention(dout, heads * D, dq, dk, dv, heads * D, sq, sk, heads, heads, D,
+                                   1.0 / np.sqrt(D), 0, dm)
+    assert lib.iris_b200_use_stream(None) == 0
+    for st in streams:
+        assert lib.iris_b200_stream_sync(st) == 0
+    for q, k, v, mask, dq, dk, dv, dm, dout, sq, sk in jobs:
+        got = ol.from_bf16(lib.to_host(dout, (sq, heads * D), np.uint16))
+        want = ol.dev_attention(ol.from_bf16(q), ol.from_bf16(k), ol.from_bf16(v), heads, key_mask=mask)
+        check_raw(got, want, heads)
+    # more streams than the library keeps scratch sets for
+    q, k, v, mask, dq, dk, dv, dm, dout, sq, sk = jobs[0]
+    want = ol.dev_attention(ol.from_bf16(q), ol.from_bf16(k), ol.from_bf16(v), heads, key_mask=mask)
+    for i in range(10):
+        st = lib.iris_b200_stream_create()
+        assert lib.iris_b200_use_stream(st) == 0
+        lib.iris_dev_attention(dout, heads * D, dq, dk, dv, heads * D, sq, sk, heads, heads, D, 1.0 / np.sqrt(D), 0, dm)
+        assert lib.iris_b200_stream_sync(st) == 0
+        assert lib.iris_b200_use_stream(None) == 0
+        check_raw(ol.from_bf16(lib.to_host(dout, (sq, heads * D), np.uint16)), want, heads)
+        lib.iris_b200_stream_destroy(st)
+    for job in jobs:
+        for p in job[4:9]:
+            lib.iris_dev_free(p)
+    for st in streams:
+        lib.iris_b200_stream_destroy(st)
+    lib.check()
+
+
 def test_empty_sequences(lib):
     got, _ = attention_raw(lib, 0, 50, 2, 0)
     assert got.size == 0
@@ -310,7 +355,7 @@ def test_gqa_causal_masked(lib):
     assert lib.iris_b200_attention_kernel_for(16, 1024, 16, 16, 16, 1024, 8, 2, 128, 1) == GEN
 
 
-@pytest.mark.parametrize("hd,heads", [(64, 4), (512, 1), (96, 2)])
+@pytest.mark.parametrize("hd,heads", [(64, 4), (512, 1), (96, 2), (72, 3), (65, 2)])
 def test_other_head_dims(lib, hd, heads):
     got, want = attention_raw(lib, 77, 130, heads, 0, hd=hd, seed=hd)
     check_raw(got, want, heads, hd)
