@@ -257,6 +257,34 @@ void iris_b200_ring_destroy(void);
 int iris_b200_ring_trace(int enable);
 int iris_b200_ring_timeline(float *ms, int cap);
 
+/* The ring protocol on host threads (no device): one thread per rank and
+ * memcpy in place of the copy engines, the same slots, pool sets, arrival
+ * words, ring order and bounded waits as ring_attention(); the consumer
+ * checks each received chunk (call number, row count, checksum) instead of
+ * computing attention and folds it into a digest. For tests of the failure
+ * paths that must not be provoked on a GPU: `faults` are injected on the host
+ * and every rank comes back with a status, never blocking: IRIS_B200_ETIMEOUT
+ * for a chunk that does not arrive within wait_limit_us, IRIS_B200_EPROTO for
+ * one that arrives with the wrong call number, row count or content.
+ * status / digest / calls_done: one entry per rank (calls_done: calls the rank
+ * completed). ring_loopback_digest(): what a rank's digest must be after
+ * `calls` fault-free calls. */
+enum {
+    IRIS_B200_LOOP_DROP = 1,      /* rank's push of (call, step) never happens */
+    IRIS_B200_LOOP_DELAY = 2,     /* it happens delay_us later */
+    IRIS_B200_LOOP_CORRUPT = 3,   /* a byte of the pushed rows is flipped */
+    IRIS_B200_LOOP_LEAVE = 4,     /* the rank stops before `call` (step ignored) */
+    IRIS_B200_LOOP_BAD_ROWS = 5   /* the pushed header announces one row too many */
+};
+typedef struct {
+    int kind, rank, call, step;   /* calls count from 1; step < 0: every step */
+    unsigned int delay_us;
+} iris_b200_loop_fault;
+int iris_b200_ring_loopback(int nranks, const int *rows_of, int row_bytes, int calls,
+                            unsigned int wait_limit_us, const iris_b200_loop_fault *faults, int nfaults,
+                            int *status_of_rank, uint64_t *digest_of_rank, int *calls_done_of_rank);
+uint64_t iris_b200_ring_loopback_digest(int nranks, const int *rows_of, int row_bytes, int calls, int rank);
+
 /* ---- attention without any allocation --------------------------------------- */
 
 /* No counterpart in the reference. Split-K attention (the keys are walked in

@@ -81,11 +81,18 @@ SIGNATURES = {
     "iris_b200_stream_sync": (INT, [VP]),
     "iris_b200_ring_configure": (INT, [INT, INT]),
     "iris_b200_ring_transport": (INT, []),
+    "iris_b200_ring_loopback": (INT, [INT, VP, INT, INT, C.c_uint, VP, INT, VP, VP, VP]),
+    "iris_b200_ring_loopback_digest": (C.c_uint64, [INT, VP, INT, INT, INT]),
     "iris_b200_ring_trace": (INT, [INT]),
     "iris_b200_ring_timeline": (INT, [VP, INT]),
 }
 
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_GENERIC = 0, 1, 2
+
+
+class LoopFault(C.Structure):
+    """iris_b200_loop_fault of include/iris_b200.h."""
+    _fields_ = [("kind", INT), ("rank", INT), ("call", INT), ("step", INT), ("delay_us", C.c_uint)]
 
 
 class KeyRun(C.Structure):
