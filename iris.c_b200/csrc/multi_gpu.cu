@@ -88,13 +88,36 @@ extern "C" int iris_b200_ring_plan(int nranks, int max_parts, int *first_step, i
      * attention launch: part i covers the steps [first_step[i], first_step[i]
      * + step_count[i]). Parts are what the work list is ordered by, so the
      * chunks that arrive first are worked on first; more than four parts buy
-     * nothing (every part costs a partial result per query block). */
-    int n = nranks < 4 ? nranks : 4;
-    if (max_parts > 0 && n > max_parts) n = max_parts;
-    for (int i = 0; i < n; i++) {
-        first_step[i] = (int)((long long)nranks * i / n);
-        step_count[i] = (int)((long long)nranks * (i + 1) / n) - first_step[i];
+     * nothing (every part costs a partial result per query block). The
+     * library's own choice (max_parts <= 0) keeps the last part to the one
+     * step that arrives last, because what is left to do after the last
+     * arrival is that part's work: the steps before it are spread evenly
+     * over the other parts, larger groups first. An explicit max_parts gives
+     * that many groups of equal size (+- 1). */
+    if (max_parts > 0) {
+        const int n = nranks < max_parts ? nranks : max_parts;
+        for (int i = 0; i < n; i++) {
+            first_step[i] = (int)((long long)nranks * i / n);
+            step_count[i] = (int)((long long)nranks * (i + 1) / n) - first_step[i];
+        }
+        return n;
     }
+    const int n = nranks < 4 ? nranks : 4;
+    if (n == 1) {
+        first_step[0] = 0;
+        step_count[0] = nranks;
+        return 1;
+    }
+    const int head = nranks - 1, groups = n - 1;         /* steps and parts before the last */
+    int s = 0;
+    for (int i = 0; i < groups; i++) {
+        const int c = head / groups + (i < head % groups ? 1 : 0);
+        first_step[i] = s;
+        step_count[i] = c;
+        s += c;
+    }
+    first_step[groups] = s;
+    step_count[groups] = 1;
     return n;
 }
 
@@ -285,6 +308,7 @@ struct Ring {
     char *pool;
     size_t slot_bytes;
     int ce;                               /* 0 not decided, 1 copy engines + IPC, -1 NCCL send/recv */
+    int packed_push;                      /* copy-engine pushes take the rows from a packed copy in slot 0 */
     FnStreamValue32 write32;
     uint32_t *flags;                      /* arrive[kMaxRanks] | seq_words[8] */
     char *peer_pool[kMaxRanks];
@@ -509,8 +533,9 @@ extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
 }
 
 extern "C" int iris_b200_ring_configure(int transport, int parts) {
-    if (ring.comm || transport < 0 || transport > 1 || parts < 0 || parts > AttnArgs::kMaxParts) return IRIS_B200_EINVAL;
+    if (ring.comm || transport < 0 || transport > 2 || parts < 0 || parts > AttnArgs::kMaxParts) return IRIS_B200_EINVAL;
     ring.ce = transport == 1 ? -1 : 0;
+    ring.packed_push = transport == 2;
     ring.parts = parts;
     return IRIS_B200_OK;
 }
@@ -624,15 +649,19 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
             /* Every earlier use of the sequence word is ordered before this
              * point on the library's stream. */
             ok = stream_value(ring.write32, g.stream, seq_word, seq, CU_STREAM_WRITE_VALUE_DEFAULT, "write seq");
-        } else {
-            /* NCCL wants the rows contiguous: K | V into slot 0. */
-            ok = cuda_ok(cudaMemcpy2DAsync(set, slot_pitch, k, (size_t)ldi * 2, row_bytes, rows,
-                                           cudaMemcpyDeviceToDevice, g.stream), "pack K") &&
-                 cuda_ok(cudaMemcpy2DAsync(set + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
-                                           cudaMemcpyDeviceToDevice, g.stream), "pack V");
         }
         ok = ok && cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record") &&
              cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
+        if (ok && (!ce || ring.packed_push)) {
+            /* NCCL wants the rows contiguous, and a copy engine moves one
+             * linear block faster than strided rows: K | V into slot 0, on the
+             * communication stream (its earlier pushes out of this slot, two
+             * calls ago, are complete by stream order). */
+            ok = cuda_ok(cudaMemcpy2DAsync(set, slot_pitch, k, (size_t)ldi * 2, row_bytes, rows,
+                                           cudaMemcpyDeviceToDevice, ring.comm_stream), "pack K") &&
+                 cuda_ok(cudaMemcpy2DAsync(set + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
+                                           cudaMemcpyDeviceToDevice, ring.comm_stream), "pack V");
+        }
     }
     /* All transfers, in step order on one stream: at step s this rank's rows
      * are wanted by rank me + s, which keeps them in its slot s. (Pushes on
@@ -643,7 +672,10 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         cudaStream_t cs = ring.comm_stream;
         if (ce) {
             char *dst = ring.peer_pool[to] + set_off + (size_t)s * ring.slot_bytes;
-            if (v == k + width) {
+            if (ring.packed_push) {
+                /* One linear copy of the packed rows. */
+                ok = cuda_ok(cudaMemcpyAsync(dst, set, (size_t)rows * slot_pitch, cudaMemcpyDefault, cs), "push packed");
+            } else if (v == k + width) {
                 /* K and V are neighbouring column blocks of one buffer: one copy of K | V rows. */
                 ok = cuda_ok(cudaMemcpy2DAsync(dst, slot_pitch, k, (size_t)ldi * 2, 2 * row_bytes, rows,
                                                cudaMemcpyDefault, cs), "push K|V");

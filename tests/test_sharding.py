@@ -93,10 +93,16 @@ def test_ring_plan_covers_the_steps_in_order(lib):
             steps = [s for f, c in plan for s in range(f, f + c)]
             assert steps == list(range(n))                       # every step once, in arrival order
             assert all(c >= 1 for _, c in plan)
-            assert nl <= min(n, 4) and (max_parts == 0 or nl <= max_parts)
             sizes = [c for _, c in plan]
-            assert max(sizes) - min(sizes) <= 1                  # groups as even as they come
-    assert ring_plan(lib, 8)[0] == [(0, 2), (2, 2), (4, 2), (6, 2)]
+            if max_parts:
+                assert nl == min(n, max_parts) and max(sizes) - min(sizes) <= 1      # as even as they come
+            else:
+                assert nl == min(n, 4)
+                assert nl == 1 or sizes[-1] == 1                 # what arrives last is a part of its own
+                assert sizes[:-1] == sorted(sizes[:-1], reverse=True) and max(sizes[:-1] or [1]) - min(sizes[:-1] or [1]) <= 1
+    assert ring_plan(lib, 8)[0] == [(0, 3), (3, 2), (5, 2), (7, 1)]
+    assert ring_plan(lib, 8, 4)[0] == [(0, 2), (2, 2), (4, 2), (6, 2)]
+    assert ring_plan(lib, 4)[0] == [(0, 1), (1, 1), (2, 1), (3, 1)]
     assert ring_plan(lib, 2)[0] == [(0, 1), (1, 1)]
     assert ring_plan(lib, 7, 2)[0] == [(0, 3), (3, 4)]
     assert lib.iris_b200_ring_plan(0, 1, None, None) == -1
