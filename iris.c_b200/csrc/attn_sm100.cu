@@ -642,7 +642,7 @@ __device__ __forceinline__ void mask_chunk(uint32_t *v, uint32_t bits) {
 }
 
 /* Half an S row (64 scores) -> P (bf16 pairs into 32 columns at tP) and the
- * four partial row sums. */
+ * four partial row sums: one fp32 exponential per score. */
 __device__ __forceinline__ void exp_half(const uint32_t *s, float sl2, float neg_ref, float *sum4, uint32_t tP) {
 #pragma unroll
     for (int ch = 0; ch < 2; ch++) {

@@ -308,7 +308,6 @@ struct Ring {
     char *pool;
     size_t slot_bytes;
     int ce;                               /* 0 not decided, 1 copy engines + IPC, -1 NCCL send/recv */
-    int packed_push;                      /* copy-engine pushes take the rows from a packed copy in slot 0 */
     FnStreamValue32 write32;
     uint32_t *flags;                      /* arrive[kMaxRanks] | seq_words[8] */
     char *peer_pool[kMaxRanks];
@@ -533,9 +532,8 @@ extern "C" int iris_b200_ring_init(int rank, int nranks, const void *id128) {
 }
 
 extern "C" int iris_b200_ring_configure(int transport, int parts) {
-    if (ring.comm || transport < 0 || transport > 2 || parts < 0 || parts > AttnArgs::kMaxParts) return IRIS_B200_EINVAL;
+    if (ring.comm || transport < 0 || transport > 1 || parts < 0 || parts > AttnArgs::kMaxParts) return IRIS_B200_EINVAL;
     ring.ce = transport == 1 ? -1 : 0;
-    ring.packed_push = transport == 2;
     ring.parts = parts;
     return IRIS_B200_OK;
 }
@@ -650,18 +648,17 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
              * point on the library's stream. */
             ok = stream_value(ring.write32, g.stream, seq_word, seq, CU_STREAM_WRITE_VALUE_DEFAULT, "write seq");
         }
+        if (ok && !ce) {
+            /* NCCL wants the rows contiguous: K | V into slot 0. (The copy
+             * engines take strided rows as they are; pushing from a packed
+             * copy was measured to be no faster, 48 us per 26 MB either way.) */
+            ok = cuda_ok(cudaMemcpy2DAsync(set, slot_pitch, k, (size_t)ldi * 2, row_bytes, rows,
+                                           cudaMemcpyDeviceToDevice, g.stream), "pack K") &&
+                 cuda_ok(cudaMemcpy2DAsync(set + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
+                                           cudaMemcpyDeviceToDevice, g.stream), "pack V");
+        }
         ok = ok && cuda_ok(cudaEventRecord(ring.packed, g.stream), "event record") &&
              cuda_ok(cudaStreamWaitEvent(ring.comm_stream, ring.packed, 0), "stream wait");
-        if (ok && (!ce || ring.packed_push)) {
-            /* NCCL wants the rows contiguous, and a copy engine moves one
-             * linear block faster than strided rows: K | V into slot 0, on the
-             * communication stream (its earlier pushes out of this slot, two
-             * calls ago, are complete by stream order). */
-            ok = cuda_ok(cudaMemcpy2DAsync(set, slot_pitch, k, (size_t)ldi * 2, row_bytes, rows,
-                                           cudaMemcpyDeviceToDevice, ring.comm_stream), "pack K") &&
-                 cuda_ok(cudaMemcpy2DAsync(set + row_bytes, slot_pitch, v, (size_t)ldi * 2, row_bytes, rows,
-                                           cudaMemcpyDeviceToDevice, ring.comm_stream), "pack V");
-        }
     }
     /* All transfers, in step order on one stream: at step s this rank's rows
      * are wanted by rank me + s, which keeps them in its slot s. (Pushes on
@@ -672,10 +669,7 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         cudaStream_t cs = ring.comm_stream;
         if (ce) {
             char *dst = ring.peer_pool[to] + set_off + (size_t)s * ring.slot_bytes;
-            if (ring.packed_push) {
-                /* One linear copy of the packed rows. */
-                ok = cuda_ok(cudaMemcpyAsync(dst, set, (size_t)rows * slot_pitch, cudaMemcpyDefault, cs), "push packed");
-            } else if (v == k + width) {
+            if (v == k + width) {
                 /* K and V are neighbouring column blocks of one buffer: one copy of K | V rows. */
                 ok = cuda_ok(cudaMemcpy2DAsync(dst, slot_pitch, k, (size_t)ldi * 2, 2 * row_bytes, rows,
                                                cudaMemcpyDefault, cs), "push K|V");
