@@ -515,6 +515,65 @@ def roofline_of(res, name, nh, S, S_full, pk):
     return roof, pro
 
 
+def projection_run(job, w, pk, reps=20):
+    """The step before the path (rank 0, N = 1): the QKV projection of one
+    block, [tokens, dim] x [3 dim, dim]^T, as the fused tcgen05 GEMM whose
+    epilogue is the prologue, next to cuBLAS (torch.matmul) followed by the
+    separate prologue kernel on the same device."""
+    lib, torch = job.lib, job.torch
+    S, H = seq_len(w), w["heads"]
+    dim, out = H * D, 3 * H * D
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((S, dim), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    W = (torch.randn((out, dim), generator=gen, device="cuda", dtype=torch.float32) / dim ** 0.5).to(torch.bfloat16)
+    ys = [torch.empty((S, out), device="cuda", dtype=torch.bfloat16) for _ in range(4)]      # 4 x 85 MB: beyond L2
+    cos, sin = rope_tables(w)
+    d_cos, d_sin, d_w = lib.to_device(cos), lib.to_device(sin), lib.to_device(np.ones(D, np.float32))
+    torch.cuda.synchronize()
+
+    def fused(i):
+        rc = lib.iris_b200_linear_qk_norm_rope(ys[i % 4].data_ptr(), out, x.data_ptr(), W.data_ptr(), S, dim, out, H,
+                                               d_w, d_w, d_cos, d_sin, w["eps"])
+        assert rc == 0, rc
+
+    def timed(fn):
+        for i in range(3):
+            fn(i)
+        lib.iris_dev_sync()
+        lib.iris_b200_mark(0)
+        for i in range(reps):
+            fn(i)
+        lib.iris_b200_mark(1)
+        return lib.iris_b200_mark_elapsed_ms(0, 1) / reps
+
+    fused_ms = timed(fused)
+    lib.check()
+    # cuBLAS + separate prologue on the library's stream
+    comp = torch.cuda.ExternalStream(int(lib.iris_b200_stream()))
+
+    def blas(i):
+        with torch.cuda.stream(comp):
+            torch.matmul(x, W.t(), out=ys[i % 4])
+
+    def blas_pro(i):
+        blas(i)
+        y = ys[i % 4].data_ptr()
+        lib.iris_b200_qk_norm_rope(y, y + dim * 2, out, d_w, d_w, d_cos, d_sin, S, H, D, w["eps"], 0)
+
+    blas_ms = timed(blas)
+    both_ms = timed(blas_pro)
+    lib.check()
+    for p in (d_cos, d_sin, d_w):
+        lib.iris_dev_free(p)
+    flops = 2.0 * S * dim * out
+    return {"shape": [S, dim, out], "kernel": "k_linear_sm100 (GEMM + RMSNorm + RoPE epilogue)",
+            "ms": round(fused_ms, 4), "tflops": round(flops / fused_ms / 1e9, 1),
+            "frac_of_bf16_peak": round(flops / fused_ms / 1e9 / pk[0], 4),
+            "cublas_ms": round(blas_ms, 4), "cublas_tflops": round(flops / blas_ms / 1e9, 1),
+            "cublas_plus_prologue_ms": round(both_ms, 4),
+            "speedup_vs_cublas_plus_prologue": round(both_ms / fused_ms, 3)}
+
+
 def extra_run(job, name, mode, steps, warmup, pk):
     """A further workload / decomposition measured in the same run: ms per
     step (max over ranks), aggregate TFLOP/s and per-GPU share of the peak."""
@@ -599,6 +658,9 @@ def run_b200(args):
         B2.free()
     if mode == "ring":
         lib.iris_b200_ring_destroy()
+    projection = None
+    if rank == 0 and world == 1 and mode == "single" and w["family"] != "zimage" and not args.no_extras:
+        projection = projection_run(job, w, pk)
 
     if rank == 0:
         sharding = {"single": "none",
@@ -619,7 +681,7 @@ def run_b200(args):
             "pct_bf16_sustained": round(100 * value / world / pk[1], 2),
             "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
             "roofline": roof, "roofline_prologue": prologue, "cpu_baseline": cpu, "parity": parity,
-            "reference_gpu": ref_gpu,
+            "reference_gpu": ref_gpu, "qkv_projection": projection,
         }
         if speedup is not None:
             out["one_gpu_ms_per_step"] = round(one_gpu, 4)
@@ -857,7 +919,8 @@ def main():
     ap.add_argument("--mode", default=None, choices=["single", "shard", "ring"],
                     help="N > 1: ring sequence parallelism (default) or independent cfg/head shards")
     ap.add_argument("--ring-parts", type=int, default=0, help="key parts of a ring call's launch (0: the library's choice)")
-    ap.add_argument("--no-extras", action="store_true", help="N > 1: skip the further workloads of the same run")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the further measurements of the same run (N > 1: other workloads; N = 1: the QKV projection)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip the reference's own CUDA kernels")
     args = ap.parse_args()

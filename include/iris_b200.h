@@ -127,6 +127,23 @@ int iris_b200_qk_norm_rope(uint16_t *q, uint16_t *k, int ld,
                            const float *rope_cos, const float *rope_sin,
                            int seq, int heads, int head_dim, float eps, int split_half);
 
+/* The QKV projection with the prologue as its epilogue: the reference's
+ * iris_dev_linear_bf16 (iris_cuda.cu:463-506, declared in iris_dev.h) and the
+ * two iris_dev_head_norm_rope calls that follow it in every transformer block
+ * (iris_transformer_flux.c:3795-3801 double blocks, :3832-3837 single blocks)
+ * as ONE tcgen05 GEMM: y [rows, out] (row stride ldy) = x [rows, in] . W [out,
+ * in]^T, bf16 in, fp32 accumulation, bf16 out; the column blocks [0, heads *
+ * 128) (Q) and [heads * 128, 2 * heads * 128) (K) leave the kernel already
+ * normalised per head (wq / wk [128], eps) and rotated (rope_cos / rope_sin
+ * [rows, 64], consecutive pairs); all other columns (V, and the MLP half of a
+ * single block's fused projection) are the plain product. Each Q / K value is
+ * computed from the bf16-rounded product, as in the reference's two-kernel
+ * sequence. Operands 16-byte aligned; in, out, ldy multiples of 8. */
+int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W,
+                                  int rows, int in, int out, int heads,
+                                  const float *wq, const float *wk,
+                                  const float *rope_cos, const float *rope_sin, float eps);
+
 /* ---- attention ---------------------------------------------------------- */
 
 enum {

@@ -51,6 +51,13 @@ void iris_dev_sync(void);
  * (iris_cuda.cu:271-274). */
 void iris_dev_f32_to_bf16(uint16_t *dst, const float *src, size_t n);
 
+/* y [rows, out] = x [rows, in] . W [out, in]^T, bf16 operands and result, fp32
+ * accumulation (row-major, W as the checkpoints store it). Replaces
+ * iris_dev.h:52-53 (iris_cuda.cu:463-506, a cuBLAS call there; a tcgen05
+ * kernel here). Operands 16-byte aligned, in and out multiples of 8. */
+void iris_dev_linear_bf16(uint16_t *y, const uint16_t *x, const uint16_t *W,
+                          int rows, int in, int out);
+
 /* In place on the bf16 heads x[s, h * head_dim + d] (row stride ld, in
  * elements): per-head RMSNorm x * rsqrt(mean(x^2) + eps) * w[d], then
  * rotation of pair i by the angle of row s (rope_cos / rope_sin:

@@ -26,6 +26,7 @@ SIGNATURES = {
     "iris_dev_upload_2d": (None, [VP, SZ, VP, SZ, SZ, SZ]),
     "iris_dev_sync": (None, []),
     "iris_dev_f32_to_bf16": (None, [VP, VP, SZ]),
+    "iris_dev_linear_bf16": (None, [VP, VP, VP, INT, INT, INT]),
     "iris_dev_head_norm_rope": (None, [VP, INT, VP, VP, VP, INT, INT, INT, FLT, INT]),
     "iris_dev_attention": (None, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP]),
     # iris_kernels.h
@@ -50,6 +51,7 @@ SIGNATURES = {
     "iris_b200_mark": (INT, [INT]),
     "iris_b200_mark_elapsed_ms": (FLT, [INT, INT]),
     "iris_b200_qk_norm_rope": (INT, [VP, VP, INT, VP, VP, VP, VP, INT, INT, INT, FLT, INT]),
+    "iris_b200_linear_qk_norm_rope": (INT, [VP, INT, VP, VP, INT, INT, INT, INT, VP, VP, VP, VP, FLT]),
     "iris_b200_attention_ex": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP, INT]),
     "iris_b200_attention_kernel_for": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT]),
     "iris_b200_head_shard": (INT, [INT, INT, INT, C.POINTER(INT), C.POINTER(INT)]),

@@ -77,6 +77,7 @@
 #include <string.h>
 
 #include "kernels.h"
+#include "tc_ptx.cuh"
 #include <math.h>
 
 namespace iris_b200 {
@@ -166,35 +167,7 @@ struct Params {
                                   3: merge with the state and write the final bf16 output */
 };
 
-/* ---------------- PTX wrappers ---------------- */
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+/* ---------------- bounded waits ---------------- */
 
 struct Ctx {
     uint32_t bars;                  /* shared address of the barrier block */
@@ -258,110 +231,9 @@ __device__ __forceinline__ bool word_wait(const Ctx &c, const uint32_t *word, ui
     }
 }
 
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-/* True in exactly one lane of a converged warp. Code around it stays
- * warp-uniform, so operands of the single-thread instructions (descriptors,
- * addresses) can live in uniform registers. */
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "elect.sync _|p, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
-}
-
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-/* D[tmem] (+)= A[smem] * B[smem] */
-__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
-}
-/* D[tmem] (+)= A[tmem] * B[smem] */
-__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
-}
-
-/* 32 consecutive fp32 columns of this thread's TMEM lane. */
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t *r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
-        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
-          "r"(taddr) : "memory");
-}
-
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
-        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(taddr) : "memory");
-}
-
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-/* Shared memory matrix descriptor (tcgen05), 128-byte swizzle:
- * start address, leading / stride byte offsets in 16-byte units, version 1. */
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo16, uint32_t sbo16) {
-    uint64_t d = (uint64_t)((addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)(lbo16 & 0x3FFFu) << 16;
-    d |= (uint64_t)(sbo16 & 0x3FFFu) << 32;
-    d |= 1ull << 46;       /* descriptor version of sm_100 */
-    d |= 2ull << 61;       /* SWIZZLE_128B */
-    return d;
-}
-
 /* Instruction descriptor, kind::f16: fp32 accumulate, bf16 operands,
  * M = 128, N = 128; bit 16 selects an MN-major B operand. */
-static constexpr uint32_t kIdescBase = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+static constexpr uint32_t kIdescBase = idesc_bf16(128, 128);
 static constexpr uint32_t kIdescQK = kIdescBase;
 static constexpr uint32_t kIdescPV = kIdescBase | (1u << 16);
 
@@ -1034,6 +906,10 @@ k_attention_sm100(const __grid_constant__ CUtensorMap tmq, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    /* Launched with programmatic stream serialisation: everything above ran
+     * while the kernel before this one (the prologue, an earlier key chunk)
+     * was still finishing; nothing below may start before its memory is final. */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp < 8) {
         /* The third warpgroup hands most of its registers to the softmax ones. */
@@ -1114,14 +990,14 @@ static EncodeTiledFn encode_fn(void) {
     return fn;
 }
 
-/* 2-D map over a bf16 [seq, heads*128] column slice with row stride ld:
- * box of 64 columns x 128 rows, 128-byte swizzle, zero fill outside. The
+/* 2-D map over a bf16 [seq, width] column slice with row stride ld: box of
+ * 64 columns x box_rows rows, 128-byte swizzle, zero fill outside. The
  * callers pass the same views block after block, so encoded maps are kept in
  * a small table keyed by the view (the map holds no data, only the address
  * and shape; a table entry stays valid for any buffer at that address). */
 struct MapKey {
     const void *base;
-    int seq, width, ld;
+    int seq, width, ld, box_rows;
 };
 static struct {
     MapKey key;
@@ -1130,11 +1006,12 @@ static struct {
 } g_maps[64];
 static unsigned long long g_map_clock = 0;
 
-static bool make_map(CUtensorMap *map, const void *base, int seq, int width, int ld) {
+bool make_tensor_map(void *map_out, const void *base, int seq, int width, int ld, int box_rows) {
+    CUtensorMap *map = static_cast<CUtensorMap *>(map_out);
     int victim = 0;
     for (int i = 0; i < 64; i++) {
         if (g_maps[i].used && g_maps[i].key.base == base && g_maps[i].key.seq == seq &&
-            g_maps[i].key.width == width && g_maps[i].key.ld == ld) {
+            g_maps[i].key.width == width && g_maps[i].key.ld == ld && g_maps[i].key.box_rows == box_rows) {
             g_maps[i].used = ++g_map_clock;
             *map = g_maps[i].map;
             return true;
@@ -1148,7 +1025,7 @@ static bool make_map(CUtensorMap *map, const void *base, int seq, int width, int
     }
     cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)seq};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64, 128};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box,
                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1159,7 +1036,7 @@ static bool make_map(CUtensorMap *map, const void *base, int seq, int width, int
         set_error(IRIS_B200_ECUDA, "cuTensorMapEncodeTiled", msg);
         return false;
     }
-    g_maps[victim].key = MapKey{base, seq, width, ld};
+    g_maps[victim].key = MapKey{base, seq, width, ld, box_rows};
     g_maps[victim].map = *map;
     g_maps[victim].used = ++g_map_clock;
     return true;
@@ -1292,6 +1169,7 @@ static int g_inject_ticket = 0;                         /* host-side fault injec
 static int g_configured = 0, g_sm_count = 0;
 
 void sm100_set_wait_limit_ns(unsigned long long ns) { g_wait_ns = ns ? ns : 1000000000ull; }
+unsigned long long wait_limit_ns(void) { return g_wait_ns; }
 void sm100_inject_stale_ticket(void) { g_inject_ticket = 1; }
 
 /* Number of key parts that shortens the schedule most, by a model in units
@@ -1407,13 +1285,13 @@ int launch_attention_sm100(const AttnArgs &a) {
     }
     CUtensorMap tmq, tmk[2] = {}, tmv[2] = {};
     const int width = heads * kHeadDim;
-    if (!make_map(&tmq, a.q, seq_q, width, a.ldq)) return IRIS_B200_ECUDA;
+    if (!make_tensor_map(&tmq, a.q, seq_q, width, a.ldq, kTileQ)) return IRIS_B200_ECUDA;
     for (int vw = 0; vw < 2; vw++) {
         if (view_rows[vw] == 0) {
             tmk[vw] = tmk[0];           /* never dereferenced */
             tmv[vw] = tmv[0];
-        } else if (!make_map(&tmk[vw], a.k[vw], view_rows[vw], width, a.ldkv[vw]) ||
-                   !make_map(&tmv[vw], a.v[vw], view_rows[vw], width, a.ldkv[vw])) {
+        } else if (!make_tensor_map(&tmk[vw], a.k[vw], view_rows[vw], width, a.ldkv[vw], kTileK) ||
+                   !make_tensor_map(&tmv[vw], a.v[vw], view_rows[vw], width, a.ldkv[vw], kTileK)) {
             return IRIS_B200_ECUDA;
         }
     }
@@ -1479,8 +1357,22 @@ int launch_attention_sm100(const AttnArgs &a) {
     p.items = p.nq * nparts;
     /* One CTA per SM at most (shared and tensor memory allow no more). */
     unsigned grid = (unsigned)(p.items < g_sm_count ? p.items : g_sm_count);
-    k_attention_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmq, tmk[0], tmv[0], tmk[1], tmv[1], p);
-    return after_launch("attention (tcgen05)") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+    /* Programmatic stream serialisation: the CTAs may be scheduled, and set
+     * up their barriers and tensor memory, as soon as the kernel ahead on the
+     * stream lets go of SMs; they wait for its completion inside the kernel. */
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = g.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, k_attention_sm100, tmq, tmk[0], tmv[0], tmk[1], tmv[1], p);
+    g.launches++;
+    return cuda_ok(err, "attention (tcgen05)") ? IRIS_B200_OK : IRIS_B200_ECUDA;
 }
 
 /* After a launch gave up on a wait: tickets and work-list counters may be
@@ -1499,6 +1391,7 @@ void sm100_release(void) {
     for (int i = 0; i < kScratchSets; i++)
         if (g_scratch[i].in_use) scratch_free(&g_scratch[i]);
     memset(g_maps, 0, sizeof(g_maps));
+    gemm_release();
     g_configured = 0;              /* the next device needs its own opt-in */
     g_sm_count = 0;
 }

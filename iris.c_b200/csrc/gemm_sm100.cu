@@ -1,0 +1,392 @@
+/*
+ * QKV projection with the attention prologue as its epilogue, for sm_100a.
+ *
+ * y[rows, out] = x[rows, in] . W[out, in]^T, bf16 operands, fp32 accumulation
+ * in tensor memory, bf16 result: the reference's iris_dev_linear_bf16
+ * (iris_cuda.cu:463-506, a cuBLAS call). In the transformer blocks that GEMM
+ * is followed at once by two iris_dev_head_norm_rope passes over the Q and K
+ * column blocks of its output (iris_transformer_flux.c:3795-3801, 3832-3837).
+ * A head is 128 columns, exactly half an N tile here, so the epilogue can do
+ * the per-head RMSNorm and the pair rotation on the accumulator row it already
+ * holds and the prologue's read-modify-write of Q and K disappears.
+ *
+ * Arithmetic of a Q / K head in the epilogue mirrors the two-kernel sequence
+ * of the reference: the accumulator is first rounded to bf16 (what the GEMM
+ * would have stored), then widened, normalised (inv = rsqrt(mean(x^2) + eps),
+ * a = x * (inv * w)), rotated, and rounded once more (iris_cuda.cu:403-420).
+ *
+ * Tiles: 128 rows x 256 columns per CTA (MMA M = 128, N = 256, K = 16), K in
+ * blocks of 64 through a four-stage TMA ring (48 KB per stage). Two fp32
+ * accumulators of 256 columns fill the tensor memory, so the epilogue of a
+ * tile runs under the main loop of the next. Persistent grid, tiles dealt
+ * round-robin with the row tiles of one column tile next to each other (they
+ * share W through L2).
+ *
+ * Warps (192 threads): 0 TMA producer, 1 MMA issuer and owner of the tensor
+ * memory, 2-5 epilogue (thread = accumulator row; rows leave through a
+ * swizzled staging area so that global memory sees whole 128-byte segments).
+ * Waits are bounded like those of the attention kernel.
+ */
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include "kernels.h"
+#include "tc_ptx.cuh"
+
+namespace iris_b200 {
+
+namespace gemm {
+
+using namespace sm100;
+
+static constexpr int kTileM = 128, kTileN = 256, kBlockK = 64;
+static constexpr int kStages = 4;
+static constexpr int kBytesA = kTileM * kBlockK * 2;        /* 16 KB */
+static constexpr int kBytesB = kTileN * kBlockK * 2;        /* 32 KB */
+static constexpr int kStageBytes = kBytesA + kBytesB;
+static constexpr int kThreads = 192;
+static constexpr int kSmemStage = kStages * kStageBytes;    /* epilogue staging: 4 warps x 4 KB */
+static constexpr int kSmemW = kSmemStage + 4 * 4096;        /* norm weights: wq[128] | wk[128] fp32 */
+static constexpr int kSmemBar = kSmemW + 1024;
+static constexpr int kSmemBytes = kSmemBar + 256 + 1024;    /* + barriers + alignment slack */
+static constexpr uint32_t kIdesc = idesc_bf16(kTileM, kTileN);
+
+enum {
+    BAR_FULL = 0,                       /* kStages */
+    BAR_EMPTY = BAR_FULL + kStages,     /* kStages */
+    BAR_ACC_FULL = BAR_EMPTY + kStages, /* 2 */
+    BAR_ACC_EMPTY = BAR_ACC_FULL + 2,   /* 2 */
+    BAR_DRAIN = BAR_ACC_EMPTY + 2,
+    BAR_COUNT
+};
+static constexpr int kSmemTmemPtr = BAR_COUNT * 8;
+static constexpr int kSmemAbort = kSmemTmemPtr + 4;
+
+struct Params {
+    uint16_t *y;
+    int ldy;
+    int rows, in, out;
+    int tiles_m, tiles_n;
+    int norm_cols;              /* columns [0, norm_cols) are Q heads, [norm_cols, 2 norm_cols) K heads; 0: plain GEMM */
+    const float *wq, *wk;       /* [128] */
+    const float *rope_cos, *rope_sin;   /* [rows, 64] */
+    float eps;
+    unsigned int *status;
+    unsigned long long wait_ns;
+};
+
+struct Ctx {
+    uint32_t bars;
+    volatile uint32_t *abort_flag;
+    unsigned int *status;
+    unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ bool wait(const Ctx &c, int idx, uint32_t parity, int site) {
+    const uint32_t bar = c.bars + idx * 8;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t spin = 0;; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 63u) {
+            if (*c.abort_flag) return false;
+            if (global_ns() - t0 > c.wait_ns || spin > (1u << 26)) {
+                *c.abort_flag = 1u;
+                if (atomicCAS(c.status, 0u, 1u) == 0u) {
+                    c.status[1] = (unsigned)site;
+                    c.status[2] = blockIdx.x;
+                    c.status[3] = parity;
+                }
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmx, const CUtensorMap *tmw,
+                                         uint32_t smem) {
+    const int nkb = (p.in + kBlockK - 1) / kBlockK;
+    int issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.tiles_m * p.tiles_n; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * kTileM, n0 = (tile / p.tiles_m) * kTileN;
+        for (int kb = 0; kb < nkb; kb++, issued++) {
+            const int s = issued % kStages;
+            if (issued >= kStages && !(ok = wait(c, BAR_EMPTY + s, ((issued / kStages) - 1) & 1u, 400 + s))) break;
+            const uint32_t full = c.bars + (BAR_FULL + s) * 8;
+            mbar_expect_tx(full, kStageBytes);
+            tma_load_2d(smem + s * kStageBytes, tmx, kb * kBlockK, m0, full);
+            tma_load_2d(smem + s * kStageBytes + kBytesA, tmw, kb * kBlockK, n0, full);
+        }
+    }
+    if (*c.abort_flag) {
+        /* Nobody may be consuming any more: wait for the copies still in flight. */
+        for (int it = issued > kStages ? issued - kStages : 0; it < issued; it++)
+            wait(c, BAR_FULL + it % kStages, (it / kStages) & 1u, 490);
+    }
+}
+
+__device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem) {
+    const int nkb = (p.in + kBlockK - 1) / kBlockK;
+    const uint32_t hi = (uint32_t)(make_desc(0, 0, 1024 / 16) >> 32);      /* 8 rows of 128 B */
+    const uint32_t lo0 = (uint32_t)make_desc(smem, 1, 0);
+    const bool leader = elect_one();
+    int consumed = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x, n = 0; ok && tile < p.tiles_m * p.tiles_n; tile += gridDim.x, n++) {
+        const int buf = n & 1;
+        /* The epilogue has emptied this accumulator (its use two tiles ago). */
+        if (n >= 2 && !(ok = __all_sync(0xffffffffu, wait(c, BAR_ACC_EMPTY + buf, ((n >> 1) - 1) & 1u, 410 + buf)))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < nkb; kb++, consumed++) {
+            const int s = consumed % kStages;
+            if (!(ok = __all_sync(0xffffffffu, wait(c, BAR_FULL + s, (consumed / kStages) & 1u, 420 + s)))) break;
+            tc_fence_after();
+            const uint32_t lo_a = lo0 + ((s * kStageBytes) >> 4), lo_b = lo_a + (kBytesA >> 4);
+#pragma unroll
+            for (int ks = 0; ks < kBlockK / 16; ks++) {
+                if (leader)
+                    mma_ss(tmem + buf * kTileN, ((uint64_t)hi << 32) | (lo_a + ks * 2), ((uint64_t)hi << 32) | (lo_b + ks * 2),
+                           kIdesc, (kb | ks) != 0);
+            }
+            if (leader) tc_commit(c.bars + (BAR_EMPTY + s) * 8);
+        }
+        if (ok && leader) tc_commit(c.bars + (BAR_ACC_FULL + buf) * 8);
+    }
+    if (!ok) {
+        if (leader) tc_commit(c.bars + BAR_DRAIN * 8);
+        const uint32_t bar = c.bars + BAR_DRAIN * 8;
+        const unsigned long long t0 = global_ns();
+        while (!mbar_try_wait(bar, 0) && global_ns() - t0 < c.wait_ns) {}
+    }
+}
+
+/* 32 rows x 64 bf16 columns (128 bytes per row) of one warp to global memory
+ * through its staging area: thread `lane` holds its row's 32 packed words;
+ * the 16-byte chunks are XOR-swizzled by the row so that neither the row-wise
+ * writes nor the segment-wise reads conflict. Rows >= nrows and columns >=
+ * ncols (a multiple of 8) are not stored. */
+__device__ __forceinline__ void store_rows_bf16(const uint32_t *pk, uint16_t *base, size_t ld, int nrows, int ncols,
+                                                unsigned char *stage_w, int lane) {
+#pragma unroll
+    for (int ch = 0; ch < 8; ch++)
+        *reinterpret_cast<uint4 *>(stage_w + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
+            make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+    __syncwarp();
+    const int ch = lane & 7;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int r = k * 4 + (lane >> 3);
+        const uint4 val = *reinterpret_cast<const uint4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4));
+        if (r < nrows && ch * 8 < ncols) *reinterpret_cast<uint4 *>(base + (size_t)r * ld + ch * 8) = val;
+    }
+    __syncwarp();
+}
+
+__device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned char *stage, const float *w_smem,
+                                         uint32_t tmem) {
+    const int lane = threadIdx.x & 31;
+    const int quarter = (threadIdx.x >> 5) & 3;                 /* TMEM lane quarter of this warp */
+    const int row_in_tile = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    unsigned char *stage_w = stage + quarter * 4096;
+    for (int tile = blockIdx.x, n = 0; tile < p.tiles_m * p.tiles_n; tile += gridDim.x, n++) {
+        const int buf = n & 1;
+        const int m0 = (tile % p.tiles_m) * kTileM, n0 = (tile / p.tiles_m) * kTileN;
+        if (!__all_sync(0xffffffffu, wait(c, BAR_ACC_FULL + buf, (n >> 1) & 1u, 430 + buf))) return;
+        tc_fence_after();
+        const int row = m0 + row_in_tile;
+        const int wrow0 = m0 + quarter * 32;
+        const int nrows = p.rows - wrow0 < 32 ? (p.rows - wrow0 < 0 ? 0 : p.rows - wrow0) : 32;
+        const bool row_ok = row < p.rows;
+#pragma unroll 1
+        for (int half = 0; half < 2; half++) {
+            const int col0 = n0 + half * 128;
+            if (col0 >= p.out) break;
+            /* 0 / 1: a Q / K head (norm + rotation), 2: plain columns */
+            const int kind = col0 < p.norm_cols ? 0 : (col0 < 2 * p.norm_cols ? 1 : 2);
+            uint32_t acc[128];
+#pragma unroll
+            for (int ch = 0; ch < 4; ch++) tmem_ld32(tmem + lane_base + buf * kTileN + half * 128 + ch * 32, acc + ch * 32);
+            tc_wait_ld();
+            float inv = 1.0f;
+            if (kind < 2) {
+                /* What the GEMM would have stored, then the sum of squares of that. */
+                float ss0 = 0.0f, ss1 = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 128; e += 2) {
+                    const uint32_t pkd = cvt_bf16x2(__uint_as_float(acc[e]), __uint_as_float(acc[e + 1]));
+                    const float a = bf_lo(pkd), b = bf_hi(pkd);
+                    acc[e] = __float_as_uint(a);
+                    acc[e + 1] = __float_as_uint(b);
+                    ss0 = fmaf(a, a, ss0);
+                    ss1 = fmaf(b, b, ss1);
+                }
+                inv = rsqrtf((ss0 + ss1) * (1.0f / 128.0f) + p.eps);
+            }
+            const float *w = w_smem + (kind == 1 ? 128 : 0);
+            const float4 *cosr = reinterpret_cast<const float4 *>(p.rope_cos + (size_t)(row_ok ? row : 0) * 64);
+            const float4 *sinr = reinterpret_cast<const float4 *>(p.rope_sin + (size_t)(row_ok ? row : 0) * 64);
+#pragma unroll
+            for (int pass = 0; pass < 2; pass++) {              /* 64 columns = 32 pairs per pass */
+                uint32_t pk[32];
+                if (kind < 2) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; q4++) {
+                        const float4 cc = cosr[pass * 8 + q4], sn = sinr[pass * 8 + q4];
+                        const float cj[4] = {cc.x, cc.y, cc.z, cc.w}, sj[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const int e = pass * 64 + q4 * 8 + 2 * j;
+                            const float a = __uint_as_float(acc[e]) * (inv * w[e]);
+                            const float b = __uint_as_float(acc[e + 1]) * (inv * w[e + 1]);
+                            pk[q4 * 4 + j] = cvt_bf16x2(a * cj[j] - b * sj[j], b * cj[j] + a * sj[j]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e++)
+                        pk[e] = cvt_bf16x2(__uint_as_float(acc[pass * 64 + 2 * e]), __uint_as_float(acc[pass * 64 + 2 * e + 1]));
+                }
+                const int c0 = col0 + pass * 64;
+                const int ncols = p.out - c0 < 64 ? (p.out - c0 < 0 ? 0 : p.out - c0) : 64;
+                store_rows_bf16(pk, p.y + (size_t)wrow0 * p.ldy + c0, (size_t)p.ldy, nrows, ncols, stage_w, lane);
+            }
+        }
+        /* Every read of this accumulator has been waited for. */
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(c.bars + (BAR_ACC_EMPTY + buf) * 8);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw,
+               const __grid_constant__ Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *smem_gen = smem_raw + (smem - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    Ctx c;
+    c.bars = smem + kSmemBar;
+    c.abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemAbort);
+    c.status = p.status;
+    c.wait_ns = p.wait_ns;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemTmemPtr);
+    float *w_smem = reinterpret_cast<float *>(smem_gen + kSmemW);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; s++) {
+            mbar_init(c.bars + (BAR_FULL + s) * 8, 1);
+            mbar_init(c.bars + (BAR_EMPTY + s) * 8, 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(c.bars + (BAR_ACC_FULL + b) * 8, 1);
+            mbar_init(c.bars + (BAR_ACC_EMPTY + b) * 8, 4);          /* one arrival per epilogue warp */
+        }
+        mbar_init(c.bars + BAR_DRAIN * 8, 1);
+        *c.abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem + kSmemBar + kSmemTmemPtr), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (p.norm_cols > 0)
+        for (int i = threadIdx.x; i < 256; i += kThreads) w_smem[i] = i < 128 ? p.wq[i] : p.wk[i - 128];
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) producer(c, p, &tmx, &tmw, smem);
+    } else if (warp == 1) {
+        mma_issuer(c, p, smem, tmem);
+    } else {
+        epilogue(c, p, smem_gen + kSmemStage, w_smem, tmem);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace gemm
+
+static int g_gemm_configured = 0;
+
+void gemm_release(void) { g_gemm_configured = 0; }
+
+/* y [rows, out] (row stride ldy) = x [rows, in] . W [out, in]^T; with heads > 0
+ * the first 2 * heads * 128 columns are Q and K heads that get the prologue. */
+static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W, int rows, int in, int out,
+                         int heads, const float *wq, const float *wk, const float *rope_cos, const float *rope_sin,
+                         float eps, const char *op) {
+    using namespace gemm;
+    if (!require_device(op)) return IRIS_B200_ENODEV;
+    if (!y || !x || !W || rows < 0 || in <= 0 || out <= 0 || ldy < out || heads < 0 ||
+        (heads > 0 && (!wq || !wk || !rope_cos || !rope_sin || 2 * heads * 128 > out))) {
+        set_error(IRIS_B200_EINVAL, op, "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    const uintptr_t bits = (uintptr_t)y | (uintptr_t)x | (uintptr_t)W | (uintptr_t)rope_cos | (uintptr_t)rope_sin;
+    if ((bits & 15) != 0 || in % 8 != 0 || out % 8 != 0 || ldy % 8 != 0) {
+        set_error(IRIS_B200_EUNSUPPORTED, op, "operands must be 16-byte aligned, in / out / ldy multiples of 8");
+        return IRIS_B200_EUNSUPPORTED;
+    }
+    if (rows == 0) return IRIS_B200_OK;
+    if (!g_gemm_configured) {
+        if (!cuda_ok(cudaFuncSetAttribute(k_linear_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                     "linear smem opt-in"))
+            return IRIS_B200_ECUDA;
+        g_gemm_configured = 1;
+    }
+    CUtensorMap tmx, tmw;
+    if (!make_tensor_map(&tmx, x, rows, in, in, kTileM) || !make_tensor_map(&tmw, W, out, in, in, kTileN))
+        return IRIS_B200_ECUDA;
+    Params p = {};
+    p.y = y;
+    p.ldy = ldy;
+    p.rows = rows;
+    p.in = in;
+    p.out = out;
+    p.tiles_m = (rows + kTileM - 1) / kTileM;
+    p.tiles_n = (out + kTileN - 1) / kTileN;
+    p.norm_cols = heads * 128;
+    p.wq = wq;
+    p.wk = wk;
+    p.rope_cos = rope_cos;
+    p.rope_sin = rope_sin;
+    p.eps = eps;
+    p.status = g.dev_status;
+    p.wait_ns = wait_limit_ns();
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    const unsigned grid = (unsigned)(tiles < g.sm_count ? tiles : g.sm_count);
+    k_linear_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmx, tmw, p);
+    return after_launch(op) ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+}  // namespace iris_b200
+
+using namespace iris_b200;
+
+extern "C" void iris_dev_linear_bf16(uint16_t *y, const uint16_t *x, const uint16_t *W, int rows, int in, int out) {
+    launch_linear(y, out, x, W, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, "linear_bf16");
+}
+
+extern "C" int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W,
+                                             int rows, int in, int out, int heads,
+                                             const float *wq, const float *wk,
+                                             const float *rope_cos, const float *rope_sin, float eps) {
+    return launch_linear(y, ldy, x, W, rows, in, out, heads, wq, wk, rope_cos, rope_sin, eps, "linear_qk_norm_rope");
+}

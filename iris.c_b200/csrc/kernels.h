@@ -49,13 +49,22 @@ AttnArgs attn_args(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uin
 
 int launch_attention_sm100(const AttnArgs &a);
 
+/* Encodes (or finds in a small table) the TMA descriptor of a bf16 [rows, width]
+ * matrix with row stride ld: boxes of 64 columns x box_rows rows, 128-byte
+ * swizzle, zero fill outside. map_out: a CUtensorMap. */
+bool make_tensor_map(void *map_out, const void *base, int rows, int width, int ld, int box_rows);
+
 void sm100_release(void);
 
 /* Clears the tickets and work-list counters (after a device wait timed out). */
 void sm100_reset_split(void);
 
-/* Limit of every wait inside the kernel (0 restores the default of 1 s). */
+/* Limit of every wait inside the kernels (0 restores the default of 1 s). */
 void sm100_set_wait_limit_ns(unsigned long long ns);
+unsigned long long wait_limit_ns(void);
+
+/* Per-device launch configuration of the GEMM is redone after a cleanup. */
+void gemm_release(void);
 
 /* Host-side fault injection: the next launch that splits its keys finds a
  * ticket that nobody took. */

@@ -141,14 +141,20 @@ k_head_norm_rope_128(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
  * and eight weights are loaded once per token and folded into four products
  * per pair (cos * w, sin * w), so a head costs one 16-byte load, the sum of
  * squares, six FMA-pipe operations per pair and one 16-byte store. kHeadsInFlight
- * heads are loaded before the first is used. */
+ * heads are loaded before the first is used, and the next kHeadsInFlight before
+ * that one is stored. */
 static constexpr int kHeadsInFlight = 4;
+static constexpr int kTokBlocksPerSM = 3;    /* two batches of heads in registers: 65536 / (3 * 256) = 85 */
 
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, kTokBlocksPerSM)
 k_head_norm_rope_128_tok(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int ld,
                          const float *__restrict__ wq, const float *__restrict__ wk,
                          const float *__restrict__ rope_cos, const float *__restrict__ rope_sin,
                          int seq, int heads, float eps) {
+    /* A launch that follows with programmatic stream serialisation (the
+     * attention) may set itself up while this grid runs; it waits for this
+     * grid's completion before it reads anything. */
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane16 = threadIdx.x & 15;
     const int group = (int)(((long long)blockIdx.x * kThreads + threadIdx.x) >> 4);
     const int ngroups = (int)(((long long)gridDim.x * kThreads) >> 4);
@@ -176,11 +182,17 @@ k_head_norm_rope_128_tok(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int
             cw1[j] = cc[j] * ww[2 * j + 1];
             sw0[j] = ss4[j] * ww[2 * j];
         }
+        /* The next batch of heads is on its way while the current one is
+         * worked on and stored: loads stay outstanding all the time. */
+        Vec8 v[kHeadsInFlight], nx[kHeadsInFlight];
+#pragma unroll
+        for (int i = 0; i < kHeadsInFlight; i++)
+            if (live && i < heads) v[i] = *reinterpret_cast<const Vec8 *>(base + i * 128);
         for (int h0 = 0; h0 < heads; h0 += kHeadsInFlight) {
-            Vec8 v[kHeadsInFlight];
 #pragma unroll
             for (int i = 0; i < kHeadsInFlight; i++)
-                if (live && h0 + i < heads) v[i] = *reinterpret_cast<const Vec8 *>(base + (h0 + i) * 128);
+                if (live && h0 + kHeadsInFlight + i < heads)
+                    nx[i] = *reinterpret_cast<const Vec8 *>(base + (h0 + kHeadsInFlight + i) * 128);
 #pragma unroll
             for (int i = 0; i < kHeadsInFlight; i++) {
                 const bool ok = live && h0 + i < heads;
@@ -206,6 +218,8 @@ k_head_norm_rope_128_tok(uint16_t *__restrict__ q, uint16_t *__restrict__ k, int
                     *reinterpret_cast<Vec8 *>(base + (h0 + i) * 128) = o;
                 }
             }
+#pragma unroll
+            for (int i = 0; i < kHeadsInFlight; i++) v[i] = nx[i];
         }
     }
 }
@@ -263,7 +277,7 @@ static int launch_prologue(uint16_t *q, uint16_t *k, int ld, const float *wq, co
         else {
             long long segs = (long long)seq * (k ? 2 : 1);
             long long tb = (segs * 16 + kThreads - 1) / kThreads;
-            if (tb > (long long)g.sm_count * 4) tb = (long long)g.sm_count * 4;
+            if (tb > (long long)g.sm_count * kTokBlocksPerSM) tb = (long long)g.sm_count * kTokBlocksPerSM;
             k_head_norm_rope_128_tok<<<(unsigned)tb, kThreads, 0, g.stream>>>(
                 q, k, ld, wq, wk, rope_cos, rope_sin, seq, heads, eps);
         }
