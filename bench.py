@@ -574,6 +574,51 @@ def projection_run(job, w, pk, reps=20):
             "speedup_vs_cublas_plus_prologue": round(both_ms / fused_ms, 3)}
 
 
+def outproj_run(job, pk, reps=20):
+    """The step after the path with the heads sharded over the ranks (N > 1):
+    the Klein-4B block's out-projection, [4608, dim / N] x [dim, dim / N]^T per
+    rank, whose fp32 partial sums are reduced across the ranks by the GEMM's
+    epilogue (stores over NVLink to the rows' owners) and folded into the
+    gated residual on the owner. Needs the group of the ring."""
+    lib, torch, rank, world = job.lib, job.torch, job.rank, job.world
+    w = WORKLOADS["klein4b-1024"]
+    S, dim = seq_len(w), w["heads"] * D
+    a, b = C.c_int(), C.c_int()
+    rows_of = np.zeros(world, np.int32)
+    for r in range(world):
+        lib.iris_b200_seq_shard(S, world, r, C.byref(a), C.byref(b))
+        rows_of[r] = b.value
+    lib.iris_b200_head_shard(w["heads"], world, rank, C.byref(a), C.byref(b))
+    k0, k = a.value * D, b.value * D
+    gen = torch.Generator(device="cuda").manual_seed(9 + rank)
+    cat = torch.randn((S, k), generator=gen, device="cuda").to(torch.bfloat16)
+    W = (torch.randn((dim, dim), generator=gen, device="cuda") / dim ** 0.5).to(torch.bfloat16)
+    x = torch.zeros((int(rows_of[rank]), dim), device="cuda", dtype=torch.float32)
+    gate = torch.ones(dim, device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+
+    def call():
+        rc = lib.iris_b200_outproj_residual(x.data_ptr(), cat.data_ptr(), k, W.data_ptr() + k0 * 2, dim, gate.data_ptr(),
+                                            rows_of.ctypes.data, k, dim)
+        assert rc == 0, rc
+
+    for _ in range(3):
+        call()
+    job.barrier()
+    lib.iris_b200_mark(0)
+    for _ in range(reps):
+        call()
+    lib.iris_b200_mark(1)
+    job.barrier()
+    ms = job.max_over_ranks([lib.iris_b200_mark_elapsed_ms(0, 1) / reps])[0]
+    lib.check()
+    sent = float(S - rows_of[rank]) * dim * 4
+    return {"shape": [S, dim // world, dim], "ms": round(ms, 4),
+            "what": "GEMM + reduce-scatter in its epilogue (peer stores) + gated residual on the owner",
+            "gemm_tflops_aggregate": round(2.0 * S * dim * dim / ms / 1e9, 1),
+            "nvlink_bytes_per_rank": sent, "nvlink_gbs_per_rank": round(sent / ms / 1e6, 1)}
+
+
 def extra_run(job, name, mode, steps, warmup, pk):
     """A further workload / decomposition measured in the same run: ms per
     step (max over ranks), aggregate TFLOP/s and per-GPU share of the peak."""
@@ -645,6 +690,8 @@ def run_b200(args):
         for other in ("klein9b-cfg", "zimage-turbo"):
             if other != name:
                 extras[other] = extra_run(job, other, "shard", args.steps, args.warmup, pk)
+        if mode == "ring":
+            extras["klein4b-1024 out-projection, heads sharded"] = outproj_run(job, pk)
 
     # CPU leg on the same inputs (rank 0), and the parity of the two results.
     cpu = parity = ref_gpu = None

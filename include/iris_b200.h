@@ -274,6 +274,27 @@ void iris_b200_ring_destroy(void);
 int iris_b200_ring_trace(int enable);
 int iris_b200_ring_timeline(float *ms, int cap);
 
+/* The out-projection after head-parallel attention, with its gated residual
+ * and the reduction across ranks in one pass. The reference runs
+ * iris_dev_linear_f32 + iris_dev_residual on one GPU
+ * (iris_transformer_flux.c:3811-3812, 3841-3842; iris_cuda.cu:339-343). Here
+ * rank r holds the k columns of the attention output that belong to its heads
+ * (cat [seq, k] bf16, row stride ldc, all seq = sum(rows_of) rows) and the
+ * matching k columns of the projection weights (W points at column k0 of the
+ * row-major [dim, dim_in] matrix, row stride ldw). Its tcgen05 GEMM produces
+ * fp32 partial sums for all rows; the epilogue stores every tile row straight
+ * into the staging slab of the rank that owns the row (plain stores over
+ * NVLink, rows_of[q] rows belong to rank q), and the owner adds
+ * x_rows [rows_of[rank], dim] += gate [dim] * (sum over ranks) once every
+ * rank's arrival word has come (bounded wait, IRIS_B200_ETIMEOUT otherwise;
+ * gate NULL: plain sum). A reduce-scatter fused into the GEMM: no collective
+ * library call and no separate pass over the partial sums. Needs the group of
+ * iris_b200_ring_init() (one rank is allowed) and peer access between the
+ * GPUs; dim a multiple of 8, k of 8, pointers 16-byte aligned. Collective:
+ * every rank calls it with the same rows_of and dim. */
+int iris_b200_outproj_residual(float *x_rows, const uint16_t *cat, int ldc, const uint16_t *W, int ldw,
+                               const float *gate, const int *rows_of, int k, int dim);
+
 /* The ring protocol on host threads (no device): one thread per rank and
  * memcpy in place of the copy engines, the same slots, pool sets, arrival
  * words, ring order and bounded waits as ring_attention(); the consumer

@@ -83,6 +83,7 @@ SIGNATURES = {
     "iris_b200_stream_sync": (INT, [VP]),
     "iris_b200_ring_configure": (INT, [INT, INT]),
     "iris_b200_ring_transport": (INT, []),
+    "iris_b200_outproj_residual": (INT, [VP, VP, INT, VP, INT, VP, VP, INT, INT]),
     "iris_b200_ring_loopback": (INT, [INT, VP, INT, INT, C.c_uint, VP, INT, VP, VP, VP]),
     "iris_b200_ring_loopback_digest": (C.c_uint64, [INT, VP, INT, INT, INT]),
     "iris_b200_ring_trace": (INT, [INT]),

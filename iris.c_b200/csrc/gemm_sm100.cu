@@ -62,6 +62,7 @@ enum {
 };
 static constexpr int kSmemTmemPtr = BAR_COUNT * 8;
 static constexpr int kSmemAbort = kSmemTmemPtr + 4;
+static constexpr int kMaxScatterRanks = 16;
 
 struct Params {
     uint16_t *y;
@@ -74,6 +75,18 @@ struct Params {
     float eps;
     unsigned int *status;
     unsigned long long wait_ns;
+    /* Row-parallel mode (the out-projection after head-parallel attention):
+     * the fp32 tile rows are not stored to y but scattered to the rank that
+     * owns each row, into this rank's slab of the owner's staging buffer,
+     * with plain stores over NVLink; the last CTA out then advances this
+     * rank's arrival word on every owner. */
+    int scatter;                /* 0: bf16 result to y; 1: fp32 rows to their owners */
+    int nranks;
+    int row_first[kMaxScatterRanks + 1];    /* rank q owns the rows [row_first[q], row_first[q + 1]) */
+    float *slab[kMaxScatterRanks];          /* where this rank's partial rows of owner q go ([rows of q, out] fp32) */
+    uint32_t *arrive[kMaxScatterRanks];     /* this rank's arrival word on owner q */
+    uint32_t seq;
+    unsigned int *done;                     /* CTAs that are through; zero between launches */
 };
 
 struct Ctx {
@@ -184,6 +197,32 @@ __device__ __forceinline__ void store_rows_bf16(const uint32_t *pk, uint16_t *ba
     __syncwarp();
 }
 
+/* 32 rows x 32 fp32 columns of one warp to the owners of the rows: staged like
+ * the bf16 rows, each 128-byte row segment then goes to the slab of the rank
+ * that owns the row (ncols a multiple of 4). */
+__device__ __forceinline__ void scatter_rows_f32(const uint32_t *src, const Params &p, int wrow0, int nrows, int c0,
+                                                 int ncols, unsigned char *stage_w, int lane) {
+#pragma unroll
+    for (int c8 = 0; c8 < 8; c8++)
+        *reinterpret_cast<uint4 *>(stage_w + lane * 128 + ((c8 ^ (lane & 7)) << 4)) =
+            make_uint4(src[4 * c8], src[4 * c8 + 1], src[4 * c8 + 2], src[4 * c8 + 3]);
+    __syncwarp();
+    const int ch = lane & 7;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int r = k * 4 + (lane >> 3);
+        const uint4 v = *reinterpret_cast<const uint4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4));
+        if (r < nrows && ch * 4 < ncols) {
+            const int row = wrow0 + r;
+            int q = 0;
+            while (q + 1 < p.nranks && row >= p.row_first[q + 1]) q++;
+            float *dst = p.slab[q] + (size_t)(row - p.row_first[q]) * p.out + c0 + ch * 4;
+            *reinterpret_cast<uint4 *>(dst) = v;
+        }
+    }
+    __syncwarp();
+}
+
 __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned char *stage, const float *w_smem,
                                          uint32_t tmem) {
     const int lane = threadIdx.x & 31;
@@ -210,6 +249,15 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) tmem_ld32(tmem + lane_base + buf * kTileN + half * 128 + ch * 32, acc + ch * 32);
             tc_wait_ld();
+            if (p.scatter) {
+#pragma unroll
+                for (int sub = 0; sub < 4; sub++) {
+                    const int c0 = col0 + sub * 32;
+                    const int ncols = p.out - c0 < 32 ? (p.out - c0 < 0 ? 0 : p.out - c0) : 32;
+                    scatter_rows_f32(acc + sub * 32, p, wrow0, nrows, c0, ncols, stage_w, lane);
+                }
+                continue;
+            }
             float inv = 1.0f;
             if (kind < 2) {
                 /* What the GEMM would have stored, then the sum of squares of that. */
@@ -312,12 +360,81 @@ k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
         epilogue(c, p, smem_gen + kSmemStage, w_smem, tmem);
     }
 
+    if (p.scatter) __threadfence_system();          /* this thread's rows are out before the CTA counts itself out */
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+    /* Row-parallel mode: once every CTA's rows are on their way (each fenced
+     * at system scope above), the last CTA tells every owner that this rank's
+     * partial sums of the call have arrived. A launch that gave up tells nobody. */
+    if (p.scatter && threadIdx.x == 0) {
+        const bool aborted = *c.abort_flag != 0u;
+        __threadfence();
+        const unsigned int prev = atomicAdd(p.done, aborted ? 0x10000u + 1u : 1u);
+        if ((prev & 0xFFFFu) == gridDim.x - 1) {
+            const bool any_aborted = aborted || (prev >> 16) != 0u;
+            *p.done = 0u;
+            if (!any_aborted) {
+                __threadfence_system();
+                for (int q = 0; q < p.nranks; q++)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.arrive[q]), "r"(p.seq) : "memory");
+            }
+        }
+    }
+}
+
+/* Owner side of the row-parallel mode: x[r, c] += gate[c] * sum over the
+ * ranks' slabs (gate NULL: plain sum), after every rank's arrival word has
+ * reached the call's sequence number (bounded wait; a word that does not come
+ * is reported in the status word and nothing is added). The reference does the
+ * same arithmetic in iris_dev_residual (iris_cuda.cu:339-343) on one GPU. */
+__global__ void k_residual_from_slabs(float *x, const float *slabs, size_t slab_stride, int nranks, const float *gate,
+                                      int rows, int dim, const uint32_t *arrive, uint32_t seq, unsigned long long wait_ns,
+                                      unsigned int *status) {
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        const unsigned long long t0 = global_ns();
+        for (int r = 0; r < nranks && ok; r++) {
+            for (uint32_t spin = 0;; spin++) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(arrive + r) : "memory");
+                if ((int32_t)(v - seq) >= 0) break;
+                if ((spin & 7u) == 7u) {
+                    if (global_ns() - t0 > wait_ns || spin > (1u << 26)) {
+                        if (atomicCAS(status, 0u, 1u) == 0u) {
+                            status[1] = 500u;
+                            status[2] = blockIdx.x;
+                            status[3] = (unsigned)r;
+                        }
+                        ok = 0;
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+            }
+        }
+        ok_s = ok;
+    }
+    __syncthreads();
+    if (!ok_s) return;
+    const size_t n4 = (size_t)rows * dim / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < nranks; r++) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(slabs + (size_t)r * slab_stride) + i);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        const int c = (int)((i * 4) % (size_t)dim);
+        float4 g4 = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (gate) g4 = *reinterpret_cast<const float4 *>(gate + c);
+        float4 xv = reinterpret_cast<float4 *>(x)[i];
+        xv.x += g4.x * sum.x; xv.y += g4.y * sum.y; xv.z += g4.z * sum.z; xv.w += g4.w * sum.w;
+        reinterpret_cast<float4 *>(x)[i] = xv;
     }
 }
 
@@ -329,19 +446,20 @@ void gemm_release(void) { g_gemm_configured = 0; }
 
 /* y [rows, out] (row stride ldy) = x [rows, in] . W [out, in]^T; with heads > 0
  * the first 2 * heads * 128 columns are Q and K heads that get the prologue. */
-static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W, int rows, int in, int out,
-                         int heads, const float *wq, const float *wk, const float *rope_cos, const float *rope_sin,
-                         float eps, const char *op) {
+static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const uint16_t *W, int ldw, int rows, int in,
+                         int out, int heads, const float *wq, const float *wk, const float *rope_cos,
+                         const float *rope_sin, float eps, const ScatterArgs *sc, const char *op) {
     using namespace gemm;
     if (!require_device(op)) return IRIS_B200_ENODEV;
-    if (!y || !x || !W || rows < 0 || in <= 0 || out <= 0 || ldy < out || heads < 0 ||
-        (heads > 0 && (!wq || !wk || !rope_cos || !rope_sin || 2 * heads * 128 > out))) {
+    if ((!y && !sc) || !x || !W || rows < 0 || in <= 0 || out <= 0 || (y && ldy < out) || heads < 0 || ldx < in || ldw < in ||
+        (heads > 0 && (!wq || !wk || !rope_cos || !rope_sin || 2 * heads * 128 > out)) ||
+        (sc && (sc->nranks < 1 || sc->nranks > kMaxScatterRanks))) {
         set_error(IRIS_B200_EINVAL, op, "bad argument");
         return IRIS_B200_EINVAL;
     }
     const uintptr_t bits = (uintptr_t)y | (uintptr_t)x | (uintptr_t)W | (uintptr_t)rope_cos | (uintptr_t)rope_sin;
-    if ((bits & 15) != 0 || in % 8 != 0 || out % 8 != 0 || ldy % 8 != 0) {
-        set_error(IRIS_B200_EUNSUPPORTED, op, "operands must be 16-byte aligned, in / out / ldy multiples of 8");
+    if ((bits & 15) != 0 || in % 8 != 0 || out % 8 != 0 || ldy % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) {
+        set_error(IRIS_B200_EUNSUPPORTED, op, "operands must be 16-byte aligned, in / out / row strides multiples of 8");
         return IRIS_B200_EUNSUPPORTED;
     }
     if (rows == 0) return IRIS_B200_OK;
@@ -352,7 +470,7 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, const uint16_t
         g_gemm_configured = 1;
     }
     CUtensorMap tmx, tmw;
-    if (!make_tensor_map(&tmx, x, rows, in, in, kTileM) || !make_tensor_map(&tmw, W, out, in, in, kTileN))
+    if (!make_tensor_map(&tmx, x, rows, in, ldx, kTileM) || !make_tensor_map(&tmw, W, out, in, ldw, kTileN))
         return IRIS_B200_ECUDA;
     Params p = {};
     p.y = y;
@@ -370,10 +488,37 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, const uint16_t
     p.eps = eps;
     p.status = g.dev_status;
     p.wait_ns = wait_limit_ns();
+    if (sc) {
+        p.scatter = 1;
+        p.nranks = sc->nranks;
+        for (int q = 0; q <= sc->nranks; q++) p.row_first[q] = sc->row_first[q];
+        for (int q = 0; q < sc->nranks; q++) {
+            p.slab[q] = sc->slab[q];
+            p.arrive[q] = sc->arrive[q];
+        }
+        p.seq = sc->seq;
+        p.done = sc->done;
+    }
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const unsigned grid = (unsigned)(tiles < g.sm_count ? tiles : g.sm_count);
     k_linear_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmx, tmw, p);
     return after_launch(op) ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+int launch_linear_scatter(const uint16_t *x, int ldx, const uint16_t *W, int ldw, int rows, int in, int out,
+                          const ScatterArgs &sc) {
+    return launch_linear(NULL, 0, x, ldx, W, ldw, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, &sc, "outproj");
+}
+
+int launch_residual_from_slabs(float *x, const float *slabs, size_t slab_stride, int nranks, const float *gate, int rows,
+                               int dim, const uint32_t *arrive, uint32_t seq) {
+    if (rows <= 0) return IRIS_B200_OK;
+    const size_t n4 = (size_t)rows * dim / 4;
+    size_t blocks = (n4 + 255) / 256;
+    if (blocks > (size_t)g.sm_count * 8) blocks = (size_t)g.sm_count * 8;
+    gemm::k_residual_from_slabs<<<(unsigned)blocks, 256, 0, g.stream>>>(x, slabs, slab_stride, nranks, gate, rows, dim, arrive,
+                                                                        seq, wait_limit_ns(), g.dev_status);
+    return after_launch("outproj residual") ? IRIS_B200_OK : IRIS_B200_ECUDA;
 }
 
 }  // namespace iris_b200
@@ -381,12 +526,13 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, const uint16_t
 using namespace iris_b200;
 
 extern "C" void iris_dev_linear_bf16(uint16_t *y, const uint16_t *x, const uint16_t *W, int rows, int in, int out) {
-    launch_linear(y, out, x, W, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, "linear_bf16");
+    launch_linear(y, out, x, in, W, in, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_bf16");
 }
 
 extern "C" int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W,
                                              int rows, int in, int out, int heads,
                                              const float *wq, const float *wk,
                                              const float *rope_cos, const float *rope_sin, float eps) {
-    return launch_linear(y, ldy, x, W, rows, in, out, heads, wq, wk, rope_cos, rope_sin, eps, "linear_qk_norm_rope");
+    return launch_linear(y, ldy, x, in, W, in, rows, in, out, heads, wq, wk, rope_cos, rope_sin, eps, NULL,
+                         "linear_qk_norm_rope");
 }

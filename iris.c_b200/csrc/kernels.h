@@ -66,6 +66,25 @@ unsigned long long wait_limit_ns(void);
 /* Per-device launch configuration of the GEMM is redone after a cleanup. */
 void gemm_release(void);
 
+/* Row-parallel GEMM: the fp32 rows of x [rows, in] . W [out, in]^T (row strides
+ * ldx, ldw) are scattered to the ranks that own them: rank q owns the rows
+ * [row_first[q], row_first[q + 1]) and receives them in slab[q] ([its rows,
+ * out] fp32, local or peer memory); when the launch is through, the word
+ * arrive[q] on every owner is set to seq. done: a zeroed device word. */
+struct ScatterArgs {
+    int nranks;
+    const int *row_first;
+    float *const *slab;
+    uint32_t *const *arrive;
+    uint32_t seq;
+    unsigned int *done;
+};
+int launch_linear_scatter(const uint16_t *x, int ldx, const uint16_t *W, int ldw, int rows, int in, int out,
+                          const ScatterArgs &sc);
+/* x [rows, dim] += gate * (sum of nranks slabs), after the arrival words reached seq. */
+int launch_residual_from_slabs(float *x, const float *slabs, size_t slab_stride, int nranks, const float *gate, int rows,
+                               int dim, const uint32_t *arrive, uint32_t seq);
+
 /* Host-side fault injection: the next launch that splits its keys finds a
  * ticket that nobody took. */
 void sm100_inject_stale_ticket(void);

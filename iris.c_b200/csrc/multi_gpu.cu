@@ -322,6 +322,10 @@ struct Ring {
 
 enum { kFlagArrive = 0, kFlagSeq = kMaxRanks, kFlagWords = kMaxRanks + 8 };
 
+/* staging of the row-parallel out-projection (further down), released with the group */
+void proj_close_peers(void);
+void proj_release(void);
+
 bool nccl_load(void) {
     if (ring.dl) return true;
     ring.dl = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
@@ -562,9 +566,11 @@ extern "C" void iris_b200_ring_destroy(void) {
     if (!ring.comm) return;
     cuda_ok(cudaDeviceSynchronize(), "sync");
     ce_close_peers();
+    proj_close_peers();
     /* Every importer has unmapped before any exporter frees. A ring that
      * failed may have lost a peer: no collective is attempted on it. */
     if (ring.nranks > 1 && ring.xchg && !ring.failed) ring_barrier();
+    proj_release();
     if (ring.pool) cuda_ok(cudaFree(ring.pool), "free");
     if (ring.flags) cuda_ok(cudaFree(ring.flags), "free");
     if (ring.xchg) cuda_ok(cudaFree(ring.xchg), "free");
@@ -756,6 +762,174 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
         return rc != IRIS_B200_OK ? rc : (g.last_error ? g.last_error : IRIS_B200_ECOMM);
     }
     return IRIS_B200_OK;
+}
+
+/* ------------------------------------------------------------------------
+ * Row-parallel out-projection with the gated residual (head-parallel ranks)
+ *
+ * After head-parallel attention rank r holds the columns of the attention
+ * output that belong to its heads. The block's out-projection
+ * (iris_dev_linear_f32 + iris_dev_residual, iris_transformer_flux.c:3811-3812,
+ * 3841-3842) then is a GEMM over a slice of the reduction dimension on every
+ * rank whose partial sums have to be added across ranks. Here the GEMM's
+ * epilogue sends each fp32 tile row straight to the rank that owns the row
+ * (plain stores over NVLink into that rank's staging slab for this sender),
+ * the last CTA advances the sender's arrival word on every owner, and the
+ * owner's residual kernel waits (bounded) for all senders, sums the slabs and
+ * applies x += gate * sum to its rows: a reduce-scatter without a collective
+ * library call, and no pass over the partial sums in between. Staging comes
+ * in two sets used by alternate calls, for the same reason as the ring's
+ * slots. Uses the communicator of iris_b200_ring_init() for the set-up
+ * exchange only.
+ * ------------------------------------------------------------------------ */
+
+namespace {
+
+struct Proj {
+    char *stage;                          /* 2 sets x nranks slabs of slab_bytes */
+    size_t slab_bytes;
+    uint32_t *words;                      /* arrive[kMaxRanks] | seq words[8] | done counter */
+    char *peer_stage[kMaxRanks];
+    uint32_t *peer_words[kMaxRanks];
+    uint32_t seq;
+} proj = {};
+
+enum { kProjDone = kMaxRanks + 8, kProjWords = kMaxRanks + 16 };
+
+void proj_close_peers(void) {
+    for (int r = 0; r < kMaxRanks; r++) {
+        if (r != ring.rank) {
+            if (proj.peer_stage[r]) cudaIpcCloseMemHandle(proj.peer_stage[r]);
+            if (proj.peer_words[r]) cudaIpcCloseMemHandle(proj.peer_words[r]);
+        }
+        proj.peer_stage[r] = NULL;
+        proj.peer_words[r] = NULL;
+    }
+    (void)cudaGetLastError();
+}
+
+/* Collective, like ring_pool(): staging of at least slab_bytes per sender and
+ * set, mapped on every peer. No fallback: without peer access the call fails. */
+bool proj_setup(size_t slab_bytes) {
+    const int G = ring.nranks;
+    if (proj.stage && slab_bytes <= proj.slab_bytes) return true;
+    if (!ring.xchg && !cuda_ok(cudaMalloc(&ring.xchg, sizeof(IpcPair) * (kMaxRanks + 1) + 4 * (kMaxRanks + 1)), "malloc"))
+        return false;
+    cuda_ok(cudaDeviceSynchronize(), "sync");
+    if (G > 1 && !ring_barrier()) return false;
+    proj_close_peers();
+    if (G > 1 && !ring_barrier()) return false;
+    if (proj.stage) cuda_ok(cudaFree(proj.stage), "free");
+    proj.stage = NULL;
+    proj.slab_bytes = 0;
+    if (!proj.words) {
+        if (!cuda_ok(cudaMalloc((void **)&proj.words, kProjWords * 4), "malloc") ||
+            !cuda_ok(cudaMemset(proj.words, 0, kProjWords * 4), "memset"))
+            return false;
+    }
+    if (cudaMalloc((void **)&proj.stage, slab_bytes * G * 2) != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_error(IRIS_B200_ENOMEM, "out-projection staging", NULL);
+        return false;
+    }
+    proj.slab_bytes = slab_bytes;
+    proj.peer_stage[ring.rank] = proj.stage;
+    proj.peer_words[ring.rank] = proj.words;
+    if (G == 1) return true;
+    IpcPair *dev = (IpcPair *)ring.xchg;
+    IpcPair mine, all[kMaxRanks];
+    bool mapped = cudaIpcGetMemHandle(&mine.pool, proj.stage) == cudaSuccess &&
+                  cudaIpcGetMemHandle(&mine.flags, proj.words) == cudaSuccess;
+    if (!mapped) memset(&mine, 0, sizeof(mine));
+    if (!cuda_ok(cudaMemcpy(dev + kMaxRanks, &mine, sizeof(mine), cudaMemcpyHostToDevice), "memcpy") ||
+        !nccl_ok(ring.all_gather(dev + kMaxRanks, dev, sizeof(IpcPair), 1, ring.comm, g.stream), "ncclAllGather") ||
+        !nccl_wait(g.stream, 30.0, "ncclAllGather") ||
+        !cuda_ok(cudaMemcpy(all, dev, sizeof(IpcPair) * G, cudaMemcpyDeviceToHost), "memcpy"))
+        return false;
+    for (int r = 0; r < G && mapped; r++) {
+        if (r == ring.rank) continue;
+        void *ps = NULL, *pw = NULL;
+        if (cudaIpcOpenMemHandle(&ps, all[r].pool, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
+            cudaIpcOpenMemHandle(&pw, all[r].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+            mapped = false;
+        proj.peer_stage[r] = (char *)ps;
+        proj.peer_words[r] = (uint32_t *)pw;
+    }
+    (void)cudaGetLastError();
+    uint32_t votes[kMaxRanks];
+    if (!exchange_word(mapped ? 1u : 0u, votes)) return false;
+    for (int r = 0; r < G; r++) mapped = mapped && votes[r] == 1u;
+    if (!mapped) {
+        set_error(IRIS_B200_ECOMM, "out-projection staging", "a peer's memory cannot be mapped (no peer access)");
+        proj_close_peers();
+        return false;
+    }
+    return true;
+}
+
+void proj_release(void) {
+    proj_close_peers();
+    if (proj.stage) cuda_ok(cudaFree(proj.stage), "free");
+    if (proj.words) cuda_ok(cudaFree(proj.words), "free");
+    proj.stage = NULL;
+    proj.words = NULL;
+    proj.slab_bytes = 0;
+    proj.seq = 0;
+}
+
+}  // namespace
+
+extern "C" int iris_b200_outproj_residual(float *x_rows, const uint16_t *cat, int ldc, const uint16_t *W, int ldw,
+                                          const float *gate, const int *rows_of, int k, int dim) {
+    if (!require_device("outproj_residual")) return IRIS_B200_ENODEV;
+    if (!ring.comm || !x_rows || !cat || !W || !rows_of || k <= 0 || dim <= 0 || dim % 8 != 0 ||
+        ((uintptr_t)x_rows & 15) != 0 || (gate && ((uintptr_t)gate & 15) != 0)) {
+        set_error(IRIS_B200_EINVAL, "outproj_residual", "group not initialised (iris_b200_ring_init) or bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    if (ring.failed) {
+        set_error(IRIS_B200_ECOMM, "outproj_residual", "an earlier call failed: destroy and re-initialise the group");
+        return IRIS_B200_ECOMM;
+    }
+    const int G = ring.nranks, me = ring.rank;
+    int row_first[kMaxRanks + 1], max_rows = 0;
+    row_first[0] = 0;
+    for (int r = 0; r < G; r++) {
+        if (rows_of[r] < 0) {
+            set_error(IRIS_B200_EINVAL, "outproj_residual", "negative row count");
+            return IRIS_B200_EINVAL;
+        }
+        row_first[r + 1] = row_first[r] + rows_of[r];
+        max_rows = rows_of[r] > max_rows ? rows_of[r] : max_rows;
+    }
+    const int seq_rows = row_first[G];
+    const size_t slab_bytes = (((size_t)max_rows * dim * 4) + 255) & ~(size_t)255;
+    if (!proj_setup(slab_bytes)) {
+        ring.failed = 1;
+        return g.last_error ? g.last_error : IRIS_B200_ECOMM;
+    }
+    const uint32_t seq = ++proj.seq;
+    const size_t set_off = (size_t)(seq & 1u) * G * proj.slab_bytes;
+    float *slab[kMaxRanks];
+    uint32_t *arrive[kMaxRanks];
+    for (int q = 0; q < G; q++) {
+        /* this rank's slab on owner q, and this rank's arrival word there */
+        slab[q] = (float *)(proj.peer_stage[q] + set_off + (size_t)me * proj.slab_bytes);
+        arrive[q] = proj.peer_words[q] + me;
+    }
+    ScatterArgs sc;
+    sc.nranks = G;
+    sc.row_first = row_first;
+    sc.slab = slab;
+    sc.arrive = arrive;
+    sc.seq = seq;
+    sc.done = proj.words + kProjDone;
+    int rc = launch_linear_scatter(cat, ldc, W, ldw, seq_rows, k, dim, sc);
+    if (rc == IRIS_B200_OK)
+        rc = launch_residual_from_slabs(x_rows, (const float *)(proj.stage + set_off), proj.slab_bytes / 4, G, gate,
+                                        rows_of[me], dim, proj.words, seq);
+    if (rc != IRIS_B200_OK) ring.failed = 1;
+    return rc;
 }
 
 /* A device wait ran out inside a ring call (iris_b200_check_device_status
