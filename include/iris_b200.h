@@ -30,7 +30,8 @@ enum {
     IRIS_B200_ENOMEM = 5,       /* device allocation failed */
     IRIS_B200_EUNSUPPORTED = 6, /* no kernel for this argument combination */
     IRIS_B200_ECOMM = 7,        /* collective transport failed, or the ring is unusable after a failure */
-    IRIS_B200_EPROTO = 8        /* ring ranks disagree (row counts, chunk sizes, sequence numbers) */
+    IRIS_B200_EPROTO = 8,       /* ring ranks disagree (row counts, chunk sizes, sequence numbers) */
+    IRIS_B200_ECHECK = 9        /* a device-side self-check of the -DIRIS_B200_CHECK build did not hold */
 };
 
 /* First error since the last clear (0 = none). The void operations of

@@ -160,6 +160,8 @@ struct Params {
     const uint32_t *mask_bits; /* packed key mask, bit j of word j/32, or NULL (single source only) */
     unsigned int *status;      /* [0] flag, [1] site, [2] block, [3] aux */
     unsigned long long wait_ns; /* limit of every wait */
+    int view_rows[2];          /* rows of the two K/V views (self-checks) */
+    int part_cap, ticket_cap;  /* 256-row partials / query blocks the scratch has room for (self-checks) */
     /* state carried across key chunks (split-K over several launches), or NULL */
     float *o_acc;              /* [seq_q, heads*128] fp32, normalised partial output */
     float *lse_acc;            /* [heads, seq_q] fp32, log2-sum-exp of the keys seen so far */
@@ -186,6 +188,27 @@ __device__ __forceinline__ void give_up(const Ctx &c, int site, unsigned aux) {
         c.status[3] = aux;
     }
 }
+
+/* Self-checks of the -DIRIS_B200_CHECK build (tile and slot indices, scratch
+ * capacities, rows handed to TMA): a violated check never traps; it records
+ * the first site in words 4-7 of the status word, which
+ * iris_b200_check_device_status() reports as IRIS_B200_ECHECK, and the access
+ * goes ahead only where it is harmless. Compiled out of the product build. */
+#ifdef IRIS_B200_CHECK
+__device__ __noinline__ void check_failed(unsigned int *status, int site, unsigned aux) {
+    if (atomicCAS(status + 4, 0u, 1u) == 0u) {
+        status[5] = (unsigned)site;
+        status[6] = blockIdx.x;
+        status[7] = aux;
+    }
+}
+#define IRIS_CHECK(status, cond, site, aux) \
+    do {                                     \
+        if (!(cond)) check_failed((status), (site), (unsigned)(aux)); \
+    } while (0)
+#else
+#define IRIS_CHECK(status, cond, site, aux) ((void)0)
+#endif
 
 /* Bounded wait. Returns false when the CTA is aborting. `site` identifies
  * the caller in the status word. */
@@ -329,6 +352,8 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const Ma
     for (int n = 0; ok && cur >= 0; n++) {
         const Item w = item_of(p, cur);
         const int col = w.head * kHeadDim;
+        IRIS_CHECK(c.status, cur < p.items && w.head < p.heads && w.q0 < p.seq_q && w.nj >= 1 && w.j0 >= 0 &&
+                   w.j0 + w.nj <= p.nkv, 900, cur);
         /* The Q tiles are replaced once every QK product of the previous item is done. */
         if (n > 0 && !mbar_wait(c, BAR_Q_EMPTY, (n - 1) & 1, 110)) break;
         mbar_expect_tx(c.bars + BAR_Q_FULL * 8, w.ntq * kTileBytes);
@@ -372,6 +397,8 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const Ma
                 break;
             }
             const KeySource &s = p.src[si];
+            IRIS_CHECK(c.status, si < p.nsrc && j >= s.tile0 && (j - s.tile0) * kTileK < s.rows &&
+                       s.row0 + (j - s.tile0) * kTileK < p.view_rows[s.view] && r.slot < kStages, 901, j);
             uint32_t full = c.bars + (BAR_KV_FULL + r.slot) * 8;
             mbar_expect_tx(full, kTileBytes);
             const CUtensorMap *map = (it & 1) ? m.v[s.view] : m.k[s.view];
@@ -441,6 +468,7 @@ __device__ __forceinline__ void mma_issuer(const Ctx &c, const Params &p, uint32
         }
         const Item w = item_of(p, item);
         const int ntq = w.ntq, nkv = w.nj;
+        IRIS_CHECK(c.status, item < p.items && (ntq == 1 || ntq == 2) && nkv >= 1 && r.slot < kStages, 910, item);
         ok = __all_sync(0xffffffffu, mbar_wait(c, BAR_Q_FULL, n & 1, 200) && mbar_wait(c, BAR_KV_FULL + r.slot, r.phase, 201));
         if (!ok) break;
         tc_fence_after();
@@ -604,6 +632,7 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
         }
         int nkeys = kTileK;
         if (jg == src_last) nkeys = tile_keys(p.src[si], jg);
+        IRIS_CHECK(c.status, si < p.nsrc && jg >= p.src[si].tile0 && jg <= src_last && nkeys >= 1 && nkeys <= kTileK, 921, jg);
         const bool partial = nkeys < kTileK || p.mask_bits != nullptr;
         uint32_t bits[4] = {0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu};
         if (partial) tile_bits(p, jg, nkeys, bits);
@@ -696,6 +725,8 @@ __device__ __forceinline__ bool softmax_item(const Ctx &c, const Params &p, unsi
         unsigned int order = 0;
         if (lane == 0) order = atomicAdd(tk, 1u);
         order = __shfl_sync(0xffffffffu, order, 0);
+        IRIS_CHECK(c.status, order < (unsigned)p.nparts && w.qitem < p.ticket_cap &&
+                   (size_t)w.qitem * others + others <= (size_t)p.part_cap, 920, order);
         if (order < (unsigned)others) {
             float *mine = prows + (size_t)order * 256 * kHeadDim;
 #pragma unroll
@@ -1268,6 +1299,8 @@ int launch_attention_sm100(const AttnArgs &a) {
     }
     p.nsrc = a.nsrc;
     p.nkv = nkv;
+    p.view_rows[0] = view_rows[0];
+    p.view_rows[1] = view_rows[1];
     p.arrive = a.arrive;
     p.arrive_seq = a.arrive_seq;
 
@@ -1346,6 +1379,8 @@ int launch_attention_sm100(const AttnArgs &a) {
         p.part_o = sc->o;
         p.part_ml = sc->ml;
         p.tickets = sc->tickets;
+        p.part_cap = (int)sc->part_blocks;
+        p.ticket_cap = (int)sc->ticket_blocks;
         if (g_inject_ticket) {
             /* Fault injection (tests): an arrival nobody made. Every part of
              * query block 0 then believes it is the last and waits for

@@ -83,6 +83,8 @@ const char *iris_b200_strerror(int code) {
     case IRIS_B200_ENOMEM: return "device allocation failed";
     case IRIS_B200_EUNSUPPORTED: return "no kernel for this argument combination";
     case IRIS_B200_ECOMM: return "collective transport failed";
+    case IRIS_B200_EPROTO: return "ring ranks disagree";
+    case IRIS_B200_ECHECK: return "self-check of the checking build failed";
     }
     return "unknown error";
 }
@@ -210,10 +212,17 @@ float iris_b200_mark_elapsed_ms(int from, int to) {
 
 int iris_b200_check_device_status(void) {
     if (!require_device("check_device_status")) return IRIS_B200_ENODEV;
-    unsigned int st[4] = {0, 0, 0, 0};
+    unsigned int st[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (!cuda_ok(cudaStreamSynchronize(g.stream), "sync")) return g.last_error;
     if (!cuda_ok(cudaMemcpy(st, g.dev_status, sizeof(st), cudaMemcpyDeviceToHost), "status read"))
         return g.last_error;
+    if (st[4] != 0) {
+        /* only the self-checking build (-DIRIS_B200_CHECK) writes these words */
+        char msg[160];
+        snprintf(msg, sizeof(msg), "self-check failed in kernel (site %u, block %u, aux %u)", st[5], st[6], st[7]);
+        set_error(IRIS_B200_ECHECK, "device check", msg);
+        if (st[0] == 0) cuda_ok(cudaMemset(g.dev_status, 0, 64), "status clear");
+    }
     if (st[0] != 0) {
         char msg[160];
         snprintf(msg, sizeof(msg), "wait timed out in kernel (site %u, block %u, aux %u)", st[1], st[2], st[3]);
