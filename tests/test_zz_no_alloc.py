@@ -46,6 +46,11 @@ def test_no_alloc_split_k_matches_plain_attention_twice_in_a_row(lib):
         assert np.isfinite(got).all()
         # same tolerance as the parity gate of the other attention tests
         assert mx.max() <= 2e-2 and cs.min() >= 0.9999, (call, mx, cs)
+        # and both against the CPU oracle, so that the two entry points cannot agree on a wrong answer
+        truth = ol.dev_attention(ol.from_bf16(q), ol.from_bf16(k), ol.from_bf16(v), H)
+        for res in (got, want):
+            mx, cs = ol.compare_heads(res, truth, H)
+            assert mx.max() <= 2e-2 and cs.min() >= 0.9999, (call, mx, cs)
         results.append(got)
     assert not np.array_equal(results[0], results[1])
     lib.iris_dev_free(dout_a)
@@ -60,4 +65,9 @@ def test_no_alloc_rejects_what_does_not_fit(lib):
     assert rc == 1                                # IRIS_B200_EINVAL, nothing launched
     lib.iris_b200_clear_error()
     assert lib.iris_b200_attention_noalloc(256, 2 * D, 256, 256, 256, 2 * D, 10, 128, 2, 0.1, 0) == 1
+    lib.iris_b200_clear_error()
+    # row strides shorter than a row of heads: the output would run past its buffer, the inputs overlap
+    assert lib.iris_b200_attention_noalloc(256, 2 * D - 8, 256, 256, 256, 2 * D, 10, 128, 2, 0.1, 2) == 1
+    lib.iris_b200_clear_error()
+    assert lib.iris_b200_attention_noalloc(256, 2 * D, 256, 256, 256, 2 * D - 8, 10, 128, 2, 0.1, 2) == 1
     lib.iris_b200_clear_error()
