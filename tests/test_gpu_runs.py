@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 
 D = 128
 MAX_ABS, MIN_COS = 2e-2, 0.9999
-ETIMEOUT = 3
+ETIMEOUT, ECHECK = 3, 9
 
 
 @pytest.fixture(scope="module")
@@ -173,7 +173,8 @@ def test_stale_split_ticket_times_out_and_the_scratch_recovers(lib):
         lib.iris_b200_set_wait_limit_us(5000)
         assert lib.iris_b200_inject_fault(1) == 0
         assert pr.launch(2) == 0
-        assert lib.iris_b200_check_device_status() == ETIMEOUT
+        # the self-checking build (-DIRIS_B200_CHECK) sees the impossible ticket first
+        assert lib.iris_b200_check_device_status() in (ETIMEOUT, ECHECK)
         lib.iris_b200_clear_error()
         lib.iris_b200_set_wait_limit_us(0)
         for nparts in (2, 3, 0):                           # tickets and work-list counters are clean again
