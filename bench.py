@@ -612,8 +612,33 @@ def outproj_run(job, pk, reps=20):
     job.barrier()
     ms = job.max_over_ranks([lib.iris_b200_mark_elapsed_ms(0, 1) / reps])[0]
     lib.check()
+    # The library sequence on the same operands: cuBLAS GEMM (bf16 result, which
+    # rounds the partial sums the fused kernel keeps in fp32), widened, NCCL
+    # reduce-scatter, residual. Equal row counts only.
+    lib_ms = None
+    if len(set(int(r) for r in rows_of)) == 1:
+        Wk = W[:, k0:k0 + k]
+        part = torch.empty((S, dim), device="cuda", dtype=torch.float32)
+        own = torch.empty((int(rows_of[rank]), dim), device="cuda", dtype=torch.float32)
+
+        def lib_call():
+            part.copy_(torch.matmul(cat, Wk.t()))
+            job.dist.reduce_scatter_tensor(own, part)
+            x.addcmul_(own, gate)
+
+        for _ in range(3):
+            lib_call()
+        job.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            lib_call()
+        e1.record()
+        job.barrier()
+        lib_ms = job.max_over_ranks([e0.elapsed_time(e1) / reps])[0]
     sent = float(S - rows_of[rank]) * dim * 4
     return {"shape": [S, dim // world, dim], "ms": round(ms, 4),
+            "cublas_nccl_reduce_scatter_residual_ms": round(lib_ms, 4) if lib_ms else None,
             "what": "GEMM + reduce-scatter in its epilogue (peer stores) + gated residual on the owner",
             "gemm_tflops_aggregate": round(2.0 * S * dim * dim / ms / 1e9, 1),
             "nvlink_bytes_per_rank": sent, "nvlink_gbs_per_rank": round(sent / ms / 1e6, 1)}
