@@ -62,7 +62,7 @@ WORKLOADS = {
 # DRAM bytes (read + written) of one attention launch as counted by an ncu capture of this workload
 # (dram__bytes_read.sum + dram__bytes_write.sum); not measured by this script. The algorithmic
 # figure for comparison is Q + K + V + O = 113.2 MB.
-NCU_DRAM_BYTES_PER_LAUNCH = {"klein4b-1024": 91.5e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"klein4b-1024": 90.3e6}
 
 METRIC = "joint-attn TFLOP/s per GPU & % bf16 peak at 1/2/4/8 B200 vs host-CPU ref"
 STEP_WORDS = "qk_norm + rope + attention"
