@@ -650,11 +650,17 @@ def extra_run(job, name, mode, steps, warmup, pk):
     w = WORKLOADS[name]
     plan = plan_of(job, w, mode)
     B = Buffers(job, w, plan)
-    res = timed_steps(job, w, plan, B, steps, warmup)
+    res = timed_steps(job, w, plan, B, steps, warmup, marks=(job.rank == 0))
     B.free()
     total = attn_flops(w["batch"], w["heads"], plan["S_full"], plan["S_full"]) / (res["ms"] * 1e-3) / 1e12
-    return {"workload": name, "mode": mode, "ms_per_step": round(res["ms"], 4), "tflops": round(total, 1),
-            "per_gpu_pct_bf16_peak": round(100 * total / job.world / pk[0], 2)}
+    out = {"workload": name, "mode": mode, "ms_per_step": round(res["ms"], 4), "tflops": round(total, 1),
+           "per_gpu_pct_bf16_peak": round(100 * total / job.world / pk[0], 2)}
+    if res.get("attn_ms"):
+        # rank 0's own launches (one batch entry per rank): what a step spends outside the attention kernel
+        kms, pms = float(np.mean(res["attn_ms"])), float(np.mean(res["pro_ms"])) if res.get("pro_ms") else None
+        out["rank0_attention_kernel_ms"] = round(kms, 4)
+        out["rank0_prologue_ms"] = round(pms, 4) if pms else None
+    return out
 
 
 def run_b200(args):
