@@ -355,7 +355,7 @@ def timed_steps(job, w, plan, B, steps, warmup, collective=True, marks=False):
     # Per-kernel marks on every fourth step of the timed region: an event record
     # between the prologue and the attention launch costs that step the overlap
     # of the two (programmatic stream serialisation), so the others run clean.
-    marked = [i for i in range(0, steps, 4)][:2500] if (marks and active and len(B.sets[0]) == 1) else []
+    marked = [i for i in range(2 if steps > 2 else 0, steps, 4)][:2500] if (marks and active and len(B.sets[0]) == 1) else []
     slot = {i: k for k, i in enumerate(marked)}
     for i in range(steps):
         if active:
