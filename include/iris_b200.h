@@ -225,7 +225,8 @@ int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t *q, int ldq
 typedef struct {
     int view;       /* 0: (k0, v0, ld0), 1: (k1, v1, ld1) */
     int row0, rows; /* key rows [row0, row0 + rows) of that view */
-    int arrive;     /* index of the arrival word guarding the run, -1: none */
+    int arrive;     /* index of the (first) arrival word guarding the run, -1: none */
+    int rows_per_word; /* 0: one word guards the whole run; > 0: consecutive words guard this many rows each */
 } iris_b200_key_run;
 int iris_b200_attention_runs(uint16_t *out, int ldo, const uint16_t *q, int ldq,
                              int seq_q, int heads, float scale,
@@ -233,6 +234,21 @@ int iris_b200_attention_runs(uint16_t *out, int ldo, const uint16_t *q, int ldq,
                              const uint16_t *k1, const uint16_t *v1, int ld1,
                              const iris_b200_key_run *runs, int nruns,
                              const uint32_t *arrive_words, uint32_t arrive_value, int nparts);
+
+/* Pure host arithmetic, for schedulers and tests: how a launch over these runs
+ * cuts the keys of a query block into parts on a device with sm_count SMs.
+ * part_tile (nparts + 1 entries, room for 9): part i covers the 128-key tiles
+ * [part_tile[i], part_tile[i + 1]); *nkv: tiles over all runs. Returns the
+ * number of parts, -1 on bad arguments. */
+int iris_b200_attention_runs_plan(const iris_b200_key_run *runs, int nruns, int seq_q, int heads, int nparts,
+                                  int sm_count, int *part_tile, int *nkv);
+
+/* The same for the attention launch of one rank's ring call (copy-engine
+ * transport): fills runs (room for 16) with "own rows, then the slots in ring
+ * order" and part_tile with the groups of iris_b200_ring_plan() as tiles.
+ * Returns runs * 100 + parts, -1 on bad arguments. */
+int iris_b200_ring_launch_plan(int rank, int nranks, const int *rows_of, int heads, int max_parts, int sm_count,
+                               iris_b200_key_run *runs, int *part_tile, int *nkv);
 
 /* Ring sequence parallelism. One rank calls ring_unique_id(), the 128-byte id
  * is handed to every rank by the caller's own means, then every rank calls

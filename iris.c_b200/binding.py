@@ -68,6 +68,8 @@ SIGNATURES = {
     "iris_b200_attention_noalloc_max_elems": (SZ, []),
     "iris_b200_attention_runs": (INT, [VP, INT, VP, INT, INT, INT, FLT, VP, VP, INT, VP, VP, INT, VP, INT, VP,
                                        C.c_uint32, INT]),
+    "iris_b200_attention_runs_plan": (INT, [VP, INT, INT, INT, INT, INT, VP, VP]),
+    "iris_b200_ring_launch_plan": (INT, [INT, INT, VP, INT, INT, INT, VP, VP, VP]),
     "iris_b200_set_wait_limit_us": (INT, [C.c_uint]),
     "iris_b200_inject_fault": (INT, [INT]),
     "iris_b200_upload_async": (INT, [VP, VP, SZ, VP]),
@@ -100,7 +102,7 @@ class LoopFault(C.Structure):
 
 class KeyRun(C.Structure):
     """iris_b200_key_run of include/iris_b200.h."""
-    _fields_ = [("view", INT), ("row0", INT), ("rows", INT), ("arrive", INT)]
+    _fields_ = [("view", INT), ("row0", INT), ("rows", INT), ("arrive", INT), ("rows_per_word", INT)]
 
 
 class Lib:

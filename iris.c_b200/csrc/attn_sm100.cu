@@ -1223,6 +1223,50 @@ static int choose_parts(int nq, int nkv, int sms, int max_parts) {
     return best;
 }
 
+/* Pure host arithmetic of a launch: the first key tile of every run, the
+ * number of key tiles, and how the keys of a query block are cut into parts
+ * (the caller's boundaries, given as key rows and moved down to a tile
+ * boundary, or equal numbers of tiles chosen by the cost model; can_split
+ * false: one part). Returns IRIS_B200_OK or IRIS_B200_EINVAL. */
+int plan_key_parts(const AttnArgs &a, int sm_count, bool can_split, KeyPlan *plan) {
+    using namespace sm100;
+    if (a.nsrc <= 0 || a.nsrc > kMaxSources || a.seq_q < 0 || a.heads <= 0) return IRIS_B200_EINVAL;
+    int nkv = 0;
+    for (int s = 0; s < a.nsrc; s++) {
+        if (a.src[s].rows <= 0) return IRIS_B200_EINVAL;
+        plan->tile0[s] = nkv;
+        nkv += (a.src[s].rows + kTileK - 1) / kTileK;
+    }
+    plan->nkv = nkv;
+    const int nq = ((a.seq_q + 2 * kTileQ - 1) / (2 * kTileQ)) * a.heads;
+    int nparts = 1;
+    if (can_split && a.nparts > 1)
+        nparts = a.nparts > kMaxParts ? kMaxParts : a.nparts;
+    else if (can_split && a.max_parts > 1)
+        nparts = choose_parts(nq, nkv, sm_count, a.max_parts);
+    plan->nparts = nparts;
+    for (int i = 0; i <= nparts; i++) {
+        if (a.nparts > 1 && nparts > 1 && i < nparts) {
+            long long row = a.part_row[i], before = 0;
+            int tile = nkv;
+            for (int sidx = 0; sidx < a.nsrc; sidx++) {
+                if (row < before + a.src[sidx].rows) {
+                    tile = plan->tile0[sidx] + (int)((row - before) / kTileK);
+                    break;
+                }
+                before += a.src[sidx].rows;
+            }
+            plan->part_tile[i] = tile;
+        } else {
+            plan->part_tile[i] = (int)((long long)nkv * i / nparts);
+        }
+    }
+    plan->part_tile[0] = 0;
+    for (int i = 0; i < nparts; i++)
+        if (plan->part_tile[i + 1] <= plan->part_tile[i]) return IRIS_B200_EINVAL;
+    return IRIS_B200_OK;
+}
+
 AttnArgs attn_args(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k, const uint16_t *v,
                    int ldkv, int seq_q, int seq_k, int heads, float scale, const int *key_mask) {
     AttnArgs a = {};
@@ -1342,39 +1386,18 @@ int launch_attention_sm100(const AttnArgs &a) {
     p.acc_mode = a.acc_mode;
     p.sched = sc ? sc->sched : NULL;
 
-    /* Key parts: the caller's (boundaries given as key rows, moved down to a
-     * tile boundary) or the model's (equal numbers of tiles); none without
-     * scratch to merge through. */
-    int nparts = 1;
-    if (sc && a.nparts > 1)
-        nparts = a.nparts > kMaxParts ? kMaxParts : a.nparts;
-    else if (sc && a.max_parts > 1)
-        nparts = choose_parts(p.nq, nkv, g_sm_count, a.max_parts);
-    if (nparts > 1 && !scratch_parts(sc, (size_t)p.nq, nparts)) nparts = 1;
+    /* Key parts (none without scratch to merge through, or when the scratch cannot be had). */
+    KeyPlan plan;
+    if (plan_key_parts(a, g_sm_count, sc != NULL, &plan) != IRIS_B200_OK) {
+        set_error(IRIS_B200_EINVAL, "attention", "empty key part");
+        return IRIS_B200_EINVAL;
+    }
+    if (plan.nparts > 1 && !scratch_parts(sc, (size_t)p.nq, plan.nparts)) {
+        plan_key_parts(a, g_sm_count, false, &plan);
+    }
+    const int nparts = plan.nparts;
     p.nparts = nparts;
-    for (int i = 0; i <= nparts; i++) {
-        if (a.nparts > 1 && nparts > 1 && i < nparts) {
-            long long row = a.part_row[i], before = 0;
-            int tile = nkv;
-            for (int sidx = 0; sidx < a.nsrc; sidx++) {
-                if (row < before + a.src[sidx].rows) {
-                    tile = p.src[sidx].tile0 + (int)((row - before) / kTileK);
-                    break;
-                }
-                before += a.src[sidx].rows;
-            }
-            p.part_tile[i] = tile;
-        } else {
-            p.part_tile[i] = (int)((long long)nkv * i / nparts);
-        }
-    }
-    p.part_tile[0] = 0;
-    for (int i = 0; i < nparts; i++) {
-        if (p.part_tile[i + 1] <= p.part_tile[i]) {
-            set_error(IRIS_B200_EINVAL, "attention", "empty key part");
-            return IRIS_B200_EINVAL;
-        }
-    }
+    for (int i = 0; i <= nparts; i++) p.part_tile[i] = plan.part_tile[i];
     if (nparts > 1) {
         p.part_o = sc->o;
         p.part_ml = sc->ml;

@@ -43,6 +43,15 @@ struct AttnArgs {
     bool no_scratch;                    /* use no library scratch: static work list, no key split, no mask */
 };
 
+/* How a launch cuts its keys (plan_key_parts): pure host arithmetic. */
+struct KeyPlan {
+    int nkv;                                   /* 128-key tiles over all runs */
+    int tile0[AttnArgs::kMaxSources];          /* first tile of every run */
+    int nparts;
+    int part_tile[AttnArgs::kMaxParts + 1];    /* part i = tiles [part_tile[i], part_tile[i + 1]) */
+};
+int plan_key_parts(const AttnArgs &a, int sm_count, bool can_split, KeyPlan *plan);
+
 /* Arguments of the plain case: one run of seq_k rows, split chosen by the library. */
 AttnArgs attn_args(uint16_t *out, int ldo, const uint16_t *q, int ldq, const uint16_t *k, const uint16_t *v,
                    int ldkv, int seq_q, int seq_k, int heads, float scale, const int *key_mask);

@@ -35,6 +35,8 @@
 
 using namespace iris_b200;
 
+enum { kMaxRanksPlan = 16 };
+
 static unsigned long long host_now_ns(void) {
     struct timespec ts;
     clock_gettime(CLOCK_MONOTONIC, &ts);
@@ -164,6 +166,56 @@ extern "C" int iris_b200_attention_chunk(uint16_t *out, int ldo, const uint16_t 
  * Attention over key runs
  * ------------------------------------------------------------------------ */
 
+/* runs -> launch arguments (views, arrival guards, requested parts). Pure
+ * host arithmetic; pointers are only stored. Returns false on a bad run. */
+static bool runs_to_args(AttnArgs &a, const iris_b200_key_run *runs, int nruns, int nparts) {
+    a.nsrc = nruns;
+    a.max_parts = AttnArgs::kMaxParts;
+    long long total = 0;
+    for (int i = 0; i < nruns; i++) {
+        const iris_b200_key_run &r = runs[i];
+        if ((r.view != 0 && r.view != 1) || r.rows <= 0 || r.row0 < 0 || r.rows_per_word < 0) return false;
+        a.src[i].view = r.view;
+        a.src[i].row0 = r.row0;
+        a.src[i].rows = r.rows;
+        a.src[i].arrive = r.arrive;
+        a.src[i].rows_per_word = r.rows_per_word > 0 ? r.rows_per_word : r.rows;
+        total += r.rows;
+    }
+    if (nparts > 1) {
+        /* Parts of whole runs, as even in rows as the runs allow: a cut
+         * before run i once the rows so far reach the part's share, or when
+         * only as many runs are left as parts. */
+        if (nparts > nruns) nparts = nruns;
+        long long before = 0;
+        int part = 1;
+        a.part_row[0] = 0;
+        for (int i = 1; i < nruns && part < nparts; i++) {
+            before += runs[i - 1].rows;
+            if (before * nparts >= total * part || nruns - i <= nparts - part) a.part_row[part++] = before;
+        }
+        a.nparts = part;
+    } else if (nparts == 1) {
+        a.max_parts = 1;
+    }
+    return true;
+}
+
+extern "C" int iris_b200_attention_runs_plan(const iris_b200_key_run *runs, int nruns, int seq_q, int heads, int nparts,
+                                             int sm_count, int *part_tile, int *nkv) {
+    if (!runs || nruns <= 0 || nruns > AttnArgs::kMaxSources || nparts < 0 || nparts > AttnArgs::kMaxParts ||
+        sm_count <= 0 || !part_tile)
+        return -1;
+    AttnArgs a = {};
+    a.seq_q = seq_q;
+    a.heads = heads;
+    KeyPlan plan;
+    if (!runs_to_args(a, runs, nruns, nparts) || plan_key_parts(a, sm_count, true, &plan) != IRIS_B200_OK) return -1;
+    for (int i = 0; i <= plan.nparts; i++) part_tile[i] = plan.part_tile[i];
+    if (nkv) *nkv = plan.nkv;
+    return plan.nparts;
+}
+
 extern "C" int iris_b200_attention_runs(uint16_t *out, int ldo, const uint16_t *q, int ldq,
                                         int seq_q, int heads, float scale,
                                         const uint16_t *k0, const uint16_t *v0, int ld0,
@@ -186,16 +238,17 @@ extern "C" int iris_b200_attention_runs(uint16_t *out, int ldo, const uint16_t *
     a.scale = scale;
     a.k[0] = k0; a.v[0] = v0; a.ldkv[0] = ld0;
     a.k[1] = k1; a.v[1] = v1; a.ldkv[1] = ld1;
-    a.nsrc = nruns;
     a.arrive = arrive_words;
     a.arrive_seq = arrive_value;
-    a.max_parts = AttnArgs::kMaxParts;
-    long long total = 0;
+    if (!runs_to_args(a, runs, nruns, nparts)) {
+        set_error(IRIS_B200_EINVAL, "attention_runs", "bad key run");
+        return IRIS_B200_EINVAL;
+    }
     for (int i = 0; i < nruns; i++) {
         const iris_b200_key_run &r = runs[i];
         const uint16_t *kb = r.view == 0 ? k0 : k1, *vb = r.view == 0 ? v0 : v1;
         const int ld = r.view == 0 ? ld0 : ld1;
-        if ((r.view != 0 && r.view != 1) || r.rows <= 0 || r.row0 < 0 || (r.arrive >= 0 && !arrive_words) ||
+        if ((r.arrive >= 0 && !arrive_words) ||
             check_attention_args("attention_runs", out, q, kb, vb, ldo, ldq, ld, seq_q, r.rows, heads, heads, 128) !=
                 IRIS_B200_OK) {
             set_error(IRIS_B200_EINVAL, "attention_runs", "bad key run");
@@ -205,31 +258,73 @@ extern "C" int iris_b200_attention_runs(uint16_t *out, int ldo, const uint16_t *
             set_error(IRIS_B200_EUNSUPPORTED, "attention_runs", "arguments outside the tcgen05 kernel's domain");
             return IRIS_B200_EUNSUPPORTED;
         }
-        a.src[i].view = r.view;
-        a.src[i].row0 = r.row0;
-        a.src[i].rows = r.rows;
-        a.src[i].arrive = r.arrive;
-        a.src[i].rows_per_word = r.rows;
-        total += r.rows;
-    }
-    if (nparts > 1) {
-        /* Parts of whole runs, as even in rows as the runs allow: a cut
-         * before run i once the rows so far reach the part's share, or when
-         * only as many runs are left as parts. */
-        if (nparts > nruns) nparts = nruns;
-        long long before = 0;
-        int part = 1;
-        a.part_row[0] = 0;
-        for (int i = 1; i < nruns && part < nparts; i++) {
-            before += runs[i - 1].rows;
-            if (before * nparts >= total * part || nruns - i <= nparts - part) a.part_row[part++] = before;
-        }
-        a.nparts = part;
-    } else if (nparts == 1) {
-        a.max_parts = 1;
     }
     if (seq_q == 0) return IRIS_B200_OK;
     return launch_attention_sm100(a);
+}
+
+/* The key runs and the part boundaries (in key rows over the runs) of one
+ * rank's attention launch in a ring call: own rows, then the slots in ring
+ * order; with equal row counts that fill their slots the slots 1 .. G-1 are
+ * one run of adjacent rows guarded by one word per slot. guarded: the slots
+ * carry arrival words (copy-engine transport). own_view: 0 = the caller's
+ * rows, 1 = slot 0 (rows packed there). Pure host arithmetic. */
+static int ring_runs(int me, int G, const int *rows_of, int slot_rows, bool guarded, int own_view, int max_parts,
+                     iris_b200_key_run *runs, long long *part_row, int *nparts) {
+    const int rows = rows_of[me];
+    bool even = true;
+    for (int r = 0; r < G; r++) even = even && rows_of[r] == rows;
+    int n = 0;
+    runs[n++] = iris_b200_key_run{own_view, 0, rows, -1, 0};
+    if (G > 1 && even && slot_rows == rows) {
+        runs[n++] = iris_b200_key_run{1, slot_rows, (G - 1) * rows, guarded ? 1 : -1, rows};
+    } else {
+        for (int s = 1; s < G; s++) {
+            const int src = iris_b200_ring_source(me, s, G);
+            runs[n++] = iris_b200_key_run{1, s * slot_rows, rows_of[src], guarded ? s : -1, 0};
+        }
+    }
+    *nparts = 1;
+    if (guarded && G > 1) {
+        /* Parts by groups of steps, so that the work list follows the arrivals. */
+        long long step_row[kMaxRanksPlan + 1];
+        step_row[0] = 0;
+        for (int s = 1; s <= G; s++) step_row[s] = step_row[s - 1] + rows_of[iris_b200_ring_source(me, s - 1, G)];
+        int first[kMaxRanksPlan], count[kMaxRanksPlan];
+        const int np = iris_b200_ring_plan(G, max_parts, first, count);
+        for (int i = 0; i < np; i++) part_row[i] = step_row[first[i]];
+        *nparts = np;
+    }
+    return n;
+}
+
+extern "C" int iris_b200_ring_launch_plan(int rank, int nranks, const int *rows_of, int heads, int max_parts, int sm_count,
+                                          iris_b200_key_run *runs, int *part_tile, int *nkv) {
+    if (nranks < 1 || nranks > kMaxRanksPlan || rank < 0 || rank >= nranks || !rows_of || !runs || !part_tile ||
+        heads <= 0 || sm_count <= 0)
+        return -1;
+    int max_rows = 0;
+    for (int r = 0; r < nranks; r++) {
+        if (rows_of[r] <= 0) return -1;
+        max_rows = rows_of[r] > max_rows ? rows_of[r] : max_rows;
+    }
+    AttnArgs a = {};
+    a.seq_q = rows_of[rank];
+    a.heads = heads;
+    int np = 1;
+    const int n = ring_runs(rank, nranks, rows_of, max_rows, true, 0, max_parts, runs, a.part_row, &np);
+    long long keep[AttnArgs::kMaxParts + 1];
+    for (int i = 0; i < np; i++) keep[i] = a.part_row[i];
+    if (!runs_to_args(a, runs, n, 0)) return -1;
+    if (np > 1) {
+        a.nparts = np;
+        for (int i = 0; i < np; i++) a.part_row[i] = keep[i];
+    }
+    KeyPlan plan;
+    if (plan_key_parts(a, sm_count, true, &plan) != IRIS_B200_OK) return -1;
+    for (int i = 0; i <= plan.nparts; i++) part_tile[i] = plan.part_tile[i];
+    if (nkv) *nkv = plan.nkv;
+    return n * 100 + plan.nparts;           /* runs * 100 + parts */
 }
 
 extern "C" int iris_b200_set_wait_limit_us(unsigned int us) {
@@ -724,35 +819,17 @@ extern "C" int iris_b200_ring_attention(uint16_t *out, int ldo,
             a.arrive = ce ? ring.flags + kFlagArrive : NULL;
             a.arrive_seq = seq;
         }
-        int n = 0;
-        long long step_row[kMaxRanks + 1];         /* first key row of step s over the runs */
-        step_row[0] = 0;
-        if (ce || G == 1) {
-            a.src[n++] = AttnArgs::Source{0, 0, rows, -1, 1};
-        } else {
-            a.src[n++] = AttnArgs::Source{1, 0, rows, -1, 1};
-        }
-        for (int s = 1; s < G; s++) step_row[s] = step_row[s - 1] + rows_of[iris_b200_ring_source(me, s - 1, G)];
-        step_row[G] = step_row[G - 1] + rows_of[iris_b200_ring_source(me, G - 1, G)];
-        if (G > 1 && even && slot_rows == rows) {
-            a.src[n++] = AttnArgs::Source{1, slot_rows, (G - 1) * rows, ce ? 1 : -1, rows};
-        } else {
-            for (int s = 1; s < G; s++)
-                a.src[n++] = AttnArgs::Source{1, s * slot_rows, rows_of[iris_b200_ring_source(me, s, G)], ce ? s : -1,
-                                              rows_of[iris_b200_ring_source(me, s, G)]};
-        }
-        a.nsrc = n;
-        if (ce) {
-            /* Parts by groups of steps, so that the work list follows the arrivals. */
-            int first[kMaxRanks], count[kMaxRanks];
-            const int np = iris_b200_ring_plan(G, ring.parts, first, count);
-            if (np > 1) {
-                a.nparts = np;
-                for (int i = 0; i < np; i++) a.part_row[i] = step_row[first[i]];
-            }
+        iris_b200_key_run runs[kMaxRanks];
+        long long part_row[AttnArgs::kMaxParts + 1];
+        int np = 1;
+        const int n = ring_runs(me, G, rows_of, slot_rows, ce, (ce || G == 1) ? 0 : 1, ring.parts, runs, part_row, &np);
+        ok = runs_to_args(a, runs, n, 0);
+        if (np > 1) {
+            a.nparts = np;
+            for (int i = 0; i < np; i++) a.part_row[i] = part_row[i];
         }
         if (trace) cudaEventRecord(ring.t_kernel[0], g.stream);
-        rc = launch_attention_sm100(a);
+        rc = ok ? launch_attention_sm100(a) : IRIS_B200_EINVAL;
         if (trace) cudaEventRecord(ring.t_kernel[1], g.stream);
     }
     /* The transfers of the local rows must not outlive the call. */

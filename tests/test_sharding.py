@@ -197,3 +197,93 @@ def test_ring_schedule_and_merge_on_two_gloo_ranks(lib, tmp_path):
     assert out.returncode == 0, out.stdout + out.stderr
     line = [l for l in out.stdout.splitlines() if l.startswith("RING_MAX_ERR")][0]
     assert float(line.split()[1]) < 2e-5
+
+
+# ---------------------------------------------------------------------------
+# how a launch cuts its keys (pure host arithmetic, no device)
+# ---------------------------------------------------------------------------
+
+def runs_plan(pkg, lib, runs, seq_q, heads, nparts, sms=148):
+    arr = (pkg.binding.KeyRun * len(runs))()
+    for i, r in enumerate(runs):
+        arr[i].view, arr[i].row0, arr[i].rows, arr[i].arrive = r[:4]
+        arr[i].rows_per_word = r[4] if len(r) > 4 else 0
+    tiles = (C.c_int * 9)()
+    nkv = C.c_int()
+    n = lib.iris_b200_attention_runs_plan(arr, len(runs), seq_q, heads, nparts, sms, tiles, C.byref(nkv))
+    return n, list(tiles[:max(n, 0) + 1]), nkv.value
+
+
+def test_key_parts_of_a_launch(lib):
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    # one run, library's choice: the headline shape fills the SMs without a split, the 768-token one is cut in two
+    assert runs_plan(pkg, lib, [(0, 0, 4608, -1)], 4608, 24, 0) == (1, [0, 36], 36)
+    assert runs_plan(pkg, lib, [(0, 0, 768, -1)], 768, 24, 0) == (2, [0, 3, 6], 6)
+    # one rank's share of the 8-rank ring as a plain launch: two parts of equal tiles
+    n, tiles, nkv = runs_plan(pkg, lib, [(0, 0, 16896, -1)], 2112, 24, 0)
+    assert (n, tiles, nkv) == (2, [0, 66, 132], 132)
+    # ragged runs: every run ends in a partial tile of its own; forced parts fall on run boundaries
+    runs = [(0, 5, 130, -1), (1, 11, 257, -1), (0, 140, 64, -1), (1, 279, 1, -1), (0, 209, 511, -1)]
+    n, tiles, nkv = runs_plan(pkg, lib, runs, 300, 3, 3)
+    assert nkv == 2 + 3 + 1 + 1 + 4 and n == 3
+    starts = [0, 2, 5, 6, 7, 11]                                  # first tile of every run, and the end
+    assert tiles[0] == 0 and tiles[-1] == nkv and all(t in starts for t in tiles)
+    assert tiles == sorted(set(tiles))                            # no empty part
+    # more parts than runs: as many as there are runs
+    assert runs_plan(pkg, lib, runs[:2], 300, 3, 8)[0] == 2
+    assert runs_plan(pkg, lib, runs, 300, 3, 1) == (1, [0, nkv], nkv)
+    # bad arguments
+    assert runs_plan(pkg, lib, [(2, 0, 10, -1)], 10, 1, 0)[0] == -1
+    assert runs_plan(pkg, lib, [(0, 0, 0, -1)], 10, 1, 0)[0] == -1
+
+
+@pytest.mark.parametrize("G", [1, 2, 3, 4, 8, 16])
+def test_ring_launch_plan(lib, G):
+    """The attention launch of every rank of a ring call: runs in ring order,
+    slots guarded by their arrival words, parts on the step boundaries of
+    iris_b200_ring_plan (moved down to a tile boundary), never empty."""
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    for S in (16896, 2037, 4608):
+        a, b = C.c_int(), C.c_int()
+        rows_of = []
+        for r in range(G):
+            lib.iris_b200_seq_shard(S, G, r, C.byref(a), C.byref(b))
+            rows_of.append(b.value)
+        rows = np.array(rows_of, np.int32)
+        even = len(set(rows_of)) == 1
+        for rank in range(G):
+            runs = (pkg.binding.KeyRun * 16)()
+            tiles = (C.c_int * 9)()
+            nkv = C.c_int()
+            code = lib.iris_b200_ring_launch_plan(rank, G, rows.ctypes.data, 24, 0, 148, runs, tiles, C.byref(nkv))
+            assert code > 0
+            nruns, nparts = divmod(code, 100)
+            assert (runs[0].view, runs[0].row0, runs[0].rows, runs[0].arrive) == (0, 0, rows_of[rank], -1)
+            if G == 1:
+                assert nruns == 1
+                continue
+            plan, npl = ring_plan(lib, G)
+            assert nparts == npl
+            if even:
+                assert nruns == 2 and runs[1].rows == (G - 1) * rows_of[rank] and runs[1].rows_per_word == rows_of[rank]
+                assert runs[1].arrive == 1 and runs[1].row0 == rows_of[rank]
+                total_tiles = -(-rows_of[rank] // 128) + -(-(G - 1) * rows_of[rank] // 128)
+            else:
+                assert nruns == G
+                slot = max(rows_of)
+                for s in range(1, G):
+                    src = lib.iris_b200_ring_source(rank, s, G)
+                    assert (runs[s].view, runs[s].row0, runs[s].rows, runs[s].arrive) == (1, s * slot, rows_of[src], s)
+                total_tiles = sum(-(-runs[i].rows // 128) for i in range(nruns))
+            assert nkv.value == total_tiles
+            t = list(tiles[:nparts + 1])
+            assert t[0] == 0 and t[-1] == total_tiles and t == sorted(set(t))
+            # a part never starts before the rows of its first step begin
+            first_row = np.concatenate([[0], np.cumsum([rows_of[lib.iris_b200_ring_source(rank, s, G)] for s in range(G)])])
+            for i, (f, _) in enumerate(plan):
+                if even or f == 0:
+                    own_tiles = -(-rows_of[rank] // 128)
+                    want = 0 if f == 0 else own_tiles + (int(first_row[f]) - rows_of[rank]) // 128
+                    assert t[i] == want
