@@ -579,6 +579,112 @@ def projection_run(job, w, pk, reps=20):
             "speedup_vs_cublas_plus_prologue": round(both_ms / fused_ms, 3)}
 
 
+def block_run(job, w, pk, reps=10):
+    """One whole single-stream block around the path (rank 0, N = 1): LayerNorm
+    with modulation, the fused QKV+MLP projection with the prologue, attention,
+    SwiGLU and the output projection with the gated residual - five launches
+    through iris_b200_single_block - next to the reference's own CUDA backend
+    issuing its eight calls (iris_transformer_flux.c:3828-3845) on the same
+    device, where that build is present."""
+    lib, torch = job.lib, job.torch
+    S, H = seq_len(w), w["heads"]
+    dim, mlp = H * D, 3 * H * D
+    ldh, ldc = 3 * dim + 2 * mlp, dim + mlp
+    gen = torch.Generator(device="cuda").manual_seed(9)
+
+    def rnd(shape, scale=1.0, dtype=torch.float32):
+        return (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+    x0 = rnd((S, dim))
+    x = x0.clone()
+    w_in, w_out = rnd((ldh, dim), dim ** -0.5, torch.bfloat16), rnd((dim, ldc), ldc ** -0.5, torch.bfloat16)
+    nq, nk, mod = 1 + 0.1 * rnd((D,)), 1 + 0.1 * rnd((D,)), rnd((3 * dim,), 0.3)
+    cos, sin = rope_tables(w)
+    d_cos, d_sin = lib.to_device(cos), lib.to_device(sin)
+    nbytes = lib.iris_b200_single_block_scratch_bytes(S, dim, mlp)
+    scratch = lib.alloc(nbytes)
+    torch.cuda.synchronize()
+
+    def ours():
+        rc = lib.iris_b200_single_block(x.data_ptr(), scratch, w_in.data_ptr(), w_out.data_ptr(), nq.data_ptr(),
+                                        nk.data_ptr(), mod.data_ptr(), d_cos, d_sin, S, dim, H, mlp, None)
+        assert rc == 0, rc
+
+    for _ in range(3):
+        ours()
+    lib.iris_dev_sync()
+    n0 = lib.iris_b200_launch_count()
+    lib.iris_b200_mark(0)
+    for _ in range(reps):
+        ours()
+    lib.iris_b200_mark(1)
+    ms = lib.iris_b200_mark_elapsed_ms(0, 1) / reps
+    launches = (lib.iris_b200_launch_count() - n0) // reps
+    lib.check()
+    # the same five launches one by one, a mark after each
+    norm = scratch
+    up256 = lambda b: (b + 255) & ~255
+    h = scratch + up256(S * dim * 2)
+    cat = h + up256(S * ldh * 2)
+    stages = ["layer_norm_mod", "qkv_mlp_projection+prologue", "attention", "swiglu", "out_projection+residual"]
+    acc = [0.0] * 5
+    for r in range(reps):
+        lib.iris_b200_mark(0)
+        lib.iris_dev_layer_norm_mod(norm, x.data_ptr(), mod.data_ptr(), mod.data_ptr() + 4 * dim, S, dim, 1e-6)
+        lib.iris_b200_mark(1)
+        lib.iris_b200_linear_qk_norm_rope(h, ldh, norm, w_in.data_ptr(), S, dim, ldh, H, nq.data_ptr(), nk.data_ptr(),
+                                          d_cos, d_sin, 1e-6)
+        lib.iris_b200_mark(2)
+        lib.iris_dev_attention(cat, ldc, h, h + 2 * dim, h + 4 * dim, ldh, S, S, H, H, D, 1.0 / np.sqrt(D), 0, None)
+        lib.iris_b200_mark(3)
+        lib.iris_dev_swiglu(cat + 2 * dim, ldc, h + 6 * dim, h + 2 * (3 * dim + mlp), ldh, S, mlp)
+        lib.iris_b200_mark(4)
+        lib.iris_b200_linear_residual(x.data_ptr(), dim, cat, ldc, w_out.data_ptr(), ldc, mod.data_ptr() + 8 * dim, S,
+                                      ldc, dim)
+        lib.iris_b200_mark(5)
+        for i in range(5):
+            acc[i] += lib.iris_b200_mark_elapsed_ms(i, i + 1)
+    lib.check()
+    flops = 2.0 * S * dim * ldh + 4.0 * S * S * dim + 2.0 * S * ldc * dim
+    out = {"shape": {"tokens": S, "dim": dim, "heads": H, "mlp": mlp}, "launches_per_block": int(launches),
+           "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+           "frac_of_bf16_sustained": round(flops / ms / 1e9 / pk[1], 4),
+           "stage_ms": {n: round(a / reps, 4) for n, a in zip(stages, acc)}}
+    # the reference's CUDA backend: eight calls per block, wall clock between its stream syncs
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    ref = ol.ref_cuda()
+    if ref is not None and ref.iris_dev_init() == 1:
+        proj = torch.empty((S, dim), device="cuda", dtype=torch.float32)
+        xr = x0.clone()
+        torch.cuda.synchronize()
+
+        def theirs():
+            ref.iris_dev_layer_norm_mod(norm, xr.data_ptr(), mod.data_ptr(), mod.data_ptr() + 4 * dim, S, dim, 1e-6)
+            ref.iris_dev_linear_bf16(h, norm, w_in.data_ptr(), S, dim, ldh)
+            ref.iris_dev_head_norm_rope(h, ldh, nq.data_ptr(), d_cos, d_sin, S, H, D, 1e-6, 0)
+            ref.iris_dev_head_norm_rope(h + 2 * dim, ldh, nk.data_ptr(), d_cos, d_sin, S, H, D, 1e-6, 0)
+            ref.iris_dev_attention(cat, ldc, h, h + 2 * dim, h + 4 * dim, ldh, S, S, H, H, D, 1.0 / np.sqrt(D), 0, None)
+            ref.iris_dev_swiglu(cat + 2 * dim, ldc, h + 6 * dim, h + 2 * (3 * dim + mlp), ldh, S, mlp)
+            ref.iris_dev_linear_f32(proj.data_ptr(), cat, w_out.data_ptr(), S, ldc, dim)
+            ref.iris_dev_residual(xr.data_ptr(), proj.data_ptr(), mod.data_ptr() + 8 * dim, S, dim)
+
+        for _ in range(2):
+            theirs()
+        ref.iris_dev_sync()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            theirs()
+        ref.iris_dev_sync()
+        rms = (time.perf_counter() - t0) * 1e3 / reps
+        out["reference_cuda_ms"] = round(rms, 4)
+        out["reference_cuda"] = "iris_cuda.cu unmodified, -arch=sm_100: cuBLAS GEMMs + its own kernels, 8 calls"
+        out["speedup_vs_reference_cuda"] = round(rms / ms, 3)
+    for p in (d_cos, d_sin, scratch):
+        lib.iris_dev_free(p)
+    return out
+
+
 def outproj_run(job, pk, reps=20):
     """The step after the path with the heads sharded over the ranks (N > 1):
     the Klein-4B block's out-projection, [4608, dim / N] x [dim, dim / N]^T per
@@ -751,6 +857,13 @@ def run_b200(args):
         except Exception as e:                     # a side measurement must not cost the headline line
             projection = {"error": repr(e)[:200]}
 
+    block = None
+    if rank == 0 and world == 1 and mode == "single" and w["family"] == "flux2" and not args.no_extras:
+        try:
+            block = block_run(job, w, pk)
+        except Exception as e:
+            block = {"error": repr(e)[:200]}
+
     if rank == 0:
         sharding = {"single": "none",
                     "ring": "ring sequence parallel: K/V rows pushed peer to peer by the copy engines, one attention "
@@ -770,7 +883,7 @@ def run_b200(args):
             "pct_bf16_sustained": round(100 * value / world / pk[1], 2),
             "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
             "roofline": roof, "roofline_prologue": prologue, "cpu_baseline": cpu, "parity": parity,
-            "reference_gpu": ref_gpu, "qkv_projection": projection,
+            "reference_gpu": ref_gpu, "qkv_projection": projection, "single_block": block,
         }
         if speedup is not None:
             out["one_gpu_ms_per_step"] = round(one_gpu, 4)

@@ -145,6 +145,39 @@ int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const
                                   const float *wq, const float *wk,
                                   const float *rope_cos, const float *rope_sin, float eps);
 
+/* The output projection with the gated residual as its epilogue: the
+ * reference's iris_dev_linear_f32 followed by iris_dev_residual
+ * (iris_transformer_flux.c:3843-3844 single blocks, :3809-3811 and :3821-3822
+ * double blocks) as ONE tcgen05 GEMM: x_rows [rows, out] (fp32, row stride ldx)
+ * += gate[c] * (a [rows, in] (bf16, row stride lda) . W [out, in]^T (row
+ * stride ldw)), gate NULL meaning 1. The product is accumulated in fp32 and
+ * never rounded, as in the reference's two-call sequence. Operands 16-byte
+ * aligned; in, out, lda, ldw multiples of 8, ldx a multiple of 4. */
+int iris_b200_linear_residual(float *x_rows, int ldx, const uint16_t *a, int lda,
+                              const uint16_t *W, int ldw, const float *gate,
+                              int rows, int in, int out);
+
+/* ---- one single-stream block --------------------------------------------- */
+
+/* Device bytes iris_b200_single_block() needs at `scratch` (256-byte aligned). */
+size_t iris_b200_single_block_scratch_bytes(int seq, int dim, int mlp);
+
+/* One FLUX.2 single-stream block on the device-resident fp32 hidden state x
+ * [seq, dim], in place: what the reference issues per block in its device
+ * forward (iris_transformer_flux.c:3828-3845; CPU form single_block_forward,
+ * :3341-3477) - LayerNorm with (shift, scale), the fused QKV+MLP projection
+ * with the Q/K prologue, joint attention over all rows, SwiGLU, the output
+ * projection over [attention | mlp] and the gated residual - in five launches.
+ * w_in [3 dim + 2 mlp, dim], w_out [dim, dim + mlp]: bf16, as the checkpoints
+ * store them. norm_q / norm_k [128]. mod = shift | scale | gate, [3 dim]
+ * (the reference's mod_single). rope_cos / rope_sin [seq, 64]. key_mask: NULL
+ * or [seq], nonzero = attend. head_dim is 128: dim == heads * 128. */
+int iris_b200_single_block(float *x, void *scratch,
+                           const uint16_t *w_in, const uint16_t *w_out,
+                           const float *norm_q, const float *norm_k, const float *mod,
+                           const float *rope_cos, const float *rope_sin,
+                           int seq, int dim, int heads, int mlp, const int *key_mask);
+
 /* ---- attention ---------------------------------------------------------- */
 
 enum {

@@ -58,6 +58,32 @@ void iris_dev_f32_to_bf16(uint16_t *dst, const float *src, size_t n);
 void iris_dev_linear_bf16(uint16_t *y, const uint16_t *x, const uint16_t *W,
                           int rows, int in, int out);
 
+/* Same product with an fp32 result (iris_dev.h:50-51, iris_cuda.cu:560-584):
+ * the output projections, whose result joins the fp32 hidden state. */
+void iris_dev_linear_f32(float *y, const uint16_t *x, const uint16_t *W,
+                         int rows, int in, int out);
+
+/* out = LayerNorm(x) * (1 + scale) + shift without affine parameters, fp32
+ * in, bf16 out; shift / scale: [dim], either may be NULL. Replaces
+ * iris_dev.h:57-59 (kernel iris_cuda.cu:349-370): mean, then the variance
+ * about the mean, both in fp32. */
+void iris_dev_layer_norm_mod(uint16_t *out, const float *x,
+                             const float *shift, const float *scale,
+                             int rows, int dim, float eps);
+
+/* out[r, c] = silu(gate[r, c]) * up[r, c] on bf16 column slices (gate / up row
+ * stride ldi, out row stride ldo). Replaces iris_dev.h:94-95 (kernel
+ * iris_cuda.cu:300-307). The exponential is the hardware approximation
+ * (ex2.approx), so a result may differ from the reference's expf() by one
+ * bf16 unit in the last place where it falls on a rounding boundary. */
+void iris_dev_swiglu(uint16_t *out, int ldo, const uint16_t *gate,
+                     const uint16_t *up, int ldi, int rows, int cols);
+
+/* x[r, c] += gate[c] * a[r, c] in fp32, or x += a when gate is NULL. Replaces
+ * iris_dev.h:98-99 (kernel iris_cuda.cu:309-314). */
+void iris_dev_residual(float *x, const float *a, const float *gate,
+                       int rows, int dim);
+
 /* In place on the bf16 heads x[s, h * head_dim + d] (row stride ld, in
  * elements): per-head RMSNorm x * rsqrt(mean(x^2) + eps) * w[d], then
  * rotation of pair i by the angle of row s (rope_cos / rope_sin:

@@ -27,6 +27,10 @@ SIGNATURES = {
     "iris_dev_sync": (None, []),
     "iris_dev_f32_to_bf16": (None, [VP, VP, SZ]),
     "iris_dev_linear_bf16": (None, [VP, VP, VP, INT, INT, INT]),
+    "iris_dev_linear_f32": (None, [VP, VP, VP, INT, INT, INT]),
+    "iris_dev_layer_norm_mod": (None, [VP, VP, VP, VP, INT, INT, FLT]),
+    "iris_dev_swiglu": (None, [VP, INT, VP, VP, INT, INT, INT]),
+    "iris_dev_residual": (None, [VP, VP, VP, INT, INT]),
     "iris_dev_head_norm_rope": (None, [VP, INT, VP, VP, VP, INT, INT, INT, FLT, INT]),
     "iris_dev_attention": (None, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP]),
     # iris_kernels.h
@@ -52,6 +56,9 @@ SIGNATURES = {
     "iris_b200_mark_elapsed_ms": (FLT, [INT, INT]),
     "iris_b200_qk_norm_rope": (INT, [VP, VP, INT, VP, VP, VP, VP, INT, INT, INT, FLT, INT]),
     "iris_b200_linear_qk_norm_rope": (INT, [VP, INT, VP, VP, INT, INT, INT, INT, VP, VP, VP, VP, FLT]),
+    "iris_b200_linear_residual": (INT, [VP, INT, VP, INT, VP, INT, VP, INT, INT, INT]),
+    "iris_b200_single_block_scratch_bytes": (SZ, [INT, INT, INT]),
+    "iris_b200_single_block": (INT, [VP, VP, VP, VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, VP]),
     "iris_b200_attention_ex": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP, INT]),
     "iris_b200_attention_kernel_for": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT]),
     "iris_b200_head_shard": (INT, [INT, INT, INT, C.POINTER(INT), C.POINTER(INT)]),

@@ -1,0 +1,272 @@
+/*
+ * The row-wise operators either side of the attention path inside one
+ * transformer block, and the FLUX.2 single-stream block assembled from them.
+ *
+ *   iris_dev_layer_norm_mod   LayerNorm without affine parameters, then
+ *                             (1 + scale) and shift, fp32 in, bf16 out
+ *                             (reference kernel: iris_cuda.cu:349-370)
+ *   iris_dev_swiglu           silu(gate) * up on bf16 column slices
+ *                             (iris_cuda.cu:300-307)
+ *   iris_dev_residual         x += gate * a in fp32 (iris_cuda.cu:309-314)
+ *   iris_b200_single_block    the sequence the reference issues per single
+ *                             block (iris_transformer_flux.c:3828-3845) in five
+ *                             launches instead of eight: the projection
+ *                             applies the Q/K prologue in its epilogue, and
+ *                             the output projection adds the gated result to
+ *                             the hidden state in its epilogue.
+ *
+ * All three kernels are HBM-bound: every element is read once and written
+ * once, 16 bytes per access.
+ */
+#include "common.cuh"
+
+#include "iris_dev.h"
+#include "kernels.h"
+
+namespace iris_b200 {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+constexpr int kRowVecs = 4;          /* float4 per thread kept in registers: dims up to 4096 */
+
+__device__ __forceinline__ float block_sum(float v, float *sh) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();                  /* sh may still be read from the previous reduction */
+    if (lane == 0) sh[warp] = v;
+    __syncthreads();
+    float t = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kRowThreads / 32; w++) t += sh[w];
+    return t;
+}
+
+/* One block per row at a time. The row stays in registers between the three
+ * passes (mean, variance about the mean, output) when it fits; longer rows
+ * are re-read, from L1/L2. Two-pass variance as in the reference. */
+__global__ void __launch_bounds__(kRowThreads)
+k_layer_norm_mod(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift,
+                 const float *__restrict__ scale, int rows, int dim, float eps) {
+    __shared__ float sh[kRowThreads / 32];
+    const int nvec = dim >> 2;
+    const bool in_regs = nvec <= kRowThreads * kRowVecs && (dim & 3) == 0;
+    const float inv_dim = 1.0f / (float)dim;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float *xr = x + (size_t)row * dim;
+        uint16_t *o = out + (size_t)row * dim;
+        if (in_regs) {
+            float4 v[kRowVecs];
+            float s = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kRowVecs; k++) {
+                const int i = threadIdx.x + k * kRowThreads;
+                v[k] = i < nvec ? reinterpret_cast<const float4 *>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+            }
+            const float mean = block_sum(s, sh) * inv_dim;
+            float q = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kRowVecs; k++) {
+                const int i = threadIdx.x + k * kRowThreads;
+                if (i < nvec) {
+                    const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
+                    q += (a * a + b * b) + (c * c + d * d);
+                }
+            }
+            const float inv = rsqrtf(block_sum(q, sh) * inv_dim + eps);
+#pragma unroll
+            for (int k = 0; k < kRowVecs; k++) {
+                const int i = threadIdx.x + k * kRowThreads;
+                if (i >= nvec) continue;
+                float n[4] = {(v[k].x - mean) * inv, (v[k].y - mean) * inv, (v[k].z - mean) * inv, (v[k].w - mean) * inv};
+                if (scale) {
+                    const float4 sc = reinterpret_cast<const float4 *>(scale)[i];
+                    n[0] *= 1.0f + sc.x; n[1] *= 1.0f + sc.y; n[2] *= 1.0f + sc.z; n[3] *= 1.0f + sc.w;
+                }
+                if (shift) {
+                    const float4 sf = reinterpret_cast<const float4 *>(shift)[i];
+                    n[0] += sf.x; n[1] += sf.y; n[2] += sf.z; n[3] += sf.w;
+                }
+                reinterpret_cast<uint2 *>(o)[i] = make_uint2(cvt_bf16x2(n[0], n[1]), cvt_bf16x2(n[2], n[3]));
+            }
+        } else {
+            float s = 0.0f;
+            for (int i = threadIdx.x; i < dim; i += kRowThreads) s += xr[i];
+            const float mean = block_sum(s, sh) * inv_dim;
+            float q = 0.0f;
+            for (int i = threadIdx.x; i < dim; i += kRowThreads) {
+                const float d = xr[i] - mean;
+                q += d * d;
+            }
+            const float inv = rsqrtf(block_sum(q, sh) * inv_dim + eps);
+            for (int i = threadIdx.x; i < dim; i += kRowThreads) {
+                float n = (xr[i] - mean) * inv;
+                if (scale) n *= 1.0f + scale[i];
+                if (shift) n += shift[i];
+                o[i] = f2bf(n);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+/* Eight columns per thread when the slices allow 16-byte accesses. */
+__global__ void __launch_bounds__(256)
+k_swiglu8(uint16_t *__restrict__ out, int ldo, const uint16_t *__restrict__ gate, const uint16_t *__restrict__ up, int ldi,
+          int cols8, size_t n8) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols8, c = (i - r * cols8) * 8;
+        const uint4 gv = *reinterpret_cast<const uint4 *>(gate + r * ldi + c);
+        const uint4 uv = *reinterpret_cast<const uint4 *>(up + r * ldi + c);
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            ow[k] = cvt_bf16x2(silu_mul(bf_lo(gw[k]), bf_lo(uw[k])), silu_mul(bf_hi(gw[k]), bf_hi(uw[k])));
+        *reinterpret_cast<uint4 *>(out + r * ldo + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_swiglu1(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi, int cols, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols, c = i - r * cols;
+        out[r * ldo + c] = f2bf(silu_mul(bf2f(gate[r * ldi + c]), bf2f(up[r * ldi + c])));
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_residual4(float *__restrict__ x, const float *__restrict__ a, const float *__restrict__ gate, int dim4, size_t n4) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 xv = reinterpret_cast<float4 *>(x)[i];
+        const float4 av = reinterpret_cast<const float4 *>(a)[i];
+        float4 g4 = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (gate) g4 = reinterpret_cast<const float4 *>(gate)[i % dim4];
+        xv.x += g4.x * av.x; xv.y += g4.y * av.y; xv.z += g4.z * av.z; xv.w += g4.w * av.w;
+        reinterpret_cast<float4 *>(x)[i] = xv;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_residual1(float *x, const float *a, const float *gate, int dim, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] += (gate ? gate[i % dim] : 1.0f) * a[i];
+}
+
+unsigned blocks_for(size_t items, int per_block, int per_sm) {
+    size_t b = (items + per_block - 1) / per_block;
+    const size_t cap = (size_t)g.sm_count * per_sm;
+    if (b > cap) b = cap;
+    return (unsigned)(b ? b : 1);
+}
+
+bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+int layer_norm_mod(uint16_t *out, const float *x, const float *shift, const float *scale, int rows, int dim, float eps) {
+    if (!require_device("layer_norm_mod")) return IRIS_B200_ENODEV;
+    if (!out || !x || rows < 0 || dim <= 0) {
+        set_error(IRIS_B200_EINVAL, "layer_norm_mod", "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    if (rows == 0) return IRIS_B200_OK;
+    /* The vector path needs 16-byte rows; anything else takes the scalar path
+     * inside the same kernel, which is chosen by dim % 4 there. */
+    if (dim % 4 == 0 && !(aligned16(x) && aligned16(shift) && aligned16(scale) && ((uintptr_t)out & 7) == 0)) {
+        set_error(IRIS_B200_EUNSUPPORTED, "layer_norm_mod", "operands must be 16-byte aligned when dim is a multiple of 4");
+        return IRIS_B200_EUNSUPPORTED;
+    }
+    k_layer_norm_mod<<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+    return after_launch("k_layer_norm_mod") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+int swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi, int rows, int cols) {
+    if (!require_device("swiglu")) return IRIS_B200_ENODEV;
+    if (!out || !gate || !up || rows < 0 || cols < 0 || ldo < cols || ldi < cols) {
+        set_error(IRIS_B200_EINVAL, "swiglu", "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    const size_t n = (size_t)rows * cols;
+    if (n == 0) return IRIS_B200_OK;
+    if (cols % 8 == 0 && ldo % 8 == 0 && ldi % 8 == 0 && aligned16(out) && aligned16(gate) && aligned16(up))
+        k_swiglu8<<<blocks_for(n / 8, 256, 8), 256, 0, g.stream>>>(out, ldo, gate, up, ldi, cols / 8, n / 8);
+    else
+        k_swiglu1<<<blocks_for(n, 256, 8), 256, 0, g.stream>>>(out, ldo, gate, up, ldi, cols, n);
+    return after_launch("k_swiglu") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+int residual(float *x, const float *a, const float *gate, int rows, int dim) {
+    if (!require_device("residual")) return IRIS_B200_ENODEV;
+    if (!x || !a || rows < 0 || dim <= 0) {
+        set_error(IRIS_B200_EINVAL, "residual", "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    const size_t n = (size_t)rows * dim;
+    if (n == 0) return IRIS_B200_OK;
+    if (dim % 4 == 0 && aligned16(x) && aligned16(a) && aligned16(gate))
+        k_residual4<<<blocks_for(n / 4, 256, 8), 256, 0, g.stream>>>(x, a, gate, dim / 4, n / 4);
+    else
+        k_residual1<<<blocks_for(n, 256, 8), 256, 0, g.stream>>>(x, a, gate, dim, n);
+    return after_launch("k_residual") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+}  // namespace
+
+}  // namespace iris_b200
+
+using namespace iris_b200;
+
+extern "C" void iris_dev_layer_norm_mod(uint16_t *out, const float *x, const float *shift, const float *scale, int rows,
+                                        int dim, float eps) {
+    layer_norm_mod(out, x, shift, scale, rows, dim, eps);
+}
+
+extern "C" void iris_dev_swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi, int rows,
+                                int cols) {
+    swiglu(out, ldo, gate, up, ldi, rows, cols);
+}
+
+extern "C" void iris_dev_residual(float *x, const float *a, const float *gate, int rows, int dim) {
+    residual(x, a, gate, rows, dim);
+}
+
+extern "C" size_t iris_b200_single_block_scratch_bytes(int seq, int dim, int mlp) {
+    if (seq < 0 || dim <= 0 || mlp <= 0) return 0;
+    const size_t ldh = 3 * (size_t)dim + 2 * (size_t)mlp, ldc = (size_t)dim + mlp;
+    /* norm [seq, dim] | h [seq, ldh] | cat [seq, ldc], bf16, each 256-byte aligned */
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    return up256((size_t)seq * dim * 2) + up256((size_t)seq * ldh * 2) + up256((size_t)seq * ldc * 2);
+}
+
+extern "C" int iris_b200_single_block(float *x, void *scratch, const uint16_t *w_in, const uint16_t *w_out,
+                                      const float *norm_q, const float *norm_k, const float *mod,
+                                      const float *rope_cos, const float *rope_sin, int seq, int dim, int heads,
+                                      int mlp, const int *key_mask) {
+    if (!require_device("single_block")) return IRIS_B200_ENODEV;
+    if (!x || !scratch || !w_in || !w_out || !norm_q || !norm_k || !mod || !rope_cos || !rope_sin || seq < 0 || dim <= 0 ||
+        heads <= 0 || mlp <= 0 || dim != heads * 128 || ((uintptr_t)scratch & 255) != 0) {
+        set_error(IRIS_B200_EINVAL, "single_block", dim != heads * 128 ? "head_dim must be 128" : "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    if (seq == 0) return IRIS_B200_OK;
+    const int ldh = 3 * dim + 2 * mlp, ldc = dim + mlp;
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    uint16_t *norm = reinterpret_cast<uint16_t *>(base);
+    uint16_t *h = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2));
+    uint16_t *cat = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2) + up256((size_t)seq * ldh * 2));
+    const float eps = 1e-6f;
+    int rc = layer_norm_mod(norm, x, mod, mod + dim, seq, dim, eps);
+    if (rc != IRIS_B200_OK) return rc;
+    rc = iris_b200_linear_qk_norm_rope(h, ldh, norm, w_in, seq, dim, ldh, heads, norm_q, norm_k, rope_cos, rope_sin, eps);
+    if (rc != IRIS_B200_OK) return rc;
+    iris_b200_clear_error();
+    iris_dev_attention(cat, ldc, h, h + dim, h + 2 * dim, ldh, seq, seq, heads, heads, 128, 0.08838834764831845f, 0, key_mask);
+    rc = iris_b200_last_error();
+    if (rc != IRIS_B200_OK) return rc;
+    rc = swiglu(cat + dim, ldc, h + 3 * dim, h + 3 * dim + mlp, ldh, seq, mlp);
+    if (rc != IRIS_B200_OK) return rc;
+    return iris_b200_linear_residual(x, dim, cat, ldc, w_out, ldc, mod + 2 * dim, seq, ldc, dim);
+}

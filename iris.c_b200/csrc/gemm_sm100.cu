@@ -80,7 +80,14 @@ struct Params {
      * owns each row, into this rank's slab of the owner's staging buffer,
      * with plain stores over NVLink; the last CTA out then advances this
      * rank's arrival word on every owner. */
-    int scatter;                /* 0: bf16 result to y; 1: fp32 rows to their owners */
+    int scatter;                /* 0: bf16 result to y; 1: fp32 rows to their owners; 2: fp32 rows to y32 */
+    /* fp32 mode (the reference's iris_dev_linear_f32, iris_cuda.cu:560-584,
+     * and, with accumulate, that followed by iris_dev_residual, :339-343, in
+     * one pass): y32[r, c] = acc, or y32[r, c] += gate[c] * acc (gate NULL: 1). */
+    float *y32;
+    int ld32;
+    int accumulate;
+    const float *gate;
     int nranks;
     int row_first[kMaxScatterRanks + 1];    /* rank q owns the rows [row_first[q], row_first[q + 1]) */
     float *slab[kMaxScatterRanks];          /* where this rank's partial rows of owner q go ([rows of q, out] fp32) */
@@ -223,6 +230,36 @@ __device__ __forceinline__ void scatter_rows_f32(const uint32_t *src, const Para
     __syncwarp();
 }
 
+/* 32 rows x 32 fp32 columns of one warp to an fp32 matrix, stored or added
+ * in place with a per-column gate (ncols a multiple of 4). Every element of
+ * the matrix belongs to exactly one warp of one tile, so the read-modify-write
+ * needs no atomics. */
+__device__ __forceinline__ void rows_f32(const uint32_t *src, const Params &p, int wrow0, int nrows, int c0, int ncols,
+                                         unsigned char *stage_w, int lane) {
+#pragma unroll
+    for (int c8 = 0; c8 < 8; c8++)
+        *reinterpret_cast<uint4 *>(stage_w + lane * 128 + ((c8 ^ (lane & 7)) << 4)) =
+            make_uint4(src[4 * c8], src[4 * c8 + 1], src[4 * c8 + 2], src[4 * c8 + 3]);
+    __syncwarp();
+    const int ch = lane & 7;
+    float4 g4 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+    if (p.gate && ch * 4 < ncols) g4 = *reinterpret_cast<const float4 *>(p.gate + c0 + ch * 4);
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int r = k * 4 + (lane >> 3);
+        float4 v = *reinterpret_cast<const float4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4));
+        if (r < nrows && ch * 4 < ncols) {
+            float4 *dst = reinterpret_cast<float4 *>(p.y32 + (size_t)(wrow0 + r) * p.ld32 + c0 + ch * 4);
+            if (p.accumulate) {
+                const float4 x = *dst;
+                v = make_float4(fmaf(g4.x, v.x, x.x), fmaf(g4.y, v.y, x.y), fmaf(g4.z, v.z, x.z), fmaf(g4.w, v.w, x.w));
+            }
+            *dst = v;
+        }
+    }
+    __syncwarp();
+}
+
 __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned char *stage, const float *w_smem,
                                          uint32_t tmem) {
     const int lane = threadIdx.x & 31;
@@ -254,7 +291,8 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
                 for (int sub = 0; sub < 4; sub++) {
                     const int c0 = col0 + sub * 32;
                     const int ncols = p.out - c0 < 32 ? (p.out - c0 < 0 ? 0 : p.out - c0) : 32;
-                    scatter_rows_f32(acc + sub * 32, p, wrow0, nrows, c0, ncols, stage_w, lane);
+                    if (p.scatter == 1) scatter_rows_f32(acc + sub * 32, p, wrow0, nrows, c0, ncols, stage_w, lane);
+                    else rows_f32(acc + sub * 32, p, wrow0, nrows, c0, ncols, stage_w, lane);
                 }
                 continue;
             }
@@ -360,7 +398,7 @@ k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
         epilogue(c, p, smem_gen + kSmemStage, w_smem, tmem);
     }
 
-    if (p.scatter) __threadfence_system();          /* this thread's rows are out before the CTA counts itself out */
+    if (p.scatter == 1) __threadfence_system();          /* this thread's rows are out before the CTA counts itself out */
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -371,7 +409,7 @@ k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
     /* Row-parallel mode: once every CTA's rows are on their way (each fenced
      * at system scope above), the last CTA tells every owner that this rank's
      * partial sums of the call have arrived. A launch that gave up tells nobody. */
-    if (p.scatter && threadIdx.x == 0) {
+    if (p.scatter == 1 && threadIdx.x == 0) {
         const bool aborted = *c.abort_flag != 0u;
         __threadfence();
         const unsigned int prev = atomicAdd(p.done, aborted ? 0x10000u + 1u : 1u);
@@ -448,10 +486,13 @@ void gemm_release(void) { g_gemm_configured = 0; }
  * the first 2 * heads * 128 columns are Q and K heads that get the prologue. */
 static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const uint16_t *W, int ldw, int rows, int in,
                          int out, int heads, const float *wq, const float *wk, const float *rope_cos,
-                         const float *rope_sin, float eps, const ScatterArgs *sc, const char *op) {
+                         const float *rope_sin, float eps, const ScatterArgs *sc, const char *op,
+                         const F32Out *f32 = NULL) {
     using namespace gemm;
     if (!require_device(op)) return IRIS_B200_ENODEV;
-    if ((!y && !sc) || !x || !W || rows < 0 || in <= 0 || out <= 0 || (y && ldy < out) || heads < 0 || ldx < in || ldw < in ||
+    if ((!y && !sc && !f32) || (f32 && (!f32->y || f32->ld < out || f32->ld % 4 != 0 || ((uintptr_t)f32->y & 15) != 0 ||
+                                        ((uintptr_t)f32->gate & 15) != 0 || sc || heads > 0)) ||
+        !x || !W || rows < 0 || in <= 0 || out <= 0 || (y && ldy < out) || heads < 0 || ldx < in || ldw < in ||
         (heads > 0 && (!wq || !wk || !rope_cos || !rope_sin || 2 * heads * 128 > out)) ||
         (sc && (sc->nranks < 1 || sc->nranks > kMaxScatterRanks))) {
         set_error(IRIS_B200_EINVAL, op, "bad argument");
@@ -499,6 +540,13 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         p.seq = sc->seq;
         p.done = sc->done;
     }
+    if (f32) {
+        p.scatter = 2;
+        p.y32 = f32->y;
+        p.ld32 = f32->ld;
+        p.accumulate = f32->accumulate;
+        p.gate = f32->gate;
+    }
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const unsigned grid = (unsigned)(tiles < g.sm_count ? tiles : g.sm_count);
     k_linear_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmx, tmw, p);
@@ -527,6 +575,20 @@ using namespace iris_b200;
 
 extern "C" void iris_dev_linear_bf16(uint16_t *y, const uint16_t *x, const uint16_t *W, int rows, int in, int out) {
     launch_linear(y, out, x, in, W, in, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_bf16");
+}
+
+/* Same arithmetic as the reference's iris_dev_linear_f32 (iris_cuda.cu:560-584):
+ * bf16 operands, fp32 accumulation, fp32 result. */
+extern "C" void iris_dev_linear_f32(float *y, const uint16_t *x, const uint16_t *W, int rows, int in, int out) {
+    const F32Out f = {y, out, NULL, 0};
+    launch_linear(NULL, 0, x, in, W, in, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_f32", &f);
+}
+
+extern "C" int iris_b200_linear_residual(float *x_rows, int ldx, const uint16_t *a, int lda, const uint16_t *W, int ldw,
+                                         const float *gate, int rows, int in, int out) {
+    const F32Out f = {x_rows, ldx, gate, 1};
+    return launch_linear(NULL, 0, a, lda, W, ldw, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_residual",
+                         &f);
 }
 
 extern "C" int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W,

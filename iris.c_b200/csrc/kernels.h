@@ -94,6 +94,15 @@ int launch_linear_scatter(const uint16_t *x, int ldx, const uint16_t *W, int ldw
 int launch_residual_from_slabs(float *x, const float *slabs, size_t slab_stride, int nranks, const float *gate, int rows,
                                int dim, const uint32_t *arrive, uint32_t seq);
 
+/* fp32 destination of a linear layer: y [rows, out] with row stride ld,
+ * stored, or (accumulate) y += gate[c] * result with gate NULL meaning 1. */
+struct F32Out {
+    float *y;
+    int ld;
+    const float *gate;
+    int accumulate;
+};
+
 /* Host-side fault injection: the next launch that splits its keys finds a
  * ticket that nobody took. */
 void sm100_inject_stale_ticket(void);

@@ -467,6 +467,144 @@ int orc_zi_positions(int *pos, int *mask, int ht, int wt, int cap_seq) {
 }
 
 /* ------------------------------------------------------------------------
+ * The operators either side of the attention path inside a block, and one
+ * FLUX.2 single-stream block in the arithmetic of the reference's device
+ * forward (every stored intermediate rounded to bf16 where the device stores
+ * bf16).
+ * ------------------------------------------------------------------------ */
+
+/* k_layer_norm_mod, iris_cuda.cu:349-370: mean, variance about the mean,
+ * n = (x - mean) * inv; n *= 1 + scale; n += shift; bf16. Sums in double here
+ * (the device sums in fp32 in tree order: results agree to one bf16 ulp). */
+void orc_layer_norm_mod(uint16_t *out, const float *x, const float *shift, const float *scale,
+                        int rows, int dim, float eps) {
+    for (int r = 0; r < rows; r++) {
+        const float *xr = x + (size_t)r * dim;
+        double s = 0;
+        for (int i = 0; i < dim; i++) s += xr[i];
+        float mean = (float)(s / dim);
+        double v = 0;
+        for (int i = 0; i < dim; i++) {
+            float d = xr[i] - mean;
+            v += (double)d * d;
+        }
+        float inv = 1.0f / sqrtf((float)(v / dim) + eps);
+        for (int i = 0; i < dim; i++) {
+            float n = (xr[i] - mean) * inv;
+            if (scale) n *= 1.0f + scale[i];
+            if (shift) n += shift[i];
+            out[(size_t)r * dim + i] = orc_f2bf(n);
+        }
+    }
+}
+
+/* k_swiglu, iris_cuda.cu:300-307. */
+void orc_swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi,
+                int rows, int cols) {
+    for (int r = 0; r < rows; r++)
+        for (int c = 0; c < cols; c++) {
+            float g = orc_bf2f(gate[(size_t)r * ldi + c]);
+            out[(size_t)r * ldo + c] = orc_f2bf(g / (1.0f + expf(-g)) * orc_bf2f(up[(size_t)r * ldi + c]));
+        }
+}
+
+/* k_residual, iris_cuda.cu:309-314. */
+void orc_residual(float *x, const float *a, const float *gate, int rows, int dim) {
+    for (int r = 0; r < rows; r++)
+        for (int c = 0; c < dim; c++)
+            x[(size_t)r * dim + c] += (gate ? gate[c] : 1.0f) * a[(size_t)r * dim + c];
+}
+
+typedef struct {
+    float *y;
+    int ldy;
+    const uint16_t *x;
+    int ldx;
+    const uint16_t *W;
+    int ldw, in, out, r0, r1;
+} lin_job_t;
+
+static void *lin_worker(void *arg) {
+    lin_job_t *w = arg;
+    float *xf = malloc((size_t)w->in * sizeof(float));
+    float *wf = malloc((size_t)w->in * sizeof(float));
+    for (int c = 0; c < w->out; c++) {
+        orc_bf16_to_f32(wf, w->W + (size_t)c * w->ldw, w->in);
+        for (int r = w->r0; r < w->r1; r++) {
+            orc_bf16_to_f32(xf, w->x + (size_t)r * w->ldx, w->in);
+            float acc[8] = {0};
+            int i = 0;
+            for (; i + 8 <= w->in; i += 8)
+                for (int l = 0; l < 8; l++) acc[l] += xf[i + l] * wf[i + l];
+            for (; i < w->in; i++) acc[0] += xf[i] * wf[i];
+            w->y[(size_t)r * w->ldy + c] =
+                ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
+        }
+    }
+    free(xf);
+    free(wf);
+    return NULL;
+}
+
+/* y [rows, out] (fp32, row stride ldy) = x [rows, in] . W [out, in]^T with
+ * bf16 operands and fp32 accumulation: the product iris_dev_linear_f32
+ * computes (iris_cuda.cu:560-584); rounding y to bf16 afterwards gives
+ * iris_dev_linear_bf16 (:463-506). Rows are split over threads. */
+void orc_linear(float *y, int ldy, const uint16_t *x, int ldx, const uint16_t *W, int ldw,
+                int rows, int in, int out, int nthreads) {
+    if (nthreads <= 0) nthreads = (int)sysconf(_SC_NPROCESSORS_ONLN);
+    if (nthreads > rows) nthreads = rows;
+    if (nthreads < 1) nthreads = 1;
+    pthread_t th[nthreads];
+    lin_job_t job[nthreads];
+    int started[nthreads];
+    for (int t = 0; t < nthreads; t++) {
+        job[t] = (lin_job_t){y, ldy, x, ldx, W, ldw, in, out,
+                             (int)((long)rows * t / nthreads), (int)((long)rows * (t + 1) / nthreads)};
+        started[t] = nthreads > 1 && pthread_create(&th[t], NULL, lin_worker, &job[t]) == 0;
+        if (!started[t]) lin_worker(&job[t]);
+    }
+    for (int t = 0; t < nthreads; t++)
+        if (started[t]) pthread_join(th[t], NULL);
+}
+
+/* One single-stream block as the reference's device forward issues it
+ * (iris_transformer_flux.c:3828-3845): layer_norm_mod -> linear_bf16 ->
+ * head_norm_rope on Q and K -> attention -> swiglu -> linear_f32 -> residual.
+ * x [seq, dim] fp32 in place; mod = shift | scale | gate. Returns 0, or -1
+ * when memory runs out. */
+int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
+                     const float *norm_q, const float *norm_k, const float *mod,
+                     const float *rope_cos, const float *rope_sin,
+                     int seq, int dim, int heads, int mlp, const int *key_mask, int nthreads) {
+    int hd = dim / heads, ldh = 3 * dim + 2 * mlp, ldc = dim + mlp;
+    size_t nh = (size_t)seq * ldh, nc = (size_t)seq * ldc, nd = (size_t)seq * dim;
+    uint16_t *norm = malloc(nd * 2), *h = malloc(nh * 2), *cat = malloc(nc * 2);
+    float *hf = malloc(nh * sizeof(float)), *qkv = malloc(3 * nd * sizeof(float));
+    float *att = malloc(nd * sizeof(float)), *proj = malloc(nd * sizeof(float));
+    int rc = -1;
+    if (norm && h && cat && hf && qkv && att && proj) {
+        orc_layer_norm_mod(norm, x, mod, mod + dim, seq, dim, 1e-6f);
+        orc_linear(hf, ldh, norm, dim, w_in, dim, seq, dim, ldh, nthreads);
+        orc_f32_to_bf16(h, hf, nh);
+        orc_head_norm_rope_bf16(h, ldh, norm_q, rope_cos, rope_sin, seq, heads, hd, 1e-6f, 0);
+        orc_head_norm_rope_bf16(h + dim, ldh, norm_k, rope_cos, rope_sin, seq, heads, hd, 1e-6f, 0);
+        for (int s = 0; s < seq; s++)
+            orc_bf16_to_f32(qkv + (size_t)s * 3 * dim, h + (size_t)s * ldh, 3 * (size_t)dim);
+        orc_dev_attention(att, dim, qkv, qkv + dim, qkv + 2 * dim, 3 * dim, seq, seq, heads, heads, hd,
+                          1.0f / sqrtf((float)hd), 0, key_mask, NULL, 0, nthreads);
+        for (int s = 0; s < seq; s++)
+            orc_f32_to_bf16(cat + (size_t)s * ldc, att + (size_t)s * dim, dim);
+        orc_swiglu(cat + dim, ldc, h + 3 * dim, h + 3 * dim + mlp, ldh, seq, mlp);
+        orc_linear(proj, dim, cat, ldc, w_out, ldc, seq, ldc, dim, nthreads);
+        orc_residual(x, proj, mod + 2 * dim, seq, dim);
+        rc = 0;
+    }
+    free(norm); free(h); free(cat); free(hf); free(qkv); free(att); free(proj);
+    return rc;
+}
+
+/* ------------------------------------------------------------------------
  * Metrics
  * ------------------------------------------------------------------------ */
 

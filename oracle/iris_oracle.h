@@ -100,6 +100,29 @@ void orc_zi_rope(float *cos_out, float *sin_out, const int *pos, int seq, float 
  * mask: [seq]. Returns seq. */
 int orc_zi_positions(int *pos, int *mask, int ht, int wt, int cap_seq);
 
+/* ---- the operators either side of the path, and one single-stream block ---- */
+/* LayerNorm without affine parameters, then (1 + scale) and shift; fp32 in,
+ * bf16 out (k_layer_norm_mod, iris_cuda.cu:349-370). shift / scale may be NULL. */
+void orc_layer_norm_mod(uint16_t *out, const float *x, const float *shift, const float *scale,
+                        int rows, int dim, float eps);
+/* silu(gate) * up on bf16 column slices (k_swiglu, iris_cuda.cu:300-307). */
+void orc_swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi,
+                int rows, int cols);
+/* x += gate * a in fp32, gate NULL = 1 (k_residual, iris_cuda.cu:309-314). */
+void orc_residual(float *x, const float *a, const float *gate, int rows, int dim);
+/* y = x . W^T, bf16 operands, fp32 accumulation and result
+ * (iris_dev_linear_f32, iris_cuda.cu:560-584). nthreads <= 0: all cores. */
+void orc_linear(float *y, int ldy, const uint16_t *x, int ldx, const uint16_t *W, int ldw,
+                int rows, int in, int out, int nthreads);
+/* One FLUX.2 single-stream block in the arithmetic of the reference's device
+ * forward (iris_transformer_flux.c:3828-3845), in place on x [seq, dim] fp32.
+ * w_in [3 dim + 2 mlp, dim], w_out [dim, dim + mlp] bf16; mod = shift | scale
+ * | gate; rope tables compact [seq, head_dim / 2]. */
+int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
+                     const float *norm_q, const float *norm_k, const float *mod,
+                     const float *rope_cos, const float *rope_sin,
+                     int seq, int dim, int heads, int mlp, const int *key_mask, int nthreads);
+
 /* ---- comparison metrics ---- */
 /* Per head over the listed rows (NULL = all): max |a - b| and cosine.
  * a, b: [seq, heads*hd] with row strides lda / ldb. Writes heads entries. */

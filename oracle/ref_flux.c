@@ -9,7 +9,8 @@
  * Reference functions reached (iris_transformer_flux.c):
  *   apply_qk_norm :1289, compute_rope_2d :823, compute_rope_2d_with_t_offset
  *   :887, apply_rope_2d :952, compute_rope_text :981, mha_forward :1585,
- *   joint_attention :1682, ensure_attn_scores :1382.
+ *   joint_attention :1682, ensure_attn_scores :1382, single_block_forward
+ *   :3341.
  */
 #include "iris_transformer_flux.c"
 
@@ -81,6 +82,52 @@ int ref_flux_mha(float *out, const float *q, const float *k, const float *v,
     mha_forward(out, q, k, v, seq, heads, head_dim, &tf);
     flux_ctx_free(&tf);
     return 0;
+}
+
+/* One single-stream block on the CPU, fp32 weights: single_block_forward with
+ * a context that holds only the work buffers the function touches (the
+ * reference allocates the same in its loader, :1443-1461). hidden [seq, dim]
+ * is updated in place. t_emb [dim] and adaln_weight [3 dim, dim] give the
+ * modulation as in the reference; rope tables are the reference's own
+ * ([rows, head_dim]). Returns 0, or -1 when memory runs out. */
+int ref_flux_single_block(float *hidden, const float *w_in, const float *w_out,
+                          const float *norm_q, const float *norm_k,
+                          const float *t_emb, const float *adaln_weight,
+                          const float *img_cos, const float *img_sin,
+                          const float *txt_cos, const float *txt_sin,
+                          int seq, int img_offset, int heads, int head_dim, int mlp) {
+    iris_transformer_flux_t tf;
+    single_block_t block;
+    if (flux_ctx(&tf, seq, 0, heads, head_dim) != 0) { flux_ctx_free(&tf); return -1; }
+    int dim = heads * head_dim, fused = 3 * dim + 2 * mlp;
+    size_t n = (size_t)seq;
+    tf.mlp_hidden = mlp;
+    tf.work1 = malloc(n * dim * sizeof(float));
+    tf.work2 = malloc((n * fused + 3 * (size_t)dim) * sizeof(float));
+    tf.single_q = malloc(n * dim * sizeof(float));
+    tf.single_k = malloc(n * dim * sizeof(float));
+    tf.single_v = malloc(n * dim * sizeof(float));
+    tf.single_mlp_gate = malloc(n * mlp * sizeof(float));
+    tf.single_mlp_up = malloc(n * mlp * sizeof(float));
+    tf.single_attn_out = malloc(n * dim * sizeof(float));
+    tf.single_concat = malloc(n * (dim + mlp) * sizeof(float));
+    tf.t_emb_silu = malloc((size_t)dim * sizeof(float));
+    int ok = tf.work1 && tf.work2 && tf.single_q && tf.single_k && tf.single_v && tf.single_mlp_gate &&
+             tf.single_mlp_up && tf.single_attn_out && tf.single_concat && tf.t_emb_silu;
+    if (ok) {
+        memset(&block, 0, sizeof(block));
+        block.qkv_mlp_weight = (float *)w_in;
+        block.proj_mlp_weight = (float *)w_out;
+        block.norm_q_weight = (float *)norm_q;
+        block.norm_k_weight = (float *)norm_k;
+        single_block_forward(hidden, &block, t_emb, adaln_weight, img_cos, img_sin, txt_cos, txt_sin,
+                             seq, img_offset, &tf);
+    }
+    free(tf.work1); free(tf.work2); free(tf.single_q); free(tf.single_k); free(tf.single_v);
+    free(tf.single_mlp_gate); free(tf.single_mlp_up); free(tf.single_attn_out); free(tf.single_concat);
+    free(tf.t_emb_silu);
+    flux_ctx_free(&tf);
+    return ok ? 0 : -1;
 }
 
 int ref_flux_attn_threads(int heads) {

@@ -1,0 +1,59 @@
+"""Inputs of one FLUX.2 single-stream block, shared by the CPU and GPU tests.
+
+Seeded synthetic tensors with the model's shapes: hidden state N(0, 1),
+weights N(0, 1 / in) rounded to bf16 (the checkpoints store bf16), per-head
+norm weights near 1, a timestep embedding and an AdaLN weight from which the
+modulation (shift | scale | gate) follows as in the reference
+(iris_transformer_flux.c:3361-3385): mod = adaln . silu(t_emb).
+"""
+import numpy as np
+
+import oracle_lib as ol
+import path_cases as pc
+
+D = 128
+
+# klein4b widths on a short sequence, and a small case the CPU reference runs in seconds
+SMALL = dict(name="flux2-block-small", family="flux2", heads=2, mlp=768, txt=32, img=(8, 8), refs=[], eps=1e-6)
+MID = dict(name="flux2-block-mid", family="flux2", heads=4, mlp=1536, txt=40, img=(12, 11), refs=[], eps=1e-6)
+KLEIN4B_SHORT = dict(name="klein4b-block-short", family="flux2", heads=24, mlp=9216, txt=64, img=(8, 16),
+                     refs=[], eps=1e-6)
+KLEIN4B = dict(name="klein4b-block-1024", family="flux2", heads=24, mlp=9216, txt=512, img=(64, 64), refs=[],
+               eps=1e-6)
+
+
+def block_inputs(case, seed=7):
+    H, mlp = case["heads"], case["mlp"]
+    dim, seq = H * D, pc.seq_len(case)
+    ldh, ldc = 3 * dim + 2 * mlp, dim + mlp
+    x = ol.randn(seed, seq, dim)
+    w_in = ol.to_bf16(ol.randn(seed + 1, ldh, dim) / np.float32(np.sqrt(dim)))
+    w_out = ol.to_bf16(ol.randn(seed + 2, dim, ldc) / np.float32(np.sqrt(ldc)))
+    norm_q = (1.0 + 0.1 * ol.randn(seed + 3, D)).astype(np.float32)
+    norm_k = (1.0 + 0.1 * ol.randn(seed + 4, D)).astype(np.float32)
+    t_emb = ol.randn(seed + 5, dim)
+    adaln = (ol.randn(seed + 6, 3 * dim, dim) * np.float32(0.5 / np.sqrt(dim))).astype(np.float32)
+    silu = (t_emb / (1.0 + np.exp(-t_emb))).astype(np.float32)
+    mod = (adaln.astype(np.float64) @ silu.astype(np.float64)).astype(np.float32)
+    cos, sin, _ = pc.rope_tables(case)
+    return dict(x=x, w_in=w_in, w_out=w_out, norm_q=norm_q, norm_k=norm_k, t_emb=t_emb, adaln=adaln, mod=mod,
+                cos=cos, sin=sin, seq=seq, dim=dim, heads=H, mlp=mlp)
+
+
+def oracle_block(inp, key_mask=None, nthreads=0):
+    """x after the block, by the CPU restatement of the device sequence."""
+    x = inp["x"].copy()
+    rc = ol.oracle().orc_single_block(x, inp["w_in"], inp["w_out"], inp["norm_q"], inp["norm_k"], inp["mod"],
+                                      inp["cos"], inp["sin"], inp["seq"], inp["dim"], inp["heads"], inp["mlp"],
+                                      key_mask, nthreads)
+    assert rc == 0
+    return x
+
+
+def delta_metrics(got, want, x0):
+    """The block adds gate * projection to x: compare what was added.
+    Returns (max |difference| / max |added|, cosine of the added parts)."""
+    a = (got - x0).astype(np.float64).ravel()
+    b = (want - x0).astype(np.float64).ravel()
+    scale = np.abs(b).max()
+    return np.abs(a - b).max() / scale, float(a @ b / np.sqrt((a @ a) * (b @ b)))

@@ -1,0 +1,61 @@
+#!/usr/bin/env python3
+"""Generate tests/golden/reference_block.npz from the reference's own CPU code.
+
+Run where the reference sources are present:
+
+    make -C oracle ref && python tests/golden/make_block_golden.py
+
+Records what the reference's single_block_forward
+(iris_transformer_flux.c:3341-3477, compiled unmodified into
+oracle/_ref/libiris_ref_generic.so) makes of the seeded inputs of
+tests/block_cases.py. Inputs are not stored: block_cases regenerates them.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+import block_cases as bc  # noqa: E402
+import oracle_lib as ol  # noqa: E402
+
+
+ROW_STEP = {bc.SMALL["name"]: 1, bc.MID["name"]: 4}
+
+
+def reference_block(r, case, inp):
+    """x after the block by the reference's CPU code (its own RoPE tables)."""
+    H, txt, (ih, iw) = case["heads"], case["txt"], case["img"]
+    img = ih * iw
+    ct = np.zeros((txt, bc.D), np.float32)
+    st = np.zeros_like(ct)
+    ci = np.zeros((img, bc.D), np.float32)
+    si = np.zeros_like(ci)
+    r.ref_flux_rope_text(ct, st, txt, 32, 2000.0)
+    r.ref_flux_rope_2d(ci, si, ih, iw, 32, 2000.0)
+    x = inp["x"].copy()
+    rc = r.ref_flux_single_block(x, ol.from_bf16(inp["w_in"]), ol.from_bf16(inp["w_out"]), inp["norm_q"],
+                                 inp["norm_k"], inp["t_emb"], inp["adaln"], ci, si, ct, st, inp["seq"], txt, H,
+                                 bc.D, case["mlp"])
+    assert rc == 0
+    return x
+
+
+def main():
+    r = ol.ref("generic")
+    if r is None:
+        sys.exit("oracle/_ref/libiris_ref_generic.so is missing: run `make -C oracle ref` first")
+    out = {}
+    for case in (bc.SMALL, bc.MID):
+        inp = bc.block_inputs(case)
+        # every row of the small case, every fourth of the other: the file stays small
+        out[case["name"]] = reference_block(r, case, inp)[::ROW_STEP[case["name"]]]
+        out[case["name"] + "/x_sum"] = np.float64(inp["x"].astype(np.float64).sum())
+    path = os.path.join(HERE, "reference_block.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -35,6 +35,7 @@ class _OptPtr:
 
 
 i32p_opt = _OptPtr(i32p)
+f32p_opt = _OptPtr(f32p)
 
 
 def _sig(lib, name, argtypes, restype=None):
@@ -71,6 +72,12 @@ def oracle():
     _sig(lib, "orc_f3_joint_rope", [f32p, f32p, INT, INT, INT, i32p, i32p, INT, INT, FLT], INT)
     _sig(lib, "orc_zi_rope", [f32p, f32p, i32p, INT, FLT])
     _sig(lib, "orc_zi_positions", [i32p, i32p, INT, INT, INT], INT)
+    _sig(lib, "orc_layer_norm_mod", [u16p, f32p, f32p_opt, f32p_opt, INT, INT, FLT])
+    _sig(lib, "orc_swiglu", [C.c_void_p, INT, C.c_void_p, C.c_void_p, INT, INT, INT])
+    _sig(lib, "orc_residual", [f32p, f32p, f32p_opt, INT, INT])
+    _sig(lib, "orc_linear", [f32p, INT, u16p, INT, u16p, INT, INT, INT, INT, INT])
+    _sig(lib, "orc_single_block", [f32p, u16p, u16p, f32p, f32p, f32p, f32p, f32p, INT, INT, INT, INT,
+                                   i32p_opt, INT], INT)
     _sig(lib, "orc_compare_heads", [C.c_void_p, INT, C.c_void_p, INT, INT, INT, INT, i32p_opt, INT, f32p, f32p])
     return lib
 
@@ -100,6 +107,7 @@ def ref(kind="generic"):
     _sig(lib, "ref_flux_joint_attention", [f32p] * 8 + [INT] * 4, INT)
     _sig(lib, "ref_flux_mha", [f32p] * 4 + [INT] * 3, INT)
     _sig(lib, "ref_flux_attn_threads", [INT], INT)
+    _sig(lib, "ref_flux_single_block", [f32p] * 11 + [INT] * 5, INT)
     _sig(lib, "ref_f3_head_rms_norm", [f32p, f32p, INT, INT, INT, FLT])
     _sig(lib, "ref_f3_apply_rope", [f32p, f32p, f32p, INT, INT, INT])
     _sig(lib, "ref_f3_joint_rope", [f32p, f32p, INT, INT, INT, i32p, i32p, INT, INT, INT, FLT], INT)
@@ -129,6 +137,11 @@ def ref_cuda():
     _sig(lib, "iris_dev_name", [], C.c_char_p)
     _sig(lib, "iris_dev_head_norm_rope", [VP, INT, VP, VP, VP, INT, INT, INT, FLT, INT])
     _sig(lib, "iris_dev_attention", [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP])
+    _sig(lib, "iris_dev_linear_bf16", [VP, VP, VP, INT, INT, INT])
+    _sig(lib, "iris_dev_linear_f32", [VP, VP, VP, INT, INT, INT])
+    _sig(lib, "iris_dev_layer_norm_mod", [VP, VP, VP, VP, INT, INT, FLT])
+    _sig(lib, "iris_dev_swiglu", [VP, INT, VP, VP, INT, INT, INT])
+    _sig(lib, "iris_dev_residual", [VP, VP, VP, INT, INT])
     return lib
 
 

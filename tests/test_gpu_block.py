@@ -1,0 +1,245 @@
+"""GPU tests of the operators around the attention path and of one FLUX.2
+single-stream block, through the C-ABI, against the CPU restatement (which the
+CPU tests pin to the reference's single_block_forward) and, where it is built,
+against the reference's own CUDA backend issuing its eight-call sequence on the
+same device buffers."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import block_cases as bc
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+
+REL_MAX, MIN_COS = 2e-2, 0.9999
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as ge
+    lib = ge.load_package().load()
+    lib.init()
+    yield lib
+    lib.check()
+
+
+def bf16_ulp(x):
+    return np.maximum(np.abs(x), 2.0 ** -126) * 2.0 ** -7
+
+
+class Dev:
+    """Device copies that are freed together."""
+
+    def __init__(self, lib):
+        self.lib, self.ptrs = lib, []
+
+    def put(self, arr):
+        p = self.lib.to_device(arr)
+        self.ptrs.append(p)
+        return p
+
+    def new(self, nbytes):
+        p = self.lib.alloc(nbytes)
+        self.ptrs.append(p)
+        return p
+
+    def free(self):
+        for p in self.ptrs:
+            self.lib.iris_dev_free(p)
+        self.ptrs = []
+
+
+@pytest.mark.parametrize("rows,dim", [(37, 3072), (300, 512), (5, 4100), (6, 1030), (3, 4096)])
+def test_layer_norm_mod(lib, rows, dim):
+    o = ol.oracle()
+    x = (ol.randn(rows + dim, rows, dim) * 2 + 0.5).astype(np.float32)
+    shift, scale = ol.randn(1, dim), (ol.randn(2, dim) * np.float32(0.3)).astype(np.float32)
+    d = Dev(lib)
+    try:
+        dx, dsh, dsc, dout = d.put(x), d.put(shift), d.put(scale), d.new(rows * dim * 2)
+        for sh, sc, psh, psc in ((shift, scale, dsh, dsc), (None, scale, None, dsc), (shift, None, dsh, None)):
+            lib.iris_dev_layer_norm_mod(dout, dx, psh, psc, rows, dim, 1e-6)
+            got = lib.to_host(dout, (rows, dim), np.uint16)
+            lib.check()
+            want = np.zeros((rows, dim), np.uint16)
+            o.orc_layer_norm_mod(want, x, sh, sc, rows, dim, 1e-6)
+            fw = ol.from_bf16(want)
+            assert (got != want).mean() < 0.02
+            assert (np.abs(ol.from_bf16(got) - fw) <= bf16_ulp(fw) * 1.01).all()
+    finally:
+        d.free()
+
+
+@pytest.mark.parametrize("rows,cols,ldi,ldo,off", [(33, 1024, 2304, 1280, 1152), (9, 40, 100, 56, 50)])
+def test_swiglu(lib, rows, cols, ldi, ldo, off):
+    o = ol.oracle()
+    src = ol.to_bf16(ol.randn(rows, rows, ldi) * 4)
+    src[0, :8] = ol.to_bf16(np.array([-100, -60, -20, 0, 20, 60, 100, 1e-3], np.float32))
+    d = Dev(lib)
+    try:
+        dsrc, dout = d.put(src), d.put(np.zeros((rows, ldo), np.uint16))
+        lib.iris_dev_swiglu(dout, ldo, dsrc, dsrc + 2 * off, ldi, rows, cols)
+        got = lib.to_host(dout, (rows, ldo), np.uint16)
+        lib.check()
+    finally:
+        d.free()
+    want = np.zeros((rows, ldo), np.uint16)
+    o.orc_swiglu(want.ctypes.data, ldo, src.ctypes.data, src.ctypes.data + 2 * off, ldi, rows, cols)
+    fw = ol.from_bf16(want)
+    assert (got != want).mean() < 0.01
+    assert (np.abs(ol.from_bf16(got) - fw) <= bf16_ulp(fw) * 1.01).all()
+    assert not got[:, cols:].any()
+
+
+@pytest.mark.parametrize("rows,dim", [(65, 3072), (7, 50)])
+def test_residual(lib, rows, dim):
+    x, a, gate = ol.randn(1, rows, dim), ol.randn(2, rows, dim), ol.randn(3, dim)
+    d = Dev(lib)
+    try:
+        da, dg = d.put(a), d.put(gate)
+        for g, pg in ((gate, dg), (None, None)):
+            dx = d.put(x)
+            lib.iris_dev_residual(dx, da, pg, rows, dim)
+            got = lib.to_host(dx, (rows, dim), np.float32)
+            lib.check()
+            want = x.astype(np.float64) + (g if g is not None else 1.0) * a.astype(np.float64)
+            np.testing.assert_allclose(got, want, rtol=1e-6, atol=1e-6)
+    finally:
+        d.free()
+
+
+@pytest.mark.parametrize("rows,cin,cout", [(200, 512, 264), (129, 1280, 512), (1, 64, 8)])
+def test_linear_f32_and_linear_residual(lib, rows, cin, cout):
+    o = ol.oracle()
+    a = ol.to_bf16(ol.randn(rows, rows, cin))
+    W = ol.to_bf16(ol.randn(cin, cout, cin) / np.float32(np.sqrt(cin)))
+    x0, gate = ol.randn(5, rows, cout), ol.randn(6, cout)
+    want = np.zeros((rows, cout), np.float32)
+    o.orc_linear(want, cout, a, cin, W, cin, rows, cin, cout, 0)
+    d = Dev(lib)
+    try:
+        da, dW, dg, dy = d.put(a), d.put(W), d.put(gate), d.new(rows * cout * 4)
+        lib.iris_dev_linear_f32(dy, da, dW, rows, cin, cout)
+        got = lib.to_host(dy, (rows, cout), np.float32)
+        lib.check()
+        np.testing.assert_allclose(got, want, rtol=2e-4, atol=2e-4)
+        for g, pg in ((gate, dg), (None, None)):
+            dx = d.put(x0)
+            assert lib.iris_b200_linear_residual(dx, cout, da, cin, dW, cin, pg, rows, cin, cout) == 0
+            got = lib.to_host(dx, (rows, cout), np.float32)
+            lib.check()
+            np.testing.assert_allclose(got, x0 + (g if g is not None else 1.0) * want, rtol=2e-4, atol=4e-4)
+    finally:
+        d.free()
+
+
+def test_linear_residual_argument_checks(lib):
+    d = Dev(lib)
+    try:
+        p = d.new(1 << 16)
+        assert lib.iris_b200_linear_residual(None, 64, p, 64, p, 64, None, 8, 64, 64) == 1
+        assert lib.iris_b200_linear_residual(p, 32, p, 64, p, 64, None, 8, 64, 64) == 1      # ldx < out
+        assert lib.iris_b200_linear_residual(p, 64, p, 60, p, 64, None, 8, 64, 64) == 1      # lda < in
+        assert lib.iris_b200_linear_residual(p, 64, p, 68, p, 64, None, 8, 64, 64) != 0      # lda % 8
+        assert lib.iris_b200_single_block(p, p, p, p, p, p, p, p, p, 8, 200, 2, 64, None) == 1   # dim != heads * 128
+        assert lib.iris_b200_single_block(p, p + 16, p, p, p, p, p, p, p, 8, 256, 2, 64, None) == 1   # scratch alignment
+        assert lib.iris_b200_single_block_scratch_bytes(8, 0, 64) == 0
+        lib.iris_b200_clear_error()
+    finally:
+        d.free()
+
+
+def device_block(lib, inp, key_mask=None, calls=1):
+    d = Dev(lib)
+    try:
+        dx = d.put(inp["x"])
+        nbytes = lib.iris_b200_single_block_scratch_bytes(inp["seq"], inp["dim"], inp["mlp"])
+        assert nbytes > 0
+        scratch = d.new(nbytes)
+        args = [d.put(inp[k]) for k in ("w_in", "w_out", "norm_q", "norm_k", "mod", "cos", "sin")]
+        dm = d.put(np.ascontiguousarray(key_mask, np.int32)) if key_mask is not None else None
+        for _ in range(calls):
+            rc = lib.iris_b200_single_block(dx, scratch, *args, inp["seq"], inp["dim"], inp["heads"], inp["mlp"], dm)
+            assert rc == 0
+        out = lib.to_host(dx, inp["x"].shape, np.float32)
+        lib.check()
+        return out
+    finally:
+        d.free()
+
+
+@pytest.mark.parametrize("case", [bc.SMALL, bc.MID, bc.KLEIN4B_SHORT], ids=lambda c: c["name"])
+def test_single_block_against_the_restatement(lib, case):
+    inp = bc.block_inputs(case)
+    got = device_block(lib, inp)
+    rel, cos = bc.delta_metrics(got, bc.oracle_block(inp), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_single_block_against_the_recorded_reference(lib):
+    """Straight against the committed output of the reference's CPU block."""
+    import os
+    gold = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_block.npz")))
+    inp = bc.block_inputs(bc.SMALL)
+    rel, cos = bc.delta_metrics(device_block(lib, inp), gold[bc.SMALL["name"]], inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_single_block_with_key_mask(lib):
+    inp = bc.block_inputs(bc.MID)
+    mask = np.ones(inp["seq"], np.int32)
+    mask[10:40] = 0
+    got = device_block(lib, inp, mask)
+    rel, cos = bc.delta_metrics(got, bc.oracle_block(inp, mask), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+    assert not np.array_equal(got, device_block(lib, inp))
+
+
+def test_two_blocks_in_a_row_reuse_the_scratch(lib):
+    """The hidden state is updated in place: a second call continues from the first."""
+    inp = bc.block_inputs(bc.SMALL)
+    twice = device_block(lib, inp, calls=2)
+    x1 = bc.oracle_block(inp)
+    x2 = bc.oracle_block(dict(inp, x=x1))
+    rel, cos = bc.delta_metrics(twice, x2, inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_single_block_against_the_reference_cuda_sequence(lib):
+    """The reference's device forward issues eight calls per single block
+    (iris_transformer_flux.c:3828-3845); its own CUDA backend runs them here on
+    the same inputs. Same arithmetic rules, so the results must sit far inside
+    the gate."""
+    ref = ol.ref_cuda()
+    if ref is None:
+        pytest.skip("oracle/_ref/libiris_ref_cuda.so not built")
+    assert ref.iris_dev_init() == 1
+    case = bc.KLEIN4B_SHORT
+    inp = bc.block_inputs(case)
+    seq, dim, H, mlp = inp["seq"], inp["dim"], inp["heads"], inp["mlp"]
+    ldh, ldc = 3 * dim + 2 * mlp, dim + mlp
+    ours = device_block(lib, inp)
+    d = Dev(lib)
+    try:
+        x, mod = d.put(inp["x"]), d.put(inp["mod"])
+        w_in, w_out, nq, nk = d.put(inp["w_in"]), d.put(inp["w_out"]), d.put(inp["norm_q"]), d.put(inp["norm_k"])
+        cos, sin = d.put(inp["cos"]), d.put(inp["sin"])
+        norm, h, cat, out = d.new(seq * dim * 2), d.new(seq * ldh * 2), d.new(seq * ldc * 2), d.new(seq * dim * 4)
+        lib.iris_dev_sync()
+        ref.iris_dev_layer_norm_mod(norm, x, mod, mod + 4 * dim, seq, dim, 1e-6)
+        ref.iris_dev_linear_bf16(h, norm, w_in, seq, dim, ldh)
+        ref.iris_dev_head_norm_rope(h, ldh, nq, cos, sin, seq, H, 128, 1e-6, 0)
+        ref.iris_dev_head_norm_rope(h + 2 * dim, ldh, nk, cos, sin, seq, H, 128, 1e-6, 0)
+        ref.iris_dev_attention(cat, ldc, h, h + 2 * dim, h + 4 * dim, ldh, seq, seq, H, H, 128, 1.0 / np.sqrt(128.0), 0, None)
+        ref.iris_dev_swiglu(cat + 2 * dim, ldc, h + 2 * 3 * dim, h + 2 * (3 * dim + mlp), ldh, seq, mlp)
+        ref.iris_dev_linear_f32(out, cat, w_out, seq, ldc, dim)
+        ref.iris_dev_residual(x, out, mod + 8 * dim, seq, dim)
+        ref.iris_dev_sync()
+        theirs = lib.to_host(x, (seq, dim), np.float32)
+        lib.check()
+    finally:
+        d.free()
+    rel, cos_ = bc.delta_metrics(ours, theirs, inp["x"])
+    assert rel <= 5e-3 and cos_ >= 0.99999, (rel, cos_)
