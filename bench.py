@@ -231,27 +231,40 @@ class Job:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return [float(x) for x in t.tolist()]
 
-    def ring_init(self, parts=0):
+    def ring_init(self, parts=0, groups=1):
+        """One ring per head group: the ranks [g * R, (g + 1) * R) with R =
+        world / groups form ring g; its first rank makes the ring's id."""
         if self.ring_ready:
             return
         torch, lib = self.torch, self.lib
+        assert self.world % groups == 0
+        size = self.world // groups
+        leader = self.rank - self.rank % size
         assert lib.iris_b200_ring_configure(0, parts) == 0
-        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if self.rank == 0:
+        mine = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if self.rank == leader:
             buf = C.create_string_buffer(128)
             assert lib.iris_b200_ring_unique_id(buf) == 0
-            ident = torch.tensor(list(buf.raw), dtype=torch.uint8, device="cuda")
+            mine = torch.tensor(list(buf.raw), dtype=torch.uint8, device="cuda")
+        ids = [mine]
         if self.dist:
-            self.dist.broadcast(ident, src=0)
-        assert lib.iris_b200_ring_init(self.rank, self.world, bytes(ident.cpu().tolist())) == 0
+            ids = [torch.zeros_like(mine) for _ in range(self.world)]
+            self.dist.all_gather(ids, mine)
+        assert lib.iris_b200_ring_init(self.rank - leader, size, bytes(ids[leader].cpu().tolist())) == 0
         self.ring_ready = True
 
+    def ring_destroy(self):
+        if self.ring_ready:
+            self.lib.iris_b200_ring_destroy()
+            self.ring_ready = False
 
-def plan_of(job, w, mode):
+
+def plan_of(job, w, mode, groups=1):
     """What this rank holds and computes. mode: 'single' (everything on this
     rank), 'shard' (batch entries on disjoint GPU groups, heads of an entry
     split over its group: independent shards, nothing exchanged) or 'ring'
-    (this rank's block of token rows, all heads)."""
+    (this rank's block of token rows; with `groups` > 1 the heads are split
+    over that many independent rings of world / groups ranks each)."""
     lib, rank, world = job.lib, job.rank, job.world
     S_full, H = seq_len(w), w["heads"]
     p = dict(mode=mode, S_full=S_full, S=S_full, row0=0, rows_of=None, entries=list(range(w["batch"])), h0=0, nh=H)
@@ -261,14 +274,19 @@ def plan_of(job, w, mode):
         p["entries"] = list(range(a.value, w["batch"], b.value)) if d.value > 0 else []
         p["h0"], p["nh"] = c.value, d.value
     elif mode == "ring":
-        assert w["batch"] == 1
-        rows_of = np.zeros(world, np.int32)
-        for r in range(world):
-            lib.iris_b200_seq_shard(S_full, world, r, C.byref(a), C.byref(b))
+        assert w["batch"] == 1 and world % groups == 0
+        size = world // groups
+        grp, rr = rank // size, rank % size
+        rows_of = np.zeros(size, np.int32)
+        for r in range(size):
+            lib.iris_b200_seq_shard(S_full, size, r, C.byref(a), C.byref(b))
             rows_of[r] = b.value
-            if r == rank:
+            if r == rr:
                 p["row0"] = a.value
-        p["rows_of"], p["S"] = rows_of, int(rows_of[rank])
+        p["rows_of"], p["S"], p["groups"] = rows_of, int(rows_of[rr]), groups
+        if groups > 1:
+            assert lib.iris_b200_head_shard(H, groups, grp, C.byref(c), C.byref(d)) == 0
+            p["h0"], p["nh"] = c.value, d.value
     return p
 
 
@@ -582,7 +600,7 @@ def projection_run(job, w, pk, reps=20):
 def block_run(job, w, pk, reps=10):
     """One whole single-stream block around the path (rank 0, N = 1): LayerNorm
     with modulation, the fused QKV+MLP projection with the prologue, attention,
-    SwiGLU and the output projection with the gated residual - five launches
+    SwiGLU and the output projection with the gated residual - four launches
     through iris_b200_single_block - next to the reference's own CUDA backend
     issuing its eight calls (iris_transformer_flux.c:3828-3845) on the same
     device, where that build is present."""
@@ -621,28 +639,26 @@ def block_run(job, w, pk, reps=10):
     ms = lib.iris_b200_mark_elapsed_ms(0, 1) / reps
     launches = (lib.iris_b200_launch_count() - n0) // reps
     lib.check()
-    # the same five launches one by one, a mark after each
+    # the same four launches one by one, a mark after each
     norm = scratch
     up256 = lambda b: (b + 255) & ~255
-    h = scratch + up256(S * dim * 2)
-    cat = h + up256(S * ldh * 2)
-    stages = ["layer_norm_mod", "qkv_mlp_projection+prologue", "attention", "swiglu", "out_projection+residual"]
-    acc = [0.0] * 5
+    qkv = scratch + up256(S * dim * 2)
+    cat = qkv + up256(S * 3 * dim * 2)
+    stages = ["layer_norm_mod", "qkv_mlp_projection+prologue+swiglu", "attention", "out_projection+residual"]
+    acc = [0.0] * 4
     for r in range(reps):
         lib.iris_b200_mark(0)
         lib.iris_dev_layer_norm_mod(norm, x.data_ptr(), mod.data_ptr(), mod.data_ptr() + 4 * dim, S, dim, 1e-6)
         lib.iris_b200_mark(1)
-        lib.iris_b200_linear_qk_norm_rope(h, ldh, norm, w_in.data_ptr(), S, dim, ldh, H, nq.data_ptr(), nk.data_ptr(),
-                                          d_cos, d_sin, 1e-6)
+        lib.iris_b200_linear_glu(qkv, 3 * dim, cat + 2 * dim, ldc, norm, w_in.data_ptr(), S, dim, H, mlp, nq.data_ptr(),
+                                 nk.data_ptr(), d_cos, d_sin, 1e-6)
         lib.iris_b200_mark(2)
-        lib.iris_dev_attention(cat, ldc, h, h + 2 * dim, h + 4 * dim, ldh, S, S, H, H, D, 1.0 / np.sqrt(D), 0, None)
+        lib.iris_dev_attention(cat, ldc, qkv, qkv + 2 * dim, qkv + 4 * dim, 3 * dim, S, S, H, H, D, 1.0 / np.sqrt(D), 0, None)
         lib.iris_b200_mark(3)
-        lib.iris_dev_swiglu(cat + 2 * dim, ldc, h + 6 * dim, h + 2 * (3 * dim + mlp), ldh, S, mlp)
-        lib.iris_b200_mark(4)
         lib.iris_b200_linear_residual(x.data_ptr(), dim, cat, ldc, w_out.data_ptr(), ldc, mod.data_ptr() + 8 * dim, S,
                                       ldc, dim)
-        lib.iris_b200_mark(5)
-        for i in range(5):
+        lib.iris_b200_mark(4)
+        for i in range(4):
             acc[i] += lib.iris_b200_mark_elapsed_ms(i, i + 1)
     lib.check()
     flops = 2.0 * S * dim * ldh + 4.0 * S * S * dim + 2.0 * S * ldc * dim
@@ -656,6 +672,8 @@ def block_run(job, w, pk, reps=10):
     ref = ol.ref_cuda()
     if ref is not None and ref.iris_dev_init() == 1:
         proj = torch.empty((S, dim), device="cuda", dtype=torch.float32)
+        r_h = torch.empty((S, ldh), device="cuda", dtype=torch.bfloat16)         # the reference's d->h
+        h = r_h.data_ptr()
         xr = x0.clone()
         torch.cuda.synchronize()
 
@@ -679,6 +697,108 @@ def block_run(job, w, pk, reps=10):
         rms = (time.perf_counter() - t0) * 1e3 / reps
         out["reference_cuda_ms"] = round(rms, 4)
         out["reference_cuda"] = "iris_cuda.cu unmodified, -arch=sm_100: cuBLAS GEMMs + its own kernels, 8 calls"
+        out["speedup_vs_reference_cuda"] = round(rms / ms, 3)
+    for p in (d_cos, d_sin, scratch):
+        lib.iris_dev_free(p)
+    return out
+
+
+def double_block_run(job, w, pk, reps=10):
+    """One double-stream block (rank 0, N = 1): twelve launches through
+    iris_b200_double_block next to the reference's CUDA backend issuing its
+    twenty-seven calls (iris_transformer_flux.c:3781-3823) on the same device."""
+    lib, torch = job.lib, job.torch
+    import ctypes as C
+    binding = sys.modules[type(lib).__module__]
+    S, H, T = seq_len(w), w["heads"], w["txt"]
+    dim, mlp = H * D, 3 * H * D
+    gen = torch.Generator(device="cuda").manual_seed(13)
+
+    def rnd(shape, scale=1.0, dtype=torch.float32):
+        return (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+    x0 = rnd((S, dim))
+    x = x0.clone()
+    keep, streams = [], []
+    for _ in range(2):
+        t = dict(qkv=rnd((3 * dim, dim), dim ** -0.5, torch.bfloat16), proj=rnd((dim, dim), dim ** -0.5, torch.bfloat16),
+                 ff_in=rnd((2 * mlp, dim), dim ** -0.5, torch.bfloat16), ff_out=rnd((dim, mlp), mlp ** -0.5, torch.bfloat16),
+                 norm_q=1 + 0.1 * rnd((D,)), norm_k=1 + 0.1 * rnd((D,)), mod=rnd((6 * dim,), 0.3))
+        keep.append(t)
+        streams.append(binding.StreamWeights(*[t[k].data_ptr() for k in
+                                               ("qkv", "proj", "ff_in", "ff_out", "norm_q", "norm_k", "mod")]))
+    cos, sin = rope_tables(w)
+    d_cos, d_sin = lib.to_device(cos), lib.to_device(sin)
+    scratch = lib.alloc(lib.iris_b200_double_block_scratch_bytes(S, dim, mlp))
+    torch.cuda.synchronize()
+
+    def ours():
+        rc = lib.iris_b200_double_block(x.data_ptr(), scratch, C.addressof(streams[0]), C.addressof(streams[1]), d_cos,
+                                        d_sin, S, T, dim, H, mlp, None)
+        assert rc == 0, rc
+
+    for _ in range(3):
+        ours()
+    lib.iris_dev_sync()
+    n0 = lib.iris_b200_launch_count()
+    lib.iris_b200_mark(0)
+    for _ in range(reps):
+        ours()
+    lib.iris_b200_mark(1)
+    ms = lib.iris_b200_mark_elapsed_ms(0, 1) / reps
+    launches = (lib.iris_b200_launch_count() - n0) // reps
+    lib.check()
+    flops = 2.0 * S * dim * 3 * dim + 4.0 * S * S * dim + 2.0 * S * dim * dim + 2.0 * S * dim * 2 * mlp + 2.0 * S * mlp * dim
+    out = {"shape": {"tokens": S, "text": T, "dim": dim, "heads": H, "mlp": mlp}, "launches_per_block": int(launches),
+           "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+           "frac_of_bf16_sustained": round(flops / ms / 1e9 / pk[1], 4)}
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    ref = ol.ref_cuda()
+    if ref is not None and ref.iris_dev_init() == 1:
+        ldh = max(3 * dim, 2 * mlp)
+        r_norm = torch.empty((S, dim), device="cuda", dtype=torch.bfloat16)
+        r_h = torch.empty((S, ldh), device="cuda", dtype=torch.bfloat16)
+        r_cat = torch.empty((S, max(dim, mlp)), device="cuda", dtype=torch.bfloat16)
+        norm, h, cat = r_norm.data_ptr(), r_h.data_ptr(), r_cat.data_ptr()
+        proj = torch.empty((S, dim), device="cuda", dtype=torch.float32)
+        xr = x0.clone()
+        torch.cuda.synchronize()
+
+        def theirs():
+            for m in range(2):
+                t, n, first = keep[m], (S - T) if m else T, T if m else 0
+                mod, xo, qkv = t["mod"].data_ptr(), xr.data_ptr() + first * dim * 4, h + 3 * first * dim * 2
+                ref.iris_dev_layer_norm_mod(norm, xo, mod, mod + 4 * dim, n, dim, 1e-6)
+                ref.iris_dev_linear_bf16(qkv, norm, t["qkv"].data_ptr(), n, dim, 3 * dim)
+                ref.iris_dev_head_norm_rope(qkv, 3 * dim, t["norm_q"].data_ptr(), d_cos + first * 64 * 4,
+                                            d_sin + first * 64 * 4, n, H, D, 1e-6, 0)
+                ref.iris_dev_head_norm_rope(qkv + 2 * dim, 3 * dim, t["norm_k"].data_ptr(), d_cos + first * 64 * 4,
+                                            d_sin + first * 64 * 4, n, H, D, 1e-6, 0)
+            ref.iris_dev_attention(cat, dim, h, h + 2 * dim, h + 4 * dim, 3 * dim, S, S, H, H, D, 1.0 / np.sqrt(D), 0, None)
+            for m in range(2):
+                t, n, first = keep[m], (S - T) if m else T, T if m else 0
+                mod, xo = t["mod"].data_ptr(), xr.data_ptr() + first * dim * 4
+                ref.iris_dev_linear_f32(proj.data_ptr(), cat + first * dim * 2, t["proj"].data_ptr(), n, dim, dim)
+                ref.iris_dev_residual(xo, proj.data_ptr(), mod + 8 * dim, n, dim)
+            for m in range(2):
+                t, n, first = keep[m], (S - T) if m else T, T if m else 0
+                mod, xo = t["mod"].data_ptr(), xr.data_ptr() + first * dim * 4
+                ref.iris_dev_layer_norm_mod(norm, xo, mod + 12 * dim, mod + 16 * dim, n, dim, 1e-6)
+                ref.iris_dev_linear_bf16(h, norm, t["ff_in"].data_ptr(), n, dim, 2 * mlp)
+                ref.iris_dev_swiglu(cat, mlp, h, h + 2 * mlp, 2 * mlp, n, mlp)
+                ref.iris_dev_linear_f32(proj.data_ptr(), cat, t["ff_out"].data_ptr(), n, mlp, dim)
+                ref.iris_dev_residual(xo, proj.data_ptr(), mod + 20 * dim, n, dim)
+
+        for _ in range(2):
+            theirs()
+        ref.iris_dev_sync()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            theirs()
+        ref.iris_dev_sync()
+        rms = (time.perf_counter() - t0) * 1e3 / reps
+        out["reference_cuda_ms"] = round(rms, 4)
         out["speedup_vs_reference_cuda"] = round(rms / ms, 3)
     for p in (d_cos, d_sin, scratch):
         lib.iris_dev_free(p)
@@ -755,11 +875,11 @@ def outproj_run(job, pk, reps=20):
             "nvlink_bytes_per_rank": sent, "nvlink_gbs_per_rank": round(sent / ms / 1e6, 1)}
 
 
-def extra_run(job, name, mode, steps, warmup, pk):
+def extra_run(job, name, mode, steps, warmup, pk, groups=1):
     """A further workload / decomposition measured in the same run: ms per
     step (max over ranks), aggregate TFLOP/s and per-GPU share of the peak."""
     w = WORKLOADS[name]
-    plan = plan_of(job, w, mode)
+    plan = plan_of(job, w, mode, groups)
     B = Buffers(job, w, plan)
     res = timed_steps(job, w, plan, B, steps, warmup, marks=(job.rank == 0))
     B.free()
@@ -781,9 +901,11 @@ def run_b200(args):
     name = args.workload or ("klein4b-1024" if world == 1 else "flux3-multiref" if mode == "ring" else "klein9b-cfg")
     w = WORKLOADS[name]
     pk = peaks()
+    groups = 1
     if mode == "ring":
-        job.ring_init(args.ring_parts)
-    plan = plan_of(job, w, mode)
+        groups = args.head_groups if args.head_groups else (2 if world >= 4 and world % 2 == 0 else 1)
+        job.ring_init(args.ring_parts, groups)
+    plan = plan_of(job, w, mode, groups)
     B = Buffers(job, w, plan)
     S_full, H = plan["S_full"], w["heads"]
 
@@ -828,6 +950,11 @@ def run_b200(args):
             job.barrier()
             one_gpu = job.max_over_ranks([one_gpu or 0.0])[0]
             speedup = one_gpu / ms_step
+            if groups > 1:
+                # the same workload as ONE ring over all ranks, every rank holding all heads
+                job.ring_destroy()
+                job.ring_init(args.ring_parts, 1)
+                extras[name + " one ring, all heads per rank"] = extra_run(job, name, "ring", args.steps, args.warmup, pk)
             extras[name + " head-parallel"] = extra_run(job, name, "shard", args.steps, args.warmup, pk)
         for other in ("klein9b-cfg", "zimage-turbo"):
             if other != name:
@@ -848,8 +975,7 @@ def run_b200(args):
         except Exception as e:
             ref_gpu = {"error": repr(e)[:200]}
         B2.free()
-    if mode == "ring":
-        lib.iris_b200_ring_destroy()
+    job.ring_destroy()
     projection = None
     if rank == 0 and world == 1 and mode == "single" and w["family"] != "zimage" and not args.no_extras:
         try:
@@ -857,17 +983,23 @@ def run_b200(args):
         except Exception as e:                     # a side measurement must not cost the headline line
             projection = {"error": repr(e)[:200]}
 
-    block = None
+    block = dblock = None
     if rank == 0 and world == 1 and mode == "single" and w["family"] == "flux2" and not args.no_extras:
         try:
             block = block_run(job, w, pk)
         except Exception as e:
             block = {"error": repr(e)[:200]}
+        try:
+            dblock = double_block_run(job, w, pk)
+        except Exception as e:
+            dblock = {"error": repr(e)[:200]}
 
     if rank == 0:
         sharding = {"single": "none",
-                    "ring": "ring sequence parallel: K/V rows pushed peer to peer by the copy engines, one attention "
-                            "launch per GPU waits for them in the kernel; NCCL for set-up",
+                    "ring": ("ring sequence parallel" if groups == 1 else
+                             "%d head groups x ring sequence parallel over %d GPUs each" % (groups, world // groups)) +
+                            ": K/V rows pushed peer to peer by the copy engines, one attention launch per GPU waits "
+                            "for them in the kernel; NCCL for set-up",
                     "shard": "cfg batch x heads, no collective"}[mode]
         out = {
             "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -884,6 +1016,7 @@ def run_b200(args):
             "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
             "roofline": roof, "roofline_prologue": prologue, "cpu_baseline": cpu, "parity": parity,
             "reference_gpu": ref_gpu, "qkv_projection": projection, "single_block": block,
+            "double_block": dblock,
         }
         if speedup is not None:
             out["one_gpu_ms_per_step"] = round(one_gpu, 4)
@@ -909,7 +1042,7 @@ def cpu_leg_with_parity(job, w, plan, got, host_inputs, width, budget_s):
     # ranks' rows are regenerated from their seeds (seed = 1000 * rank).
     if rank == 0:
         if mode == "ring" and world > 1:
-            blocks = [host_inputs] + [make_qkv(int(plan["rows_of"][r]), width, 1000 * r) for r in range(1, world)]
+            blocks = [host_inputs] + [make_qkv(int(n), width, 1000 * r) for r, n in enumerate(plan["rows_of"]) if r > 0]
             full = torch.cat([b.cpu() for b in blocks], 0)
         else:
             full = host_inputs
@@ -918,7 +1051,7 @@ def cpu_leg_with_parity(job, w, plan, got, host_inputs, width, budget_s):
             n = hs * D
             return tuple(np.ascontiguousarray(bf16_to_f32(full[:, i * width:i * width + n])) for i in range(3))
 
-        r = cpu_reference(w, budget_s=budget_s, steps=1, warmup=0, inputs=inputs)
+        r = cpu_reference(w, budget_s=budget_s, steps=1, warmup=0, inputs=inputs, max_heads=width // D)
         cpu, hs, want = r["cpu_baseline"], r["heads_sampled"], r["out"]
     else:
         hs, want = 0, None
@@ -934,7 +1067,8 @@ def cpu_leg_with_parity(job, w, plan, got, host_inputs, width, budget_s):
         gathered = [torch.empty_like(pad) for _ in range(world)] if rank == 0 else None
         job.dist.gather(pad, gathered, dst=0)
         if rank == 0:
-            got_all = torch.cat([g[:int(plan["rows_of"][r])].cpu() for r, g in enumerate(gathered)], 0)
+            # rank 0's ring is the ranks [0, ring size): their rows, in order, are the whole sequence
+            got_all = torch.cat([gathered[r][:int(n)].cpu() for r, n in enumerate(plan["rows_of"])], 0)
     else:
         got_all = got[:, :hs * D]
     if rank == 0:
@@ -988,7 +1122,7 @@ def reference_gpu_kernels(lib, w, bufs, consts, S, nh, scale, reps=20):
     return out
 
 
-def cpu_reference(w, budget_s, steps, warmup, inputs=None):
+def cpu_reference(w, budget_s, steps, warmup, inputs=None, max_heads=None):
     """Times the reference's CPU code for one step of workload `w` on the host
     cores: Q/K norm + RoPE, then attention. Uses oracle/_ref (the reference
     sources compiled unmodified: BLAS build if it loads, else generic), else
@@ -1055,6 +1189,7 @@ def cpu_reference(w, budget_s, steps, warmup, inputs=None):
     # generic build walk heads serially. One calibration pass sizes the
     # sample to the time budget, then the timed passes run.
     threads, unit = 1, 1
+    H = min(H, max_heads) if max_heads else H          # the inputs at hand may hold fewer heads than the model
     if kind == "reference" and "blas" in variant:
         if w["family"] == "flux3":
             ref.openblas_set_num_threads(ncpu)
@@ -1120,6 +1255,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffer) measurement")
     ap.add_argument("--mode", default=None, choices=["single", "shard", "ring"],
                     help="N > 1: ring sequence parallelism (default) or independent cfg/head shards")
+    ap.add_argument("--head-groups", type=int, default=0,
+                    help="ring mode: split the heads over this many independent rings (0: 2 from four GPUs up, else 1)")
     ap.add_argument("--ring-parts", type=int, default=0, help="key parts of a ring call's launch (0: the library's choice)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the further measurements of the same run (N > 1: other workloads; N = 1: the QKV projection)")

@@ -145,6 +145,24 @@ int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const
                                   const float *wq, const float *wk,
                                   const float *rope_cos, const float *rope_sin, float eps);
 
+/* A block's input projection with the prologue AND SwiGLU as its epilogue: W
+ * [3 * heads * 128 + 2 * mlp, in] holds the Q, K, V rows, then mlp gate rows,
+ * then mlp up rows (the single blocks' fused weight,
+ * iris_transformer_flux.c:3832-3842; with heads == 0 the gate | up weight of a
+ * double block's feed-forward, :3818-3820). qkv [rows, 3 * heads * 128] (row
+ * stride ldq) receives Q and K normalised and rotated and V, as
+ * iris_b200_linear_qk_norm_rope stores them; act [rows, mlp] (row stride lda)
+ * receives silu(gate) * up, gate and up rounded to bf16 first as the
+ * reference's GEMM stores them before its k_swiglu (iris_cuda.cu:300-307).
+ * One GEMM column tile pairs 128 gate columns with their 128 up columns (two
+ * TMA boxes), so the [rows, 2 mlp] intermediate never exists. qkv may be NULL
+ * when heads == 0. mlp a multiple of 8; operands 16-byte aligned. */
+int iris_b200_linear_glu(uint16_t *qkv, int ldq, uint16_t *act, int lda,
+                         const uint16_t *x, const uint16_t *W,
+                         int rows, int in, int heads, int mlp,
+                         const float *wq, const float *wk,
+                         const float *rope_cos, const float *rope_sin, float eps);
+
 /* The output projection with the gated residual as its epilogue: the
  * reference's iris_dev_linear_f32 followed by iris_dev_residual
  * (iris_transformer_flux.c:3843-3844 single blocks, :3809-3811 and :3821-3822
@@ -167,7 +185,8 @@ size_t iris_b200_single_block_scratch_bytes(int seq, int dim, int mlp);
  * forward (iris_transformer_flux.c:3828-3845; CPU form single_block_forward,
  * :3341-3477) - LayerNorm with (shift, scale), the fused QKV+MLP projection
  * with the Q/K prologue, joint attention over all rows, SwiGLU, the output
- * projection over [attention | mlp] and the gated residual - in five launches.
+ * projection over [attention | mlp] and the gated residual - in four launches
+ * (SwiGLU is part of the projection's epilogue).
  * w_in [3 dim + 2 mlp, dim], w_out [dim, dim + mlp]: bf16, as the checkpoints
  * store them. norm_q / norm_k [128]. mod = shift | scale | gate, [3 dim]
  * (the reference's mod_single). rope_cos / rope_sin [seq, 64]. key_mask: NULL
@@ -177,6 +196,41 @@ int iris_b200_single_block(float *x, void *scratch,
                            const float *norm_q, const float *norm_k, const float *mod,
                            const float *rope_cos, const float *rope_sin,
                            int seq, int dim, int heads, int mlp, const int *key_mask);
+
+/* ---- one double-stream block --------------------------------------------- */
+
+/* The weights of one stream (text or image) of a double block, bf16 as the
+ * checkpoints store them; the reference's device copy is dev_stream_flux_t
+ * (iris_transformer_flux.c:3491-3494). */
+typedef struct iris_b200_stream_weights {
+    const uint16_t *qkv;      /* [3 dim, dim]: the Q, K and V rows */
+    const uint16_t *proj;     /* [dim, dim] */
+    const uint16_t *ff_in;    /* [2 mlp, dim]: the gate rows, then the up rows */
+    const uint16_t *ff_out;   /* [dim, mlp] */
+    const float *norm_q;      /* [128] */
+    const float *norm_k;      /* [128] */
+    const float *mod;         /* [6 dim]: shift1 scale1 gate1 shift2 scale2 gate2 */
+} iris_b200_stream_weights;
+
+size_t iris_b200_double_block_scratch_bytes(int seq, int dim, int mlp);
+
+/* One FLUX.2 double-stream block on the device-resident fp32 hidden state x
+ * [seq, dim] = [TEXT rows | IMAGE rows], in place: what the reference issues
+ * per block in its device forward (iris_transformer_flux.c:3781-3823; CPU form
+ * double_block_forward, :2133-2327). Per stream: LayerNorm with (shift1,
+ * scale1), QKV projection with the Q/K prologue into the joint attention
+ * input; joint attention over all rows; per stream: output projection with
+ * the gate1 residual, LayerNorm with (shift2, scale2), the gate|up projection,
+ * with SwiGLU in its epilogue, the down projection with the gate2 residual.
+ * Twelve launches.
+ * txt_seq: the number of text rows. rope tables [seq, 64] in row order.
+ * key_mask: NULL or [seq]. head_dim is 128. */
+int iris_b200_double_block(float *x, void *scratch,
+                           const iris_b200_stream_weights *txt,
+                           const iris_b200_stream_weights *img,
+                           const float *rope_cos, const float *rope_sin,
+                           int seq, int txt_seq, int dim, int heads, int mlp,
+                           const int *key_mask);
 
 /* ---- attention ---------------------------------------------------------- */
 

@@ -56,9 +56,12 @@ SIGNATURES = {
     "iris_b200_mark_elapsed_ms": (FLT, [INT, INT]),
     "iris_b200_qk_norm_rope": (INT, [VP, VP, INT, VP, VP, VP, VP, INT, INT, INT, FLT, INT]),
     "iris_b200_linear_qk_norm_rope": (INT, [VP, INT, VP, VP, INT, INT, INT, INT, VP, VP, VP, VP, FLT]),
+    "iris_b200_linear_glu": (INT, [VP, INT, VP, INT, VP, VP, INT, INT, INT, INT, VP, VP, VP, VP, FLT]),
     "iris_b200_linear_residual": (INT, [VP, INT, VP, INT, VP, INT, VP, INT, INT, INT]),
     "iris_b200_single_block_scratch_bytes": (SZ, [INT, INT, INT]),
     "iris_b200_single_block": (INT, [VP, VP, VP, VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, VP]),
+    "iris_b200_double_block_scratch_bytes": (SZ, [INT, INT, INT]),
+    "iris_b200_double_block": (INT, [VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, INT, VP]),
     "iris_b200_attention_ex": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP, INT]),
     "iris_b200_attention_kernel_for": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT]),
     "iris_b200_head_shard": (INT, [INT, INT, INT, C.POINTER(INT), C.POINTER(INT)]),
@@ -105,6 +108,11 @@ KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_GENERIC = 0, 1, 2
 class LoopFault(C.Structure):
     """iris_b200_loop_fault of include/iris_b200.h."""
     _fields_ = [("kind", INT), ("rank", INT), ("call", INT), ("step", INT), ("delay_us", C.c_uint)]
+
+
+class StreamWeights(C.Structure):
+    """iris_b200_stream_weights of include/iris_b200.h."""
+    _fields_ = [(n, VP) for n in ("qkv", "proj", "ff_in", "ff_out", "norm_q", "norm_k", "mod")]
 
 
 class KeyRun(C.Structure):

@@ -8,12 +8,15 @@
  *   iris_dev_swiglu           silu(gate) * up on bf16 column slices
  *                             (iris_cuda.cu:300-307)
  *   iris_dev_residual         x += gate * a in fp32 (iris_cuda.cu:309-314)
+ *   iris_b200_double_block    the sequence the reference issues per double
+ *                             block (iris_transformer_flux.c:3781-3823) in
+ *                             twelve launches instead of twenty-seven.
  *   iris_b200_single_block    the sequence the reference issues per single
- *                             block (iris_transformer_flux.c:3828-3845) in five
+ *                             block (iris_transformer_flux.c:3828-3845) in four
  *                             launches instead of eight: the projection
- *                             applies the Q/K prologue in its epilogue, and
- *                             the output projection adds the gated result to
- *                             the hidden state in its epilogue.
+ *                             applies the Q/K prologue and SwiGLU in its
+ *                             epilogue, and the output projection adds the
+ *                             gated result to the hidden state in its epilogue.
  *
  * All three kernels are HBM-bound: every element is read once and written
  * once, 16 bytes per access.
@@ -28,7 +31,6 @@ namespace iris_b200 {
 namespace {
 
 constexpr int kRowThreads = 256;
-constexpr int kRowVecs = 4;          /* float4 per thread kept in registers: dims up to 4096 */
 
 __device__ __forceinline__ float block_sum(float v, float *sh) {
 #pragma unroll
@@ -43,70 +45,85 @@ __device__ __forceinline__ float block_sum(float v, float *sh) {
     return t;
 }
 
-/* One block per row at a time. The row stays in registers between the three
- * passes (mean, variance about the mean, output) when it fits; longer rows
- * are re-read, from L1/L2. Two-pass variance as in the reference. */
+/* One warp per row, the row in registers between the three passes (mean,
+ * variance about the mean, output): no block barrier, one read of x. VPL
+ * float4 per lane, so dims up to 128 * VPL. Two-pass variance as in the
+ * reference. */
+template <int VPL>
 __global__ void __launch_bounds__(kRowThreads)
-k_layer_norm_mod(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift,
-                 const float *__restrict__ scale, int rows, int dim, float eps) {
-    __shared__ float sh[kRowThreads / 32];
+k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift,
+                      const float *__restrict__ scale, int rows, int dim, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * kRowThreads) >> 5;
     const int nvec = dim >> 2;
-    const bool in_regs = nvec <= kRowThreads * kRowVecs && (dim & 3) == 0;
+    const float inv_dim = 1.0f / (float)dim;
+    for (int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5; row < rows; row += warps) {
+        const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * dim);
+        uint2 *o = reinterpret_cast<uint2 *>(out + (size_t)row * dim);
+        float4 v[VPL];
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const int i = lane + 32 * k;
+            v[k] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
+        const float mean = s * inv_dim;
+        float q = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            if (lane + 32 * k < nvec) {
+                const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
+                q += (a * a + b * b) + (c * c + d * d);
+            }
+        }
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o2);
+        const float inv = rsqrtf(q * inv_dim + eps);
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const int i = lane + 32 * k;
+            if (i >= nvec) continue;
+            float n[4] = {(v[k].x - mean) * inv, (v[k].y - mean) * inv, (v[k].z - mean) * inv, (v[k].w - mean) * inv};
+            if (scale) {
+                const float4 sc = reinterpret_cast<const float4 *>(scale)[i];
+                n[0] *= 1.0f + sc.x; n[1] *= 1.0f + sc.y; n[2] *= 1.0f + sc.z; n[3] *= 1.0f + sc.w;
+            }
+            if (shift) {
+                const float4 sf = reinterpret_cast<const float4 *>(shift)[i];
+                n[0] += sf.x; n[1] += sf.y; n[2] += sf.z; n[3] += sf.w;
+            }
+            o[i] = make_uint2(cvt_bf16x2(n[0], n[1]), cvt_bf16x2(n[2], n[3]));
+        }
+    }
+}
+
+/* Any other row length: one block per row at a time, the row re-read from
+ * L1 / L2 for each pass. */
+__global__ void __launch_bounds__(kRowThreads)
+k_layer_norm_mod_any(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift,
+                     const float *__restrict__ scale, int rows, int dim, float eps) {
+    __shared__ float sh[kRowThreads / 32];
     const float inv_dim = 1.0f / (float)dim;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float *xr = x + (size_t)row * dim;
         uint16_t *o = out + (size_t)row * dim;
-        if (in_regs) {
-            float4 v[kRowVecs];
-            float s = 0.0f;
-#pragma unroll
-            for (int k = 0; k < kRowVecs; k++) {
-                const int i = threadIdx.x + k * kRowThreads;
-                v[k] = i < nvec ? reinterpret_cast<const float4 *>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-                s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
-            }
-            const float mean = block_sum(s, sh) * inv_dim;
-            float q = 0.0f;
-#pragma unroll
-            for (int k = 0; k < kRowVecs; k++) {
-                const int i = threadIdx.x + k * kRowThreads;
-                if (i < nvec) {
-                    const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
-                    q += (a * a + b * b) + (c * c + d * d);
-                }
-            }
-            const float inv = rsqrtf(block_sum(q, sh) * inv_dim + eps);
-#pragma unroll
-            for (int k = 0; k < kRowVecs; k++) {
-                const int i = threadIdx.x + k * kRowThreads;
-                if (i >= nvec) continue;
-                float n[4] = {(v[k].x - mean) * inv, (v[k].y - mean) * inv, (v[k].z - mean) * inv, (v[k].w - mean) * inv};
-                if (scale) {
-                    const float4 sc = reinterpret_cast<const float4 *>(scale)[i];
-                    n[0] *= 1.0f + sc.x; n[1] *= 1.0f + sc.y; n[2] *= 1.0f + sc.z; n[3] *= 1.0f + sc.w;
-                }
-                if (shift) {
-                    const float4 sf = reinterpret_cast<const float4 *>(shift)[i];
-                    n[0] += sf.x; n[1] += sf.y; n[2] += sf.z; n[3] += sf.w;
-                }
-                reinterpret_cast<uint2 *>(o)[i] = make_uint2(cvt_bf16x2(n[0], n[1]), cvt_bf16x2(n[2], n[3]));
-            }
-        } else {
-            float s = 0.0f;
-            for (int i = threadIdx.x; i < dim; i += kRowThreads) s += xr[i];
-            const float mean = block_sum(s, sh) * inv_dim;
-            float q = 0.0f;
-            for (int i = threadIdx.x; i < dim; i += kRowThreads) {
-                const float d = xr[i] - mean;
-                q += d * d;
-            }
-            const float inv = rsqrtf(block_sum(q, sh) * inv_dim + eps);
-            for (int i = threadIdx.x; i < dim; i += kRowThreads) {
-                float n = (xr[i] - mean) * inv;
-                if (scale) n *= 1.0f + scale[i];
-                if (shift) n += shift[i];
-                o[i] = f2bf(n);
-            }
+        float s = 0.0f;
+        for (int i = threadIdx.x; i < dim; i += kRowThreads) s += xr[i];
+        const float mean = block_sum(s, sh) * inv_dim;
+        float q = 0.0f;
+        for (int i = threadIdx.x; i < dim; i += kRowThreads) {
+            const float d = xr[i] - mean;
+            q += d * d;
+        }
+        const float inv = rsqrtf(block_sum(q, sh) * inv_dim + eps);
+        for (int i = threadIdx.x; i < dim; i += kRowThreads) {
+            float n = (xr[i] - mean) * inv;
+            if (scale) n *= 1.0f + scale[i];
+            if (shift) n += shift[i];
+            o[i] = f2bf(n);
         }
     }
 }
@@ -172,13 +189,22 @@ int layer_norm_mod(uint16_t *out, const float *x, const float *shift, const floa
         return IRIS_B200_EINVAL;
     }
     if (rows == 0) return IRIS_B200_OK;
-    /* The vector path needs 16-byte rows; anything else takes the scalar path
-     * inside the same kernel, which is chosen by dim % 4 there. */
-    if (dim % 4 == 0 && !(aligned16(x) && aligned16(shift) && aligned16(scale) && ((uintptr_t)out & 7) == 0)) {
-        set_error(IRIS_B200_EUNSUPPORTED, "layer_norm_mod", "operands must be 16-byte aligned when dim is a multiple of 4");
-        return IRIS_B200_EUNSUPPORTED;
+    const int nvec = dim / 4;
+    const bool vec = dim % 4 == 0 && nvec <= 32 * 32 && aligned16(x) && aligned16(shift) && aligned16(scale) &&
+                     ((uintptr_t)out & 7) == 0;
+    if (vec) {
+        const unsigned grid = blocks_for((size_t)rows, kRowThreads / 32, 8);
+        if (nvec <= 32 * 8)
+            k_layer_norm_mod_warp<8><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+        else if (nvec <= 32 * 16)
+            k_layer_norm_mod_warp<16><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+        else if (nvec <= 32 * 24)
+            k_layer_norm_mod_warp<24><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+        else
+            k_layer_norm_mod_warp<32><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+    } else {
+        k_layer_norm_mod_any<<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
     }
-    k_layer_norm_mod<<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
     return after_launch("k_layer_norm_mod") ? IRIS_B200_OK : IRIS_B200_ECUDA;
 }
 
@@ -234,10 +260,9 @@ extern "C" void iris_dev_residual(float *x, const float *a, const float *gate, i
 
 extern "C" size_t iris_b200_single_block_scratch_bytes(int seq, int dim, int mlp) {
     if (seq < 0 || dim <= 0 || mlp <= 0) return 0;
-    const size_t ldh = 3 * (size_t)dim + 2 * (size_t)mlp, ldc = (size_t)dim + mlp;
-    /* norm [seq, dim] | h [seq, ldh] | cat [seq, ldc], bf16, each 256-byte aligned */
+    /* norm [seq, dim] | qkv [seq, 3 dim] | cat [seq, dim + mlp], bf16, each 256-byte aligned */
     auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
-    return up256((size_t)seq * dim * 2) + up256((size_t)seq * ldh * 2) + up256((size_t)seq * ldc * 2);
+    return up256((size_t)seq * dim * 2) + up256((size_t)seq * 3 * dim * 2) + up256((size_t)seq * ((size_t)dim + mlp) * 2);
 }
 
 extern "C" int iris_b200_single_block(float *x, void *scratch, const uint16_t *w_in, const uint16_t *w_out,
@@ -251,22 +276,96 @@ extern "C" int iris_b200_single_block(float *x, void *scratch, const uint16_t *w
         return IRIS_B200_EINVAL;
     }
     if (seq == 0) return IRIS_B200_OK;
-    const int ldh = 3 * dim + 2 * mlp, ldc = dim + mlp;
+    const int ldc = dim + mlp;
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    uint16_t *norm = reinterpret_cast<uint16_t *>(base);
+    uint16_t *qkv = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2));
+    uint16_t *cat = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2) + up256((size_t)seq * 3 * dim * 2));
+    const float eps = 1e-6f;
+    int rc = layer_norm_mod(norm, x, mod, mod + dim, seq, dim, eps);
+    if (rc != IRIS_B200_OK) return rc;
+    /* Q, K (normalised, rotated) and V to qkv; silu(gate) * up straight into the MLP half of cat */
+    rc = iris_b200_linear_glu(qkv, 3 * dim, cat + dim, ldc, norm, w_in, seq, dim, heads, mlp, norm_q, norm_k, rope_cos,
+                              rope_sin, eps);
+    if (rc != IRIS_B200_OK) return rc;
+    iris_b200_clear_error();
+    iris_dev_attention(cat, ldc, qkv, qkv + dim, qkv + 2 * dim, 3 * dim, seq, seq, heads, heads, 128, 0.08838834764831845f, 0,
+                       key_mask);
+    rc = iris_b200_last_error();
+    if (rc != IRIS_B200_OK) return rc;
+    return iris_b200_linear_residual(x, dim, cat, ldc, w_out, ldc, mod + 2 * dim, seq, ldc, dim);
+}
+
+/* norm [seq, dim] | qkv [seq, 3 dim] | cat [seq, max(dim, mlp)], bf16 */
+extern "C" size_t iris_b200_double_block_scratch_bytes(int seq, int dim, int mlp) {
+    if (seq < 0 || dim <= 0 || mlp <= 0) return 0;
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t ldc = dim > mlp ? dim : mlp;
+    return up256((size_t)seq * dim * 2) + up256((size_t)seq * 3 * dim * 2) + up256((size_t)seq * ldc * 2);
+}
+
+extern "C" int iris_b200_double_block(float *x, void *scratch, const iris_b200_stream_weights *txt,
+                                      const iris_b200_stream_weights *img, const float *rope_cos,
+                                      const float *rope_sin, int seq, int txt_seq, int dim, int heads, int mlp,
+                                      const int *key_mask) {
+    if (!require_device("double_block")) return IRIS_B200_ENODEV;
+    bool ok = x && scratch && txt && img && rope_cos && rope_sin && seq >= 0 && txt_seq >= 0 && txt_seq <= seq && dim > 0 &&
+              heads > 0 && mlp > 0 && dim == heads * 128 && ((uintptr_t)scratch & 255) == 0;
+    const iris_b200_stream_weights *sw[2] = {txt, img};
+    for (int m = 0; m < 2 && ok; m++)
+        ok = sw[m]->qkv && sw[m]->proj && sw[m]->ff_in && sw[m]->ff_out && sw[m]->norm_q && sw[m]->norm_k && sw[m]->mod;
+    if (!ok) {
+        set_error(IRIS_B200_EINVAL, "double_block", dim > 0 && dim != heads * 128 ? "head_dim must be 128" : "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    if (seq == 0) return IRIS_B200_OK;
     auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
     unsigned char *base = static_cast<unsigned char *>(scratch);
     uint16_t *norm = reinterpret_cast<uint16_t *>(base);
     uint16_t *h = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2));
-    uint16_t *cat = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2) + up256((size_t)seq * ldh * 2));
+    uint16_t *cat = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2) + up256((size_t)seq * 3 * dim * 2));
     const float eps = 1e-6f;
-    int rc = layer_norm_mod(norm, x, mod, mod + dim, seq, dim, eps);
-    if (rc != IRIS_B200_OK) return rc;
-    rc = iris_b200_linear_qk_norm_rope(h, ldh, norm, w_in, seq, dim, ldh, heads, norm_q, norm_k, rope_cos, rope_sin, eps);
-    if (rc != IRIS_B200_OK) return rc;
+    const int first[2] = {0, txt_seq}, rows[2] = {txt_seq, seq - txt_seq};
+    int rc;
+    /* attention half: both streams write their rows of the joint [seq, 3 dim] input */
+    for (int m = 0; m < 2; m++) {
+        const size_t r0 = (size_t)first[m];
+        if ((rc = layer_norm_mod(norm + r0 * dim, x + r0 * dim, sw[m]->mod, sw[m]->mod + dim, rows[m], dim, eps))) return rc;
+    }
+    for (int m = 0; m < 2; m++) {
+        const size_t r0 = (size_t)first[m];
+        rc = iris_b200_linear_qk_norm_rope(h + r0 * 3 * dim, 3 * dim, norm + r0 * dim, sw[m]->qkv, rows[m], dim, 3 * dim,
+                                           heads, sw[m]->norm_q, sw[m]->norm_k, rope_cos + r0 * 64, rope_sin + r0 * 64, eps);
+        if (rc != IRIS_B200_OK) return rc;
+    }
     iris_b200_clear_error();
-    iris_dev_attention(cat, ldc, h, h + dim, h + 2 * dim, ldh, seq, seq, heads, heads, 128, 0.08838834764831845f, 0, key_mask);
-    rc = iris_b200_last_error();
-    if (rc != IRIS_B200_OK) return rc;
-    rc = swiglu(cat + dim, ldc, h + 3 * dim, h + 3 * dim + mlp, ldh, seq, mlp);
-    if (rc != IRIS_B200_OK) return rc;
-    return iris_b200_linear_residual(x, dim, cat, ldc, w_out, ldc, mod + 2 * dim, seq, ldc, dim);
+    iris_dev_attention(cat, dim, h, h + dim, h + 2 * dim, 3 * dim, seq, seq, heads, heads, 128, 0.08838834764831845f, 0,
+                       key_mask);
+    if ((rc = iris_b200_last_error()) != IRIS_B200_OK) return rc;
+    for (int m = 0; m < 2; m++) {
+        const size_t r0 = (size_t)first[m];
+        rc = iris_b200_linear_residual(x + r0 * dim, dim, cat + r0 * dim, dim, sw[m]->proj, dim, sw[m]->mod + 2 * dim,
+                                       rows[m], dim, dim);
+        if (rc != IRIS_B200_OK) return rc;
+    }
+    /* feed-forward half: the gate | up projection stores silu(gate) * up */
+    for (int m = 0; m < 2; m++) {
+        const size_t r0 = (size_t)first[m];
+        if ((rc = layer_norm_mod(norm + r0 * dim, x + r0 * dim, sw[m]->mod + 3 * dim, sw[m]->mod + 4 * dim, rows[m], dim, eps)))
+            return rc;
+    }
+    for (int m = 0; m < 2; m++) {
+        const size_t r0 = (size_t)first[m];
+        rc = iris_b200_linear_glu(NULL, 0, cat + r0 * mlp, mlp, norm + r0 * dim, sw[m]->ff_in, rows[m], dim, 0, mlp, NULL, NULL,
+                                  NULL, NULL, eps);
+        if (rc != IRIS_B200_OK) return rc;
+    }
+    for (int m = 0; m < 2; m++) {
+        const size_t r0 = (size_t)first[m];
+        rc = iris_b200_linear_residual(x + r0 * dim, dim, cat + r0 * mlp, mlp, sw[m]->ff_out, mlp, sw[m]->mod + 5 * dim,
+                                       rows[m], mlp, dim);
+        if (rc != IRIS_B200_OK) return rc;
+    }
+    return IRIS_B200_OK;
 }

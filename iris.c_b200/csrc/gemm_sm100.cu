@@ -88,6 +88,16 @@ struct Params {
     int ld32;
     int accumulate;
     const float *gate;
+    /* Gated-linear-unit columns (the MLP half of a block's input projection):
+     * from column tile glu_tile0 on, a tile is 128 gate columns next to their
+     * 128 up columns (W rows glu_col0 + 128 j and glu_col0 + glu_cols + 128 j,
+     * two TMA boxes per stage), and the epilogue stores silu(gate) * up, both
+     * rounded to bf16 first as the reference's GEMM stores them
+     * (iris_dev_linear_bf16 then k_swiglu, iris_cuda.cu:300-307), to y2. The
+     * columns before glu_col0 are ordinary tiles. glu_tile0 == tiles_n: off. */
+    int glu_tile0, glu_col0, glu_cols;
+    uint16_t *y2;
+    int ldy2;
     int nranks;
     int row_first[kMaxScatterRanks + 1];    /* rank q owns the rows [row_first[q], row_first[q + 1]) */
     float *slab[kMaxScatterRanks];          /* where this rank's partial rows of owner q go ([rows of q, out] fp32) */
@@ -130,7 +140,13 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
     int issued = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.tiles_m * p.tiles_n; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * kTileM, n0 = (tile / p.tiles_m) * kTileN;
+        const int m0 = (tile % p.tiles_m) * kTileM, nt = tile / p.tiles_m;
+        const bool halves = p.glu_tile0 < p.tiles_n;           /* W comes in two boxes of 128 rows */
+        int n0 = nt * kTileN, n1 = n0 + kTileN / 2;
+        if (nt >= p.glu_tile0) {
+            n0 = p.glu_col0 + (nt - p.glu_tile0) * (kTileN / 2);
+            n1 = n0 + p.glu_cols;
+        }
         for (int kb = 0; kb < nkb; kb++, issued++) {
             const int s = issued % kStages;
             if (issued >= kStages && !(ok = wait(c, BAR_EMPTY + s, ((issued / kStages) - 1) & 1u, 400 + s))) break;
@@ -138,6 +154,7 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
             mbar_expect_tx(full, kStageBytes);
             tma_load_2d(smem + s * kStageBytes, tmx, kb * kBlockK, m0, full);
             tma_load_2d(smem + s * kStageBytes + kBytesA, tmw, kb * kBlockK, n0, full);
+            if (halves) tma_load_2d(smem + s * kStageBytes + kBytesA + kBytesB / 2, tmw, kb * kBlockK, n1, full);
         }
     }
     if (*c.abort_flag) {
@@ -269,13 +286,41 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
     unsigned char *stage_w = stage + quarter * 4096;
     for (int tile = blockIdx.x, n = 0; tile < p.tiles_m * p.tiles_n; tile += gridDim.x, n++) {
         const int buf = n & 1;
-        const int m0 = (tile % p.tiles_m) * kTileM, n0 = (tile / p.tiles_m) * kTileN;
+        const int m0 = (tile % p.tiles_m) * kTileM, n0 = (tile / p.tiles_m) * kTileN;     /* n0: ordinary tiles only */
         if (!__all_sync(0xffffffffu, wait(c, BAR_ACC_FULL + buf, (n >> 1) & 1u, 430 + buf))) return;
         tc_fence_after();
         const int row = m0 + row_in_tile;
         const int wrow0 = m0 + quarter * 32;
         const int nrows = p.rows - wrow0 < 32 ? (p.rows - wrow0 < 0 ? 0 : p.rows - wrow0) : 32;
         const bool row_ok = row < p.rows;
+        const int nt = tile / p.tiles_m;
+        if (nt >= p.glu_tile0) {
+            const int cbase = (nt - p.glu_tile0) * (kTileN / 2);            /* column of y2 */
+#pragma unroll 1
+            for (int pass = 0; pass < 2; pass++) {
+                uint32_t gt[64], up[64], pk[32];
+                tmem_ld32(tmem + lane_base + buf * kTileN + pass * 64, gt);
+                tmem_ld32(tmem + lane_base + buf * kTileN + pass * 64 + 32, gt + 32);
+                tmem_ld32(tmem + lane_base + buf * kTileN + 128 + pass * 64, up);
+                tmem_ld32(tmem + lane_base + buf * kTileN + 128 + pass * 64 + 32, up + 32);
+                tc_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; e++) {
+                    const uint32_t g2 = cvt_bf16x2(__uint_as_float(gt[2 * e]), __uint_as_float(gt[2 * e + 1]));
+                    const uint32_t u2 = cvt_bf16x2(__uint_as_float(up[2 * e]), __uint_as_float(up[2 * e + 1]));
+                    const float g0 = bf_lo(g2), g1 = bf_hi(g2);
+                    pk[e] = cvt_bf16x2(__fdividef(g0, 1.0f + __expf(-g0)) * bf_lo(u2),
+                                       __fdividef(g1, 1.0f + __expf(-g1)) * bf_hi(u2));
+                }
+                const int c0 = cbase + pass * 64;
+                const int ncols = p.glu_cols - c0 < 64 ? (p.glu_cols - c0 < 0 ? 0 : p.glu_cols - c0) : 64;
+                store_rows_bf16(pk, p.y2 + (size_t)wrow0 * p.ldy2 + c0, (size_t)p.ldy2, nrows, ncols, stage_w, lane);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(c.bars + (BAR_ACC_EMPTY + buf) * 8);
+            continue;
+        }
 #pragma unroll 1
         for (int half = 0; half < 2; half++) {
             const int col0 = n0 + half * 128;
@@ -487,12 +532,12 @@ void gemm_release(void) { g_gemm_configured = 0; }
 static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const uint16_t *W, int ldw, int rows, int in,
                          int out, int heads, const float *wq, const float *wk, const float *rope_cos,
                          const float *rope_sin, float eps, const ScatterArgs *sc, const char *op,
-                         const F32Out *f32 = NULL) {
+                         const F32Out *f32 = NULL, const GluOut *glu = NULL) {
     using namespace gemm;
     if (!require_device(op)) return IRIS_B200_ENODEV;
-    if ((!y && !sc && !f32) || (f32 && (!f32->y || f32->ld < out || f32->ld % 4 != 0 || ((uintptr_t)f32->y & 15) != 0 ||
+    if ((!y && !sc && !f32 && !(glu && out == 0)) || (f32 && (!f32->y || f32->ld < out || f32->ld % 4 != 0 || ((uintptr_t)f32->y & 15) != 0 ||
                                         ((uintptr_t)f32->gate & 15) != 0 || sc || heads > 0)) ||
-        !x || !W || rows < 0 || in <= 0 || out <= 0 || (y && ldy < out) || heads < 0 || ldx < in || ldw < in ||
+        !x || !W || rows < 0 || in <= 0 || out < 0 || (out == 0 && !glu) || (y && ldy < out) || heads < 0 || ldx < in || ldw < in ||
         (heads > 0 && (!wq || !wk || !rope_cos || !rope_sin || 2 * heads * 128 > out)) ||
         (sc && (sc->nranks < 1 || sc->nranks > kMaxScatterRanks))) {
         set_error(IRIS_B200_EINVAL, op, "bad argument");
@@ -503,6 +548,12 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         set_error(IRIS_B200_EUNSUPPORTED, op, "operands must be 16-byte aligned, in / out / row strides multiples of 8");
         return IRIS_B200_EUNSUPPORTED;
     }
+    /* With glu, `out` counts the ordinary columns only (may be 0); W has out + 2 * glu->cols rows. */
+    if (glu && (!glu->y || glu->cols <= 0 || glu->cols % 8 != 0 || glu->ld < glu->cols || glu->ld % 8 != 0 ||
+                ((uintptr_t)glu->y & 15) != 0 || out % kTileN != 0 || sc || f32)) {
+        set_error(IRIS_B200_EINVAL, op, "bad gated-linear-unit argument");
+        return IRIS_B200_EINVAL;
+    }
     if (rows == 0) return IRIS_B200_OK;
     if (!g_gemm_configured) {
         if (!cuda_ok(cudaFuncSetAttribute(k_linear_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
@@ -511,7 +562,9 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         g_gemm_configured = 1;
     }
     CUtensorMap tmx, tmw;
-    if (!make_tensor_map(&tmx, x, rows, in, ldx, kTileM) || !make_tensor_map(&tmw, W, out, in, ldw, kTileN))
+    const int w_rows = glu ? out + 2 * glu->cols : out;
+    if (!make_tensor_map(&tmx, x, rows, in, ldx, kTileM) ||
+        !make_tensor_map(&tmw, W, w_rows, in, ldw, glu ? kTileN / 2 : kTileN))
         return IRIS_B200_ECUDA;
     Params p = {};
     p.y = y;
@@ -521,6 +574,14 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
     p.out = out;
     p.tiles_m = (rows + kTileM - 1) / kTileM;
     p.tiles_n = (out + kTileN - 1) / kTileN;
+    p.glu_tile0 = p.tiles_n;
+    if (glu) {
+        p.glu_col0 = out;
+        p.glu_cols = glu->cols;
+        p.y2 = glu->y;
+        p.ldy2 = glu->ld;
+        p.tiles_n += (glu->cols + kTileN / 2 - 1) / (kTileN / 2);
+    }
     p.norm_cols = heads * 128;
     p.wq = wq;
     p.wk = wk;
@@ -589,6 +650,14 @@ extern "C" int iris_b200_linear_residual(float *x_rows, int ldx, const uint16_t 
     const F32Out f = {x_rows, ldx, gate, 1};
     return launch_linear(NULL, 0, a, lda, W, ldw, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_residual",
                          &f);
+}
+
+extern "C" int iris_b200_linear_glu(uint16_t *qkv, int ldq, uint16_t *act, int lda, const uint16_t *x, const uint16_t *W,
+                                    int rows, int in, int heads, int mlp, const float *wq, const float *wk,
+                                    const float *rope_cos, const float *rope_sin, float eps) {
+    const GluOut glu = {act, lda, mlp};
+    return launch_linear(qkv, ldq, x, in, W, in, rows, in, 3 * heads * 128, heads, wq, wk, rope_cos, rope_sin, eps, NULL,
+                         "linear_glu", NULL, &glu);
 }
 
 extern "C" int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W,

@@ -103,6 +103,15 @@ struct F32Out {
     int accumulate;
 };
 
+/* Gated-linear-unit destination of a linear layer: the last 2 * cols rows of W
+ * are `cols` gate rows then `cols` up rows; y [rows, cols] (bf16, row stride
+ * ld) = silu(gate) * up. */
+struct GluOut {
+    uint16_t *y;
+    int ld;
+    int cols;
+};
+
 /* Host-side fault injection: the next launch that splits its keys finds a
  * ticket that nobody took. */
 void sm100_inject_stale_ticket(void);

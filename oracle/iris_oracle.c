@@ -604,6 +604,59 @@ int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
     return rc;
 }
 
+/* One double-stream block as the reference's device forward issues it
+ * (iris_transformer_flux.c:3781-3823). x [seq, dim] = [text rows | image
+ * rows], in place. w[0] text, w[1] image. */
+int orc_double_block(float *x, const orc_stream_weights *txt, const orc_stream_weights *img,
+                     const float *rope_cos, const float *rope_sin,
+                     int seq, int txt_seq, int dim, int heads, int mlp, const int *key_mask, int nthreads) {
+    const orc_stream_weights *w[2] = {txt, img};
+    int hd = dim / heads, half = hd / 2;
+    int first[2] = {0, txt_seq}, rows[2] = {txt_seq, seq - txt_seq};
+    size_t nd = (size_t)seq * dim, nm = (size_t)seq * mlp;
+    uint16_t *norm = malloc(nd * 2), *h = malloc(3 * nd * 2), *cat = malloc(nd * 2);
+    uint16_t *ff = malloc(2 * nm * 2), *act = malloc(nm * 2);
+    float *hf = malloc((3 * nd > 2 * nm ? 3 * nd : 2 * nm) * sizeof(float));
+    float *att = malloc(nd * sizeof(float)), *proj = malloc(nd * sizeof(float));
+    int rc = -1;
+    if (norm && h && cat && ff && act && hf && att && proj) {
+        for (int m = 0; m < 2; m++) {
+            size_t r0 = (size_t)first[m];
+            int n = rows[m];
+            uint16_t *qkv = h + 3 * r0 * dim;
+            orc_layer_norm_mod(norm, x + r0 * dim, w[m]->mod, w[m]->mod + dim, n, dim, 1e-6f);
+            orc_linear(hf, 3 * dim, norm, dim, w[m]->qkv, dim, n, dim, 3 * dim, nthreads);
+            orc_f32_to_bf16(qkv, hf, (size_t)n * 3 * dim);
+            orc_head_norm_rope_bf16(qkv, 3 * dim, w[m]->norm_q, rope_cos + r0 * half, rope_sin + r0 * half,
+                                    n, heads, hd, 1e-6f, 0);
+            orc_head_norm_rope_bf16(qkv + dim, 3 * dim, w[m]->norm_k, rope_cos + r0 * half, rope_sin + r0 * half,
+                                    n, heads, hd, 1e-6f, 0);
+        }
+        orc_bf16_to_f32(hf, h, 3 * nd);
+        orc_dev_attention(att, dim, hf, hf + dim, hf + 2 * dim, 3 * dim, seq, seq, heads, heads, hd,
+                          1.0f / sqrtf((float)hd), 0, key_mask, NULL, 0, nthreads);
+        orc_f32_to_bf16(cat, att, nd);
+        for (int m = 0; m < 2; m++) {
+            size_t r0 = (size_t)first[m];
+            orc_linear(proj, dim, cat + r0 * dim, dim, w[m]->proj, dim, rows[m], dim, dim, nthreads);
+            orc_residual(x + r0 * dim, proj, w[m]->mod + 2 * dim, rows[m], dim);
+        }
+        for (int m = 0; m < 2; m++) {
+            size_t r0 = (size_t)first[m];
+            int n = rows[m];
+            orc_layer_norm_mod(norm, x + r0 * dim, w[m]->mod + 3 * dim, w[m]->mod + 4 * dim, n, dim, 1e-6f);
+            orc_linear(hf, 2 * mlp, norm, dim, w[m]->ff_in, dim, n, dim, 2 * mlp, nthreads);
+            orc_f32_to_bf16(ff, hf, (size_t)n * 2 * mlp);
+            orc_swiglu(act, mlp, ff, ff + mlp, 2 * mlp, n, mlp);
+            orc_linear(proj, dim, act, mlp, w[m]->ff_out, mlp, n, mlp, dim, nthreads);
+            orc_residual(x + r0 * dim, proj, w[m]->mod + 5 * dim, n, dim);
+        }
+        rc = 0;
+    }
+    free(norm); free(h); free(cat); free(ff); free(act); free(hf); free(att); free(proj);
+    return rc;
+}
+
 /* ------------------------------------------------------------------------
  * Metrics
  * ------------------------------------------------------------------------ */

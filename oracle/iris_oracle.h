@@ -123,6 +123,22 @@ int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
                      const float *rope_cos, const float *rope_sin,
                      int seq, int dim, int heads, int mlp, const int *key_mask, int nthreads);
 
+/* The weights of one stream of a double block (the reference's
+ * dev_stream_flux_t, iris_transformer_flux.c:3491-3494, plus the stream's
+ * modulation): qkv [3 dim, dim], proj [dim, dim], ff_in [2 mlp, dim] (gate
+ * rows, then up rows), ff_out [dim, mlp] in bf16; norm_q / norm_k [head_dim];
+ * mod [6 dim] = shift1 scale1 gate1 shift2 scale2 gate2. */
+typedef struct {
+    const uint16_t *qkv, *proj, *ff_in, *ff_out;
+    const float *norm_q, *norm_k, *mod;
+} orc_stream_weights;
+/* One FLUX.2 double-stream block in the arithmetic of the reference's device
+ * forward (iris_transformer_flux.c:3781-3823), in place on x [seq, dim] =
+ * [text rows | image rows]. */
+int orc_double_block(float *x, const orc_stream_weights *txt, const orc_stream_weights *img,
+                     const float *rope_cos, const float *rope_sin,
+                     int seq, int txt_seq, int dim, int heads, int mlp, const int *key_mask, int nthreads);
+
 /* ---- comparison metrics ---- */
 /* Per head over the listed rows (NULL = all): max |a - b| and cosine.
  * a, b: [seq, heads*hd] with row strides lda / ldb. Writes heads entries. */

@@ -10,7 +10,7 @@
  *   apply_qk_norm :1289, compute_rope_2d :823, compute_rope_2d_with_t_offset
  *   :887, apply_rope_2d :952, compute_rope_text :981, mha_forward :1585,
  *   joint_attention :1682, ensure_attn_scores :1382, single_block_forward
- *   :3341.
+ *   :3341, double_block_forward :2133.
  */
 #include "iris_transformer_flux.c"
 
@@ -126,6 +126,50 @@ int ref_flux_single_block(float *hidden, const float *w_in, const float *w_out,
     free(tf.work1); free(tf.work2); free(tf.single_q); free(tf.single_k); free(tf.single_v);
     free(tf.single_mlp_gate); free(tf.single_mlp_up); free(tf.single_attn_out); free(tf.single_concat);
     free(tf.t_emb_silu);
+    flux_ctx_free(&tf);
+    return ok ? 0 : -1;
+}
+
+/* One double-stream block on the CPU, fp32 weights: double_block_forward with
+ * a context that holds only the work buffers it touches. w[9] per stream: Q,
+ * K, V, proj [dim, dim], mlp gate, up [mlp, dim], down [dim, mlp], norm_q,
+ * norm_k [head_dim]. mod [6 dim] per stream. Hidden states in place. */
+int ref_flux_double_block(float *img_hidden, float *txt_hidden,
+                          const float *const *img_w, const float *const *txt_w,
+                          const float *img_mod, const float *txt_mod,
+                          const float *img_cos, const float *img_sin,
+                          const float *txt_cos, const float *txt_sin,
+                          int img_seq, int txt_seq, int heads, int head_dim, int mlp) {
+    iris_transformer_flux_t tf;
+    double_block_t b;
+    if (flux_ctx(&tf, img_seq, txt_seq, heads, head_dim) != 0) { flux_ctx_free(&tf); return -1; }
+    int dim = heads * head_dim;
+    size_t n = (size_t)img_seq + txt_seq;
+    tf.mlp_hidden = mlp;
+    tf.work1 = malloc(n * dim * sizeof(float));
+    tf.work2 = malloc(3 * n * dim * sizeof(float));
+    tf.ffn_gate = malloc(n * mlp * sizeof(float));
+    tf.ffn_up = malloc(n * mlp * sizeof(float));
+    tf.double_img_attn_out = malloc((size_t)img_seq * dim * sizeof(float));
+    tf.double_txt_attn_out = malloc((size_t)txt_seq * dim * sizeof(float));
+    int ok = tf.work1 && tf.work2 && tf.ffn_gate && tf.ffn_up && tf.double_img_attn_out && tf.double_txt_attn_out;
+    if (ok) {
+        memset(&b, 0, sizeof(b));
+        b.img_q_weight = (float *)img_w[0]; b.img_k_weight = (float *)img_w[1]; b.img_v_weight = (float *)img_w[2];
+        b.img_proj_weight = (float *)img_w[3];
+        b.img_mlp_gate_weight = (float *)img_w[4]; b.img_mlp_up_weight = (float *)img_w[5];
+        b.img_mlp_down_weight = (float *)img_w[6];
+        b.img_norm_q_weight = (float *)img_w[7]; b.img_norm_k_weight = (float *)img_w[8];
+        b.txt_q_weight = (float *)txt_w[0]; b.txt_k_weight = (float *)txt_w[1]; b.txt_v_weight = (float *)txt_w[2];
+        b.txt_proj_weight = (float *)txt_w[3];
+        b.txt_mlp_gate_weight = (float *)txt_w[4]; b.txt_mlp_up_weight = (float *)txt_w[5];
+        b.txt_mlp_down_weight = (float *)txt_w[6];
+        b.txt_norm_q_weight = (float *)txt_w[7]; b.txt_norm_k_weight = (float *)txt_w[8];
+        double_block_forward(img_hidden, txt_hidden, &b, img_mod, txt_mod, img_cos, img_sin, txt_cos, txt_sin,
+                             img_seq, txt_seq, &tf);
+    }
+    free(tf.work1); free(tf.work2); free(tf.ffn_gate); free(tf.ffn_up);
+    free(tf.double_img_attn_out); free(tf.double_txt_attn_out);
     flux_ctx_free(&tf);
     return ok ? 0 : -1;
 }

@@ -57,3 +57,58 @@ def delta_metrics(got, want, x0):
     b = (want - x0).astype(np.float64).ravel()
     scale = np.abs(b).max()
     return np.abs(a - b).max() / scale, float(a @ b / np.sqrt((a @ a) * (b @ b)))
+
+
+# ---------------------------------------------------------------------------
+# double-stream block
+# ---------------------------------------------------------------------------
+
+import ctypes as C  # noqa: E402
+
+
+class StreamWeights(C.Structure):
+    """iris_b200_stream_weights of include/iris_b200.h; orc_stream_weights of
+    oracle/iris_oracle.h has the same layout."""
+    _fields_ = [(n, C.c_void_p) for n in ("qkv", "proj", "ff_in", "ff_out", "norm_q", "norm_k", "mod")]
+
+
+STREAM_KEYS = ("qkv", "proj", "ff_in", "ff_out", "norm_q", "norm_k", "mod")
+
+
+def stream_inputs(dim, mlp, seed):
+    s = np.float32
+    return dict(
+        qkv=ol.to_bf16(ol.randn(seed, 3 * dim, dim) / s(np.sqrt(dim))),
+        proj=ol.to_bf16(ol.randn(seed + 1, dim, dim) / s(np.sqrt(dim))),
+        ff_in=ol.to_bf16(ol.randn(seed + 2, 2 * mlp, dim) / s(np.sqrt(dim))),
+        ff_out=ol.to_bf16(ol.randn(seed + 3, dim, mlp) / s(np.sqrt(mlp))),
+        norm_q=(1.0 + 0.1 * ol.randn(seed + 4, D)).astype(s),
+        norm_k=(1.0 + 0.1 * ol.randn(seed + 5, D)).astype(s),
+        mod=(0.4 * ol.randn(seed + 6, 6 * dim)).astype(s))
+
+
+def double_inputs(case, seed=11):
+    H, mlp = case["heads"], case["mlp"]
+    dim, seq = H * D, pc.seq_len(case)
+    cos, sin, _ = pc.rope_tables(case)
+    return dict(x=ol.randn(seed, seq, dim), txt=stream_inputs(dim, mlp, seed + 10), img=stream_inputs(dim, mlp, seed + 20),
+                cos=cos, sin=sin, seq=seq, txt_seq=case["txt"], dim=dim, heads=H, mlp=mlp)
+
+
+def host_stream(st):
+    """StreamWeights over host arrays (for the oracle)."""
+    return StreamWeights(*[st[k].ctypes.data for k in STREAM_KEYS])
+
+
+def oracle_double_block(inp, key_mask=None, nthreads=0):
+    x = inp["x"].copy()
+    o = ol.oracle()
+    fn = o.orc_double_block
+    fn.restype = C.c_int
+    fn.argtypes = [ol.f32p, C.POINTER(StreamWeights), C.POINTER(StreamWeights), ol.f32p, ol.f32p] + [C.c_int] * 5 + \
+                  [ol.i32p_opt, C.c_int]
+    t, i = host_stream(inp["txt"]), host_stream(inp["img"])
+    rc = fn(x, C.byref(t), C.byref(i), inp["cos"], inp["sin"], inp["seq"], inp["txt_seq"], inp["dim"], inp["heads"],
+            inp["mlp"], key_mask, nthreads)
+    assert rc == 0
+    return x

@@ -5,9 +5,9 @@ Run where the reference sources are present:
 
     make -C oracle ref && python tests/golden/make_block_golden.py
 
-Records what the reference's single_block_forward
-(iris_transformer_flux.c:3341-3477, compiled unmodified into
-oracle/_ref/libiris_ref_generic.so) makes of the seeded inputs of
+Records what the reference's single_block_forward and double_block_forward
+(iris_transformer_flux.c:3341-3477, :2133-2327, compiled unmodified into
+oracle/_ref/libiris_ref_generic.so) make of the seeded inputs of
 tests/block_cases.py. Inputs are not stored: block_cases regenerates them.
 """
 import os
@@ -42,6 +42,34 @@ def reference_block(r, case, inp):
     return x
 
 
+def reference_double_block(r, case, inp):
+    """x after a double block by the reference's CPU code: separate Q / K / V
+    and gate / up matrices (the slices of the fused device weights), its own
+    RoPE tables, text and image hidden states as separate arrays."""
+    import ctypes as C
+    H, txt, (ih, iw), dim, mlp = case["heads"], case["txt"], case["img"], inp["dim"], inp["mlp"]
+    img = ih * iw
+    ct = np.zeros((txt, bc.D), np.float32)
+    st = np.zeros_like(ct)
+    ci = np.zeros((img, bc.D), np.float32)
+    si = np.zeros_like(ci)
+    r.ref_flux_rope_text(ct, st, txt, 32, 2000.0)
+    r.ref_flux_rope_2d(ci, si, ih, iw, 32, 2000.0)
+    keep, ptrs = [], []
+    for s in (inp["img"], inp["txt"]):
+        qkv, ff_in = ol.from_bf16(s["qkv"]), ol.from_bf16(s["ff_in"])
+        mats = [qkv[:dim], qkv[dim:2 * dim], qkv[2 * dim:], ol.from_bf16(s["proj"]), ff_in[:mlp], ff_in[mlp:],
+                ol.from_bf16(s["ff_out"]), s["norm_q"], s["norm_k"]]
+        mats = [np.ascontiguousarray(m, np.float32) for m in mats]
+        keep.append(mats)
+        ptrs.append((C.c_void_p * 9)(*[m.ctypes.data for m in mats]))
+    xt, xi = inp["x"][:txt].copy(), inp["x"][txt:].copy()
+    rc = r.ref_flux_double_block(xi, xt, ptrs[0], ptrs[1], inp["img"]["mod"], inp["txt"]["mod"], ci, si, ct, st,
+                                 img, txt, H, bc.D, mlp)
+    assert rc == 0
+    return np.concatenate([xt, xi])
+
+
 def main():
     r = ol.ref("generic")
     if r is None:
@@ -52,6 +80,9 @@ def main():
         # every row of the small case, every fourth of the other: the file stays small
         out[case["name"]] = reference_block(r, case, inp)[::ROW_STEP[case["name"]]]
         out[case["name"] + "/x_sum"] = np.float64(inp["x"].astype(np.float64).sum())
+    for case in (bc.SMALL,):
+        inp = bc.double_inputs(case)
+        out["double/" + case["name"]] = reference_double_block(r, case, inp)
     path = os.path.join(HERE, "reference_block.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

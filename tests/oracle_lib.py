@@ -108,6 +108,7 @@ def ref(kind="generic"):
     _sig(lib, "ref_flux_mha", [f32p] * 4 + [INT] * 3, INT)
     _sig(lib, "ref_flux_attn_threads", [INT], INT)
     _sig(lib, "ref_flux_single_block", [f32p] * 11 + [INT] * 5, INT)
+    _sig(lib, "ref_flux_double_block", [f32p, f32p, C.c_void_p, C.c_void_p] + [f32p] * 6 + [INT] * 5, INT)
     _sig(lib, "ref_f3_head_rms_norm", [f32p, f32p, INT, INT, INT, FLT])
     _sig(lib, "ref_f3_apply_rope", [f32p, f32p, f32p, INT, INT, INT])
     _sig(lib, "ref_f3_joint_rope", [f32p, f32p, INT, INT, INT, i32p, i32p, INT, INT, INT, FLT], INT)

@@ -6,7 +6,9 @@ checked against the CPU oracle over the full sequence.
     ring_gpu_worker.py config5   24 heads x 16 896 tokens (the FLUX.3 multi-reference
                                  shape), sampled query rows of every rank checked
 
-RING_TEST_TRANSPORT=nccl selects the send/recv transport."""
+RING_TEST_TRANSPORT=nccl selects the send/recv transport. RING_TEST_GROUPS=g
+splits the heads over g independent rings of world / g ranks each (ranks
+[i * world / g, (i + 1) * world / g) form ring i and take head slice i)."""
 import ctypes as C
 import os
 import sys
@@ -29,26 +31,31 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     lib = ge.load_package().load()
     lib.init(int(os.environ.get("LOCAL_RANK", rank)))
-    ident = [bytes(128)]
-    if rank == 0:
+    groups = int(os.environ.get("RING_TEST_GROUPS", "1"))
+    assert world % groups == 0
+    size = world // groups
+    grp, rr = rank // size, rank % size
+    mine = None
+    if rr == 0:                                # the first rank of every ring makes its id
         buf = C.create_string_buffer(128)
         assert lib.iris_b200_ring_unique_id(buf) == 0
-        ident = [buf.raw]
-    dist.broadcast_object_list(ident, src=0)
+        mine = buf.raw
+    ids = [None] * world
+    dist.all_gather_object(ids, mine)
     nccl = os.environ.get("RING_TEST_TRANSPORT", "auto") == "nccl"
     assert lib.iris_b200_ring_configure(1 if nccl else 0, 0) == 0
-    assert lib.iris_b200_ring_init(rank, world, ident[0]) == 0
+    assert lib.iris_b200_ring_init(rr, size, ids[grp * size]) == 0
 
     worst = torch.tensor([0.0, -1.0])
     mode = sys.argv[1] if len(sys.argv) > 1 else "toy"
     if mode == "config5":
-        cases = ((24, 16896, 24),)
+        cases = ((24 // groups, 16896, 24),)
     else:
         # equal rows per rank (the slots then form one run of rows), a length that leaves
         # a partial tile in every slot, then uneven rows, which also makes the pool grow
-        cases = ((2, 384 * world, None), (3, 200 * world, None), (4, 2000 + 37, None))
-    for H, S, nsample in cases:
-        res = one_case(lib, rank, world, H, S, nsample)
+        cases = ((2, 384 * size, None), (3, 200 * size, None), (4, 2000 + 37, None))
+    for H, S, nsample in cases:               # H heads per ring
+        res = one_case(lib, rr, size, H, S, nsample, grp, groups)
         worst = torch.maximum(worst, res)
     dist.all_reduce(worst, op=dist.ReduceOp.MAX)
     transport = lib.iris_b200_ring_transport()
@@ -60,8 +67,11 @@ def main():
     dist.destroy_process_group()
 
 
-def one_case(lib, rank, world, H, S, nsample):
-    q, k, v = (ol.to_bf16(ol.randn(70 + i, S, H * D)) for i in range(3))
+def one_case(lib, rank, world, H, S, nsample, grp=0, groups=1):
+    """rank / world: this rank inside its ring. The ring takes heads
+    [grp * H, (grp + 1) * H) of tensors generated for groups * H heads."""
+    cols = slice(grp * H * D, (grp + 1) * H * D)
+    q, k, v = (np.ascontiguousarray(ol.to_bf16(ol.randn(70 + i, S, groups * H * D))[:, cols]) for i in range(3))
     a, b = C.c_int(), C.c_int()
     rows = []
     for r in range(world):

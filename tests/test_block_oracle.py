@@ -100,3 +100,29 @@ def test_key_mask_reaches_the_block():
     m = ones.copy()
     m[5:20] = 0
     assert not np.array_equal(bc.oracle_block(inp, m), base)
+
+
+def test_double_block_restatement_against_recorded_reference():
+    gold = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_block.npz")))
+    inp = bc.double_inputs(bc.SMALL)
+    rel, cos = bc.delta_metrics(bc.oracle_double_block(inp), gold["double/" + bc.SMALL["name"]], inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_double_block_restatement_against_reference_build():
+    r = ol.ref("generic")
+    if r is None:
+        pytest.skip("oracle/_ref is not built here")
+    case = dict(bc.MID, name="flux2-double-other", txt=17, img=(7, 9))
+    inp = bc.double_inputs(case, seed=41)
+    want = mg.reference_double_block(r, case, inp)
+    rel, cos = bc.delta_metrics(bc.oracle_double_block(inp), want, inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_double_block_streams_use_their_own_weights():
+    """Swapping the two streams' weights changes the result: no stream is read twice."""
+    inp = bc.double_inputs(bc.SMALL)
+    base = bc.oracle_double_block(inp)
+    swapped = bc.oracle_double_block(dict(inp, txt=inp["img"], img=inp["txt"]))
+    assert not np.allclose(base, swapped)

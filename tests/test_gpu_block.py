@@ -243,3 +243,128 @@ def test_single_block_against_the_reference_cuda_sequence(lib):
         d.free()
     rel, cos_ = bc.delta_metrics(ours, theirs, inp["x"])
     assert rel <= 5e-3 and cos_ >= 0.99999, (rel, cos_)
+
+
+# ---------------------------------------------------------------------------
+# double-stream block
+# ---------------------------------------------------------------------------
+
+def device_double_block(lib, inp, key_mask=None):
+    d = Dev(lib)
+    try:
+        dx = d.put(inp["x"])
+        nbytes = lib.iris_b200_double_block_scratch_bytes(inp["seq"], inp["dim"], inp["mlp"])
+        assert nbytes > 0
+        scratch = d.new(nbytes)
+        streams = [bc.StreamWeights(*[d.put(inp[s][k]) for k in bc.STREAM_KEYS]) for s in ("txt", "img")]
+        dcos, dsin = d.put(inp["cos"]), d.put(inp["sin"])
+        dm = d.put(np.ascontiguousarray(key_mask, np.int32)) if key_mask is not None else None
+        rc = lib.iris_b200_double_block(dx, scratch, C.addressof(streams[0]), C.addressof(streams[1]), dcos, dsin,
+                                        inp["seq"], inp["txt_seq"], inp["dim"], inp["heads"], inp["mlp"], dm)
+        assert rc == 0
+        out = lib.to_host(dx, inp["x"].shape, np.float32)
+        lib.check()
+        return out
+    finally:
+        d.free()
+
+
+@pytest.mark.parametrize("case", [bc.SMALL, bc.MID, bc.KLEIN4B_SHORT], ids=lambda c: c["name"])
+def test_double_block_against_the_restatement(lib, case):
+    inp = bc.double_inputs(case)
+    got = device_double_block(lib, inp)
+    rel, cos = bc.delta_metrics(got, bc.oracle_double_block(inp), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_double_block_against_the_recorded_reference(lib):
+    import os
+    gold = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_block.npz")))
+    inp = bc.double_inputs(bc.SMALL)
+    rel, cos = bc.delta_metrics(device_double_block(lib, inp), gold["double/" + bc.SMALL["name"]], inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_double_block_with_key_mask_and_no_text(lib):
+    inp = bc.double_inputs(bc.MID)
+    mask = np.ones(inp["seq"], np.int32)
+    mask[3:25] = 0
+    got = device_double_block(lib, inp, mask)
+    rel, cos = bc.delta_metrics(got, bc.oracle_double_block(inp, mask), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+    # a block whose text stream is empty is a block over the image rows alone
+    case = dict(bc.SMALL, name="flux2-double-no-text", txt=0)
+    inp = bc.double_inputs(case)
+    rel, cos = bc.delta_metrics(device_double_block(lib, inp), bc.oracle_double_block(inp), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_double_block_argument_checks(lib):
+    d = Dev(lib)
+    try:
+        p = d.new(1 << 16)
+        good = bc.StreamWeights(*[p] * 7)
+        bad = bc.StreamWeights(p, p, None, p, p, p, p)
+        a, b = C.addressof(good), C.addressof(bad)
+        assert lib.iris_b200_double_block(p, p, a, b, p, p, 8, 4, 256, 2, 64, None) == 1      # a weight is missing
+        assert lib.iris_b200_double_block(p, p, a, a, p, p, 8, 9, 256, 2, 64, None) == 1      # txt_seq > seq
+        assert lib.iris_b200_double_block(p, p, a, a, p, p, 8, 4, 250, 2, 64, None) == 1      # dim != heads * 128
+        assert lib.iris_b200_double_block(p, p, a, None, p, p, 8, 4, 256, 2, 64, None) == 1
+        lib.iris_b200_clear_error()
+    finally:
+        d.free()
+
+
+# ---------------------------------------------------------------------------
+# the input projection with SwiGLU in its epilogue
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cin,heads,mlp", [(200, 256, 2, 384), (129, 512, 2, 200), (77, 256, 0, 136),
+                                                (300, 384, 0, 1024)])
+def test_linear_glu(lib, rows, cin, heads, mlp):
+    """Q / K / V columns as iris_b200_linear_qk_norm_rope stores them, and
+    silu(gate) * up for the gate | up rows of W, against the restatement of
+    the reference's sequence linear_bf16 -> head_norm_rope x 2 -> swiglu."""
+    o = ol.oracle()
+    nq = 3 * heads * 128
+    x = ol.to_bf16(ol.randn(rows + mlp, rows, cin))
+    W = ol.to_bf16(ol.randn(cin + mlp, nq + 2 * mlp, cin) / np.float32(np.sqrt(cin)))
+    wq = (1 + 0.1 * ol.randn(3, 128)).astype(np.float32)
+    wk = (1 + 0.1 * ol.randn(4, 128)).astype(np.float32)
+    ang = ol.randn(5, rows, 64)
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    hf = np.zeros((rows, nq + 2 * mlp), np.float32)
+    o.orc_linear(hf, nq + 2 * mlp, x, cin, W, cin, rows, cin, nq + 2 * mlp, 0)
+    h = ol.to_bf16(hf)
+    if heads:
+        o.orc_head_norm_rope_bf16(h.ctypes.data, nq + 2 * mlp, wq, cos, sin, rows, heads, 128, 1e-6, 0)
+        o.orc_head_norm_rope_bf16(h.ctypes.data + 2 * heads * 128, nq + 2 * mlp, wk, cos, sin, rows, heads, 128, 1e-6, 0)
+    want_act = np.zeros((rows, mlp), np.uint16)
+    o.orc_swiglu(want_act.ctypes.data, mlp, h.ctypes.data + 2 * nq, h.ctypes.data + 2 * (nq + mlp), nq + 2 * mlp, rows, mlp)
+    lda = mlp + 16
+    d = Dev(lib)
+    try:
+        dx, dW, dwq, dwk, dcos, dsin = (d.put(a) for a in (x, W, wq, wk, cos, sin))
+        dqkv = d.put(np.full((rows, max(nq, 8)), 0x7FC0, np.uint16)) if heads else None
+        dact = d.put(np.full((rows, lda), 0x7FC0, np.uint16))
+        rc = lib.iris_b200_linear_glu(dqkv, nq, dact, lda, dx, dW, rows, cin, heads, mlp,
+                                      dwq if heads else None, dwk if heads else None,
+                                      dcos if heads else None, dsin if heads else None, 1e-6)
+        assert rc == 0
+        act = lib.to_host(dact, (rows, lda), np.uint16)
+        qkv = lib.to_host(dqkv, (rows, nq), np.uint16) if heads else None
+        lib.check()
+    finally:
+        d.free()
+    assert (act[:, mlp:] == 0x7FC0).all()                     # nothing beyond the mlp columns is written
+    fa, fw = ol.from_bf16(act[:, :mlp]), ol.from_bf16(want_act)
+    assert np.isfinite(fa).all()
+    # fp32 accumulation order differs from the restatement: a product on a bf16 rounding boundary may fall
+    # either way, so allow two units in the last place of the larger of |value| and the operands' scale
+    tol = np.maximum(np.abs(fw), 0.05) * 2.0 ** -6
+    assert (np.abs(fa - fw) <= tol).all(), float(np.abs(fa - fw).max())
+    assert (act[:, :mlp] != want_act).mean() < 0.1
+    if heads:
+        fq, fh = ol.from_bf16(qkv), ol.from_bf16(h[:, :nq])
+        assert (np.abs(fq - fh) <= np.maximum(np.abs(fh), 0.05) * 2.0 ** -6).all()
+        assert (qkv != h[:, :nq]).mean() < 0.1

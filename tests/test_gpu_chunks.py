@@ -109,11 +109,12 @@ def test_chunk_argument_checks(lib):
     lib.iris_b200_clear_error()
 
 
-def run_ring_worker(nproc, transport, mode, port):
+def run_ring_worker(nproc, transport, mode, port, groups=1):
     import torch
     if torch.cuda.device_count() < nproc:
         pytest.skip("needs %d GPUs" % nproc)
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", RING_TEST_TRANSPORT=transport)
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", RING_TEST_TRANSPORT=transport,
+               RING_TEST_GROUPS=str(groups))
     out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % nproc,
                           "--master-addr", "127.0.0.1", "--master-port", str(port),
                           os.path.join(ROOT, "tests", "ring_gpu_worker.py"), mode],
@@ -130,6 +131,14 @@ def test_ring_across_gpus(nproc, transport):
     while one attention launch waits for them inside the kernel, `nccl`
     forces the send/recv transport (all chunks first, then the launch)."""
     run_ring_worker(nproc, transport, "toy", 29437)
+
+
+@pytest.mark.parametrize("nproc,groups,mode", [(4, 2, "toy"), (8, 2, "toy"), (8, 2, "config5"), (8, 4, "toy")])
+def test_ring_across_gpus_in_head_groups(nproc, groups, mode):
+    """The heads split over independent rings (2 rings of 4 GPUs, 4 rings of
+    2, ...): each ring has its own communicator and slot pools, nothing
+    crosses between them."""
+    run_ring_worker(nproc, "auto", mode, 29441, groups)
 
 
 @pytest.mark.parametrize("nproc", [2, 4, 8])
