@@ -10,7 +10,7 @@
  *   iris_dev_residual         x += gate * a in fp32 (iris_cuda.cu:309-314)
  *   iris_b200_double_block    the sequence the reference issues per double
  *                             block (iris_transformer_flux.c:3781-3823) in
- *                             twelve launches instead of twenty-seven.
+ *                             thirteen launches instead of twenty-seven.
  *   iris_b200_single_block    the sequence the reference issues per single
  *                             block (iris_transformer_flux.c:3828-3845) in four
  *                             launches instead of eight: the projection
