@@ -704,7 +704,7 @@ def block_run(job, w, pk, reps=10):
 
 
 def double_block_run(job, w, pk, reps=10):
-    """One double-stream block (rank 0, N = 1): thirteen launches through
+    """One double-stream block (rank 0, N = 1): seven launches through
     iris_b200_double_block next to the reference's CUDA backend issuing its
     twenty-seven calls (iris_transformer_flux.c:3781-3823) on the same device."""
     lib, torch = job.lib, job.torch

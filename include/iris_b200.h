@@ -222,7 +222,7 @@ size_t iris_b200_double_block_scratch_bytes(int seq, int dim, int mlp);
  * input; joint attention over all rows; per stream: output projection with
  * the gate1 residual, LayerNorm with (shift2, scale2), the gate|up projection,
  * with SwiGLU in its epilogue, the down projection with the gate2 residual.
- * Thirteen launches.
+ * Seven launches: each covers both streams (two row groups with their own weights).
  * txt_seq: the number of text rows. rope tables [seq, 64] in row order.
  * key_mask: NULL or [seq]. head_dim is 128. */
 int iris_b200_double_block(float *x, void *scratch,

@@ -10,7 +10,8 @@
  *   iris_dev_residual         x += gate * a in fp32 (iris_cuda.cu:309-314)
  *   iris_b200_double_block    the sequence the reference issues per double
  *                             block (iris_transformer_flux.c:3781-3823) in
- *                             thirteen launches instead of twenty-seven.
+ *                             seven launches instead of twenty-seven: every
+ *                             launch covers the text and the image stream.
  *   iris_b200_single_block    the sequence the reference issues per single
  *                             block (iris_transformer_flux.c:3828-3845) in four
  *                             launches instead of eight: the projection
@@ -51,8 +52,9 @@ __device__ __forceinline__ float block_sum(float v, float *sh) {
  * reference. */
 template <int VPL>
 __global__ void __launch_bounds__(kRowThreads)
-k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift,
-                      const float *__restrict__ scale, int rows, int dim, float eps) {
+k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift0,
+                      const float *__restrict__ scale0, const float *__restrict__ shift1,
+                      const float *__restrict__ scale1, int split, int rows, int dim, float eps) {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * kRowThreads) >> 5;
     const int nvec = dim >> 2;
@@ -60,6 +62,7 @@ k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, c
     for (int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5; row < rows; row += warps) {
         const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * dim);
         uint2 *o = reinterpret_cast<uint2 *>(out + (size_t)row * dim);
+        const float *shift = row < split ? shift0 : shift1, *scale = row < split ? scale0 : scale1;
         float4 v[VPL];
         float s = 0.0f;
 #pragma unroll
@@ -103,13 +106,15 @@ k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, c
 /* Any other row length: one block per row at a time, the row re-read from
  * L1 / L2 for each pass. */
 __global__ void __launch_bounds__(kRowThreads)
-k_layer_norm_mod_any(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift,
-                     const float *__restrict__ scale, int rows, int dim, float eps) {
+k_layer_norm_mod_any(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift0,
+                     const float *__restrict__ scale0, const float *__restrict__ shift1,
+                     const float *__restrict__ scale1, int split, int rows, int dim, float eps) {
     __shared__ float sh[kRowThreads / 32];
     const float inv_dim = 1.0f / (float)dim;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float *xr = x + (size_t)row * dim;
         uint16_t *o = out + (size_t)row * dim;
+        const float *shift = row < split ? shift0 : shift1, *scale = row < split ? scale0 : scale1;
         float s = 0.0f;
         for (int i = threadIdx.x; i < dim; i += kRowThreads) s += xr[i];
         const float mean = block_sum(s, sh) * inv_dim;
@@ -182,30 +187,36 @@ unsigned blocks_for(size_t items, int per_block, int per_sm) {
 
 bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
-int layer_norm_mod(uint16_t *out, const float *x, const float *shift, const float *scale, int rows, int dim, float eps) {
+/* Rows [0, split) take (shift, scale), rows [split, rows) take (shift1, scale1). */
+int layer_norm_mod2(uint16_t *out, const float *x, const float *shift, const float *scale, const float *shift1,
+                    const float *scale1, int split, int rows, int dim, float eps) {
     if (!require_device("layer_norm_mod")) return IRIS_B200_ENODEV;
-    if (!out || !x || rows < 0 || dim <= 0) {
+    if (!out || !x || rows < 0 || dim <= 0 || split < 0 || split > rows) {
         set_error(IRIS_B200_EINVAL, "layer_norm_mod", "bad argument");
         return IRIS_B200_EINVAL;
     }
     if (rows == 0) return IRIS_B200_OK;
     const int nvec = dim / 4;
     const bool vec = dim % 4 == 0 && nvec <= 32 * 32 && aligned16(x) && aligned16(shift) && aligned16(scale) &&
-                     ((uintptr_t)out & 7) == 0;
+                     aligned16(shift1) && aligned16(scale1) && ((uintptr_t)out & 7) == 0;
     if (vec) {
         const unsigned grid = blocks_for((size_t)rows, kRowThreads / 32, 8);
-        if (nvec <= 32 * 8)
-            k_layer_norm_mod_warp<8><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
-        else if (nvec <= 32 * 16)
-            k_layer_norm_mod_warp<16><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
-        else if (nvec <= 32 * 24)
-            k_layer_norm_mod_warp<24><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
-        else
-            k_layer_norm_mod_warp<32><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+#define IRIS_LN_LAUNCH(VPL) \
+    k_layer_norm_mod_warp<VPL><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, shift1, scale1, split, rows, dim, eps)
+        if (nvec <= 32 * 8) IRIS_LN_LAUNCH(8);
+        else if (nvec <= 32 * 16) IRIS_LN_LAUNCH(16);
+        else if (nvec <= 32 * 24) IRIS_LN_LAUNCH(24);
+        else IRIS_LN_LAUNCH(32);
+#undef IRIS_LN_LAUNCH
     } else {
-        k_layer_norm_mod_any<<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+        k_layer_norm_mod_any<<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, x, shift, scale, shift1, scale1,
+                                                                                         split, rows, dim, eps);
     }
     return after_launch("k_layer_norm_mod") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+int layer_norm_mod(uint16_t *out, const float *x, const float *shift, const float *scale, int rows, int dim, float eps) {
+    return layer_norm_mod2(out, x, shift, scale, shift, scale, rows, rows, dim, eps);
 }
 
 int swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi, int rows, int cols) {
@@ -326,46 +337,68 @@ extern "C" int iris_b200_double_block(float *x, void *scratch, const iris_b200_s
     uint16_t *h = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2));
     uint16_t *cat = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2) + up256((size_t)seq * 3 * dim * 2));
     const float eps = 1e-6f;
-    const int first[2] = {0, txt_seq}, rows[2] = {txt_seq, seq - txt_seq};
+    const float *tm = txt->mod, *im = img->mod;
     int rc;
-    /* attention half: both streams write their rows of the joint [seq, 3 dim] input */
-    for (int m = 0; m < 2; m++) {
-        const size_t r0 = (size_t)first[m];
-        if ((rc = layer_norm_mod(norm + r0 * dim, x + r0 * dim, sw[m]->mod, sw[m]->mod + dim, rows[m], dim, eps))) return rc;
-    }
-    for (int m = 0; m < 2; m++) {
-        const size_t r0 = (size_t)first[m];
-        rc = iris_b200_linear_qk_norm_rope(h + r0 * 3 * dim, 3 * dim, norm + r0 * dim, sw[m]->qkv, rows[m], dim, 3 * dim,
-                                           heads, sw[m]->norm_q, sw[m]->norm_k, rope_cos + r0 * 64, rope_sin + r0 * 64, eps);
-        if (rc != IRIS_B200_OK) return rc;
-    }
+    /* attention half: both streams in every launch, text rows first */
+    if ((rc = layer_norm_mod2(norm, x, tm, tm + dim, im, im + dim, txt_seq, seq, dim, eps))) return rc;
+    TwoStreamLinear l = {};
+    l.x = norm;
+    l.ldx = l.ldw = l.in = dim;
+    l.W[0] = txt->qkv;
+    l.W[1] = img->qkv;
+    l.rows = seq;
+    l.split = txt_seq;
+    l.qkv = h;
+    l.ldy = 3 * dim;
+    l.heads = heads;
+    l.wq[0] = txt->norm_q;
+    l.wq[1] = img->norm_q;
+    l.wk[0] = txt->norm_k;
+    l.wk[1] = img->norm_k;
+    l.rope_cos = rope_cos;
+    l.rope_sin = rope_sin;
+    l.eps = eps;
+    if ((rc = launch_linear_two(l))) return rc;
     iris_b200_clear_error();
     iris_dev_attention(cat, dim, h, h + dim, h + 2 * dim, 3 * dim, seq, seq, heads, heads, 128, 0.08838834764831845f, 0,
                        key_mask);
     if ((rc = iris_b200_last_error()) != IRIS_B200_OK) return rc;
-    for (int m = 0; m < 2; m++) {
-        const size_t r0 = (size_t)first[m];
-        rc = iris_b200_linear_residual(x + r0 * dim, dim, cat + r0 * dim, dim, sw[m]->proj, dim, sw[m]->mod + 2 * dim,
-                                       rows[m], dim, dim);
-        if (rc != IRIS_B200_OK) return rc;
-    }
+    TwoStreamLinear o = {};
+    o.x = cat;
+    o.ldx = o.ldw = o.in = dim;
+    o.W[0] = txt->proj;
+    o.W[1] = img->proj;
+    o.rows = seq;
+    o.split = txt_seq;
+    o.out = dim;
+    o.y32 = x;
+    o.ldy = dim;
+    o.gate[0] = tm + 2 * dim;
+    o.gate[1] = im + 2 * dim;
+    if ((rc = launch_linear_two(o))) return rc;
     /* feed-forward half: the gate | up projection stores silu(gate) * up */
-    for (int m = 0; m < 2; m++) {
-        const size_t r0 = (size_t)first[m];
-        if ((rc = layer_norm_mod(norm + r0 * dim, x + r0 * dim, sw[m]->mod + 3 * dim, sw[m]->mod + 4 * dim, rows[m], dim, eps)))
-            return rc;
-    }
-    for (int m = 0; m < 2; m++) {
-        const size_t r0 = (size_t)first[m];
-        rc = iris_b200_linear_glu(NULL, 0, cat + r0 * mlp, mlp, norm + r0 * dim, sw[m]->ff_in, rows[m], dim, 0, mlp, NULL, NULL,
-                                  NULL, NULL, eps);
-        if (rc != IRIS_B200_OK) return rc;
-    }
-    for (int m = 0; m < 2; m++) {
-        const size_t r0 = (size_t)first[m];
-        rc = iris_b200_linear_residual(x + r0 * dim, dim, cat + r0 * mlp, mlp, sw[m]->ff_out, mlp, sw[m]->mod + 5 * dim,
-                                       rows[m], mlp, dim);
-        if (rc != IRIS_B200_OK) return rc;
-    }
-    return IRIS_B200_OK;
+    if ((rc = layer_norm_mod2(norm, x, tm + 3 * dim, tm + 4 * dim, im + 3 * dim, im + 4 * dim, txt_seq, seq, dim, eps))) return rc;
+    TwoStreamLinear f = {};
+    f.x = norm;
+    f.ldx = f.ldw = f.in = dim;
+    f.W[0] = txt->ff_in;
+    f.W[1] = img->ff_in;
+    f.rows = seq;
+    f.split = txt_seq;
+    f.act = cat;
+    f.lda = f.mlp = mlp;
+    if ((rc = launch_linear_two(f))) return rc;
+    TwoStreamLinear d = {};
+    d.x = cat;
+    d.ldx = d.ldw = d.in = mlp;
+    d.W[0] = txt->ff_out;
+    d.W[1] = img->ff_out;
+    d.rows = seq;
+    d.split = txt_seq;
+    d.out = dim;
+    d.y32 = x;
+    d.ldy = dim;
+    d.gate[0] = tm + 5 * dim;
+    d.gate[1] = im + 5 * dim;
+    return launch_linear_two(d);
 }

@@ -47,8 +47,8 @@ static constexpr int kBytesB = kTileN * kBlockK * 2;        /* 32 KB */
 static constexpr int kStageBytes = kBytesA + kBytesB;
 static constexpr int kThreads = 192;
 static constexpr int kSmemStage = kStages * kStageBytes;    /* epilogue staging: 4 warps x 4 KB */
-static constexpr int kSmemW = kSmemStage + 4 * 4096;        /* norm weights: wq[128] | wk[128] fp32 */
-static constexpr int kSmemBar = kSmemW + 1024;
+static constexpr int kSmemW = kSmemStage + 4 * 4096;        /* norm weights: wq[128] | wk[128] fp32, per row group */
+static constexpr int kSmemBar = kSmemW + 2048;
 static constexpr int kSmemBytes = kSmemBar + 256 + 1024;    /* + barriers + alignment slack */
 static constexpr uint32_t kIdesc = idesc_bf16(kTileM, kTileN);
 
@@ -98,6 +98,14 @@ struct Params {
     int glu_tile0, glu_col0, glu_cols;
     uint16_t *y2;
     int ldy2;
+    /* Two row groups with their own weights in one launch (the text and
+     * image streams of a double block, whose rows are adjacent in every
+     * buffer): rows [0, split) use the first W map, norm weights and gate,
+     * rows [split, rows) the second. Row tiles never straddle the boundary:
+     * group 0 has tiles_m0 of them, the rows a partial tile reads beyond its
+     * group are computed and not stored. split == rows: one group. */
+    int split, tiles_m0;
+    const float *wq1, *wk1, *gate1;
     int nranks;
     int row_first[kMaxScatterRanks + 1];    /* rank q owns the rows [row_first[q], row_first[q + 1]) */
     float *slab[kMaxScatterRanks];          /* where this rank's partial rows of owner q go ([rows of q, out] fp32) */
@@ -105,6 +113,15 @@ struct Params {
     uint32_t seq;
     unsigned int *done;                     /* CTAs that are through; zero between launches */
 };
+
+/* Row tile tm of a launch: its first row, the end of its row group, the group. */
+struct RowTile {
+    int m0, row_end, grp;
+};
+__device__ __forceinline__ RowTile row_tile(const Params &p, int tm) {
+    if (tm < p.tiles_m0) return {tm * kTileM, p.split, 0};
+    return {p.split + (tm - p.tiles_m0) * kTileM, p.rows, 1};
+}
 
 struct Ctx {
     uint32_t bars;
@@ -134,13 +151,15 @@ __device__ __forceinline__ bool wait(const Ctx &c, int idx, uint32_t parity, int
     }
 }
 
-__device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmx, const CUtensorMap *tmw,
-                                         uint32_t smem) {
+__device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmx, const CUtensorMap *tmw0,
+                                         const CUtensorMap *tmw1, uint32_t smem) {
     const int nkb = (p.in + kBlockK - 1) / kBlockK;
     int issued = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.tiles_m * p.tiles_n; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * kTileM, nt = tile / p.tiles_m;
+        const RowTile rt = row_tile(p, tile % p.tiles_m);
+        const int m0 = rt.m0, nt = tile / p.tiles_m;
+        const CUtensorMap *tmw = rt.grp ? tmw1 : tmw0;
         const bool halves = p.glu_tile0 < p.tiles_n;           /* W comes in two boxes of 128 rows */
         int n0 = nt * kTileN, n1 = n0 + kTileN / 2;
         if (nt >= p.glu_tile0) {
@@ -251,8 +270,8 @@ __device__ __forceinline__ void scatter_rows_f32(const uint32_t *src, const Para
  * in place with a per-column gate (ncols a multiple of 4). Every element of
  * the matrix belongs to exactly one warp of one tile, so the read-modify-write
  * needs no atomics. */
-__device__ __forceinline__ void rows_f32(const uint32_t *src, const Params &p, int wrow0, int nrows, int c0, int ncols,
-                                         unsigned char *stage_w, int lane) {
+__device__ __forceinline__ void rows_f32(const uint32_t *src, const Params &p, const float *gate, int wrow0, int nrows, int c0,
+                                         int ncols, unsigned char *stage_w, int lane) {
 #pragma unroll
     for (int c8 = 0; c8 < 8; c8++)
         *reinterpret_cast<uint4 *>(stage_w + lane * 128 + ((c8 ^ (lane & 7)) << 4)) =
@@ -260,7 +279,7 @@ __device__ __forceinline__ void rows_f32(const uint32_t *src, const Params &p, i
     __syncwarp();
     const int ch = lane & 7;
     float4 g4 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-    if (p.gate && ch * 4 < ncols) g4 = *reinterpret_cast<const float4 *>(p.gate + c0 + ch * 4);
+    if (gate && ch * 4 < ncols) g4 = *reinterpret_cast<const float4 *>(gate + c0 + ch * 4);
 #pragma unroll
     for (int k = 0; k < 8; k++) {
         const int r = k * 4 + (lane >> 3);
@@ -286,13 +305,14 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
     unsigned char *stage_w = stage + quarter * 4096;
     for (int tile = blockIdx.x, n = 0; tile < p.tiles_m * p.tiles_n; tile += gridDim.x, n++) {
         const int buf = n & 1;
-        const int m0 = (tile % p.tiles_m) * kTileM, n0 = (tile / p.tiles_m) * kTileN;     /* n0: ordinary tiles only */
+        const RowTile rt = row_tile(p, tile % p.tiles_m);
+        const int m0 = rt.m0, n0 = (tile / p.tiles_m) * kTileN;     /* n0: ordinary tiles only */
         if (!__all_sync(0xffffffffu, wait(c, BAR_ACC_FULL + buf, (n >> 1) & 1u, 430 + buf))) return;
         tc_fence_after();
         const int row = m0 + row_in_tile;
         const int wrow0 = m0 + quarter * 32;
-        const int nrows = p.rows - wrow0 < 32 ? (p.rows - wrow0 < 0 ? 0 : p.rows - wrow0) : 32;
-        const bool row_ok = row < p.rows;
+        const int nrows = rt.row_end - wrow0 < 32 ? (rt.row_end - wrow0 < 0 ? 0 : rt.row_end - wrow0) : 32;
+        const bool row_ok = row < rt.row_end;
         const int nt = tile / p.tiles_m;
         if (nt >= p.glu_tile0) {
             const int cbase = (nt - p.glu_tile0) * (kTileN / 2);            /* column of y2 */
@@ -337,7 +357,7 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
                     const int c0 = col0 + sub * 32;
                     const int ncols = p.out - c0 < 32 ? (p.out - c0 < 0 ? 0 : p.out - c0) : 32;
                     if (p.scatter == 1) scatter_rows_f32(acc + sub * 32, p, wrow0, nrows, c0, ncols, stage_w, lane);
-                    else rows_f32(acc + sub * 32, p, wrow0, nrows, c0, ncols, stage_w, lane);
+                    else rows_f32(acc + sub * 32, p, rt.grp ? p.gate1 : p.gate, wrow0, nrows, c0, ncols, stage_w, lane);
                 }
                 continue;
             }
@@ -356,7 +376,7 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
                 }
                 inv = rsqrtf((ss0 + ss1) * (1.0f / 128.0f) + p.eps);
             }
-            const float *w = w_smem + (kind == 1 ? 128 : 0);
+            const float *w = w_smem + rt.grp * 256 + (kind == 1 ? 128 : 0);
             const float4 *cosr = reinterpret_cast<const float4 *>(p.rope_cos + (size_t)(row_ok ? row : 0) * 64);
             const float4 *sinr = reinterpret_cast<const float4 *>(p.rope_sin + (size_t)(row_ok ? row : 0) * 64);
 #pragma unroll
@@ -394,7 +414,7 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
 
 __global__ void __launch_bounds__(kThreads, 1)
 k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw,
-               const __grid_constant__ Params p) {
+               const __grid_constant__ CUtensorMap tmw1, const __grid_constant__ Params p) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char *smem_gen = smem_raw + (smem - smem_u32(smem_raw));
@@ -429,14 +449,17 @@ k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (p.norm_cols > 0)
-        for (int i = threadIdx.x; i < 256; i += kThreads) w_smem[i] = i < 128 ? p.wq[i] : p.wk[i - 128];
+        for (int i = threadIdx.x; i < 512; i += kThreads) {
+            const float *src = i < 256 ? (i < 128 ? p.wq : p.wk) : (i < 384 ? p.wq1 : p.wk1);
+            w_smem[i] = src[i & 127];
+        }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) producer(c, p, &tmx, &tmw, smem);
+        if (lane == 0) producer(c, p, &tmx, &tmw, &tmw1, smem);
     } else if (warp == 1) {
         mma_issuer(c, p, smem, tmem);
     } else {
@@ -532,7 +555,7 @@ void gemm_release(void) { g_gemm_configured = 0; }
 static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const uint16_t *W, int ldw, int rows, int in,
                          int out, int heads, const float *wq, const float *wk, const float *rope_cos,
                          const float *rope_sin, float eps, const ScatterArgs *sc, const char *op,
-                         const F32Out *f32 = NULL, const GluOut *glu = NULL) {
+                         const F32Out *f32 = NULL, const GluOut *glu = NULL, const SecondGroup *g2 = NULL) {
     using namespace gemm;
     if (!require_device(op)) return IRIS_B200_ENODEV;
     if ((!y && !sc && !f32 && !(glu && out == 0)) || (f32 && (!f32->y || f32->ld < out || f32->ld % 4 != 0 || ((uintptr_t)f32->y & 15) != 0 ||
@@ -554,6 +577,11 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         set_error(IRIS_B200_EINVAL, op, "bad gated-linear-unit argument");
         return IRIS_B200_EINVAL;
     }
+    if (g2 && (g2->split < 0 || g2->split > rows || !g2->W || ((uintptr_t)g2->W & 15) != 0 || ((uintptr_t)g2->gate & 15) != 0 ||
+               (heads > 0 && (!g2->wq || !g2->wk)) || sc)) {
+        set_error(IRIS_B200_EINVAL, op, "bad second row group");
+        return IRIS_B200_EINVAL;
+    }
     if (rows == 0) return IRIS_B200_OK;
     if (!g_gemm_configured) {
         if (!cuda_ok(cudaFuncSetAttribute(k_linear_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
@@ -561,10 +589,11 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
             return IRIS_B200_ECUDA;
         g_gemm_configured = 1;
     }
-    CUtensorMap tmx, tmw;
+    CUtensorMap tmx, tmw, tmw1;
     const int w_rows = glu ? out + 2 * glu->cols : out;
     if (!make_tensor_map(&tmx, x, rows, in, ldx, kTileM) ||
-        !make_tensor_map(&tmw, W, w_rows, in, ldw, glu ? kTileN / 2 : kTileN))
+        !make_tensor_map(&tmw, W, w_rows, in, ldw, glu ? kTileN / 2 : kTileN) ||
+        !make_tensor_map(&tmw1, g2 ? g2->W : W, w_rows, in, ldw, glu ? kTileN / 2 : kTileN))
         return IRIS_B200_ECUDA;
     Params p = {};
     p.y = y;
@@ -572,7 +601,12 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
     p.rows = rows;
     p.in = in;
     p.out = out;
-    p.tiles_m = (rows + kTileM - 1) / kTileM;
+    p.split = g2 ? g2->split : rows;
+    p.tiles_m0 = (p.split + kTileM - 1) / kTileM;
+    p.tiles_m = p.tiles_m0 + (rows - p.split + kTileM - 1) / kTileM;
+    p.wq1 = g2 ? g2->wq : wq;
+    p.wk1 = g2 ? g2->wk : wk;
+    p.gate1 = g2 ? g2->gate : (f32 ? f32->gate : NULL);
     p.tiles_n = (out + kTileN - 1) / kTileN;
     p.glu_tile0 = p.tiles_n;
     if (glu) {
@@ -610,7 +644,7 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
     }
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const unsigned grid = (unsigned)(tiles < g.sm_count ? tiles : g.sm_count);
-    k_linear_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmx, tmw, p);
+    k_linear_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmx, tmw, tmw1, p);
     return after_launch(op) ? IRIS_B200_OK : IRIS_B200_ECUDA;
 }
 
@@ -658,6 +692,18 @@ extern "C" int iris_b200_linear_glu(uint16_t *qkv, int ldq, uint16_t *act, int l
     const GluOut glu = {act, lda, mlp};
     return launch_linear(qkv, ldq, x, in, W, in, rows, in, 3 * heads * 128, heads, wq, wk, rope_cos, rope_sin, eps, NULL,
                          "linear_glu", NULL, &glu);
+}
+
+/* The two streams of a double block in one launch: rows [0, split) against
+ * the first set of weights, rows [split, rows) against the second. */
+int iris_b200::launch_linear_two(const TwoStreamLinear &a) {
+    const SecondGroup g2 = {a.split, a.W[1], a.wq[1], a.wk[1], a.gate[1]};
+    const F32Out f = {a.y32, a.ldy, a.gate[0], 1};
+    const GluOut glu = {a.act, a.lda, a.mlp};
+    const int out = a.y32 ? a.out : 3 * a.heads * 128;
+    return launch_linear(a.y32 ? NULL : a.qkv, a.y32 ? 0 : a.ldy, a.x, a.ldx, a.W[0], a.ldw, a.rows, a.in, out, a.heads, a.wq[0],
+                         a.wk[0], a.rope_cos, a.rope_sin, a.eps, NULL, "linear (two streams)", a.y32 ? &f : NULL,
+                         a.act ? &glu : NULL, &g2);
 }
 
 extern "C" int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W,

@@ -112,6 +112,37 @@ struct GluOut {
     int cols;
 };
 
+/* A second row group of a linear layer: rows [split, rows) use these weights. */
+struct SecondGroup {
+    int split;
+    const uint16_t *W;
+    const float *wq, *wk, *gate;
+};
+
+/* One linear layer over the two streams of a double block (rows [0, split)
+ * text, [split, rows) image; W / wq / wk / gate indexed by stream). Exactly
+ * one kind of output: y32 != NULL: y32 [rows, out] (fp32, row stride ldy) +=
+ * gate * product; else qkv [rows, 3 * heads * 128] (row stride ldy) with the
+ * Q/K prologue when heads > 0, and / or act [rows, mlp] (row stride lda) =
+ * silu(gate rows) * up rows when act != NULL. */
+struct TwoStreamLinear {
+    const uint16_t *x;
+    int ldx;
+    const uint16_t *W[2];
+    int ldw;
+    int rows, split, in, out;
+    float *y32;
+    uint16_t *qkv;
+    int ldy;
+    uint16_t *act;
+    int lda, mlp;
+    int heads;
+    const float *wq[2], *wk[2], *gate[2];
+    const float *rope_cos, *rope_sin;
+    float eps;
+};
+int launch_linear_two(const TwoStreamLinear &a);
+
 /* Host-side fault injection: the next launch that splits its keys finds a
  * ticket that nobody took. */
 void sm100_inject_stale_ticket(void);
