@@ -27,6 +27,8 @@
  * swizzled staging area so that global memory sees whole 128-byte segments).
  * Waits are bounded like those of the attention kernel.
  */
+#include <stdlib.h>
+
 #include "common.cuh"
 
 #include <cuda.h>
@@ -106,6 +108,14 @@ struct Params {
      * group are computed and not stored. split == rows: one group. */
     int split, tiles_m0;
     const float *wq1, *wk1, *gate1;
+    /* Order of the work list: column tiles are taken in bands of band_n; inside
+     * a band the tiles of one row tile are adjacent. The CTAs of the grid work
+     * on ~148 consecutive tiles at a time, i.e. on 148 / band_n row tiles x
+     * band_n column tiles, whose operands (A: 128 x in, W: 256 x in per tile)
+     * should fit L2 together. band_n == 1: all row tiles of a column tile are
+     * adjacent (small x, the input projections); band_n == tiles_n: all column
+     * tiles of a row tile are adjacent (large x and in, the output projections). */
+    int band_n;
     int nranks;
     int row_first[kMaxScatterRanks + 1];    /* rank q owns the rows [row_first[q], row_first[q + 1]) */
     float *slab[kMaxScatterRanks];          /* where this rank's partial rows of owner q go ([rows of q, out] fp32) */
@@ -121,6 +131,16 @@ struct RowTile {
 __device__ __forceinline__ RowTile row_tile(const Params &p, int tm) {
     if (tm < p.tiles_m0) return {tm * kTileM, p.split, 0};
     return {p.split + (tm - p.tiles_m0) * kTileM, p.rows, 1};
+}
+
+/* Work item `tile` of the list: its row tile and its column tile. */
+__device__ __forceinline__ void tile_of(const Params &p, int tile, int *tm, int *nt) {
+    const int per_band = p.tiles_m * p.band_n;
+    const int band = tile / per_band, rem = tile - band * per_band;
+    const int left = p.tiles_n - band * p.band_n;
+    const int width = left < p.band_n ? left : p.band_n;
+    *tm = rem / width;
+    *nt = band * p.band_n + rem - *tm * width;
 }
 
 struct Ctx {
@@ -157,8 +177,10 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
     int issued = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.tiles_m * p.tiles_n; tile += gridDim.x) {
-        const RowTile rt = row_tile(p, tile % p.tiles_m);
-        const int m0 = rt.m0, nt = tile / p.tiles_m;
+        int tm, nt;
+        tile_of(p, tile, &tm, &nt);
+        const RowTile rt = row_tile(p, tm);
+        const int m0 = rt.m0;
         const CUtensorMap *tmw = rt.grp ? tmw1 : tmw0;
         const bool halves = p.glu_tile0 < p.tiles_n;           /* W comes in two boxes of 128 rows */
         int n0 = nt * kTileN, n1 = n0 + kTileN / 2;
@@ -305,15 +327,16 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
     unsigned char *stage_w = stage + quarter * 4096;
     for (int tile = blockIdx.x, n = 0; tile < p.tiles_m * p.tiles_n; tile += gridDim.x, n++) {
         const int buf = n & 1;
-        const RowTile rt = row_tile(p, tile % p.tiles_m);
-        const int m0 = rt.m0, n0 = (tile / p.tiles_m) * kTileN;     /* n0: ordinary tiles only */
+        int tm, nt;
+        tile_of(p, tile, &tm, &nt);
+        const RowTile rt = row_tile(p, tm);
+        const int m0 = rt.m0, n0 = nt * kTileN;     /* n0: ordinary tiles only */
         if (!__all_sync(0xffffffffu, wait(c, BAR_ACC_FULL + buf, (n >> 1) & 1u, 430 + buf))) return;
         tc_fence_after();
         const int row = m0 + row_in_tile;
         const int wrow0 = m0 + quarter * 32;
         const int nrows = rt.row_end - wrow0 < 32 ? (rt.row_end - wrow0 < 0 ? 0 : rt.row_end - wrow0) : 32;
         const bool row_ok = row < rt.row_end;
-        const int nt = tile / p.tiles_m;
         if (nt >= p.glu_tile0) {
             const int cbase = (nt - p.glu_tile0) * (kTileN / 2);            /* column of y2 */
 #pragma unroll 1
@@ -641,6 +664,21 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         p.ld32 = f32->ld;
         p.accumulate = f32->accumulate;
         p.gate = f32->gate;
+    }
+    /* m-fastest order keeps every row tile of x plus ~4 column tiles of W in
+     * flight; when that does not fit L2 comfortably, go through the columns of
+     * a row tile first (all of W, a twelfth of x in flight). */
+    {
+        const double a_tile = (double)kTileM * in * 2, w_tile = (double)kTileN * in * 2;
+        const double m_fast = p.tiles_m * a_tile + ((double)g.sm_count / p.tiles_m + 1) * w_tile;
+        p.band_n = 1;
+        if (m_fast > 96e6 && p.tiles_n * w_tile < m_fast) p.band_n = p.tiles_n;
+#ifdef IRIS_B200_TUNE
+        if (const char *e = getenv("IRIS_B200_BAND_N")) {
+            const int v = atoi(e);
+            if (v > 0) p.band_n = v < p.tiles_n ? v : p.tiles_n;
+        }
+#endif
     }
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const unsigned grid = (unsigned)(tiles < g.sm_count ? tiles : g.sm_count);
