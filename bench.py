@@ -951,7 +951,14 @@ def run_b200(args):
             one_gpu = job.max_over_ranks([one_gpu or 0.0])[0]
             speedup = one_gpu / ms_step
             if groups > 1:
-                # the same workload as ONE ring over all ranks, every rank holding all heads
+                # other splits of the same workload: more head groups (shorter rings), then ONE ring over
+                # all ranks with every rank holding all heads
+                for g2 in (4,):
+                    if g2 != groups and world % g2 == 0 and world // g2 >= 2 and H % g2 == 0:
+                        job.ring_destroy()
+                        job.ring_init(args.ring_parts, g2)
+                        extras[name + " %d head groups x rings of %d" % (g2, world // g2)] = extra_run(
+                            job, name, "ring", args.steps, args.warmup, pk, groups=g2)
                 job.ring_destroy()
                 job.ring_init(args.ring_parts, 1)
                 extras[name + " one ring, all heads per rank"] = extra_run(job, name, "ring", args.steps, args.warmup, pk)

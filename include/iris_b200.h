@@ -163,6 +163,17 @@ int iris_b200_linear_glu(uint16_t *qkv, int ldq, uint16_t *act, int lda,
                          const float *wq, const float *wk,
                          const float *rope_cos, const float *rope_sin, float eps);
 
+/* How a linear-layer launch cuts its work, as host arithmetic (for schedulers
+ * and tests; nothing is launched): rows [0, split) and [split, rows) are the
+ * two row groups (split == rows: one), `out` ordinary output columns followed
+ * by glu_cols gate|up column pairs. Returns the number of 128 x 256 tiles, or
+ * -1 for bad arguments, and writes the tile counts and the column-band width
+ * of the work list. order (may be NULL): for the first `cap` work items, in
+ * the order the persistent grid takes them, {first row, end of the row group,
+ * column tile, 1 if a gate|up tile}. */
+int iris_b200_linear_plan(int rows, int split, int in, int out, int glu_cols, int sm_count,
+                          int *tiles_m, int *tiles_n, int *band_n, int *order, int cap);
+
 /* The output projection with the gated residual as its epilogue: the
  * reference's iris_dev_linear_f32 followed by iris_dev_residual
  * (iris_transformer_flux.c:3843-3844 single blocks, :3809-3811 and :3821-3822

@@ -128,13 +128,13 @@ struct Params {
 struct RowTile {
     int m0, row_end, grp;
 };
-__device__ __forceinline__ RowTile row_tile(const Params &p, int tm) {
+__host__ __device__ __forceinline__ RowTile row_tile(const Params &p, int tm) {
     if (tm < p.tiles_m0) return {tm * kTileM, p.split, 0};
     return {p.split + (tm - p.tiles_m0) * kTileM, p.rows, 1};
 }
 
 /* Work item `tile` of the list: its row tile and its column tile. */
-__device__ __forceinline__ void tile_of(const Params &p, int tile, int *tm, int *nt) {
+__host__ __device__ __forceinline__ void tile_of(const Params &p, int tile, int *tm, int *nt) {
     const int per_band = p.tiles_m * p.band_n;
     const int band = tile / per_band, rem = tile - band * per_band;
     const int left = p.tiles_n - band * p.band_n;
@@ -569,6 +569,31 @@ __global__ void k_residual_from_slabs(float *x, const float *slabs, size_t slab_
 
 }  // namespace gemm
 
+/* The tile grid of a launch: row tiles per row group, column tiles (ordinary
+ * ones, then the gate|up pairs), and the order of the work list. m-fastest
+ * order keeps every row tile of x plus a few column tiles of W in flight;
+ * when that does not fit L2 comfortably and all of W is smaller, the list goes
+ * through the columns of a row tile first (all of W and 1/tiles_n of the
+ * concurrently processed x in flight). */
+static void plan_grid(gemm::Params *p, int rows, int split, int in, int out, int glu_cols, int sm_count) {
+    using namespace gemm;
+    p->rows = rows;
+    p->in = in;
+    p->out = out;
+    p->split = split;
+    p->tiles_m0 = (split + kTileM - 1) / kTileM;
+    p->tiles_m = p->tiles_m0 + (rows - split + kTileM - 1) / kTileM;
+    p->tiles_n = (out + kTileN - 1) / kTileN;
+    p->glu_tile0 = p->tiles_n;
+    p->glu_col0 = out;
+    p->glu_cols = glu_cols;
+    p->tiles_n += (glu_cols + kTileN / 2 - 1) / (kTileN / 2);
+    const double a_tile = (double)kTileM * in * 2, w_tile = (double)kTileN * in * 2;
+    const double m_fast = p->tiles_m * a_tile + ((double)sm_count / (p->tiles_m > 0 ? p->tiles_m : 1) + 1) * w_tile;
+    p->band_n = 1;
+    if (m_fast > 96e6 && p->tiles_n * w_tile < m_fast) p->band_n = p->tiles_n;
+}
+
 static int g_gemm_configured = 0;
 
 void gemm_release(void) { g_gemm_configured = 0; }
@@ -624,20 +649,13 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
     p.rows = rows;
     p.in = in;
     p.out = out;
-    p.split = g2 ? g2->split : rows;
-    p.tiles_m0 = (p.split + kTileM - 1) / kTileM;
-    p.tiles_m = p.tiles_m0 + (rows - p.split + kTileM - 1) / kTileM;
+    plan_grid(&p, rows, g2 ? g2->split : rows, in, out, glu ? glu->cols : 0, g.sm_count);
     p.wq1 = g2 ? g2->wq : wq;
     p.wk1 = g2 ? g2->wk : wk;
     p.gate1 = g2 ? g2->gate : (f32 ? f32->gate : NULL);
-    p.tiles_n = (out + kTileN - 1) / kTileN;
-    p.glu_tile0 = p.tiles_n;
     if (glu) {
-        p.glu_col0 = out;
-        p.glu_cols = glu->cols;
         p.y2 = glu->y;
         p.ldy2 = glu->ld;
-        p.tiles_n += (glu->cols + kTileN / 2 - 1) / (kTileN / 2);
     }
     p.norm_cols = heads * 128;
     p.wq = wq;
@@ -665,21 +683,12 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         p.accumulate = f32->accumulate;
         p.gate = f32->gate;
     }
-    /* m-fastest order keeps every row tile of x plus ~4 column tiles of W in
-     * flight; when that does not fit L2 comfortably, go through the columns of
-     * a row tile first (all of W, a twelfth of x in flight). */
-    {
-        const double a_tile = (double)kTileM * in * 2, w_tile = (double)kTileN * in * 2;
-        const double m_fast = p.tiles_m * a_tile + ((double)g.sm_count / p.tiles_m + 1) * w_tile;
-        p.band_n = 1;
-        if (m_fast > 96e6 && p.tiles_n * w_tile < m_fast) p.band_n = p.tiles_n;
 #ifdef IRIS_B200_TUNE
-        if (const char *e = getenv("IRIS_B200_BAND_N")) {
-            const int v = atoi(e);
-            if (v > 0) p.band_n = v < p.tiles_n ? v : p.tiles_n;
-        }
-#endif
+    if (const char *e = getenv("IRIS_B200_BAND_N")) {
+        const int v = atoi(e);
+        if (v > 0) p.band_n = v < p.tiles_n ? v : p.tiles_n;
     }
+#endif
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const unsigned grid = (unsigned)(tiles < g.sm_count ? tiles : g.sm_count);
     k_linear_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmx, tmw, tmw1, p);
@@ -742,6 +751,31 @@ int iris_b200::launch_linear_two(const TwoStreamLinear &a) {
     return launch_linear(a.y32 ? NULL : a.qkv, a.y32 ? 0 : a.ldy, a.x, a.ldx, a.W[0], a.ldw, a.rows, a.in, out, a.heads, a.wq[0],
                          a.wk[0], a.rope_cos, a.rope_sin, a.eps, NULL, "linear (two streams)", a.y32 ? &f : NULL,
                          a.act ? &glu : NULL, &g2);
+}
+
+extern "C" int iris_b200_linear_plan(int rows, int split, int in, int out, int glu_cols, int sm_count, int *tiles_m,
+                                     int *tiles_n, int *band_n, int *order, int cap) {
+    if (rows < 0 || split < 0 || split > rows || in <= 0 || out < 0 || glu_cols < 0 || sm_count <= 0 || !tiles_m || !tiles_n ||
+        !band_n)
+        return -1;
+    gemm::Params p = {};
+    plan_grid(&p, rows, split, in, out, glu_cols, sm_count);
+    *tiles_m = p.tiles_m;
+    *tiles_n = p.tiles_n;
+    *band_n = p.band_n;
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    if (order) {
+        for (long long t = 0; t < tiles && t < cap; t++) {
+            int tm, nt;
+            gemm::tile_of(p, (int)t, &tm, &nt);
+            const gemm::RowTile rt = gemm::row_tile(p, tm);
+            order[4 * t] = rt.m0;
+            order[4 * t + 1] = rt.row_end;
+            order[4 * t + 2] = nt;
+            order[4 * t + 3] = nt >= p.glu_tile0;
+        }
+    }
+    return tiles > 0x7fffffff ? -1 : (int)tiles;
 }
 
 extern "C" int iris_b200_linear_qk_norm_rope(uint16_t *y, int ldy, const uint16_t *x, const uint16_t *W,

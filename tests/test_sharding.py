@@ -287,3 +287,52 @@ def test_ring_launch_plan(lib, G):
                     own_tiles = -(-rows_of[rank] // 128)
                     want = 0 if f == 0 else own_tiles + (int(first_row[f]) - rows_of[rank]) // 128
                     assert t[i] == want
+
+
+# ---------------------------------------------------------------------------
+# work list of a linear-layer launch (host arithmetic shared with the launcher)
+# ---------------------------------------------------------------------------
+
+def linear_plan(lib, rows, split, cin, out, glu_cols, sms=148):
+    tm, tn, band = C.c_int(), C.c_int(), C.c_int()
+    n = lib.iris_b200_linear_plan(rows, split, cin, out, glu_cols, sms, C.byref(tm), C.byref(tn), C.byref(band), None, 0)
+    assert n == tm.value * tn.value
+    order = np.zeros((n, 4), np.int32)
+    assert lib.iris_b200_linear_plan(rows, split, cin, out, glu_cols, sms, C.byref(tm), C.byref(tn), C.byref(band),
+                                     order.ctypes.data, n) == n
+    return tm.value, tn.value, band.value, order
+
+
+@pytest.mark.parametrize("rows,split,cin,out,glu", [(4608, 4608, 3072, 9216, 9216), (4608, 512, 3072, 9216, 0),
+                                                    (4608, 4608, 12288, 3072, 0), (4608, 512, 9216, 3072, 0),
+                                                    (300, 77, 256, 0, 200), (129, 0, 64, 264, 0), (5, 5, 64, 8, 0)])
+def test_linear_work_list_covers_every_tile_once(lib, rows, split, cin, out, glu):
+    tm, tn, band, order = linear_plan(lib, rows, split, cin, out, glu)
+    assert tm == -(-split // 128) + -(-(rows - split) // 128)
+    assert tn == -(-out // 256) + -(-glu // 128)
+    assert 1 <= band <= max(tn, 1)
+    seen = set()
+    for m0, row_end, nt, is_glu in order:
+        assert (m0, nt) not in seen
+        seen.add((int(m0), int(nt)))
+        # a row tile stays inside its row group
+        assert (m0 < split and row_end == split) or (m0 >= split and row_end == rows)
+        assert m0 < row_end and (m0 - (0 if m0 < split else split)) % 128 == 0
+        assert bool(is_glu) == (nt >= -(-out // 256))
+    assert len(seen) == tm * tn
+    # every row is covered by exactly one row tile
+    firsts = sorted({m for m, _ in seen})
+    covered = sum(min(128, (split if m < split else rows) - m) for m in firsts)
+    assert covered == rows
+
+
+def test_linear_work_list_order_follows_the_l2_working_set(lib):
+    """Small x (the input projections): all row tiles of a column tile are
+    adjacent. Large x and long rows (the output projection of a single block:
+    113 MB of activations, 75 MB of weights): all column tiles of a row tile
+    are adjacent, so that the ~148 tiles in flight share 12 row tiles."""
+    _, tn, band, order = linear_plan(lib, 4608, 4608, 3072, 9216, 9216)
+    assert band == 1 and (order[:36, 2] == 0).all() and len(set(order[:36, 0])) == 36
+    _, tn, band, order = linear_plan(lib, 4608, 4608, 12288, 3072, 0)
+    assert band == tn == 12 and (order[:12, 0] == 0).all() and sorted(order[:12, 2]) == list(range(12))
+    assert lib.iris_b200_linear_plan(10, 11, 64, 8, 0, 148, None, None, None, None, 0) == -1
