@@ -208,6 +208,30 @@ int iris_b200_single_block(float *x, void *scratch,
                            const float *rope_cos, const float *rope_sin,
                            int seq, int dim, int heads, int mlp, const int *key_mask);
 
+/* A run of consecutive rows that share one modulation vector mod [3 dim] =
+ * shift | scale | gate: the reference's f3_segment_t
+ * (iris_transformer_flux3.c:118-121). */
+typedef struct iris_b200_segment {
+    int start, len;
+    const float *mod;
+} iris_b200_segment;
+
+/* iris_b200_single_block with the rows in up to four segments, each with its
+ * own modulation, and the norm epsilon as an argument: one FLUX.3 block as the
+ * reference's dev_block_forward issues it (iris_transformer_flux3.c:680-703;
+ * CPU form block_forward, :371-417), where text, image and reference-image rows
+ * are modulated separately but share the weights. The segments must follow
+ * one another and cover [0, seq). The gate of the residual is picked per row
+ * inside the output projection's epilogue; LayerNorm picks shift and scale per
+ * row. Four launches, like the single block. */
+int iris_b200_single_block_segments(float *x, void *scratch,
+                                    const uint16_t *w_in, const uint16_t *w_out,
+                                    const float *norm_q, const float *norm_k,
+                                    const iris_b200_segment *segs, int nsegs,
+                                    const float *rope_cos, const float *rope_sin,
+                                    int seq, int dim, int heads, int mlp, float eps,
+                                    const int *key_mask);
+
 /* ---- one double-stream block --------------------------------------------- */
 
 /* The weights of one stream (text or image) of a double block, bf16 as the

@@ -61,6 +61,7 @@ SIGNATURES = {
     "iris_b200_linear_residual": (INT, [VP, INT, VP, INT, VP, INT, VP, INT, INT, INT]),
     "iris_b200_single_block_scratch_bytes": (SZ, [INT, INT, INT]),
     "iris_b200_single_block": (INT, [VP, VP, VP, VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, VP]),
+    "iris_b200_single_block_segments": (INT, [VP, VP, VP, VP, VP, VP, VP, INT, VP, VP, INT, INT, INT, INT, FLT, VP]),
     "iris_b200_double_block_scratch_bytes": (SZ, [INT, INT, INT]),
     "iris_b200_double_block": (INT, [VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, INT, VP]),
     "iris_b200_attention_ex": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP, INT]),
@@ -109,6 +110,11 @@ KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_GENERIC = 0, 1, 2
 class LoopFault(C.Structure):
     """iris_b200_loop_fault of include/iris_b200.h."""
     _fields_ = [("kind", INT), ("rank", INT), ("call", INT), ("step", INT), ("delay_us", C.c_uint)]
+
+
+class Segment(C.Structure):
+    """iris_b200_segment of include/iris_b200.h."""
+    _fields_ = [("start", INT), ("len", INT), ("mod", VP)]
 
 
 class StreamWeights(C.Structure):

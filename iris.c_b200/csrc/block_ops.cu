@@ -32,6 +32,22 @@ namespace iris_b200 {
 namespace {
 
 constexpr int kRowThreads = 256;
+constexpr int kMaxSegments = 4;
+
+/* Modulation by runs of rows: rows below end[i] (and not below end[i - 1])
+ * take shift[i] / scale[i] (either may be NULL). */
+struct RowMods {
+    int n;
+    int end[kMaxSegments];
+    const float *shift[kMaxSegments];
+    const float *scale[kMaxSegments];
+};
+
+__device__ __forceinline__ int segment_of(const RowMods &m, int row) {
+    int i = 0;
+    while (i + 1 < m.n && row >= m.end[i]) i++;
+    return i;
+}
 
 __device__ __forceinline__ float block_sum(float v, float *sh) {
 #pragma unroll
@@ -52,9 +68,8 @@ __device__ __forceinline__ float block_sum(float v, float *sh) {
  * reference. */
 template <int VPL>
 __global__ void __launch_bounds__(kRowThreads)
-k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift0,
-                      const float *__restrict__ scale0, const float *__restrict__ shift1,
-                      const float *__restrict__ scale1, int split, int rows, int dim, float eps) {
+k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, const __grid_constant__ RowMods mods, int rows,
+                      int dim, float eps) {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * kRowThreads) >> 5;
     const int nvec = dim >> 2;
@@ -62,7 +77,8 @@ k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, c
     for (int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5; row < rows; row += warps) {
         const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * dim);
         uint2 *o = reinterpret_cast<uint2 *>(out + (size_t)row * dim);
-        const float *shift = row < split ? shift0 : shift1, *scale = row < split ? scale0 : scale1;
+        const int seg = segment_of(mods, row);
+        const float *shift = mods.shift[seg], *scale = mods.scale[seg];
         float4 v[VPL];
         float s = 0.0f;
 #pragma unroll
@@ -106,15 +122,15 @@ k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, c
 /* Any other row length: one block per row at a time, the row re-read from
  * L1 / L2 for each pass. */
 __global__ void __launch_bounds__(kRowThreads)
-k_layer_norm_mod_any(uint16_t *__restrict__ out, const float *__restrict__ x, const float *__restrict__ shift0,
-                     const float *__restrict__ scale0, const float *__restrict__ shift1,
-                     const float *__restrict__ scale1, int split, int rows, int dim, float eps) {
+k_layer_norm_mod_any(uint16_t *__restrict__ out, const float *__restrict__ x, const __grid_constant__ RowMods mods, int rows,
+                     int dim, float eps) {
     __shared__ float sh[kRowThreads / 32];
     const float inv_dim = 1.0f / (float)dim;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float *xr = x + (size_t)row * dim;
         uint16_t *o = out + (size_t)row * dim;
-        const float *shift = row < split ? shift0 : shift1, *scale = row < split ? scale0 : scale1;
+        const int seg = segment_of(mods, row);
+        const float *shift = mods.shift[seg], *scale = mods.scale[seg];
         float s = 0.0f;
         for (int i = threadIdx.x; i < dim; i += kRowThreads) s += xr[i];
         const float mean = block_sum(s, sh) * inv_dim;
@@ -187,36 +203,37 @@ unsigned blocks_for(size_t items, int per_block, int per_sm) {
 
 bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
-/* Rows [0, split) take (shift, scale), rows [split, rows) take (shift1, scale1). */
-int layer_norm_mod2(uint16_t *out, const float *x, const float *shift, const float *scale, const float *shift1,
-                    const float *scale1, int split, int rows, int dim, float eps) {
+int layer_norm_mods(uint16_t *out, const float *x, const RowMods &mods, int rows, int dim, float eps) {
     if (!require_device("layer_norm_mod")) return IRIS_B200_ENODEV;
-    if (!out || !x || rows < 0 || dim <= 0 || split < 0 || split > rows) {
+    if (!out || !x || rows < 0 || dim <= 0 || mods.n < 1 || mods.n > kMaxSegments) {
         set_error(IRIS_B200_EINVAL, "layer_norm_mod", "bad argument");
         return IRIS_B200_EINVAL;
     }
     if (rows == 0) return IRIS_B200_OK;
     const int nvec = dim / 4;
-    const bool vec = dim % 4 == 0 && nvec <= 32 * 32 && aligned16(x) && aligned16(shift) && aligned16(scale) &&
-                     aligned16(shift1) && aligned16(scale1) && ((uintptr_t)out & 7) == 0;
+    bool vec = dim % 4 == 0 && nvec <= 32 * 32 && aligned16(x) && ((uintptr_t)out & 7) == 0;
+    for (int i = 0; i < mods.n; i++) vec = vec && aligned16(mods.shift[i]) && aligned16(mods.scale[i]);
     if (vec) {
         const unsigned grid = blocks_for((size_t)rows, kRowThreads / 32, 8);
-#define IRIS_LN_LAUNCH(VPL) \
-    k_layer_norm_mod_warp<VPL><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, shift1, scale1, split, rows, dim, eps)
+#define IRIS_LN_LAUNCH(VPL) k_layer_norm_mod_warp<VPL><<<grid, kRowThreads, 0, g.stream>>>(out, x, mods, rows, dim, eps)
         if (nvec <= 32 * 8) IRIS_LN_LAUNCH(8);
         else if (nvec <= 32 * 16) IRIS_LN_LAUNCH(16);
         else if (nvec <= 32 * 24) IRIS_LN_LAUNCH(24);
         else IRIS_LN_LAUNCH(32);
 #undef IRIS_LN_LAUNCH
     } else {
-        k_layer_norm_mod_any<<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, x, shift, scale, shift1, scale1,
-                                                                                         split, rows, dim, eps);
+        k_layer_norm_mod_any<<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, x, mods, rows, dim, eps);
     }
     return after_launch("k_layer_norm_mod") ? IRIS_B200_OK : IRIS_B200_ECUDA;
 }
 
 int layer_norm_mod(uint16_t *out, const float *x, const float *shift, const float *scale, int rows, int dim, float eps) {
-    return layer_norm_mod2(out, x, shift, scale, shift, scale, rows, rows, dim, eps);
+    RowMods m = {};
+    m.n = 1;
+    m.end[0] = rows;
+    m.shift[0] = shift;
+    m.scale[0] = scale;
+    return layer_norm_mods(out, x, m, rows, dim, eps);
 }
 
 int swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi, int rows, int cols) {
@@ -276,14 +293,22 @@ extern "C" size_t iris_b200_single_block_scratch_bytes(int seq, int dim, int mlp
     return up256((size_t)seq * dim * 2) + up256((size_t)seq * 3 * dim * 2) + up256((size_t)seq * ((size_t)dim + mlp) * 2);
 }
 
-extern "C" int iris_b200_single_block(float *x, void *scratch, const uint16_t *w_in, const uint16_t *w_out,
-                                      const float *norm_q, const float *norm_k, const float *mod,
-                                      const float *rope_cos, const float *rope_sin, int seq, int dim, int heads,
-                                      int mlp, const int *key_mask) {
+extern "C" int iris_b200_single_block_segments(float *x, void *scratch, const uint16_t *w_in, const uint16_t *w_out,
+                                               const float *norm_q, const float *norm_k, const iris_b200_segment *segs,
+                                               int nsegs, const float *rope_cos, const float *rope_sin, int seq, int dim,
+                                               int heads, int mlp, float eps, const int *key_mask) {
     if (!require_device("single_block")) return IRIS_B200_ENODEV;
-    if (!x || !scratch || !w_in || !w_out || !norm_q || !norm_k || !mod || !rope_cos || !rope_sin || seq < 0 || dim <= 0 ||
-        heads <= 0 || mlp <= 0 || dim != heads * 128 || ((uintptr_t)scratch & 255) != 0) {
-        set_error(IRIS_B200_EINVAL, "single_block", dim != heads * 128 ? "head_dim must be 128" : "bad argument");
+    bool ok = x && scratch && w_in && w_out && norm_q && norm_k && segs && nsegs >= 1 && nsegs <= kMaxSegments && rope_cos &&
+              rope_sin && seq >= 0 && dim > 0 && heads > 0 && mlp > 0 && dim == heads * 128 && ((uintptr_t)scratch & 255) == 0;
+    /* the segments follow one another and cover the rows */
+    int next = 0;
+    for (int i = 0; ok && i < nsegs; i++) {
+        ok = segs[i].start == next && segs[i].len >= 0 && segs[i].mod;
+        next += segs[i].len;
+    }
+    if (!ok || next != seq) {
+        set_error(IRIS_B200_EINVAL, "single_block",
+                  dim > 0 && dim != heads * 128 ? "head_dim must be 128" : "bad argument, or segments that do not tile the rows");
         return IRIS_B200_EINVAL;
     }
     if (seq == 0) return IRIS_B200_OK;
@@ -293,8 +318,17 @@ extern "C" int iris_b200_single_block(float *x, void *scratch, const uint16_t *w
     uint16_t *norm = reinterpret_cast<uint16_t *>(base);
     uint16_t *qkv = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2));
     uint16_t *cat = reinterpret_cast<uint16_t *>(base + up256((size_t)seq * dim * 2) + up256((size_t)seq * 3 * dim * 2));
-    const float eps = 1e-6f;
-    int rc = layer_norm_mod(norm, x, mod, mod + dim, seq, dim, eps);
+    RowMods mods = {};
+    int seg_end[kMaxSegments];
+    const float *seg_gate[kMaxSegments];
+    mods.n = nsegs;
+    for (int i = 0; i < nsegs; i++) {
+        mods.end[i] = seg_end[i] = segs[i].start + segs[i].len;
+        mods.shift[i] = segs[i].mod;
+        mods.scale[i] = segs[i].mod + dim;
+        seg_gate[i] = segs[i].mod + 2 * dim;
+    }
+    int rc = layer_norm_mods(norm, x, mods, seq, dim, eps);
     if (rc != IRIS_B200_OK) return rc;
     /* Q, K (normalised, rotated) and V to qkv; silu(gate) * up straight into the MLP half of cat */
     rc = iris_b200_linear_glu(qkv, 3 * dim, cat + dim, ldc, norm, w_in, seq, dim, heads, mlp, norm_q, norm_k, rope_cos,
@@ -305,7 +339,16 @@ extern "C" int iris_b200_single_block(float *x, void *scratch, const uint16_t *w
                        key_mask);
     rc = iris_b200_last_error();
     if (rc != IRIS_B200_OK) return rc;
-    return iris_b200_linear_residual(x, dim, cat, ldc, w_out, ldc, mod + 2 * dim, seq, ldc, dim);
+    return launch_linear_residual_segments(x, dim, cat, ldc, w_out, ldc, seg_end, seg_gate, nsegs, seq, ldc, dim);
+}
+
+extern "C" int iris_b200_single_block(float *x, void *scratch, const uint16_t *w_in, const uint16_t *w_out,
+                                      const float *norm_q, const float *norm_k, const float *mod,
+                                      const float *rope_cos, const float *rope_sin, int seq, int dim, int heads,
+                                      int mlp, const int *key_mask) {
+    const iris_b200_segment all = {0, seq, mod};
+    return iris_b200_single_block_segments(x, scratch, w_in, w_out, norm_q, norm_k, mod ? &all : NULL, 1, rope_cos, rope_sin,
+                                           seq, dim, heads, mlp, 1e-6f, key_mask);
 }
 
 /* norm [seq, dim] | qkv [seq, 3 dim] | cat [seq, max(dim, mlp)], bf16 */
@@ -340,7 +383,15 @@ extern "C" int iris_b200_double_block(float *x, void *scratch, const iris_b200_s
     const float *tm = txt->mod, *im = img->mod;
     int rc;
     /* attention half: both streams in every launch, text rows first */
-    if ((rc = layer_norm_mod2(norm, x, tm, tm + dim, im, im + dim, txt_seq, seq, dim, eps))) return rc;
+    RowMods m1 = {};
+    m1.n = 2;
+    m1.end[0] = txt_seq;
+    m1.end[1] = seq;
+    m1.shift[0] = tm;
+    m1.scale[0] = tm + dim;
+    m1.shift[1] = im;
+    m1.scale[1] = im + dim;
+    if ((rc = layer_norm_mods(norm, x, m1, seq, dim, eps))) return rc;
     TwoStreamLinear l = {};
     l.x = norm;
     l.ldx = l.ldw = l.in = dim;
@@ -377,7 +428,12 @@ extern "C" int iris_b200_double_block(float *x, void *scratch, const iris_b200_s
     o.gate[1] = im + 2 * dim;
     if ((rc = launch_linear_two(o))) return rc;
     /* feed-forward half: the gate | up projection stores silu(gate) * up */
-    if ((rc = layer_norm_mod2(norm, x, tm + 3 * dim, tm + 4 * dim, im + 3 * dim, im + 4 * dim, txt_seq, seq, dim, eps))) return rc;
+    RowMods m2 = m1;
+    m2.shift[0] = tm + 3 * dim;
+    m2.scale[0] = tm + 4 * dim;
+    m2.shift[1] = im + 3 * dim;
+    m2.scale[1] = im + 4 * dim;
+    if ((rc = layer_norm_mods(norm, x, m2, seq, dim, eps))) return rc;
     TwoStreamLinear f = {};
     f.x = norm;
     f.ldx = f.ldw = f.in = dim;

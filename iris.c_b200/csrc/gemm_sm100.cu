@@ -65,6 +65,7 @@ enum {
 static constexpr int kSmemTmemPtr = BAR_COUNT * 8;
 static constexpr int kSmemAbort = kSmemTmemPtr + 4;
 static constexpr int kMaxScatterRanks = 16;
+static constexpr int kMaxSegments = 4;
 
 struct Params {
     uint16_t *y;
@@ -108,6 +109,13 @@ struct Params {
      * group are computed and not stored. split == rows: one group. */
     int split, tiles_m0;
     const float *wq1, *wk1, *gate1;
+    /* Gates by runs of rows that share the weights (the segments of a FLUX.3
+     * block: text, image, reference rows, each with its own modulation):
+     * rows below seg_end[i] (and not below seg_end[i - 1]) take seg_gate[i].
+     * nseg == 0: the row group's gate. */
+    int nseg;
+    int seg_end[kMaxSegments];
+    const float *seg_gate[kMaxSegments];
     /* Order of the work list: column tiles are taken in bands of band_n; inside
      * a band the tiles of one row tile are adjacent. The CTAs of the grid work
      * on ~148 consecutive tiles at a time, i.e. on 148 / band_n row tiles x
@@ -300,13 +308,20 @@ __device__ __forceinline__ void rows_f32(const uint32_t *src, const Params &p, c
             make_uint4(src[4 * c8], src[4 * c8 + 1], src[4 * c8 + 2], src[4 * c8 + 3]);
     __syncwarp();
     const int ch = lane & 7;
+    const bool col_ok = ch * 4 < ncols;
     float4 g4 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-    if (gate && ch * 4 < ncols) g4 = *reinterpret_cast<const float4 *>(gate + c0 + ch * 4);
+    if (gate && col_ok && p.nseg == 0) g4 = *reinterpret_cast<const float4 *>(gate + c0 + ch * 4);
 #pragma unroll
     for (int k = 0; k < 8; k++) {
         const int r = k * 4 + (lane >> 3);
         float4 v = *reinterpret_cast<const float4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4));
-        if (r < nrows && ch * 4 < ncols) {
+        if (r < nrows && col_ok) {
+            if (p.nseg > 0) {
+                int i = 0;
+                while (i + 1 < p.nseg && wrow0 + r >= p.seg_end[i]) i++;
+                const float *gs = p.seg_gate[i];
+                g4 = gs ? *reinterpret_cast<const float4 *>(gs + c0 + ch * 4) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+            }
             float4 *dst = reinterpret_cast<float4 *>(p.y32 + (size_t)(wrow0 + r) * p.ld32 + c0 + ch * 4);
             if (p.accumulate) {
                 const float4 x = *dst;
@@ -607,7 +622,8 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
     using namespace gemm;
     if (!require_device(op)) return IRIS_B200_ENODEV;
     if ((!y && !sc && !f32 && !(glu && out == 0)) || (f32 && (!f32->y || f32->ld < out || f32->ld % 4 != 0 || ((uintptr_t)f32->y & 15) != 0 ||
-                                        ((uintptr_t)f32->gate & 15) != 0 || sc || heads > 0)) ||
+                                        ((uintptr_t)f32->gate & 15) != 0 || f32->nseg < 0 || f32->nseg > kMaxSegments ||
+                                        sc || heads > 0)) ||
         !x || !W || rows < 0 || in <= 0 || out < 0 || (out == 0 && !glu) || (y && ldy < out) || heads < 0 || ldx < in || ldw < in ||
         (heads > 0 && (!wq || !wk || !rope_cos || !rope_sin || 2 * heads * 128 > out)) ||
         (sc && (sc->nranks < 1 || sc->nranks > kMaxScatterRanks))) {
@@ -682,6 +698,11 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         p.ld32 = f32->ld;
         p.accumulate = f32->accumulate;
         p.gate = f32->gate;
+        p.nseg = f32->nseg;
+        for (int i = 0; i < f32->nseg; i++) {
+            p.seg_end[i] = f32->seg_end[i];
+            p.seg_gate[i] = f32->seg_gate[i];
+        }
     }
 #ifdef IRIS_B200_TUNE
     if (const char *e = getenv("IRIS_B200_BAND_N")) {
@@ -722,15 +743,45 @@ extern "C" void iris_dev_linear_bf16(uint16_t *y, const uint16_t *x, const uint1
 /* Same arithmetic as the reference's iris_dev_linear_f32 (iris_cuda.cu:560-584):
  * bf16 operands, fp32 accumulation, fp32 result. */
 extern "C" void iris_dev_linear_f32(float *y, const uint16_t *x, const uint16_t *W, int rows, int in, int out) {
-    const F32Out f = {y, out, NULL, 0};
+    F32Out f = {};
+    f.y = y;
+    f.ld = out;
     launch_linear(NULL, 0, x, in, W, in, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_f32", &f);
 }
 
 extern "C" int iris_b200_linear_residual(float *x_rows, int ldx, const uint16_t *a, int lda, const uint16_t *W, int ldw,
                                          const float *gate, int rows, int in, int out) {
-    const F32Out f = {x_rows, ldx, gate, 1};
+    F32Out f = {};
+    f.y = x_rows;
+    f.ld = ldx;
+    f.gate = gate;
+    f.accumulate = 1;
     return launch_linear(NULL, 0, a, lda, W, ldw, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_residual",
                          &f);
+}
+
+/* iris_b200_linear_residual with one gate per run of rows (a gate may be NULL: 1). */
+int iris_b200::launch_linear_residual_segments(float *x_rows, int ldx, const uint16_t *a, int lda, const uint16_t *W, int ldw,
+                                               const int *seg_end, const float *const *seg_gate, int nseg, int rows, int in,
+                                               int out) {
+    F32Out f = {};
+    f.y = x_rows;
+    f.ld = ldx;
+    f.accumulate = 1;
+    if (nseg < 1 || nseg > gemm::kMaxSegments) {
+        set_error(IRIS_B200_EINVAL, "linear_residual", "1 to 4 segments");
+        return IRIS_B200_EINVAL;
+    }
+    f.nseg = nseg;
+    for (int i = 0; i < nseg; i++) {
+        f.seg_end[i] = seg_end[i];
+        f.seg_gate[i] = seg_gate[i];
+        if (((uintptr_t)seg_gate[i] & 15) != 0) {
+            set_error(IRIS_B200_EUNSUPPORTED, "linear_residual", "gates must be 16-byte aligned");
+            return IRIS_B200_EUNSUPPORTED;
+        }
+    }
+    return launch_linear(NULL, 0, a, lda, W, ldw, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_residual", &f);
 }
 
 extern "C" int iris_b200_linear_glu(uint16_t *qkv, int ldq, uint16_t *act, int lda, const uint16_t *x, const uint16_t *W,
@@ -745,7 +796,11 @@ extern "C" int iris_b200_linear_glu(uint16_t *qkv, int ldq, uint16_t *act, int l
  * the first set of weights, rows [split, rows) against the second. */
 int iris_b200::launch_linear_two(const TwoStreamLinear &a) {
     const SecondGroup g2 = {a.split, a.W[1], a.wq[1], a.wk[1], a.gate[1]};
-    const F32Out f = {a.y32, a.ldy, a.gate[0], 1};
+    F32Out f = {};
+    f.y = a.y32;
+    f.ld = a.ldy;
+    f.gate = a.gate[0];
+    f.accumulate = 1;
     const GluOut glu = {a.act, a.lda, a.mlp};
     const int out = a.y32 ? a.out : 3 * a.heads * 128;
     return launch_linear(a.y32 ? NULL : a.qkv, a.y32 ? 0 : a.ldy, a.x, a.ldx, a.W[0], a.ldw, a.rows, a.in, out, a.heads, a.wq[0],

@@ -101,7 +101,14 @@ struct F32Out {
     int ld;
     const float *gate;
     int accumulate;
+    /* nseg > 0: one gate per run of rows instead (rows below seg_end[i] and
+     * not below seg_end[i - 1] take seg_gate[i]; NULL: 1). */
+    int nseg;
+    int seg_end[4];
+    const float *seg_gate[4];
 };
+int launch_linear_residual_segments(float *x_rows, int ldx, const uint16_t *a, int lda, const uint16_t *W, int ldw,
+                                    const int *seg_end, const float *const *seg_gate, int nseg, int rows, int in, int out);
 
 /* Gated-linear-unit destination of a linear layer: the last 2 * cols rows of W
  * are `cols` gate rows then `cols` up rows; y [rows, cols] (bf16, row stride

@@ -568,15 +568,17 @@ void orc_linear(float *y, int ldy, const uint16_t *x, int ldx, const uint16_t *W
         if (started[t]) pthread_join(th[t], NULL);
 }
 
-/* One single-stream block as the reference's device forward issues it
- * (iris_transformer_flux.c:3828-3845): layer_norm_mod -> linear_bf16 ->
- * head_norm_rope on Q and K -> attention -> swiglu -> linear_f32 -> residual.
- * x [seq, dim] fp32 in place; mod = shift | scale | gate. Returns 0, or -1
- * when memory runs out. */
-int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
-                     const float *norm_q, const float *norm_k, const float *mod,
-                     const float *rope_cos, const float *rope_sin,
-                     int seq, int dim, int heads, int mlp, const int *key_mask, int nthreads) {
+/* One single-stream block as the reference's device forwards issue it
+ * (FLUX.2: iris_transformer_flux.c:3828-3845; FLUX.3, rows in segments with
+ * their own modulation: iris_transformer_flux3.c:680-703): layer_norm_mod per
+ * segment -> linear_bf16 -> head_norm_rope on Q and K -> attention -> swiglu ->
+ * linear_f32 -> residual per segment. x [seq, dim] fp32 in place; seg_mod[i] =
+ * shift | scale | gate of segment i. Returns 0, or -1 when memory runs out. */
+int orc_single_block_segments(float *x, const uint16_t *w_in, const uint16_t *w_out,
+                              const float *norm_q, const float *norm_k,
+                              const int *seg_start, const int *seg_len, const float *const *seg_mod, int nsegs,
+                              const float *rope_cos, const float *rope_sin,
+                              int seq, int dim, int heads, int mlp, float eps, const int *key_mask, int nthreads) {
     int hd = dim / heads, ldh = 3 * dim + 2 * mlp, ldc = dim + mlp;
     size_t nh = (size_t)seq * ldh, nc = (size_t)seq * ldc, nd = (size_t)seq * dim;
     uint16_t *norm = malloc(nd * 2), *h = malloc(nh * 2), *cat = malloc(nc * 2);
@@ -584,11 +586,14 @@ int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
     float *att = malloc(nd * sizeof(float)), *proj = malloc(nd * sizeof(float));
     int rc = -1;
     if (norm && h && cat && hf && qkv && att && proj) {
-        orc_layer_norm_mod(norm, x, mod, mod + dim, seq, dim, 1e-6f);
+        for (int g = 0; g < nsegs; g++) {
+            size_t off = (size_t)seg_start[g] * dim;
+            orc_layer_norm_mod(norm + off, x + off, seg_mod[g], seg_mod[g] + dim, seg_len[g], dim, eps);
+        }
         orc_linear(hf, ldh, norm, dim, w_in, dim, seq, dim, ldh, nthreads);
         orc_f32_to_bf16(h, hf, nh);
-        orc_head_norm_rope_bf16(h, ldh, norm_q, rope_cos, rope_sin, seq, heads, hd, 1e-6f, 0);
-        orc_head_norm_rope_bf16(h + dim, ldh, norm_k, rope_cos, rope_sin, seq, heads, hd, 1e-6f, 0);
+        orc_head_norm_rope_bf16(h, ldh, norm_q, rope_cos, rope_sin, seq, heads, hd, eps, 0);
+        orc_head_norm_rope_bf16(h + dim, ldh, norm_k, rope_cos, rope_sin, seq, heads, hd, eps, 0);
         for (int s = 0; s < seq; s++)
             orc_bf16_to_f32(qkv + (size_t)s * 3 * dim, h + (size_t)s * ldh, 3 * (size_t)dim);
         orc_dev_attention(att, dim, qkv, qkv + dim, qkv + 2 * dim, 3 * dim, seq, seq, heads, heads, hd,
@@ -597,11 +602,23 @@ int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
             orc_f32_to_bf16(cat + (size_t)s * ldc, att + (size_t)s * dim, dim);
         orc_swiglu(cat + dim, ldc, h + 3 * dim, h + 3 * dim + mlp, ldh, seq, mlp);
         orc_linear(proj, dim, cat, ldc, w_out, ldc, seq, ldc, dim, nthreads);
-        orc_residual(x, proj, mod + 2 * dim, seq, dim);
+        for (int g = 0; g < nsegs; g++) {
+            size_t off = (size_t)seg_start[g] * dim;
+            orc_residual(x + off, proj + off, seg_mod[g] + 2 * dim, seg_len[g], dim);
+        }
         rc = 0;
     }
     free(norm); free(h); free(cat); free(hf); free(qkv); free(att); free(proj);
     return rc;
+}
+
+int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
+                     const float *norm_q, const float *norm_k, const float *mod,
+                     const float *rope_cos, const float *rope_sin,
+                     int seq, int dim, int heads, int mlp, const int *key_mask, int nthreads) {
+    int start = 0;
+    return orc_single_block_segments(x, w_in, w_out, norm_q, norm_k, &start, &seq, &mod, 1, rope_cos, rope_sin,
+                                     seq, dim, heads, mlp, 1e-6f, key_mask, nthreads);
 }
 
 /* One double-stream block as the reference's device forward issues it

@@ -123,6 +123,15 @@ int orc_single_block(float *x, const uint16_t *w_in, const uint16_t *w_out,
                      const float *rope_cos, const float *rope_sin,
                      int seq, int dim, int heads, int mlp, const int *key_mask, int nthreads);
 
+/* The same with the rows in segments (start, len) that carry their own
+ * modulation seg_mod[i] [3 dim], and the norm epsilon as an argument: one
+ * FLUX.3 block (iris_transformer_flux3.c:680-703). */
+int orc_single_block_segments(float *x, const uint16_t *w_in, const uint16_t *w_out,
+                              const float *norm_q, const float *norm_k,
+                              const int *seg_start, const int *seg_len, const float *const *seg_mod, int nsegs,
+                              const float *rope_cos, const float *rope_sin,
+                              int seq, int dim, int heads, int mlp, float eps, const int *key_mask, int nthreads);
+
 /* The weights of one stream of a double block (the reference's
  * dev_stream_flux_t, iris_transformer_flux.c:3491-3494, plus the stream's
  * modulation): qkv [3 dim, dim], proj [dim, dim], ff_in [2 mlp, dim] (gate

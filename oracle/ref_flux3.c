@@ -6,7 +6,8 @@
  *
  * Reference functions reached (iris_transformer_flux3.c):
  *   head_rms_norm :172, apply_rope :185, attention :204, rope_rows :282,
- *   image_positions :300, joint_rope :314.
+ *   image_positions :300, joint_rope :314, ensure_work :344,
+ *   block_forward :371.
  */
 #include "iris_transformer_flux3.c"
 
@@ -53,5 +54,32 @@ int ref_f3_attention(float *out, const float *q, const float *k, const float *v,
     if (!scores) return -1;
     attention(out, q, k, v, scores, seq, heads, head_dim);
     free(scores);
+    return 0;
+}
+
+/* One FLUX.3 block on the CPU: block_forward over x [seq, dim] in place, with
+ * the rows in nsegs segments (start, len, mod [3 dim]). w[6]: to_q, to_k,
+ * to_v, to_out [dim, dim], ff_in [2 mlp, dim], ff_out [dim, mlp], bf16 as the
+ * checkpoints store them. rope tables compact [seq, head_dim / 2]. */
+int ref_f3_block(float *x, const uint16_t *const *w, const float *norm_q, const float *norm_k,
+                 const int *seg_start, const int *seg_len, const float *const *seg_mod, int nsegs,
+                 const float *rope_cos, const float *rope_sin, int seq, int heads, int head_dim, int mlp,
+                 float eps) {
+    iris_transformer_flux3_t tf;
+    f3_block_t b;
+    f3_work_t work;
+    f3_segment_t segs[8];
+    if (nsegs < 1 || nsegs > 8) return -1;
+    f3_ctx(&tf, heads, head_dim, 10000.0f);
+    tf.mlp = mlp;
+    tf.eps = eps;
+    if (!ensure_work(&tf, seq, &work)) return -1;
+    memset(&b, 0, sizeof(b));
+    b.to_q = w[0]; b.to_k = w[1]; b.to_v = w[2]; b.to_out = w[3]; b.ff_in = w[4]; b.ff_out = w[5];
+    b.norm_q = norm_q; b.norm_k = norm_k;
+    for (int i = 0; i < nsegs; i++) segs[i] = (f3_segment_t){seg_start[i], seg_len[i], seg_mod[i]};
+    block_forward(&tf, &b, x, seq, segs, nsegs, rope_cos, rope_sin, &work);
+    free(tf.work);
+    free(tf.wbuf);
     return 0;
 }

@@ -112,3 +112,47 @@ def oracle_double_block(inp, key_mask=None, nthreads=0):
             inp["mlp"], key_mask, nthreads)
     assert rc == 0
     return x
+
+
+# ---------------------------------------------------------------------------
+# FLUX.3 block: the single-stream layout with the rows in segments (text,
+# image, reference images), each with its own modulation
+# ---------------------------------------------------------------------------
+
+F3_SMALL = dict(name="flux3-block-small", family="flux3", heads=2, mlp=768, txt=33, img=(10, 10), refs=[(6, 6), (5, 7)],
+                eps=1e-6)
+F3_MID = dict(name="flux3-block-mid", family="flux3", heads=4, mlp=1536, txt=40, img=(12, 11), refs=[(8, 8)], eps=1e-6)
+F3_KLEIN_SHORT = dict(name="flux3-block-24-heads", family="flux3", heads=24, mlp=9216, txt=64, img=(8, 12), refs=[(4, 8)],
+                      eps=1e-6)
+
+
+class Segment(C.Structure):
+    """iris_b200_segment of include/iris_b200.h."""
+    _fields_ = [("start", C.c_int), ("len", C.c_int), ("mod", C.c_void_p)]
+
+
+def f3_inputs(case, seed=51):
+    inp = block_inputs(case, seed)
+    dim, txt = inp["dim"], case["txt"]
+    img = case["img"][0] * case["img"][1]
+    cond = sum(h * w for h, w in case["refs"])
+    lens = [n for n in (txt, img, cond) if n > 0]
+    starts = [int(sum(lens[:i])) for i in range(len(lens))]
+    mods = [(0.4 * ol.randn(seed + 30 + i, 3 * dim)).astype(np.float32) for i in range(len(lens))]
+    inp.update(seg_start=np.array(starts, np.int32), seg_len=np.array(lens, np.int32), seg_mod=mods)
+    return inp
+
+
+def oracle_f3_block(inp, eps=1e-6, key_mask=None, nthreads=0):
+    x = inp["x"].copy()
+    o = ol.oracle()
+    fn = o.orc_single_block_segments
+    fn.restype = C.c_int
+    fn.argtypes = [ol.f32p, ol.u16p, ol.u16p, ol.f32p, ol.f32p, ol.i32p, ol.i32p, C.c_void_p, C.c_int, ol.f32p, ol.f32p] + \
+                  [C.c_int] * 4 + [C.c_float, ol.i32p_opt, C.c_int]
+    n = len(inp["seg_mod"])
+    mods = (C.c_void_p * n)(*[m.ctypes.data for m in inp["seg_mod"]])
+    rc = fn(x, inp["w_in"], inp["w_out"], inp["norm_q"], inp["norm_k"], inp["seg_start"], inp["seg_len"], mods, n,
+            inp["cos"], inp["sin"], inp["seq"], inp["dim"], inp["heads"], inp["mlp"], eps, key_mask, nthreads)
+    assert rc == 0
+    return x

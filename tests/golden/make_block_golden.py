@@ -6,8 +6,9 @@ Run where the reference sources are present:
     make -C oracle ref && python tests/golden/make_block_golden.py
 
 Records what the reference's single_block_forward and double_block_forward
-(iris_transformer_flux.c:3341-3477, :2133-2327, compiled unmodified into
-oracle/_ref/libiris_ref_generic.so) make of the seeded inputs of
+(iris_transformer_flux.c:3341-3477, :2133-2327) and its FLUX.3 block_forward
+(iris_transformer_flux3.c:371-417), compiled unmodified into
+oracle/_ref/libiris_ref_generic.so, make of the seeded inputs of
 tests/block_cases.py. Inputs are not stored: block_cases regenerates them.
 """
 import os
@@ -70,6 +71,24 @@ def reference_double_block(r, case, inp):
     return np.concatenate([xt, xi])
 
 
+def reference_f3_block(r, case, inp):
+    """x after a FLUX.3 block by the reference's CPU code: block_forward with
+    the separate matrices that the fused device weights are made of."""
+    import ctypes as C
+    dim, mlp = inp["dim"], inp["mlp"]
+    w_in, w_out = inp["w_in"], inp["w_out"]
+    mats = [w_in[:dim], w_in[dim:2 * dim], w_in[2 * dim:3 * dim], w_out[:, :dim], w_in[3 * dim:], w_out[:, dim:]]
+    mats = [np.ascontiguousarray(m) for m in mats]
+    ptrs = (C.c_void_p * 6)(*[m.ctypes.data for m in mats])
+    n = len(inp["seg_mod"])
+    mods = (C.c_void_p * n)(*[m.ctypes.data for m in inp["seg_mod"]])
+    x = inp["x"].copy()
+    rc = r.ref_f3_block(x, ptrs, inp["norm_q"], inp["norm_k"], inp["seg_start"], inp["seg_len"], mods, n, inp["cos"],
+                        inp["sin"], inp["seq"], inp["heads"], bc.D, mlp, case["eps"])
+    assert rc == 0
+    return x
+
+
 def main():
     r = ol.ref("generic")
     if r is None:
@@ -83,6 +102,9 @@ def main():
     for case in (bc.SMALL,):
         inp = bc.double_inputs(case)
         out["double/" + case["name"]] = reference_double_block(r, case, inp)
+    for case in (bc.F3_SMALL,):
+        inp = bc.f3_inputs(case)
+        out["f3/" + case["name"]] = reference_f3_block(r, case, inp)[::2]          # every second row
     path = os.path.join(HERE, "reference_block.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

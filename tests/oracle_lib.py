@@ -113,6 +113,7 @@ def ref(kind="generic"):
     _sig(lib, "ref_f3_apply_rope", [f32p, f32p, f32p, INT, INT, INT])
     _sig(lib, "ref_f3_joint_rope", [f32p, f32p, INT, INT, INT, i32p, i32p, INT, INT, INT, FLT], INT)
     _sig(lib, "ref_f3_attention", [f32p] * 4 + [INT] * 3, INT)
+    _sig(lib, "ref_f3_block", [f32p, C.c_void_p, f32p, f32p, i32p, i32p, C.c_void_p, INT, f32p, f32p, INT, INT, INT, INT, FLT], INT)
     _sig(lib, "ref_zi_qk_norm", [f32p, f32p, INT, INT, INT, FLT])
     _sig(lib, "ref_zi_apply_rope", [f32p, i32p, INT, INT, INT])
     _sig(lib, "ref_zi_attention_identity", [f32p, f32p, i32p, i32p_opt, INT, INT, INT], INT)

@@ -126,3 +126,30 @@ def test_double_block_streams_use_their_own_weights():
     base = bc.oracle_double_block(inp)
     swapped = bc.oracle_double_block(dict(inp, txt=inp["img"], img=inp["txt"]))
     assert not np.allclose(base, swapped)
+
+
+def test_f3_block_restatement_against_recorded_reference():
+    """FLUX.3: one block over text, image and reference-image segments with
+    their own modulation, against the recorded output of the reference's
+    block_forward (iris_transformer_flux3.c:371-417)."""
+    gold = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_block.npz")))
+    inp = bc.f3_inputs(bc.F3_SMALL)
+    assert len(inp["seg_mod"]) == 3
+    rel, cos = bc.delta_metrics(bc.oracle_f3_block(inp)[::2], gold["f3/" + bc.F3_SMALL["name"]], inp["x"][::2])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_f3_block_restatement_against_reference_build():
+    r = ol.ref("generic")
+    if r is None:
+        pytest.skip("oracle/_ref is not built here")
+    inp = bc.f3_inputs(bc.F3_MID, seed=77)
+    want = mg.reference_f3_block(r, bc.F3_MID, inp)
+    rel, cos = bc.delta_metrics(bc.oracle_f3_block(inp), want, inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_one_segment_is_the_single_block():
+    inp = bc.block_inputs(bc.SMALL)
+    seg = dict(inp, seg_start=np.array([0], np.int32), seg_len=np.array([inp["seq"]], np.int32), seg_mod=[inp["mod"]])
+    assert np.array_equal(bc.oracle_f3_block(seg), bc.oracle_block(inp))

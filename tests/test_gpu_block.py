@@ -368,3 +368,61 @@ def test_linear_glu(lib, rows, cin, heads, mlp):
         fq, fh = ol.from_bf16(qkv), ol.from_bf16(h[:, :nq])
         assert (np.abs(fq - fh) <= np.maximum(np.abs(fh), 0.05) * 2.0 ** -6).all()
         assert (qkv != h[:, :nq]).mean() < 0.1
+
+
+# ---------------------------------------------------------------------------
+# FLUX.3 block: rows in segments with their own modulation
+# ---------------------------------------------------------------------------
+
+def device_f3_block(lib, inp, eps=1e-6, key_mask=None):
+    d = Dev(lib)
+    try:
+        dx = d.put(inp["x"])
+        scratch = d.new(lib.iris_b200_single_block_scratch_bytes(inp["seq"], inp["dim"], inp["mlp"]))
+        args = [d.put(inp[k]) for k in ("w_in", "w_out", "norm_q", "norm_k")]
+        n = len(inp["seg_mod"])
+        segs = (bc.Segment * n)(*[bc.Segment(int(s), int(l), d.put(m))
+                                  for s, l, m in zip(inp["seg_start"], inp["seg_len"], inp["seg_mod"])])
+        dcos, dsin = d.put(inp["cos"]), d.put(inp["sin"])
+        dm = d.put(np.ascontiguousarray(key_mask, np.int32)) if key_mask is not None else None
+        rc = lib.iris_b200_single_block_segments(dx, scratch, *args, C.addressof(segs), n, dcos, dsin, inp["seq"],
+                                                 inp["dim"], inp["heads"], inp["mlp"], eps, dm)
+        assert rc == 0
+        out = lib.to_host(dx, inp["x"].shape, np.float32)
+        lib.check()
+        return out
+    finally:
+        d.free()
+
+
+@pytest.mark.parametrize("case", [bc.F3_SMALL, bc.F3_MID, bc.F3_KLEIN_SHORT], ids=lambda c: c["name"])
+def test_f3_block_against_the_restatement(lib, case):
+    """Segment boundaries fall inside 32-row groups and 128-row tiles (33, 133;
+    40, 172; 64, 160): shift, scale and gate are picked per row."""
+    inp = bc.f3_inputs(case)
+    got = device_f3_block(lib, inp)
+    rel, cos = bc.delta_metrics(got, bc.oracle_f3_block(inp), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_f3_block_against_the_recorded_reference(lib):
+    import os
+    gold = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_block.npz")))
+    inp = bc.f3_inputs(bc.F3_SMALL)
+    rel, cos = bc.delta_metrics(device_f3_block(lib, inp)[::2], gold["f3/" + bc.F3_SMALL["name"]], inp["x"][::2])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_segments_must_tile_the_rows(lib):
+    d = Dev(lib)
+    try:
+        p = d.new(1 << 16)
+        gap = (bc.Segment * 2)(bc.Segment(0, 4, p), bc.Segment(5, 3, p))
+        short = (bc.Segment * 1)(bc.Segment(0, 7, p))
+        five = (bc.Segment * 5)(*[bc.Segment(i, 1, p) for i in range(5)])
+        for segs, n in ((gap, 2), (short, 1), (five, 5)):
+            assert lib.iris_b200_single_block_segments(p, p, p, p, p, p, C.addressof(segs), n, p, p, 8, 256, 2, 64,
+                                                       1e-6, None) == 1
+        lib.iris_b200_clear_error()
+    finally:
+        d.free()
