@@ -267,6 +267,36 @@ int iris_b200_double_block(float *x, void *scratch,
                            int seq, int txt_seq, int dim, int heads, int mlp,
                            const int *key_mask);
 
+/* ---- one Z-Image block --------------------------------------------------- */
+
+/* The weights of one Z-Image (S3-DiT) block, bf16 matrices as the checkpoints
+ * store them: the reference's zi_dev_block_t
+ * (iris_transformer_zimage.c:1693-1697). */
+typedef struct iris_b200_zimage_weights {
+    const uint16_t *qkv;       /* [3 dim, dim] */
+    const uint16_t *proj;      /* [dim, dim] */
+    const uint16_t *ff_in;     /* [2 ff, dim]: the gate (w1) rows, then the up (w3) rows */
+    const uint16_t *ff_out;    /* [dim, ff] (w2) */
+    const float *norm_q;       /* [128] */
+    const float *norm_k;       /* [128] */
+    const float *attn_norm1, *attn_norm2, *ffn_norm1, *ffn_norm2;   /* [dim] */
+} iris_b200_zimage_weights;
+
+size_t iris_b200_zimage_block_scratch_bytes(int seq, int dim, int ff);
+
+/* One Z-Image block on the device-resident fp32 hidden state x [seq, dim], in
+ * place: what the reference's zi_dev_block issues
+ * (iris_transformer_zimage.c:1940-1959; CPU form zi_block_forward, :801-880):
+ * RMSNorm with (1 + scale_msa), QKV projection with the Q/K prologue,
+ * attention under the key mask, output projection, x += tanh(gate_msa) *
+ * RMSNorm(result), then the same around the SwiGLU feed-forward. Nine
+ * launches for the reference's twelve calls. mod [4 dim] = scale_msa |
+ * gate_msa | scale_mlp | gate_mlp, or NULL for the unmodulated context
+ * refiner blocks. The norm epsilon is the reference's 1e-5. head_dim is 128. */
+int iris_b200_zimage_block(float *x, void *scratch, const iris_b200_zimage_weights *w,
+                           const float *mod, const float *rope_cos, const float *rope_sin,
+                           int seq, int dim, int heads, int ff, const int *key_mask);
+
 /* ---- attention ---------------------------------------------------------- */
 
 enum {

@@ -71,6 +71,19 @@ void iris_dev_layer_norm_mod(uint16_t *out, const float *x,
                              const float *shift, const float *scale,
                              int rows, int dim, float eps);
 
+/* out = RMSNorm(x) * w, and the same times (1 + scale) with scale [dim] or
+ * NULL; fp32 in, bf16 out. Replace iris_dev.h:61-68 (kernel
+ * iris_cuda.cu:372-386). */
+void iris_dev_rms_norm(uint16_t *out, const float *x, const float *w,
+                       int rows, int dim, float eps);
+void iris_dev_rms_norm_mod(uint16_t *out, const float *x, const float *w,
+                           const float *scale, int rows, int dim, float eps);
+
+/* x += tanh(gate) * RMSNorm(a) * w in fp32; gate [dim] or NULL for an ungated
+ * residual. Replaces iris_dev.h:70-73 (kernel iris_cuda.cu:388-400). */
+void iris_dev_rms_norm_residual(float *x, const float *a, const float *w,
+                                const float *gate, int rows, int dim, float eps);
+
 /* out[r, c] = silu(gate[r, c]) * up[r, c] on bf16 column slices (gate / up row
  * stride ldi, out row stride ldo). Replaces iris_dev.h:94-95 (kernel
  * iris_cuda.cu:300-307). The exponential is the hardware approximation

@@ -29,6 +29,9 @@ SIGNATURES = {
     "iris_dev_linear_bf16": (None, [VP, VP, VP, INT, INT, INT]),
     "iris_dev_linear_f32": (None, [VP, VP, VP, INT, INT, INT]),
     "iris_dev_layer_norm_mod": (None, [VP, VP, VP, VP, INT, INT, FLT]),
+    "iris_dev_rms_norm": (None, [VP, VP, VP, INT, INT, FLT]),
+    "iris_dev_rms_norm_mod": (None, [VP, VP, VP, VP, INT, INT, FLT]),
+    "iris_dev_rms_norm_residual": (None, [VP, VP, VP, VP, INT, INT, FLT]),
     "iris_dev_swiglu": (None, [VP, INT, VP, VP, INT, INT, INT]),
     "iris_dev_residual": (None, [VP, VP, VP, INT, INT]),
     "iris_dev_head_norm_rope": (None, [VP, INT, VP, VP, VP, INT, INT, INT, FLT, INT]),
@@ -62,6 +65,8 @@ SIGNATURES = {
     "iris_b200_single_block_scratch_bytes": (SZ, [INT, INT, INT]),
     "iris_b200_single_block": (INT, [VP, VP, VP, VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, VP]),
     "iris_b200_single_block_segments": (INT, [VP, VP, VP, VP, VP, VP, VP, INT, VP, VP, INT, INT, INT, INT, FLT, VP]),
+    "iris_b200_zimage_block_scratch_bytes": (SZ, [INT, INT, INT]),
+    "iris_b200_zimage_block": (INT, [VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, VP]),
     "iris_b200_double_block_scratch_bytes": (SZ, [INT, INT, INT]),
     "iris_b200_double_block": (INT, [VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, INT, VP]),
     "iris_b200_attention_ex": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP, INT]),
@@ -115,6 +120,12 @@ class LoopFault(C.Structure):
 class Segment(C.Structure):
     """iris_b200_segment of include/iris_b200.h."""
     _fields_ = [("start", INT), ("len", INT), ("mod", VP)]
+
+
+class ZImageWeights(C.Structure):
+    """iris_b200_zimage_weights of include/iris_b200.h."""
+    _fields_ = [(n, VP) for n in ("qkv", "proj", "ff_in", "ff_out", "norm_q", "norm_k", "attn_norm1", "attn_norm2",
+                                  "ffn_norm1", "ffn_norm2")]
 
 
 class StreamWeights(C.Structure):

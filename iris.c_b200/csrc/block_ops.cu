@@ -5,6 +5,10 @@
  *   iris_dev_layer_norm_mod   LayerNorm without affine parameters, then
  *                             (1 + scale) and shift, fp32 in, bf16 out
  *                             (reference kernel: iris_cuda.cu:349-370)
+ *   iris_dev_rms_norm(_mod)   RMSNorm with weight and optional (1 + scale),
+ *                             fp32 in, bf16 out (iris_cuda.cu:372-386)
+ *   iris_dev_rms_norm_residual  x += tanh(gate) * RMSNorm(a) * w in fp32
+ *                             (iris_cuda.cu:388-400)
  *   iris_dev_swiglu           silu(gate) * up on bf16 column slices
  *                             (iris_cuda.cu:300-307)
  *   iris_dev_residual         x += gate * a in fp32 (iris_cuda.cu:309-314)
@@ -12,6 +16,9 @@
  *                             block (iris_transformer_flux.c:3781-3823) in
  *                             seven launches instead of twenty-seven: every
  *                             launch covers the text and the image stream.
+ *   iris_b200_zimage_block    the sequence of one Z-Image block
+ *                             (iris_transformer_zimage.c:1940-1959) in nine
+ *                             launches instead of twelve.
  *   iris_b200_single_block    the sequence the reference issues per single
  *                             block (iris_transformer_flux.c:3828-3845) in four
  *                             launches instead of eight: the projection
@@ -149,6 +156,75 @@ k_layer_norm_mod_any(uint16_t *__restrict__ out, const float *__restrict__ x, co
     }
 }
 
+/* RMSNorm rows, one warp per row with the row in registers. RESIDUAL false:
+ * out (bf16) = x * inv * w * (1 + scale); true: xres (fp32) += tanh(gate) *
+ * x * inv * w, where x is the projection result. scale / gate may be NULL. */
+template <int VPL, bool RESIDUAL>
+__global__ void __launch_bounds__(kRowThreads)
+k_rms_norm_warp(uint16_t *__restrict__ out, float *__restrict__ xres, const float *__restrict__ x,
+                const float *__restrict__ w, const float *__restrict__ mod, int rows, int dim, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * kRowThreads) >> 5;
+    const int nvec = dim >> 2;
+    const float inv_dim = 1.0f / (float)dim;
+    for (int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5; row < rows; row += warps) {
+        const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * dim);
+        float4 v[VPL];
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const int i = lane + 32 * k;
+            v[k] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+        }
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
+        const float inv = rsqrtf(s * inv_dim + eps);
+#pragma unroll
+        for (int k = 0; k < VPL; k++) {
+            const int i = lane + 32 * k;
+            if (i >= nvec) continue;
+            const float4 w4 = reinterpret_cast<const float4 *>(w)[i];
+            float n[4] = {v[k].x * inv * w4.x, v[k].y * inv * w4.y, v[k].z * inv * w4.z, v[k].w * inv * w4.w};
+            if (RESIDUAL) {
+                float4 g = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (mod) {
+                    const float4 m = reinterpret_cast<const float4 *>(mod)[i];
+                    g = make_float4(tanhf(m.x), tanhf(m.y), tanhf(m.z), tanhf(m.w));
+                }
+                float4 *xo = reinterpret_cast<float4 *>(xres + (size_t)row * dim) + i;
+                float4 xv = *xo;
+                xv.x += g.x * n[0]; xv.y += g.y * n[1]; xv.z += g.z * n[2]; xv.w += g.w * n[3];
+                *xo = xv;
+            } else {
+                if (mod) {
+                    const float4 m = reinterpret_cast<const float4 *>(mod)[i];
+                    n[0] *= 1.0f + m.x; n[1] *= 1.0f + m.y; n[2] *= 1.0f + m.z; n[3] *= 1.0f + m.w;
+                }
+                reinterpret_cast<uint2 *>(out + (size_t)row * dim)[i] = make_uint2(cvt_bf16x2(n[0], n[1]), cvt_bf16x2(n[2], n[3]));
+            }
+        }
+    }
+}
+
+template <bool RESIDUAL>
+__global__ void __launch_bounds__(kRowThreads)
+k_rms_norm_any(uint16_t *__restrict__ out, float *__restrict__ xres, const float *__restrict__ x, const float *__restrict__ w,
+               const float *__restrict__ mod, int rows, int dim, float eps) {
+    __shared__ float sh[kRowThreads / 32];
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float *xr = x + (size_t)row * dim;
+        float s = 0.0f;
+        for (int i = threadIdx.x; i < dim; i += kRowThreads) s += xr[i] * xr[i];
+        const float inv = rsqrtf(block_sum(s, sh) / (float)dim + eps);
+        for (int i = threadIdx.x; i < dim; i += kRowThreads) {
+            const float n = xr[i] * inv * w[i];
+            if (RESIDUAL) xres[(size_t)row * dim + i] += (mod ? tanhf(mod[i]) : 1.0f) * n;
+            else out[(size_t)row * dim + i] = f2bf(mod ? n * (1.0f + mod[i]) : n);
+        }
+    }
+}
+
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 /* Eight columns per thread when the slices allow 16-byte accesses. */
@@ -236,6 +312,33 @@ int layer_norm_mod(uint16_t *out, const float *x, const float *shift, const floa
     return layer_norm_mods(out, x, m, rows, dim, eps);
 }
 
+template <bool RESIDUAL>
+int rms_norm_rows(uint16_t *out, float *xres, const float *x, const float *w, const float *mod, int rows, int dim, float eps,
+                  const char *op) {
+    if (!require_device(op)) return IRIS_B200_ENODEV;
+    if ((RESIDUAL ? !xres : !out) || !x || !w || rows < 0 || dim <= 0) {
+        set_error(IRIS_B200_EINVAL, op, "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    if (rows == 0) return IRIS_B200_OK;
+    const int nvec = dim / 4;
+    const bool vec = dim % 4 == 0 && nvec <= 32 * 32 && aligned16(x) && aligned16(w) && aligned16(mod) && aligned16(xres) &&
+                     ((uintptr_t)out & 7) == 0;
+    if (vec) {
+        const unsigned grid = blocks_for((size_t)rows, kRowThreads / 32, 8);
+#define IRIS_RMS_LAUNCH(VPL) \
+    k_rms_norm_warp<VPL, RESIDUAL><<<grid, kRowThreads, 0, g.stream>>>(out, xres, x, w, mod, rows, dim, eps)
+        if (nvec <= 32 * 8) IRIS_RMS_LAUNCH(8);
+        else if (nvec <= 32 * 16) IRIS_RMS_LAUNCH(16);
+        else if (nvec <= 32 * 24) IRIS_RMS_LAUNCH(24);
+        else IRIS_RMS_LAUNCH(32);
+#undef IRIS_RMS_LAUNCH
+    } else {
+        k_rms_norm_any<RESIDUAL><<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, xres, x, w, mod, rows, dim, eps);
+    }
+    return after_launch("k_rms_norm") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
 int swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi, int rows, int cols) {
     if (!require_device("swiglu")) return IRIS_B200_ENODEV;
     if (!out || !gate || !up || rows < 0 || cols < 0 || ldo < cols || ldi < cols) {
@@ -275,6 +378,20 @@ using namespace iris_b200;
 extern "C" void iris_dev_layer_norm_mod(uint16_t *out, const float *x, const float *shift, const float *scale, int rows,
                                         int dim, float eps) {
     layer_norm_mod(out, x, shift, scale, rows, dim, eps);
+}
+
+extern "C" void iris_dev_rms_norm(uint16_t *out, const float *x, const float *w, int rows, int dim, float eps) {
+    rms_norm_rows<false>(out, NULL, x, w, NULL, rows, dim, eps, "rms_norm");
+}
+
+extern "C" void iris_dev_rms_norm_mod(uint16_t *out, const float *x, const float *w, const float *scale, int rows, int dim,
+                                      float eps) {
+    rms_norm_rows<false>(out, NULL, x, w, scale, rows, dim, eps, "rms_norm_mod");
+}
+
+extern "C" void iris_dev_rms_norm_residual(float *x, const float *a, const float *w, const float *gate, int rows, int dim,
+                                           float eps) {
+    rms_norm_rows<true>(NULL, x, a, w, gate, rows, dim, eps, "rms_norm_residual");
 }
 
 extern "C" void iris_dev_swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi, int rows,
@@ -457,4 +574,58 @@ extern "C" int iris_b200_double_block(float *x, void *scratch, const iris_b200_s
     d.gate[0] = tm + 5 * dim;
     d.gate[1] = im + 5 * dim;
     return launch_linear_two(d);
+}
+
+/* norm [seq, dim] | qkv [seq, 3 dim] | act [seq, max(dim, ff)] bf16, then the projection result [seq, dim] fp32 */
+extern "C" size_t iris_b200_zimage_block_scratch_bytes(int seq, int dim, int ff) {
+    if (seq < 0 || dim <= 0 || ff <= 0) return 0;
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t lda = dim > ff ? dim : ff;
+    return up256((size_t)seq * dim * 2) + up256((size_t)seq * 3 * dim * 2) + up256((size_t)seq * lda * 2) +
+           up256((size_t)seq * dim * 4);
+}
+
+extern "C" int iris_b200_zimage_block(float *x, void *scratch, const iris_b200_zimage_weights *w, const float *mod,
+                                      const float *rope_cos, const float *rope_sin, int seq, int dim, int heads, int ff,
+                                      const int *key_mask) {
+    if (!require_device("zimage_block")) return IRIS_B200_ENODEV;
+    const bool ok = x && scratch && w && w->qkv && w->proj && w->ff_in && w->ff_out && w->norm_q && w->norm_k && w->attn_norm1 &&
+                    w->attn_norm2 && w->ffn_norm1 && w->ffn_norm2 && rope_cos && rope_sin && seq >= 0 && dim > 0 && heads > 0 &&
+                    ff > 0 && dim == heads * 128 && ((uintptr_t)scratch & 255) == 0;
+    if (!ok) {
+        set_error(IRIS_B200_EINVAL, "zimage_block", dim > 0 && dim != heads * 128 ? "head_dim must be 128" : "bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    if (seq == 0) return IRIS_B200_OK;
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t lda = dim > ff ? dim : ff;
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+    uint16_t *norm = reinterpret_cast<uint16_t *>(base);
+    base += up256((size_t)seq * dim * 2);
+    uint16_t *qkv = reinterpret_cast<uint16_t *>(base);
+    base += up256((size_t)seq * 3 * dim * 2);
+    uint16_t *act = reinterpret_cast<uint16_t *>(base);
+    base += up256((size_t)seq * lda * 2);
+    float *out = reinterpret_cast<float *>(base);
+    const float eps = 1e-5f;                    /* ZI_NORM_EPS, iris_transformer_zimage.c:47 */
+    int rc;
+    if ((rc = rms_norm_rows<false>(norm, NULL, x, w->attn_norm1, mod, seq, dim, eps, "rms_norm_mod"))) return rc;
+    rc = iris_b200_linear_qk_norm_rope(qkv, 3 * dim, norm, w->qkv, seq, dim, 3 * dim, heads, w->norm_q, w->norm_k, rope_cos,
+                                       rope_sin, eps);
+    if (rc != IRIS_B200_OK) return rc;
+    iris_b200_clear_error();
+    iris_dev_attention(act, dim, qkv, qkv + dim, qkv + 2 * dim, 3 * dim, seq, seq, heads, heads, 128, 0.08838834764831845f, 0,
+                       key_mask);
+    if ((rc = iris_b200_last_error()) != IRIS_B200_OK) return rc;
+    iris_dev_linear_f32(out, act, w->proj, seq, dim, dim);
+    if ((rc = iris_b200_last_error()) != IRIS_B200_OK) return rc;
+    if ((rc = rms_norm_rows<true>(NULL, x, out, w->attn_norm2, mod ? mod + dim : NULL, seq, dim, eps, "rms_norm_residual")))
+        return rc;
+    if ((rc = rms_norm_rows<false>(norm, NULL, x, w->ffn_norm1, mod ? mod + 2 * dim : NULL, seq, dim, eps, "rms_norm_mod")))
+        return rc;
+    rc = iris_b200_linear_glu(NULL, 0, act, ff, norm, w->ff_in, seq, dim, 0, ff, NULL, NULL, NULL, NULL, eps);
+    if (rc != IRIS_B200_OK) return rc;
+    iris_dev_linear_f32(out, act, w->ff_out, seq, ff, dim);
+    if ((rc = iris_b200_last_error()) != IRIS_B200_OK) return rc;
+    return rms_norm_rows<true>(NULL, x, out, w->ffn_norm2, mod ? mod + 3 * dim : NULL, seq, dim, eps, "rms_norm_residual");
 }

@@ -674,6 +674,74 @@ int orc_double_block(float *x, const orc_stream_weights *txt, const orc_stream_w
     return rc;
 }
 
+/* k_rms_norm, iris_cuda.cu:372-386: out = x * inv * w, times (1 + scale) when
+ * scale is given; sum of squares in double here. */
+void orc_rms_norm_mod(uint16_t *out, const float *x, const float *w, const float *scale,
+                      int rows, int dim, float eps) {
+    for (int r = 0; r < rows; r++) {
+        const float *xr = x + (size_t)r * dim;
+        double s = 0;
+        for (int i = 0; i < dim; i++) s += (double)xr[i] * xr[i];
+        float inv = 1.0f / sqrtf((float)(s / dim) + eps);
+        for (int i = 0; i < dim; i++) {
+            float v = xr[i] * inv * w[i];
+            if (scale) v *= 1.0f + scale[i];
+            out[(size_t)r * dim + i] = orc_f2bf(v);
+        }
+    }
+}
+
+/* k_rms_norm_residual, iris_cuda.cu:388-400: x += tanh(gate) * a * inv * w. */
+void orc_rms_norm_residual(float *x, const float *a, const float *w, const float *gate,
+                           int rows, int dim, float eps) {
+    for (int r = 0; r < rows; r++) {
+        const float *ar = a + (size_t)r * dim;
+        double s = 0;
+        for (int i = 0; i < dim; i++) s += (double)ar[i] * ar[i];
+        float inv = 1.0f / sqrtf((float)(s / dim) + eps);
+        for (int i = 0; i < dim; i++)
+            x[(size_t)r * dim + i] += (gate ? tanhf(gate[i]) : 1.0f) * (ar[i] * inv * w[i]);
+    }
+}
+
+/* One Z-Image block as zi_dev_block issues it
+ * (iris_transformer_zimage.c:1940-1959), in place on x [seq, dim]. mod [4 dim]
+ * = scale_msa | gate_msa | scale_mlp | gate_mlp or NULL. */
+int orc_zimage_block(float *x, const orc_zimage_weights *w, const float *mod,
+                     const float *rope_cos, const float *rope_sin,
+                     int seq, int dim, int heads, int ff, const int *key_mask, int nthreads) {
+    int hd = dim / heads;
+    float eps = 1e-5f;
+    size_t nd = (size_t)seq * dim, nf = (size_t)seq * ff;
+    uint16_t *norm = malloc(nd * 2), *h = malloc(3 * nd * 2), *act = malloc((nd > nf ? nd : nf) * 2);
+    uint16_t *ffh = malloc(2 * nf * 2);
+    float *hf = malloc((3 * nd > 2 * nf ? 3 * nd : 2 * nf) * sizeof(float));
+    float *att = malloc(nd * sizeof(float)), *out = malloc(nd * sizeof(float));
+    int rc = -1;
+    if (norm && h && act && ffh && hf && att && out) {
+        orc_rms_norm_mod(norm, x, w->attn_norm1, mod, seq, dim, eps);
+        orc_linear(hf, 3 * dim, norm, dim, w->qkv, dim, seq, dim, 3 * dim, nthreads);
+        orc_f32_to_bf16(h, hf, 3 * nd);
+        orc_head_norm_rope_bf16(h, 3 * dim, w->norm_q, rope_cos, rope_sin, seq, heads, hd, eps, 0);
+        orc_head_norm_rope_bf16(h + dim, 3 * dim, w->norm_k, rope_cos, rope_sin, seq, heads, hd, eps, 0);
+        orc_bf16_to_f32(hf, h, 3 * nd);
+        orc_dev_attention(att, dim, hf, hf + dim, hf + 2 * dim, 3 * dim, seq, seq, heads, heads, hd,
+                          1.0f / sqrtf((float)hd), 0, key_mask, NULL, 0, nthreads);
+        orc_f32_to_bf16(act, att, nd);
+        orc_linear(out, dim, act, dim, w->proj, dim, seq, dim, dim, nthreads);
+        orc_rms_norm_residual(x, out, w->attn_norm2, mod ? mod + dim : NULL, seq, dim, eps);
+        orc_rms_norm_mod(norm, x, w->ffn_norm1, mod ? mod + 2 * dim : NULL, seq, dim, eps);
+        orc_linear(hf, 2 * ff, norm, dim, w->ff_in, dim, seq, dim, 2 * ff, nthreads);
+        orc_f32_to_bf16(ffh, hf, 2 * nf);
+        orc_swiglu(act, ff, ffh, ffh + ff, 2 * ff, seq, ff);
+        orc_linear(out, dim, act, ff, w->ff_out, ff, seq, ff, dim, nthreads);
+        orc_rms_norm_residual(x, out, w->ffn_norm2, mod ? mod + 3 * dim : NULL, seq, dim, eps);
+        rc = 0;
+    }
+    free(norm); free(h); free(act); free(ffh); free(hf); free(att); free(out);
+    return rc;
+}
+
 /* ------------------------------------------------------------------------
  * Metrics
  * ------------------------------------------------------------------------ */

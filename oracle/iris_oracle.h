@@ -148,6 +148,25 @@ int orc_double_block(float *x, const orc_stream_weights *txt, const orc_stream_w
                      const float *rope_cos, const float *rope_sin,
                      int seq, int txt_seq, int dim, int heads, int mlp, const int *key_mask, int nthreads);
 
+/* RMSNorm rows (k_rms_norm, iris_cuda.cu:372-386; k_rms_norm_residual,
+ * :388-400). scale / gate may be NULL. */
+void orc_rms_norm_mod(uint16_t *out, const float *x, const float *w, const float *scale,
+                      int rows, int dim, float eps);
+void orc_rms_norm_residual(float *x, const float *a, const float *w, const float *gate,
+                           int rows, int dim, float eps);
+/* The weights of one Z-Image block (the reference's zi_dev_block_t,
+ * iris_transformer_zimage.c:1693-1697): bf16 matrices, fp32 norm weights. */
+typedef struct {
+    const uint16_t *qkv, *proj, *ff_in, *ff_out;
+    const float *norm_q, *norm_k, *attn_norm1, *attn_norm2, *ffn_norm1, *ffn_norm2;
+} orc_zimage_weights;
+/* One Z-Image block in the arithmetic of zi_dev_block
+ * (iris_transformer_zimage.c:1940-1959), in place on x [seq, dim]; norm
+ * epsilon 1e-5. */
+int orc_zimage_block(float *x, const orc_zimage_weights *w, const float *mod,
+                     const float *rope_cos, const float *rope_sin,
+                     int seq, int dim, int heads, int ff, const int *key_mask, int nthreads);
+
 /* ---- comparison metrics ---- */
 /* Per head over the listed rows (NULL = all): max |a - b| and cosine.
  * a, b: [seq, heads*hd] with row strides lda / ldb. Writes heads entries. */

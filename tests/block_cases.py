@@ -156,3 +156,61 @@ def oracle_f3_block(inp, eps=1e-6, key_mask=None, nthreads=0):
             inp["cos"], inp["sin"], inp["seq"], inp["dim"], inp["heads"], inp["mlp"], eps, key_mask, nthreads)
     assert rc == 0
     return x
+
+
+# ---------------------------------------------------------------------------
+# Z-Image block
+# ---------------------------------------------------------------------------
+
+ZI_SMALL = dict(name="zimage-block-small", family="zimage", heads=2, ff=704, txt=50, img=(9, 13), refs=[], eps=1e-5)
+ZI_MID = dict(name="zimage-block-mid", family="zimage", heads=4, ff=1368, txt=40, img=(12, 11), refs=[], eps=1e-5)
+ZI_30_HEADS = dict(name="zimage-block-30-heads", family="zimage", heads=30, ff=10240, txt=40, img=(8, 12), refs=[], eps=1e-5)
+
+ZI_KEYS = ("qkv", "proj", "ff_in", "ff_out", "norm_q", "norm_k", "attn_norm1", "attn_norm2", "ffn_norm1", "ffn_norm2")
+
+
+class ZImageWeights(C.Structure):
+    """iris_b200_zimage_weights of include/iris_b200.h; orc_zimage_weights of
+    oracle/iris_oracle.h has the same layout."""
+    _fields_ = [(n, C.c_void_p) for n in ZI_KEYS]
+
+
+def zi_positions(case):
+    o = ol.oracle()
+    seq = pc.seq_len(case)
+    pos = np.zeros((seq, 3), np.int32)
+    mask = np.zeros(seq, np.int32)
+    assert o.orc_zi_positions(pos.reshape(-1), mask, case["img"][0], case["img"][1], case["txt"]) == seq
+    return pos, mask
+
+
+def zi_inputs(case, seed=91, modulated=True):
+    H, ff = case["heads"], case["ff"]
+    dim, seq = H * D, pc.seq_len(case)
+    s = np.float32
+    cos, sin, mask = pc.rope_tables(case)
+    pos, full_mask = zi_positions(case)
+    w = dict(
+        qkv=ol.to_bf16(ol.randn(seed + 1, 3 * dim, dim) / s(np.sqrt(dim))),
+        proj=ol.to_bf16(ol.randn(seed + 2, dim, dim) / s(np.sqrt(dim))),
+        ff_in=ol.to_bf16(ol.randn(seed + 3, 2 * ff, dim) / s(np.sqrt(dim))),
+        ff_out=ol.to_bf16(ol.randn(seed + 4, dim, ff) / s(np.sqrt(ff))),
+        norm_q=(1.0 + 0.1 * ol.randn(seed + 5, D)).astype(s), norm_k=(1.0 + 0.1 * ol.randn(seed + 6, D)).astype(s))
+    for i, k in enumerate(("attn_norm1", "attn_norm2", "ffn_norm1", "ffn_norm2")):
+        w[k] = (1.0 + 0.1 * ol.randn(seed + 7 + i, dim)).astype(s)
+    mod = (0.5 * ol.randn(seed + 20, 4 * dim)).astype(s) if modulated else None
+    return dict(x=ol.randn(seed, seq, dim), w=w, mod=mod, cos=cos, sin=sin, mask=mask, pos=pos, full_mask=full_mask, seq=seq,
+                dim=dim, heads=H, ff=ff)
+
+
+def oracle_zi_block(inp, nthreads=0):
+    x = inp["x"].copy()
+    o = ol.oracle()
+    fn = o.orc_zimage_block
+    fn.restype = C.c_int
+    fn.argtypes = [ol.f32p, C.POINTER(ZImageWeights), ol.f32p_opt, ol.f32p, ol.f32p] + [C.c_int] * 4 + [ol.i32p_opt, C.c_int]
+    w = ZImageWeights(*[inp["w"][k].ctypes.data for k in ZI_KEYS])
+    rc = fn(x, C.byref(w), inp["mod"], inp["cos"], inp["sin"], inp["seq"], inp["dim"], inp["heads"], inp["ff"], inp["mask"],
+            nthreads)
+    assert rc == 0
+    return x

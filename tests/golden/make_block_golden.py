@@ -7,7 +7,8 @@ Run where the reference sources are present:
 
 Records what the reference's single_block_forward and double_block_forward
 (iris_transformer_flux.c:3341-3477, :2133-2327) and its FLUX.3 block_forward
-(iris_transformer_flux3.c:371-417), compiled unmodified into
+(iris_transformer_flux3.c:371-417) and its Z-Image zi_block_forward
+(iris_transformer_zimage.c:801-880), compiled unmodified into
 oracle/_ref/libiris_ref_generic.so, make of the seeded inputs of
 tests/block_cases.py. Inputs are not stored: block_cases regenerates them.
 """
@@ -89,6 +90,24 @@ def reference_f3_block(r, case, inp):
     return x
 
 
+def reference_zi_block(r, case, inp):
+    """x after a Z-Image block by the reference's CPU code (zi_block_forward
+    with the separate fp32 matrices the fused device weights are made of, its
+    own RoPE tables from the position ids, the padding mask)."""
+    import ctypes as C
+    dim, ff, w = inp["dim"], inp["ff"], inp["w"]
+    qkv, ff_in = ol.from_bf16(w["qkv"]), ol.from_bf16(w["ff_in"])
+    mats = [qkv[:dim], qkv[dim:2 * dim], qkv[2 * dim:], ol.from_bf16(w["proj"]), ff_in[:ff], ff_in[ff:],
+            ol.from_bf16(w["ff_out"]), w["attn_norm1"], w["attn_norm2"], w["ffn_norm1"], w["ffn_norm2"]]
+    mats = [np.ascontiguousarray(m, np.float32) for m in mats]
+    ptrs = (C.c_void_p * 11)(*[m.ctypes.data for m in mats])
+    x = inp["x"].copy()
+    rc = r.ref_zi_block(x, ptrs, w["norm_q"], w["norm_k"], inp["mod"], np.ascontiguousarray(inp["pos"].reshape(-1)),
+                        inp["mask"], inp["seq"], inp["heads"], bc.D, ff)
+    assert rc == 0
+    return x
+
+
 def main():
     r = ol.ref("generic")
     if r is None:
@@ -105,6 +124,9 @@ def main():
     for case in (bc.F3_SMALL,):
         inp = bc.f3_inputs(case)
         out["f3/" + case["name"]] = reference_f3_block(r, case, inp)[::2]          # every second row
+    for case in (bc.ZI_SMALL,):
+        inp = bc.zi_inputs(case)
+        out["zi/" + case["name"]] = reference_zi_block(r, case, inp)[::2]          # every second row
     path = os.path.join(HERE, "reference_block.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -78,6 +78,8 @@ def oracle():
     _sig(lib, "orc_linear", [f32p, INT, u16p, INT, u16p, INT, INT, INT, INT, INT])
     _sig(lib, "orc_single_block", [f32p, u16p, u16p, f32p, f32p, f32p, f32p, f32p, INT, INT, INT, INT,
                                    i32p_opt, INT], INT)
+    _sig(lib, "orc_rms_norm_mod", [u16p, f32p, f32p, f32p_opt, INT, INT, FLT])
+    _sig(lib, "orc_rms_norm_residual", [f32p, f32p, f32p, f32p_opt, INT, INT, FLT])
     _sig(lib, "orc_compare_heads", [C.c_void_p, INT, C.c_void_p, INT, INT, INT, INT, i32p_opt, INT, f32p, f32p])
     return lib
 
@@ -116,6 +118,7 @@ def ref(kind="generic"):
     _sig(lib, "ref_f3_block", [f32p, C.c_void_p, f32p, f32p, i32p, i32p, C.c_void_p, INT, f32p, f32p, INT, INT, INT, INT, FLT], INT)
     _sig(lib, "ref_zi_qk_norm", [f32p, f32p, INT, INT, INT, FLT])
     _sig(lib, "ref_zi_apply_rope", [f32p, i32p, INT, INT, INT])
+    _sig(lib, "ref_zi_block", [f32p, C.c_void_p, f32p, f32p, f32p_opt, i32p, i32p_opt, INT, INT, INT, INT], INT)
     _sig(lib, "ref_zi_attention_identity", [f32p, f32p, i32p, i32p_opt, INT, INT, INT], INT)
     if kind == "blas":
         _sig(lib, "openblas_set_num_threads", [INT])

@@ -153,3 +153,45 @@ def test_one_segment_is_the_single_block():
     inp = bc.block_inputs(bc.SMALL)
     seg = dict(inp, seg_start=np.array([0], np.int32), seg_len=np.array([inp["seq"]], np.int32), seg_mod=[inp["mod"]])
     assert np.array_equal(bc.oracle_f3_block(seg), bc.oracle_block(inp))
+
+
+def test_rms_norm_rows_against_float64():
+    o = ol.oracle()
+    rows, dim = 7, 200
+    x, a = ol.randn(1, rows, dim) * 2, ol.randn(2, rows, dim)
+    w, m = (1 + 0.1 * ol.randn(3, dim)).astype(np.float32), (0.5 * ol.randn(4, dim)).astype(np.float32)
+    x64 = x.astype(np.float64)
+    n = x64 / np.sqrt((x64 ** 2).mean(1, keepdims=True) + 1e-5) * w
+    for scale in (m, None):
+        out = np.zeros((rows, dim), np.uint16)
+        o.orc_rms_norm_mod(out, x, w, scale, rows, dim, 1e-5)
+        want = n * (1 + scale) if scale is not None else n
+        assert (np.abs(ol.from_bf16(out) - want) <= bf16_ulp(want)).all()
+    a64 = a.astype(np.float64)
+    na = a64 / np.sqrt((a64 ** 2).mean(1, keepdims=True) + 1e-5) * w
+    for gate in (m, None):
+        y = x.copy()
+        o.orc_rms_norm_residual(y, a, w, gate, rows, dim, 1e-5)
+        np.testing.assert_allclose(y, x64 + (np.tanh(gate) if gate is not None else 1.0) * na, rtol=2e-6, atol=2e-6)
+
+
+@pytest.mark.parametrize("modulated", [True, False], ids=["modulated", "context-refiner"])
+def test_zimage_block_restatement_against_reference_build(modulated):
+    r = ol.ref("generic")
+    if r is None:
+        pytest.skip("oracle/_ref is not built here")
+    inp = bc.zi_inputs(bc.ZI_MID, seed=123, modulated=modulated)
+    want = mg.reference_zi_block(r, bc.ZI_MID, inp)
+    rel, cos = bc.delta_metrics(bc.oracle_zi_block(inp), want, inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_zimage_block_restatement_against_recorded_reference():
+    """One Z-Image block with padded image and caption rows under the key
+    mask, against the recorded output of zi_block_forward
+    (iris_transformer_zimage.c:801-880)."""
+    gold = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_block.npz")))
+    inp = bc.zi_inputs(bc.ZI_SMALL)
+    assert inp["mask"] is not None and not inp["mask"].all()
+    rel, cos = bc.delta_metrics(bc.oracle_zi_block(inp)[::2], gold["zi/" + bc.ZI_SMALL["name"]], inp["x"][::2])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)

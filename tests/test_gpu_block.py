@@ -426,3 +426,90 @@ def test_segments_must_tile_the_rows(lib):
         lib.iris_b200_clear_error()
     finally:
         d.free()
+
+
+# ---------------------------------------------------------------------------
+# Z-Image block and its row operators
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,dim", [(40, 3840), (9, 512), (5, 4100), (6, 1030)])
+def test_rms_norm_rows(lib, rows, dim):
+    o = ol.oracle()
+    x, a = (ol.randn(rows, rows, dim) * 2).astype(np.float32), ol.randn(rows + 1, rows, dim)
+    w, m = (1 + 0.1 * ol.randn(3, dim)).astype(np.float32), (0.5 * ol.randn(4, dim)).astype(np.float32)
+    d = Dev(lib)
+    try:
+        dx, da, dw, dm, dout = d.put(x), d.put(a), d.put(w), d.put(m), d.new(rows * dim * 2)
+        for scale, ps in ((m, dm), (None, None)):
+            if scale is None:
+                lib.iris_dev_rms_norm(dout, dx, dw, rows, dim, 1e-5)
+            else:
+                lib.iris_dev_rms_norm_mod(dout, dx, dw, ps, rows, dim, 1e-5)
+            got = lib.to_host(dout, (rows, dim), np.uint16)
+            lib.check()
+            want = np.zeros((rows, dim), np.uint16)
+            o.orc_rms_norm_mod(want, x, w, scale, rows, dim, 1e-5)
+            fw = ol.from_bf16(want)
+            assert (got != want).mean() < 0.02
+            assert (np.abs(ol.from_bf16(got) - fw) <= bf16_ulp(fw) * 1.01).all()
+        for gate, pg in ((m, dm), (None, None)):
+            dy = d.put(x)
+            lib.iris_dev_rms_norm_residual(dy, da, dw, pg, rows, dim, 1e-5)
+            got = lib.to_host(dy, (rows, dim), np.float32)
+            lib.check()
+            want = x.copy()
+            o.orc_rms_norm_residual(want, a, w, gate, rows, dim, 1e-5)
+            np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    finally:
+        d.free()
+
+
+def device_zi_block(lib, inp):
+    d = Dev(lib)
+    try:
+        dx = d.put(inp["x"])
+        scratch = d.new(lib.iris_b200_zimage_block_scratch_bytes(inp["seq"], inp["dim"], inp["ff"]))
+        w = bc.ZImageWeights(*[d.put(inp["w"][k]) for k in bc.ZI_KEYS])
+        dmod = d.put(inp["mod"]) if inp["mod"] is not None else None
+        dcos, dsin = d.put(inp["cos"]), d.put(inp["sin"])
+        dm = d.put(np.ascontiguousarray(inp["mask"], np.int32)) if inp["mask"] is not None else None
+        rc = lib.iris_b200_zimage_block(dx, scratch, C.addressof(w), dmod, dcos, dsin, inp["seq"], inp["dim"], inp["heads"],
+                                        inp["ff"], dm)
+        assert rc == 0
+        out = lib.to_host(dx, inp["x"].shape, np.float32)
+        lib.check()
+        return out
+    finally:
+        d.free()
+
+
+@pytest.mark.parametrize("case,modulated", [(bc.ZI_SMALL, True), (bc.ZI_SMALL, False), (bc.ZI_MID, True),
+                                            (bc.ZI_30_HEADS, True)], ids=lambda v: v["name"] if isinstance(v, dict) else str(v))
+def test_zimage_block_against_the_restatement(lib, case, modulated):
+    inp = bc.zi_inputs(case, modulated=modulated)
+    got = device_zi_block(lib, inp)
+    rel, cos = bc.delta_metrics(got, bc.oracle_zi_block(inp), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_zimage_block_against_the_recorded_reference(lib):
+    import os
+    gold = dict(np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_block.npz")))
+    inp = bc.zi_inputs(bc.ZI_SMALL)
+    rel, cos = bc.delta_metrics(device_zi_block(lib, inp)[::2], gold["zi/" + bc.ZI_SMALL["name"]], inp["x"][::2])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+
+
+def test_zimage_block_argument_checks(lib):
+    d = Dev(lib)
+    try:
+        p = d.new(1 << 16)
+        good = bc.ZImageWeights(*[p] * 10)
+        bad = bc.ZImageWeights(*([p] * 9 + [None]))
+        assert lib.iris_b200_zimage_block(p, p, C.addressof(bad), p, p, p, 8, 256, 2, 64, None) == 1
+        assert lib.iris_b200_zimage_block(p, p, C.addressof(good), p, p, p, 8, 250, 2, 64, None) == 1
+        assert lib.iris_b200_zimage_block(p, p + 8, C.addressof(good), p, p, p, 8, 256, 2, 64, None) == 1
+        assert lib.iris_b200_zimage_block_scratch_bytes(8, 256, 0) == 0
+        lib.iris_b200_clear_error()
+    finally:
+        d.free()
