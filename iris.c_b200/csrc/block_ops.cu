@@ -69,48 +69,44 @@ __device__ __forceinline__ float block_sum(float v, float *sh) {
     return t;
 }
 
-/* One warp per row, the row in registers between the three passes (mean,
- * variance about the mean, output): no block barrier, one read of x. VPL
- * float4 per lane, so dims up to 128 * VPL. Two-pass variance as in the
- * reference. */
-template <int VPL>
-__global__ void __launch_bounds__(kRowThreads)
-k_layer_norm_mod_warp(uint16_t *__restrict__ out, const float *__restrict__ x, const __grid_constant__ RowMods mods, int rows,
+/* One block per row at a time, the row in registers (VPT float4 per thread,
+ * so dims up to 1024 * VPT) between the three passes: mean, variance about
+ * the mean (two-pass, as in the reference), output. Eight blocks per SM keep
+ * enough loads in flight; one warp per row was measured slower (3.2 against
+ * 4.8 TB/s at 4608 x 3072). */
+template <int VPT>
+__global__ void __launch_bounds__(kRowThreads, VPT <= 2 ? 8 : 6)
+k_layer_norm_mod_rows(uint16_t *__restrict__ out, const float *__restrict__ x, const __grid_constant__ RowMods mods, int rows,
                       int dim, float eps) {
-    const int lane = threadIdx.x & 31;
-    const int warps = (gridDim.x * kRowThreads) >> 5;
+    __shared__ float sh[kRowThreads / 32];
     const int nvec = dim >> 2;
     const float inv_dim = 1.0f / (float)dim;
-    for (int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5; row < rows; row += warps) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * dim);
         uint2 *o = reinterpret_cast<uint2 *>(out + (size_t)row * dim);
         const int seg = segment_of(mods, row);
         const float *shift = mods.shift[seg], *scale = mods.scale[seg];
-        float4 v[VPL];
+        float4 v[VPT];
         float s = 0.0f;
 #pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            const int i = lane + 32 * k;
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * kRowThreads;
             v[k] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
             s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
         }
-#pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
-        const float mean = s * inv_dim;
+        const float mean = block_sum(s, sh) * inv_dim;
         float q = 0.0f;
 #pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            if (lane + 32 * k < nvec) {
+        for (int k = 0; k < VPT; k++) {
+            if (threadIdx.x + k * kRowThreads < nvec) {
                 const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
                 q += (a * a + b * b) + (c * c + d * d);
             }
         }
+        const float inv = rsqrtf(block_sum(q, sh) * inv_dim + eps);
 #pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o2);
-        const float inv = rsqrtf(q * inv_dim + eps);
-#pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            const int i = lane + 32 * k;
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * kRowThreads;
             if (i >= nvec) continue;
             float n[4] = {(v[k].x - mean) * inv, (v[k].y - mean) * inv, (v[k].z - mean) * inv, (v[k].w - mean) * inv};
             if (scale) {
@@ -156,33 +152,31 @@ k_layer_norm_mod_any(uint16_t *__restrict__ out, const float *__restrict__ x, co
     }
 }
 
-/* RMSNorm rows, one warp per row with the row in registers. RESIDUAL false:
- * out (bf16) = x * inv * w * (1 + scale); true: xres (fp32) += tanh(gate) *
- * x * inv * w, where x is the projection result. scale / gate may be NULL. */
-template <int VPL, bool RESIDUAL>
-__global__ void __launch_bounds__(kRowThreads)
-k_rms_norm_warp(uint16_t *__restrict__ out, float *__restrict__ xres, const float *__restrict__ x,
+/* RMSNorm rows, one block per row at a time with the row in registers.
+ * RESIDUAL false: out (bf16) = x * inv * w * (1 + scale); true: xres (fp32) +=
+ * tanh(gate) * x * inv * w, where x is the projection result. scale / gate
+ * may be NULL. */
+template <int VPT, bool RESIDUAL>
+__global__ void __launch_bounds__(kRowThreads, VPT <= 2 ? 8 : 6)
+k_rms_norm_rows(uint16_t *__restrict__ out, float *__restrict__ xres, const float *__restrict__ x,
                 const float *__restrict__ w, const float *__restrict__ mod, int rows, int dim, float eps) {
-    const int lane = threadIdx.x & 31;
-    const int warps = (gridDim.x * kRowThreads) >> 5;
+    __shared__ float sh[kRowThreads / 32];
     const int nvec = dim >> 2;
     const float inv_dim = 1.0f / (float)dim;
-    for (int row = (blockIdx.x * kRowThreads + threadIdx.x) >> 5; row < rows; row += warps) {
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * dim);
-        float4 v[VPL];
+        float4 v[VPT];
         float s = 0.0f;
 #pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            const int i = lane + 32 * k;
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * kRowThreads;
             v[k] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
             s += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
         }
+        const float inv = rsqrtf(block_sum(s, sh) * inv_dim + eps);
 #pragma unroll
-        for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
-        const float inv = rsqrtf(s * inv_dim + eps);
-#pragma unroll
-        for (int k = 0; k < VPL; k++) {
-            const int i = lane + 32 * k;
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * kRowThreads;
             if (i >= nvec) continue;
             const float4 w4 = reinterpret_cast<const float4 *>(w)[i];
             float n[4] = {v[k].x * inv * w4.x, v[k].y * inv * w4.y, v[k].z * inv * w4.z, v[k].w * inv * w4.w};
@@ -287,15 +281,15 @@ int layer_norm_mods(uint16_t *out, const float *x, const RowMods &mods, int rows
     }
     if (rows == 0) return IRIS_B200_OK;
     const int nvec = dim / 4;
-    bool vec = dim % 4 == 0 && nvec <= 32 * 32 && aligned16(x) && ((uintptr_t)out & 7) == 0;
+    bool vec = dim % 4 == 0 && nvec <= 4 * kRowThreads && aligned16(x) && ((uintptr_t)out & 7) == 0;
     for (int i = 0; i < mods.n; i++) vec = vec && aligned16(mods.shift[i]) && aligned16(mods.scale[i]);
     if (vec) {
-        const unsigned grid = blocks_for((size_t)rows, kRowThreads / 32, 8);
-#define IRIS_LN_LAUNCH(VPL) k_layer_norm_mod_warp<VPL><<<grid, kRowThreads, 0, g.stream>>>(out, x, mods, rows, dim, eps)
-        if (nvec <= 32 * 8) IRIS_LN_LAUNCH(8);
-        else if (nvec <= 32 * 16) IRIS_LN_LAUNCH(16);
-        else if (nvec <= 32 * 24) IRIS_LN_LAUNCH(24);
-        else IRIS_LN_LAUNCH(32);
+        const unsigned grid = blocks_for((size_t)rows, 1, 8);
+#define IRIS_LN_LAUNCH(VPT) k_layer_norm_mod_rows<VPT><<<grid, kRowThreads, 0, g.stream>>>(out, x, mods, rows, dim, eps)
+        if (nvec <= kRowThreads) IRIS_LN_LAUNCH(1);
+        else if (nvec <= 2 * kRowThreads) IRIS_LN_LAUNCH(2);
+        else if (nvec <= 3 * kRowThreads) IRIS_LN_LAUNCH(3);
+        else IRIS_LN_LAUNCH(4);
 #undef IRIS_LN_LAUNCH
     } else {
         k_layer_norm_mod_any<<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, x, mods, rows, dim, eps);
@@ -322,16 +316,16 @@ int rms_norm_rows(uint16_t *out, float *xres, const float *x, const float *w, co
     }
     if (rows == 0) return IRIS_B200_OK;
     const int nvec = dim / 4;
-    const bool vec = dim % 4 == 0 && nvec <= 32 * 32 && aligned16(x) && aligned16(w) && aligned16(mod) && aligned16(xres) &&
-                     ((uintptr_t)out & 7) == 0;
+    const bool vec = dim % 4 == 0 && nvec <= 4 * kRowThreads && aligned16(x) && aligned16(w) && aligned16(mod) &&
+                     aligned16(xres) && ((uintptr_t)out & 7) == 0;
     if (vec) {
-        const unsigned grid = blocks_for((size_t)rows, kRowThreads / 32, 8);
-#define IRIS_RMS_LAUNCH(VPL) \
-    k_rms_norm_warp<VPL, RESIDUAL><<<grid, kRowThreads, 0, g.stream>>>(out, xres, x, w, mod, rows, dim, eps)
-        if (nvec <= 32 * 8) IRIS_RMS_LAUNCH(8);
-        else if (nvec <= 32 * 16) IRIS_RMS_LAUNCH(16);
-        else if (nvec <= 32 * 24) IRIS_RMS_LAUNCH(24);
-        else IRIS_RMS_LAUNCH(32);
+        const unsigned grid = blocks_for((size_t)rows, 1, 8);
+#define IRIS_RMS_LAUNCH(VPT) \
+    k_rms_norm_rows<VPT, RESIDUAL><<<grid, kRowThreads, 0, g.stream>>>(out, xres, x, w, mod, rows, dim, eps)
+        if (nvec <= kRowThreads) IRIS_RMS_LAUNCH(1);
+        else if (nvec <= 2 * kRowThreads) IRIS_RMS_LAUNCH(2);
+        else if (nvec <= 3 * kRowThreads) IRIS_RMS_LAUNCH(3);
+        else IRIS_RMS_LAUNCH(4);
 #undef IRIS_RMS_LAUNCH
     } else {
         k_rms_norm_any<RESIDUAL><<<blocks_for((size_t)rows, 1, 8), kRowThreads, 0, g.stream>>>(out, xres, x, w, mod, rows, dim, eps);

@@ -296,41 +296,77 @@ __device__ __forceinline__ void scatter_rows_f32(const uint32_t *src, const Para
     __syncwarp();
 }
 
-/* 32 rows x 32 fp32 columns of one warp to an fp32 matrix, stored or added
- * in place with a per-column gate (ncols a multiple of 4). Every element of
- * the matrix belongs to exactly one warp of one tile, so the read-modify-write
- * needs no atomics. */
-__device__ __forceinline__ void rows_f32(const uint32_t *src, const Params &p, const float *gate, int wrow0, int nrows, int c0,
-                                         int ncols, unsigned char *stage_w, int lane) {
-#pragma unroll
-    for (int c8 = 0; c8 < 8; c8++)
-        *reinterpret_cast<uint4 *>(stage_w + lane * 128 + ((c8 ^ (lane & 7)) << 4)) =
-            make_uint4(src[4 * c8], src[4 * c8 + 1], src[4 * c8 + 2], src[4 * c8 + 3]);
-    __syncwarp();
+/* fp32 destination of a tile (scatter == 2). Each warp owns 32 rows; it goes
+ * through the tile in chunks of 32 columns: the accumulator chunk comes from
+ * TMEM, is transposed through the swizzled staging area so that eight lanes
+ * cover 128 contiguous bytes of a row, and is stored, or added in place with
+ * a per-column gate. Every element belongs to exactly one warp of one tile,
+ * so the read-modify-write needs no atomics. The old values of chunk c + 1
+ * are fetched before chunk c is processed: a load issued next to the store it
+ * feeds would leave every row segment waiting a full memory round trip. */
+struct XChunk {
+    float4 v[8];
+};
+
+__device__ __forceinline__ const float *gate_of_row(const Params &p, const float *group_gate, int row) {
+    if (p.nseg == 0) return group_gate;
+    int i = 0;
+    while (i + 1 < p.nseg && row >= p.seg_end[i]) i++;
+    return p.seg_gate[i];
+}
+
+__device__ __forceinline__ void load_old(XChunk &x, const Params &p, int wrow0, int nrows, int c0, int lane) {
     const int ch = lane & 7;
-    const bool col_ok = ch * 4 < ncols;
-    float4 g4 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-    if (gate && col_ok && p.nseg == 0) g4 = *reinterpret_cast<const float4 *>(gate + c0 + ch * 4);
+    const int ncols = p.out - c0;
 #pragma unroll
     for (int k = 0; k < 8; k++) {
         const int r = k * 4 + (lane >> 3);
-        float4 v = *reinterpret_cast<const float4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4));
-        if (r < nrows && col_ok) {
-            if (p.nseg > 0) {
-                int i = 0;
-                while (i + 1 < p.nseg && wrow0 + r >= p.seg_end[i]) i++;
-                const float *gs = p.seg_gate[i];
-                g4 = gs ? *reinterpret_cast<const float4 *>(gs + c0 + ch * 4) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-            }
-            float4 *dst = reinterpret_cast<float4 *>(p.y32 + (size_t)(wrow0 + r) * p.ld32 + c0 + ch * 4);
-            if (p.accumulate) {
-                const float4 x = *dst;
-                v = make_float4(fmaf(g4.x, v.x, x.x), fmaf(g4.y, v.y, x.y), fmaf(g4.z, v.z, x.z), fmaf(g4.w, v.w, x.w));
-            }
-            *dst = v;
-        }
+        x.v[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (r < nrows && ch * 4 < ncols)
+            x.v[k] = *reinterpret_cast<const float4 *>(p.y32 + (size_t)(wrow0 + r) * p.ld32 + c0 + ch * 4);
     }
-    __syncwarp();
+}
+
+__device__ __forceinline__ void tile_f32(const Params &p, const float *group_gate, uint32_t tmem_tile, int wrow0, int nrows,
+                                         int col0, unsigned char *stage_w, int lane) {
+    const int ch = lane & 7;
+    XChunk cur, next;
+    if (p.accumulate) load_old(next, p, wrow0, nrows, col0, lane);
+#pragma unroll 1
+    for (int c = 0; c < kTileN / 32; c++) {
+        const int c0 = col0 + c * 32;
+        if (c0 >= p.out) break;
+        uint32_t acc[32];
+        tmem_ld32(tmem_tile + c * 32, acc);
+        cur = next;
+        if (p.accumulate && c + 1 < kTileN / 32 && c0 + 32 < p.out) load_old(next, p, wrow0, nrows, c0 + 32, lane);
+        tc_wait_ld();
+#pragma unroll
+        for (int c8 = 0; c8 < 8; c8++)
+            *reinterpret_cast<uint4 *>(stage_w + lane * 128 + ((c8 ^ (lane & 7)) << 4)) =
+                make_uint4(acc[4 * c8], acc[4 * c8 + 1], acc[4 * c8 + 2], acc[4 * c8 + 3]);
+        __syncwarp();
+        const bool col_ok = ch * 4 < p.out - c0;
+        float4 g4 = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (p.nseg == 0 && group_gate && col_ok) g4 = *reinterpret_cast<const float4 *>(group_gate + c0 + ch * 4);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int r = k * 4 + (lane >> 3);
+            float4 v = *reinterpret_cast<const float4 *>(stage_w + r * 128 + ((ch ^ (r & 7)) << 4));
+            if (r < nrows && col_ok) {
+                if (p.nseg > 0) {
+                    const float *gs = gate_of_row(p, group_gate, wrow0 + r);
+                    g4 = gs ? *reinterpret_cast<const float4 *>(gs + c0 + ch * 4) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                }
+                if (p.accumulate) {
+                    const float4 x = cur.v[k];
+                    v = make_float4(fmaf(g4.x, v.x, x.x), fmaf(g4.y, v.y, x.y), fmaf(g4.z, v.z, x.z), fmaf(g4.w, v.w, x.w));
+                }
+                *reinterpret_cast<float4 *>(p.y32 + (size_t)(wrow0 + r) * p.ld32 + c0 + ch * 4) = v;
+            }
+        }
+        __syncwarp();
+    }
 }
 
 __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned char *stage, const float *w_smem,
@@ -352,6 +388,13 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
         const int wrow0 = m0 + quarter * 32;
         const int nrows = rt.row_end - wrow0 < 32 ? (rt.row_end - wrow0 < 0 ? 0 : rt.row_end - wrow0) : 32;
         const bool row_ok = row < rt.row_end;
+        if (p.scatter == 2) {
+            tile_f32(p, rt.grp ? p.gate1 : p.gate, tmem + lane_base + buf * kTileN, wrow0, nrows, n0, stage_w, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(c.bars + (BAR_ACC_EMPTY + buf) * 8);
+            continue;
+        }
         if (nt >= p.glu_tile0) {
             const int cbase = (nt - p.glu_tile0) * (kTileN / 2);            /* column of y2 */
 #pragma unroll 1
@@ -394,8 +437,7 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
                 for (int sub = 0; sub < 4; sub++) {
                     const int c0 = col0 + sub * 32;
                     const int ncols = p.out - c0 < 32 ? (p.out - c0 < 0 ? 0 : p.out - c0) : 32;
-                    if (p.scatter == 1) scatter_rows_f32(acc + sub * 32, p, wrow0, nrows, c0, ncols, stage_w, lane);
-                    else rows_f32(acc + sub * 32, p, rt.grp ? p.gate1 : p.gate, wrow0, nrows, c0, ncols, stage_w, lane);
+                    scatter_rows_f32(acc + sub * 32, p, wrow0, nrows, c0, ncols, stage_w, lane);
                 }
                 continue;
             }
