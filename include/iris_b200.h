@@ -163,6 +163,14 @@ int iris_b200_linear_glu(uint16_t *qkv, int ldq, uint16_t *act, int lda,
                          const float *wq, const float *wk,
                          const float *rope_cos, const float *rope_sin, float eps);
 
+/* The linear layers run as pairs of CTAs on 256 x 256 tiles
+ * (tcgen05.mma.cta_group::2: each CTA stages half of the W tile, a third less
+ * shared-memory traffic per SM) unless this is switched off, which leaves
+ * single CTAs on 128 x 256 tiles (same results to the bit). enable: 1 on
+ * (the default), 0 off, negative: only report. Returns the previous setting.
+ * The row-parallel scatter mode always runs single CTAs. */
+int iris_b200_linear_cta_pairs(int enable);
+
 /* How a linear-layer launch cuts its work, as host arithmetic (for schedulers
  * and tests; nothing is launched): rows [0, split) and [split, rows) are the
  * two row groups (split == rows: one), `out` ordinary output columns followed

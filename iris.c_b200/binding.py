@@ -59,6 +59,7 @@ SIGNATURES = {
     "iris_b200_mark_elapsed_ms": (FLT, [INT, INT]),
     "iris_b200_qk_norm_rope": (INT, [VP, VP, INT, VP, VP, VP, VP, INT, INT, INT, FLT, INT]),
     "iris_b200_linear_qk_norm_rope": (INT, [VP, INT, VP, VP, INT, INT, INT, INT, VP, VP, VP, VP, FLT]),
+    "iris_b200_linear_cta_pairs": (INT, [INT]),
     "iris_b200_linear_plan": (INT, [INT, INT, INT, INT, INT, INT, VP, VP, VP, VP, INT]),
     "iris_b200_linear_glu": (INT, [VP, INT, VP, INT, VP, VP, INT, INT, INT, INT, VP, VP, VP, VP, FLT]),
     "iris_b200_linear_residual": (INT, [VP, INT, VP, INT, VP, INT, VP, INT, INT, INT]),

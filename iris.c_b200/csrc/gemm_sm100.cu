@@ -109,6 +109,7 @@ struct Params {
      * group are computed and not stored. split == rows: one group. */
     int split, tiles_m0;
     const float *wq1, *wk1, *gate1;
+    int ctas;                   /* 1, or 2: a row tile is 256 rows worked on by a CTA pair (k_linear_pair_sm100) */
     /* Gates by runs of rows that share the weights (the segments of a FLUX.3
      * block: text, image, reference rows, each with its own modulation):
      * rows below seg_end[i] (and not below seg_end[i - 1]) take seg_gate[i].
@@ -136,9 +137,10 @@ struct Params {
 struct RowTile {
     int m0, row_end, grp;
 };
-__host__ __device__ __forceinline__ RowTile row_tile(const Params &p, int tm) {
-    if (tm < p.tiles_m0) return {tm * kTileM, p.split, 0};
-    return {p.split + (tm - p.tiles_m0) * kTileM, p.rows, 1};
+__host__ __device__ __forceinline__ RowTile row_tile(const Params &p, int tm, int rank = 0) {
+    const int span = kTileM * p.ctas;           /* rows of a row tile; CTA `rank` of a pair takes the second half */
+    if (tm < p.tiles_m0) return {tm * span + rank * kTileM, p.split, 0};
+    return {p.split + (tm - p.tiles_m0) * span + rank * kTileM, p.rows, 1};
 }
 
 /* Work item `tile` of the list: its row tile and its column tile. */
@@ -156,6 +158,7 @@ struct Ctx {
     volatile uint32_t *abort_flag;
     unsigned int *status;
     unsigned long long wait_ns;
+    uint32_t peer_abort;        /* shared::cluster address of the other CTA's abort flag; 0: no pair */
 };
 
 __device__ __forceinline__ bool wait(const Ctx &c, int idx, uint32_t parity, int site) {
@@ -168,6 +171,7 @@ __device__ __forceinline__ bool wait(const Ctx &c, int idx, uint32_t parity, int
             if (*c.abort_flag) return false;
             if (global_ns() - t0 > c.wait_ns || spin > (1u << 26)) {
                 *c.abort_flag = 1u;
+                if (c.peer_abort) st_cluster_u32(c.peer_abort, 1u);
                 if (atomicCAS(c.status, 0u, 1u) == 0u) {
                     c.status[1] = (unsigned)site;
                     c.status[2] = blockIdx.x;
@@ -369,20 +373,35 @@ __device__ __forceinline__ void tile_f32(const Params &p, const float *group_gat
     }
 }
 
+/* Where an epilogue finds its tiles and barriers: CTA `rank` of a pair (0 for
+ * a single CTA) takes the tiles first, first + stride, ...; acc_empty_remote
+ * != 0: the barrier array of the pair's first CTA (shared::cluster address),
+ * on which both CTAs' epilogue warps arrive. */
+struct EpiSched {
+    int first, stride, rank;
+    int bar_acc_full, bar_acc_empty;
+    uint32_t acc_empty_remote;
+};
+
+__device__ __forceinline__ void acc_release(const Ctx &c, const EpiSched &e, int buf) {
+    if (e.acc_empty_remote) mbar_arrive_cluster(e.acc_empty_remote + (e.bar_acc_empty + buf) * 8);
+    else mbar_arrive(c.bars + (e.bar_acc_empty + buf) * 8);
+}
+
 __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned char *stage, const float *w_smem,
-                                         uint32_t tmem) {
+                                         uint32_t tmem, const EpiSched &e) {
     const int lane = threadIdx.x & 31;
     const int quarter = (threadIdx.x >> 5) & 3;                 /* TMEM lane quarter of this warp */
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     unsigned char *stage_w = stage + quarter * 4096;
-    for (int tile = blockIdx.x, n = 0; tile < p.tiles_m * p.tiles_n; tile += gridDim.x, n++) {
+    for (int tile = e.first, n = 0; tile < p.tiles_m * p.tiles_n; tile += e.stride, n++) {
         const int buf = n & 1;
         int tm, nt;
         tile_of(p, tile, &tm, &nt);
-        const RowTile rt = row_tile(p, tm);
+        const RowTile rt = row_tile(p, tm, e.rank);
         const int m0 = rt.m0, n0 = nt * kTileN;     /* n0: ordinary tiles only */
-        if (!__all_sync(0xffffffffu, wait(c, BAR_ACC_FULL + buf, (n >> 1) & 1u, 430 + buf))) return;
+        if (!__all_sync(0xffffffffu, wait(c, e.bar_acc_full + buf, (n >> 1) & 1u, 430 + buf))) return;
         tc_fence_after();
         const int row = m0 + row_in_tile;
         const int wrow0 = m0 + quarter * 32;
@@ -392,7 +411,7 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
             tile_f32(p, rt.grp ? p.gate1 : p.gate, tmem + lane_base + buf * kTileN, wrow0, nrows, n0, stage_w, lane);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(c.bars + (BAR_ACC_EMPTY + buf) * 8);
+            if (lane == 0) acc_release(c, e, buf);
             continue;
         }
         if (nt >= p.glu_tile0) {
@@ -419,7 +438,7 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(c.bars + (BAR_ACC_EMPTY + buf) * 8);
+            if (lane == 0) acc_release(c, e, buf);
             continue;
         }
 #pragma unroll 1
@@ -488,7 +507,7 @@ __device__ __forceinline__ void epilogue(const Ctx &c, const Params &p, unsigned
         /* Every read of this accumulator has been waited for. */
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(c.bars + (BAR_ACC_EMPTY + buf) * 8);
+        if (lane == 0) acc_release(c, e, buf);
     }
 }
 
@@ -505,6 +524,7 @@ k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
     c.abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemAbort);
     c.status = p.status;
     c.wait_ns = p.wait_ns;
+    c.peer_abort = 0u;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kSmemTmemPtr);
     float *w_smem = reinterpret_cast<float *>(smem_gen + kSmemW);
 
@@ -543,7 +563,8 @@ k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
     } else if (warp == 1) {
         mma_issuer(c, p, smem, tmem);
     } else {
-        epilogue(c, p, smem_gen + kSmemStage, w_smem, tmem);
+        const EpiSched e = {(int)blockIdx.x, (int)gridDim.x, 0, BAR_ACC_FULL, BAR_ACC_EMPTY, 0u};
+        epilogue(c, p, smem_gen + kSmemStage, w_smem, tmem, e);
     }
 
     if (p.scatter == 1) __threadfence_system();          /* this thread's rows are out before the CTA counts itself out */
@@ -570,6 +591,173 @@ k_linear_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ 
                     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.arrive[q]), "r"(p.seq) : "memory");
             }
         }
+    }
+}
+
+/* ------------------------------------------------------------------------
+ * CTA pairs: the same GEMM with a 256 x 256 tile per pair of CTAs
+ * (tcgen05.mma.cta_group::2). Each CTA holds 128 rows of x and HALF of the W
+ * tile per stage (32 KB instead of 48 KB, so six stages fit), the pair's
+ * first CTA issues the MMAs, which read both halves of W from the two CTAs'
+ * shared memory and write 128 x 256 accumulators into each CTA's TMEM. Per
+ * unit of work every SM moves a third less through its shared memory, which
+ * is what bounds the single-CTA kernel. Loads are plain TMA loads (each CTA
+ * fetches what it holds; nothing is multicast); their byte counts go to the
+ * first CTA's FULL barrier. EMPTY and ACC_FULL barriers of both CTAs are
+ * signalled by the MMA commits; both CTAs' epilogue warps arrive on the first
+ * CTA's ACC_EMPTY barrier. Every wait is bounded as in the single-CTA kernel,
+ * and a CTA that gives up raises the peer's abort flag too.
+ * ------------------------------------------------------------------------ */
+static constexpr int kPairStages = 6;
+static constexpr int kPairBytesB = kBytesB / 2;
+static constexpr int kPairStageBytes = kBytesA + kPairBytesB;      /* 32 KB per CTA */
+static_assert(kPairStages * kPairStageBytes == kSmemStage, "the pair kernel reuses the single-CTA shared-memory layout");
+static constexpr uint32_t kPairIdesc = idesc_bf16(2 * kTileM, kTileN);
+enum {
+    PBAR_FULL = 0,
+    PBAR_EMPTY = PBAR_FULL + kPairStages,
+    PBAR_ACC_FULL = PBAR_EMPTY + kPairStages,
+    PBAR_ACC_EMPTY = PBAR_ACC_FULL + 2,
+    PBAR_DRAIN = PBAR_ACC_EMPTY + 2,
+    PBAR_COUNT
+};
+static constexpr int kPairTmemPtr = PBAR_COUNT * 8;
+static constexpr int kPairAbort = kPairTmemPtr + 4;
+static_assert(kPairAbort + 4 <= 256, "barrier area");
+
+__device__ __forceinline__ void pair_producer(const Ctx &c, const Params &p, const CUtensorMap *tmx, const CUtensorMap *tmw0,
+                                              const CUtensorMap *tmw1, uint32_t smem, int rank, int first, int stride) {
+    const int nkb = (p.in + kBlockK - 1) / kBlockK;
+    const uint32_t full0 = map_to_cta(c.bars + PBAR_FULL * 8, 0);          /* the first CTA's FULL barriers */
+    int issued = 0;
+    bool ok = true;
+    for (int tile = first; ok && tile < p.tiles_m * p.tiles_n; tile += stride) {
+        int tm, nt;
+        tile_of(p, tile, &tm, &nt);
+        const RowTile rt = row_tile(p, tm, rank);
+        const CUtensorMap *tmw = rt.grp ? tmw1 : tmw0;
+        /* this CTA's 128 rows of W: an ordinary tile's first or second half, or the gate or the up rows */
+        int n = nt * kTileN + rank * (kTileN / 2);
+        if (nt >= p.glu_tile0) n = p.glu_col0 + (nt - p.glu_tile0) * (kTileN / 2) + rank * p.glu_cols;
+        for (int kb = 0; kb < nkb; kb++, issued++) {
+            const int s = issued % kPairStages;
+            if (issued >= kPairStages && !(ok = wait(c, PBAR_EMPTY + s, ((issued / kPairStages) - 1) & 1u, 600 + s))) break;
+            if (rank == 0) mbar_expect_tx(c.bars + (PBAR_FULL + s) * 8, 2 * kPairStageBytes);
+            tma_load_2d_pair(smem + s * kPairStageBytes, tmx, kb * kBlockK, rt.m0, full0 + s * 8);
+            tma_load_2d_pair(smem + s * kPairStageBytes + kBytesA, tmw, kb * kBlockK, n, full0 + s * 8);
+        }
+    }
+    if (*c.abort_flag && rank == 0) {
+        /* Nobody may be consuming any more: wait for the pair's copies still in flight. */
+        for (int it = issued > kPairStages ? issued - kPairStages : 0; it < issued; it++)
+            wait(c, PBAR_FULL + it % kPairStages, (it / kPairStages) & 1u, 690);
+    }
+}
+
+__device__ __forceinline__ void pair_mma_issuer(const Ctx &c, const Params &p, uint32_t smem, uint32_t tmem, int first,
+                                                int stride) {
+    const int nkb = (p.in + kBlockK - 1) / kBlockK;
+    const uint32_t hi = (uint32_t)(make_desc(0, 0, 1024 / 16) >> 32);      /* 8 rows of 128 B */
+    const uint32_t lo0 = (uint32_t)make_desc(smem, 1, 0);
+    const bool leader = elect_one();
+    int consumed = 0;
+    bool ok = true;
+    for (int tile = first, n = 0; ok && tile < p.tiles_m * p.tiles_n; tile += stride, n++) {
+        const int buf = n & 1;
+        /* Both CTAs' epilogues have emptied this accumulator (its use two tiles ago). */
+        if (n >= 2 && !(ok = __all_sync(0xffffffffu, wait(c, PBAR_ACC_EMPTY + buf, ((n >> 1) - 1) & 1u, 610 + buf)))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < nkb; kb++, consumed++) {
+            const int s = consumed % kPairStages;
+            if (!(ok = __all_sync(0xffffffffu, wait(c, PBAR_FULL + s, (consumed / kPairStages) & 1u, 620 + s)))) break;
+            tc_fence_after();
+            const uint32_t lo_a = lo0 + ((s * kPairStageBytes) >> 4), lo_b = lo_a + (kBytesA >> 4);
+#pragma unroll
+            for (int ks = 0; ks < kBlockK / 16; ks++) {
+                if (leader)
+                    mma_ss_pair(tmem + buf * kTileN, ((uint64_t)hi << 32) | (lo_a + ks * 2),
+                                ((uint64_t)hi << 32) | (lo_b + ks * 2), kPairIdesc, (kb | ks) != 0);
+            }
+            if (leader) tc_commit_pair(c.bars + (PBAR_EMPTY + s) * 8, 3);
+        }
+        if (ok && leader) tc_commit_pair(c.bars + (PBAR_ACC_FULL + buf) * 8, 3);
+    }
+    if (!ok) {
+        if (leader) tc_commit_pair(c.bars + PBAR_DRAIN * 8, 1);
+        const uint32_t bar = c.bars + PBAR_DRAIN * 8;
+        const unsigned long long t0 = global_ns();
+        while (!mbar_try_wait(bar, 0) && global_ns() - t0 < c.wait_ns) {}
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+k_linear_pair_sm100(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmw,
+                    const __grid_constant__ CUtensorMap tmw1, const __grid_constant__ Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char *smem_gen = smem_raw + (smem - smem_u32(smem_raw));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_cta_rank();
+    const int first = (int)(blockIdx.x >> 1), stride = (int)(gridDim.x >> 1);
+
+    Ctx c;
+    c.bars = smem + kSmemBar;
+    c.abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kPairAbort);
+    c.status = p.status;
+    c.wait_ns = p.wait_ns;
+    c.peer_abort = map_to_cta(smem + kSmemBar + kPairAbort, (uint32_t)(rank ^ 1));
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_gen + kSmemBar + kPairTmemPtr);
+    float *w_smem = reinterpret_cast<float *>(smem_gen + kSmemW);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; s++) {
+            mbar_init(c.bars + (PBAR_FULL + s) * 8, 1);
+            mbar_init(c.bars + (PBAR_EMPTY + s) * 8, 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(c.bars + (PBAR_ACC_FULL + b) * 8, 1);
+            mbar_init(c.bars + (PBAR_ACC_EMPTY + b) * 8, 8);         /* four epilogue warps in each CTA */
+        }
+        mbar_init(c.bars + PBAR_DRAIN * 8, 1);
+        *c.abort_flag = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem + kSmemBar + kPairTmemPtr), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    if (p.norm_cols > 0)
+        for (int i = threadIdx.x; i < 512; i += kThreads) {
+            const float *src = i < 256 ? (i < 128 ? p.wq : p.wk) : (i < 384 ? p.wq1 : p.wk1);
+            w_smem[i] = src[i & 127];
+        }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();               /* the peer's barriers exist before anything arrives on them */
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) pair_producer(c, p, &tmx, &tmw, &tmw1, smem, rank, first, stride);
+    } else if (warp == 1) {
+        if (rank == 0) pair_mma_issuer(c, p, smem, tmem, first, stride);
+    } else {
+        const EpiSched e = {first, stride, rank, PBAR_ACC_FULL, PBAR_ACC_EMPTY, map_to_cta(c.bars, 0)};
+        epilogue(c, p, smem_gen + kSmemStage, w_smem, tmem, e);
+    }
+
+    /* Neither CTA leaves, or frees its TMEM, while the other may still read its
+     * shared memory or arrive on its barriers. */
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
     }
 }
 
@@ -632,28 +820,35 @@ __global__ void k_residual_from_slabs(float *x, const float *slabs, size_t slab_
  * when that does not fit L2 comfortably and all of W is smaller, the list goes
  * through the columns of a row tile first (all of W and 1/tiles_n of the
  * concurrently processed x in flight). */
-static void plan_grid(gemm::Params *p, int rows, int split, int in, int out, int glu_cols, int sm_count) {
+static void plan_grid(gemm::Params *p, int rows, int split, int in, int out, int glu_cols, int sm_count, int ctas = 1) {
     using namespace gemm;
     p->rows = rows;
     p->in = in;
     p->out = out;
     p->split = split;
-    p->tiles_m0 = (split + kTileM - 1) / kTileM;
-    p->tiles_m = p->tiles_m0 + (rows - split + kTileM - 1) / kTileM;
+    p->ctas = ctas;
+    const int span = kTileM * ctas;
+    p->tiles_m0 = (split + span - 1) / span;
+    p->tiles_m = p->tiles_m0 + (rows - split + span - 1) / span;
     p->tiles_n = (out + kTileN - 1) / kTileN;
     p->glu_tile0 = p->tiles_n;
     p->glu_col0 = out;
     p->glu_cols = glu_cols;
     p->tiles_n += (glu_cols + kTileN / 2 - 1) / (kTileN / 2);
-    const double a_tile = (double)kTileM * in * 2, w_tile = (double)kTileN * in * 2;
-    const double m_fast = p->tiles_m * a_tile + ((double)sm_count / (p->tiles_m > 0 ? p->tiles_m : 1) + 1) * w_tile;
+    const double a_tile = (double)span * in * 2, w_tile = (double)kTileN * in * 2;
+    const double m_fast = p->tiles_m * a_tile + ((double)sm_count / ctas / (p->tiles_m > 0 ? p->tiles_m : 1) + 1) * w_tile;
     p->band_n = 1;
     if (m_fast > 96e6 && p->tiles_n * w_tile < m_fast) p->band_n = p->tiles_n;
 }
 
 static int g_gemm_configured = 0;
+static int g_pair_mode = 1;             /* CTA pairs unless iris_b200_linear_cta_pairs(0) */
+static int g_pair_clusters = 0;         /* CTA pairs that can be resident at once */
 
-void gemm_release(void) { g_gemm_configured = 0; }
+void gemm_release(void) {
+    g_gemm_configured = 0;
+    g_pair_clusters = 0;
+}
 
 /* y [rows, out] (row stride ldy) = x [rows, in] . W [out, in]^T; with heads > 0
  * the first 2 * heads * 128 columns are Q and K heads that get the prologue. */
@@ -695,11 +890,36 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
             return IRIS_B200_ECUDA;
         g_gemm_configured = 1;
     }
+    /* CTA pairs for everything but the row-parallel scatter (whose completion count is per CTA) */
+    int ctas = g_pair_mode && !sc ? 2 : 1;
+    if (ctas == 2 && !g_pair_clusters) {
+        if (!cuda_ok(cudaFuncSetAttribute(k_linear_pair_sm100, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+                     "linear smem opt-in"))
+            return IRIS_B200_ECUDA;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(g.sm_count & ~1));
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, k_linear_pair_sm100, &cfg) != cudaSuccess || n < 1) {
+            (void)cudaGetLastError();
+            n = -1;                     /* pairs cannot be placed: stay with single CTAs */
+        }
+        g_pair_clusters = n;
+    }
+    if (ctas == 2 && g_pair_clusters < 1) ctas = 1;
     CUtensorMap tmx, tmw, tmw1;
     const int w_rows = glu ? out + 2 * glu->cols : out;
-    if (!make_tensor_map(&tmx, x, rows, in, ldx, kTileM) ||
-        !make_tensor_map(&tmw, W, w_rows, in, ldw, glu ? kTileN / 2 : kTileN) ||
-        !make_tensor_map(&tmw1, g2 ? g2->W : W, w_rows, in, ldw, glu ? kTileN / 2 : kTileN))
+    const int w_box = glu || ctas == 2 ? kTileN / 2 : kTileN;
+    if (!make_tensor_map(&tmx, x, rows, in, ldx, kTileM) || !make_tensor_map(&tmw, W, w_rows, in, ldw, w_box) ||
+        !make_tensor_map(&tmw1, g2 ? g2->W : W, w_rows, in, ldw, w_box))
         return IRIS_B200_ECUDA;
     Params p = {};
     p.y = y;
@@ -707,7 +927,7 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
     p.rows = rows;
     p.in = in;
     p.out = out;
-    plan_grid(&p, rows, g2 ? g2->split : rows, in, out, glu ? glu->cols : 0, g.sm_count);
+    plan_grid(&p, rows, g2 ? g2->split : rows, in, out, glu ? glu->cols : 0, g.sm_count, ctas);
     p.wq1 = g2 ? g2->wq : wq;
     p.wk1 = g2 ? g2->wk : wk;
     p.gate1 = g2 ? g2->gate : (f32 ? f32->gate : NULL);
@@ -753,6 +973,11 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
     }
 #endif
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    if (ctas == 2) {
+        const unsigned clusters = (unsigned)(tiles < g_pair_clusters ? tiles : g_pair_clusters);
+        k_linear_pair_sm100<<<2 * clusters, kThreads, kSmemBytes, g.stream>>>(tmx, tmw, tmw1, p);
+        return after_launch(op) ? IRIS_B200_OK : IRIS_B200_ECUDA;
+    }
     const unsigned grid = (unsigned)(tiles < g.sm_count ? tiles : g.sm_count);
     k_linear_sm100<<<grid, kThreads, kSmemBytes, g.stream>>>(tmx, tmw, tmw1, p);
     return after_launch(op) ? IRIS_B200_OK : IRIS_B200_ECUDA;
@@ -848,6 +1073,12 @@ int iris_b200::launch_linear_two(const TwoStreamLinear &a) {
     return launch_linear(a.y32 ? NULL : a.qkv, a.y32 ? 0 : a.ldy, a.x, a.ldx, a.W[0], a.ldw, a.rows, a.in, out, a.heads, a.wq[0],
                          a.wk[0], a.rope_cos, a.rope_sin, a.eps, NULL, "linear (two streams)", a.y32 ? &f : NULL,
                          a.act ? &glu : NULL, &g2);
+}
+
+extern "C" int iris_b200_linear_cta_pairs(int enable) {
+    const int was = g_pair_mode;
+    if (enable >= 0) g_pair_mode = enable ? 1 : 0;
+    return was;
 }
 
 extern "C" int iris_b200_linear_plan(int rows, int split, int in, int out, int glu_cols, int sm_count, int *tiles_m,

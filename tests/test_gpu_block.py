@@ -513,3 +513,66 @@ def test_zimage_block_argument_checks(lib):
         lib.iris_b200_clear_error()
     finally:
         d.free()
+
+
+# ---------------------------------------------------------------------------
+# the linear layers as single CTAs (128 x 256 tiles) instead of the default
+# CTA pairs (256 x 256 tiles, tcgen05.mma.cta_group::2)
+# ---------------------------------------------------------------------------
+
+@pytest.fixture
+def pairs(lib):
+    """The library with the other of its two GEMM kernels selected."""
+    was = lib.iris_b200_linear_cta_pairs(0)
+    assert was == 1                       # pairs are the default
+    yield lib
+    lib.iris_b200_linear_cta_pairs(was)
+    lib.check()
+
+
+@pytest.mark.parametrize("rows,cin,cout", [(200, 512, 264), (129, 1280, 512), (1, 64, 8), (700, 256, 1032)])
+def test_single_ctas_linear_f32_and_residual(pairs, rows, cin, cout):
+    test_linear_f32_and_linear_residual(pairs, rows, cin, cout)
+
+
+@pytest.mark.parametrize("rows,cin,heads,mlp", [(200, 256, 2, 384), (129, 512, 2, 200), (77, 256, 0, 136), (300, 384, 0, 1024)])
+def test_single_ctas_linear_glu(pairs, rows, cin, heads, mlp):
+    test_linear_glu(pairs, rows, cin, heads, mlp)
+
+
+def test_pairs_bf16_linear_matches_single_ctas(lib):
+    """The plain bf16 GEMM on an odd number of row tiles and a partial column
+    tile: identical bits from pairs and from single CTAs (same k order)."""
+    rows, cin, cout = 900, 1024, 1160
+    a = ol.to_bf16(ol.randn(1, rows, cin))
+    W = ol.to_bf16(ol.randn(2, cout, cin) / np.float32(32.0))
+    d = Dev(lib)
+    try:
+        da, dW, dy = d.put(a), d.put(W), d.new(rows * cout * 2)
+        outs = []
+        for mode in (0, 1):
+            was = lib.iris_b200_linear_cta_pairs(mode)
+            lib.iris_dev_linear_bf16(dy, da, dW, rows, cin, cout)
+            outs.append(lib.to_host(dy, (rows, cout), np.uint16))
+            lib.iris_b200_linear_cta_pairs(was)
+            lib.check()
+    finally:
+        d.free()
+    assert np.array_equal(outs[0], outs[1])
+    want = ol.from_bf16(a).astype(np.float64) @ ol.from_bf16(W).astype(np.float64).T
+    assert np.abs(ol.from_bf16(outs[1]) - want).max() <= 0.02 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("case", [bc.SMALL, bc.MID], ids=lambda c: c["name"])
+def test_single_ctas_blocks(pairs, case):
+    """Single, double (two row groups) and segmented blocks with every linear layer on single CTAs."""
+    inp = bc.block_inputs(case)
+    rel, cos = bc.delta_metrics(device_block(pairs, inp), bc.oracle_block(inp), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+    inp = bc.double_inputs(case)
+    rel, cos = bc.delta_metrics(device_double_block(pairs, inp), bc.oracle_double_block(inp), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
+    f3 = bc.F3_SMALL if case is bc.SMALL else bc.F3_MID
+    inp = bc.f3_inputs(f3)
+    rel, cos = bc.delta_metrics(device_f3_block(pairs, inp), bc.oracle_f3_block(inp), inp["x"])
+    assert rel <= REL_MAX and cos >= MIN_COS, (rel, cos)
