@@ -901,12 +901,42 @@ def run_b200(args):
     name = args.workload or ("klein4b-1024" if world == 1 else "flux3-multiref" if mode == "ring" else "klein9b-cfg")
     w = WORKLOADS[name]
     pk = peaks()
-    groups = 1
+    groups, fallback = 1, None
     if mode == "ring":
         groups = args.head_groups if args.head_groups else (2 if world >= 4 and world % 2 == 0 else 1)
+    plan = B = None
+    if mode == "ring" and groups > 1:
+        # Head groups x rings: every rank tries two steps; unless all of them got through, all of them go back
+        # to ONE ring over all ranks (the decomposition every multi-GPU test covers).
+        ok, why = 1, ""
+        try:
+            job.ring_init(args.ring_parts, groups)
+            plan = plan_of(job, w, mode, groups)
+            B = Buffers(job, w, plan)
+            for _ in range(2):
+                run_step(job, w, plan, B, B.sets[0])
+            lib.iris_dev_sync()
+            lib.check()
+        except Exception as e:
+            ok, why = 0, repr(e)[:160]
+        flag = torch.tensor([ok], device="cuda", dtype=torch.int32)
+        job.dist.all_reduce(flag, op=job.dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            fallback = "head groups failed on some rank (%s): one ring over all ranks instead" % (why or "another rank")
+            try:
+                if B is not None:
+                    B.free()
+                lib.iris_b200_clear_error()
+                job.ring_destroy()
+            except Exception:
+                pass
+            job.ring_ready = False
+            groups, plan, B = 1, None, None
+    if mode == "ring" and plan is None:
         job.ring_init(args.ring_parts, groups)
-    plan = plan_of(job, w, mode, groups)
-    B = Buffers(job, w, plan)
+    if plan is None:
+        plan = plan_of(job, w, mode, groups)
+        B = Buffers(job, w, plan)
     S_full, H = plan["S_full"], w["heads"]
 
     sampler = ClockSampler(job.local) if rank == 0 else None
@@ -1014,7 +1044,7 @@ def run_b200(args):
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": name, "batch": w["batch"], "heads": H, "head_dim": D, "tokens": S_full,
                        "step": STEP_WORDS},
-            "sharding": sharding,
+            "sharding": sharding if not fallback else sharding + " [" + fallback + "]",
             "l2": "inputs rotate over %d buffer sets (%.0f MB)" % (B.nsets, B.nsets * B.per_set / 1e6),
             "per_gpu_tflops": round(value / world, 2),
             "host_enqueue_ms_per_step": round(res["enqueue_ms"], 4),
