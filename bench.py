@@ -904,10 +904,6 @@ def run_b200(args):
     groups, fallback = 1, None
     if mode == "ring":
         groups = args.head_groups if args.head_groups else (2 if world >= 4 and world % 2 == 0 else 1)
-        if args.ring_parts == 0 and groups > 1 and world // groups == 2:
-            # a ring of two with half the heads: the one chunk (52 MB) arrives before any work item is through its
-            # own rows, so one key part (no partial results to merge) is faster than two: 0.743 vs 0.773 ms at N = 4
-            args.ring_parts = 1
     plan = B = None
     if mode == "ring" and groups > 1:
         # Head groups x rings: every rank tries two steps; unless all of them got through, all of them go back
