@@ -805,6 +805,164 @@ def double_block_run(job, w, pk, reps=10):
     return out
 
 
+def other_blocks_run(job, pk, reps=6):
+    """One Z-Image block (config 4: 4608 padded rows, dim 3840, ff 10240) and one
+    FLUX.3 block over the multi-reference sequence (config 5: 16 896 rows in
+    three segments, dim 3072, mlp 9216) through iris_b200_zimage_block and
+    iris_b200_single_block_segments, each next to the reference's CUDA backend
+    issuing its own calls (iris_transformer_zimage.c:1940-1959,
+    iris_transformer_flux3.c:680-703) on the same device (rank 0, N = 1)."""
+    lib, torch = job.lib, job.torch
+    import ctypes as C
+    binding = sys.modules[type(lib).__module__]
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    ref = ol.ref_cuda()
+    if ref is not None and ref.iris_dev_init() != 1:
+        ref = None
+    gen = torch.Generator(device="cuda").manual_seed(17)
+
+    def rnd(shape, scale=1.0, dtype=torch.float32):
+        return (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+    def timed(fn, sync):
+        for _ in range(2):
+            fn()
+        sync()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        sync()
+        return (time.perf_counter() - t0) * 1e3 / reps
+
+    def ours_ms(fn):
+        for _ in range(2):
+            fn()
+        lib.iris_dev_sync()
+        lib.iris_b200_mark(0)
+        for _ in range(reps):
+            fn()
+        lib.iris_b200_mark(1)
+        ms = lib.iris_b200_mark_elapsed_ms(0, 1) / reps
+        lib.check()
+        return ms
+
+    out = {}
+    # ---- Z-Image ----
+    w = WORKLOADS["zimage-turbo"]
+    S, H = seq_len(w), w["heads"]
+    dim, ff = H * D, 10240
+    cos, sin = rope_tables(w)
+    d_cos, d_sin = lib.to_device(cos), lib.to_device(sin)
+    x = rnd((S, dim))
+    t = dict(qkv=rnd((3 * dim, dim), dim ** -0.5, torch.bfloat16), proj=rnd((dim, dim), dim ** -0.5, torch.bfloat16),
+             ff_in=rnd((2 * ff, dim), dim ** -0.5, torch.bfloat16), ff_out=rnd((dim, ff), ff ** -0.5, torch.bfloat16),
+             norm_q=1 + 0.1 * rnd((D,)), norm_k=1 + 0.1 * rnd((D,)))
+    norms = [1 + 0.1 * rnd((dim,)) for _ in range(4)]
+    mod = rnd((4 * dim,), 0.3)
+    wz = binding.ZImageWeights(*[t[k].data_ptr() for k in ("qkv", "proj", "ff_in", "ff_out", "norm_q", "norm_k")],
+                               *[n.data_ptr() for n in norms])
+    scratch = lib.alloc(lib.iris_b200_zimage_block_scratch_bytes(S, dim, ff))
+    torch.cuda.synchronize()
+
+    def zi():
+        rc = lib.iris_b200_zimage_block(x.data_ptr(), scratch, C.addressof(wz), mod.data_ptr(), d_cos, d_sin, S, dim, H, ff, None)
+        assert rc == 0, rc
+
+    n0 = lib.iris_b200_launch_count()
+    ms = ours_ms(zi)
+    launches = (lib.iris_b200_launch_count() - n0) // (reps + 2)
+    flops = 2.0 * S * dim * (3 * dim + dim + 2 * ff + ff) + 4.0 * S * S * dim
+    z = {"shape": {"tokens": S, "dim": dim, "heads": H, "ff": ff}, "launches_per_block": int(launches), "ms": round(ms, 4),
+         "tflops": round(flops / ms / 1e9, 1), "frac_of_bf16_sustained": round(flops / ms / 1e9 / pk[1], 4)}
+    if ref is not None:
+        norm = torch.empty((S, dim), device="cuda", dtype=torch.bfloat16).data_ptr()
+        r_h = torch.empty((S, max(3 * dim, 2 * ff)), device="cuda", dtype=torch.bfloat16)
+        r_act = torch.empty((S, max(dim, ff)), device="cuda", dtype=torch.bfloat16)
+        r_out = torch.empty((S, dim), device="cuda", dtype=torch.float32)
+        h, act, o, xp, m = r_h.data_ptr(), r_act.data_ptr(), r_out.data_ptr(), x.data_ptr(), mod.data_ptr()
+
+        def zi_ref():
+            ref.iris_dev_rms_norm_mod(norm, xp, norms[0].data_ptr(), m, S, dim, 1e-5)
+            ref.iris_dev_linear_bf16(h, norm, t["qkv"].data_ptr(), S, dim, 3 * dim)
+            ref.iris_dev_head_norm_rope(h, 3 * dim, t["norm_q"].data_ptr(), d_cos, d_sin, S, H, D, 1e-5, 0)
+            ref.iris_dev_head_norm_rope(h + 2 * dim, 3 * dim, t["norm_k"].data_ptr(), d_cos, d_sin, S, H, D, 1e-5, 0)
+            ref.iris_dev_attention(act, dim, h, h + 2 * dim, h + 4 * dim, 3 * dim, S, S, H, H, D, 1.0 / np.sqrt(D), 0, None)
+            ref.iris_dev_linear_f32(o, act, t["proj"].data_ptr(), S, dim, dim)
+            ref.iris_dev_rms_norm_residual(xp, o, norms[1].data_ptr(), m + 4 * dim, S, dim, 1e-5)
+            ref.iris_dev_rms_norm_mod(norm, xp, norms[2].data_ptr(), m + 8 * dim, S, dim, 1e-5)
+            ref.iris_dev_linear_bf16(h, norm, t["ff_in"].data_ptr(), S, dim, 2 * ff)
+            ref.iris_dev_swiglu(act, ff, h, h + 2 * ff, 2 * ff, S, ff)
+            ref.iris_dev_linear_f32(o, act, t["ff_out"].data_ptr(), S, ff, dim)
+            ref.iris_dev_rms_norm_residual(xp, o, norms[3].data_ptr(), m + 12 * dim, S, dim, 1e-5)
+
+        lib.iris_dev_sync()
+        rms = timed(zi_ref, ref.iris_dev_sync)
+        z["reference_cuda_ms"] = round(rms, 4)
+        z["speedup_vs_reference_cuda"] = round(rms / ms, 3)
+        del r_h, r_act, r_out
+    for p in (d_cos, d_sin, scratch):
+        lib.iris_dev_free(p)
+    del x, t, norms
+    out["zimage_block"] = z
+    # ---- FLUX.3, three segments ----
+    w = WORKLOADS["flux3-multiref"]
+    S, H = seq_len(w), w["heads"]
+    dim, mlp = H * D, 3 * H * D
+    ldh, ldc = 3 * dim + 2 * mlp, dim + mlp
+    cos, sin = rope_tables(w)
+    d_cos, d_sin = lib.to_device(cos), lib.to_device(sin)
+    x = rnd((S, dim))
+    w_in, w_out = rnd((ldh, dim), dim ** -0.5, torch.bfloat16), rnd((dim, ldc), ldc ** -0.5, torch.bfloat16)
+    nq, nk = 1 + 0.1 * rnd((D,)), 1 + 0.1 * rnd((D,))
+    img = w["img"][0] * w["img"][1]
+    lens = [w["txt"], img, S - w["txt"] - img]
+    mods = [rnd((3 * dim,), 0.3) for _ in lens]
+    segs = (binding.Segment * 3)(*[binding.Segment(int(sum(lens[:i])), int(n), mods[i].data_ptr()) for i, n in enumerate(lens)])
+    scratch = lib.alloc(lib.iris_b200_single_block_scratch_bytes(S, dim, mlp))
+    torch.cuda.synchronize()
+
+    def f3():
+        rc = lib.iris_b200_single_block_segments(x.data_ptr(), scratch, w_in.data_ptr(), w_out.data_ptr(), nq.data_ptr(),
+                                                 nk.data_ptr(), C.addressof(segs), 3, d_cos, d_sin, S, dim, H, mlp, 1e-6, None)
+        assert rc == 0, rc
+
+    ms = ours_ms(f3)
+    flops = 2.0 * S * dim * ldh + 4.0 * S * S * dim + 2.0 * S * ldc * dim
+    f = {"shape": {"tokens": S, "segments": lens, "dim": dim, "heads": H, "mlp": mlp}, "launches_per_block": 4,
+         "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "frac_of_bf16_sustained": round(flops / ms / 1e9 / pk[1], 4)}
+    if ref is not None:
+        norm = torch.empty((S, dim), device="cuda", dtype=torch.bfloat16)
+        r_h = torch.empty((S, ldh), device="cuda", dtype=torch.bfloat16)
+        r_cat = torch.empty((S, ldc), device="cuda", dtype=torch.bfloat16)
+        r_out = torch.empty((S, dim), device="cuda", dtype=torch.float32)
+        nr, h, cat, o, xp = norm.data_ptr(), r_h.data_ptr(), r_cat.data_ptr(), r_out.data_ptr(), x.data_ptr()
+
+        def f3_ref():
+            for i, n in enumerate(lens):
+                off = int(sum(lens[:i])) * dim
+                m = mods[i].data_ptr()
+                ref.iris_dev_layer_norm_mod(nr + off * 2, xp + off * 4, m, m + 4 * dim, n, dim, 1e-6)
+            ref.iris_dev_linear_bf16(h, nr, w_in.data_ptr(), S, dim, ldh)
+            ref.iris_dev_head_norm_rope(h, ldh, nq.data_ptr(), d_cos, d_sin, S, H, D, 1e-6, 0)
+            ref.iris_dev_head_norm_rope(h + 2 * dim, ldh, nk.data_ptr(), d_cos, d_sin, S, H, D, 1e-6, 0)
+            ref.iris_dev_attention(cat, ldc, h, h + 2 * dim, h + 4 * dim, ldh, S, S, H, H, D, 1.0 / np.sqrt(D), 0, None)
+            ref.iris_dev_swiglu(cat + 2 * dim, ldc, h + 6 * dim, h + 2 * (3 * dim + mlp), ldh, S, mlp)
+            ref.iris_dev_linear_f32(o, cat, w_out.data_ptr(), S, ldc, dim)
+            for i, n in enumerate(lens):
+                off = int(sum(lens[:i])) * dim
+                ref.iris_dev_residual(xp + off * 4, o + off * 4, mods[i].data_ptr() + 8 * dim, n, dim)
+
+        lib.iris_dev_sync()
+        rms = timed(f3_ref, ref.iris_dev_sync)
+        f["reference_cuda_ms"] = round(rms, 4)
+        f["speedup_vs_reference_cuda"] = round(rms / ms, 3)
+    for p in (d_cos, d_sin, scratch):
+        lib.iris_dev_free(p)
+    out["flux3_block"] = f
+    return out
+
+
 def outproj_run(job, pk, reps=20):
     """The step after the path with the heads sharded over the ranks (N > 1):
     the Klein-4B block's out-projection, [4608, dim / N] x [dim, dim / N]^T per
@@ -1020,7 +1178,7 @@ def run_b200(args):
         except Exception as e:                     # a side measurement must not cost the headline line
             projection = {"error": repr(e)[:200]}
 
-    block = dblock = None
+    block = dblock = others = None
     if rank == 0 and world == 1 and mode == "single" and w["family"] == "flux2" and not args.no_extras:
         try:
             block = block_run(job, w, pk)
@@ -1030,6 +1188,10 @@ def run_b200(args):
             dblock = double_block_run(job, w, pk)
         except Exception as e:
             dblock = {"error": repr(e)[:200]}
+        try:
+            others = other_blocks_run(job, pk)
+        except Exception as e:
+            others = {"error": repr(e)[:200]}
 
     if rank == 0:
         sharding = {"single": "none",
@@ -1053,7 +1215,7 @@ def run_b200(args):
             "clocks": clocks, "e2e": e2e, "gpu_launches": res["launches"],
             "roofline": roof, "roofline_prologue": prologue, "cpu_baseline": cpu, "parity": parity,
             "reference_gpu": ref_gpu, "qkv_projection": projection, "single_block": block,
-            "double_block": dblock,
+            "double_block": dblock, "other_blocks": others,
         }
         if speedup is not None:
             out["one_gpu_ms_per_step"] = round(one_gpu, 4)

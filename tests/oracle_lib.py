@@ -147,6 +147,8 @@ def ref_cuda():
     _sig(lib, "iris_dev_layer_norm_mod", [VP, VP, VP, VP, INT, INT, FLT])
     _sig(lib, "iris_dev_swiglu", [VP, INT, VP, VP, INT, INT, INT])
     _sig(lib, "iris_dev_residual", [VP, VP, VP, INT, INT])
+    _sig(lib, "iris_dev_rms_norm_mod", [VP, VP, VP, VP, INT, INT, FLT])
+    _sig(lib, "iris_dev_rms_norm_residual", [VP, VP, VP, VP, INT, INT, FLT])
     return lib
 
 
