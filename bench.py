@@ -1033,6 +1033,75 @@ def outproj_run(job, pk, reps=20):
             "nvlink_bytes_per_rank": sent, "nvlink_gbs_per_rank": round(sent / ms / 1e6, 1)}
 
 
+def tp_block_run(job, pk, reps=10):
+    """One Klein-4B single-stream block, tensor parallel over the ranks (N > 1):
+    rows of the hidden state owned by the ranks, heads and MLP columns sharded;
+    the all-gather lives in the LayerNorm's stores and the projection's arrival
+    waits, the reduce-scatter in the output projection's epilogue
+    (iris_b200_single_block_tp). Needs the group of the ring. ms per block, max
+    over ranks; the one-GPU block is `single_block` of the N = 1 line."""
+    lib, torch, rank, world = job.lib, job.torch, job.rank, job.world
+    w = WORKLOADS["klein4b-1024"]
+    S, H = seq_len(w), w["heads"]
+    dim, mlp = H * D, 3 * H * D
+    if H % world or mlp % (8 * world):
+        return None
+    hl, ml = H // world, mlp // world
+    a, b = C.c_int(), C.c_int()
+    rows_of = np.zeros(world, np.int32)
+    for r in range(world):
+        lib.iris_b200_seq_shard(S, world, r, C.byref(a), C.byref(b))
+        rows_of[r] = b.value
+    gen = torch.Generator(device="cuda").manual_seed(21 + rank)
+
+    def rnd(shape, scale=1.0, dtype=torch.float32):
+        return (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+    x = rnd((int(rows_of[rank]), dim))
+    w_in = rnd((3 * hl * D + 2 * ml, dim), dim ** -0.5, torch.bfloat16)
+    w_out = rnd((dim, hl * D + ml), (dim + mlp) ** -0.5, torch.bfloat16)
+    nq, nk, mod = 1 + 0.1 * rnd((D,)), 1 + 0.1 * rnd((D,)), rnd((3 * dim,), 0.3)
+    cos, sin = rope_tables(w)
+    d_cos, d_sin = lib.to_device(cos), lib.to_device(sin)
+    scratch = lib.alloc(lib.iris_b200_single_block_tp_scratch_bytes(S, hl, ml))
+    torch.cuda.synchronize()
+
+    def call():
+        rc = lib.iris_b200_single_block_tp(x.data_ptr(), scratch, w_in.data_ptr(), w_out.data_ptr(), nq.data_ptr(),
+                                           nk.data_ptr(), mod.data_ptr(), d_cos, d_sin, rows_of.ctypes.data, dim, hl, ml, None)
+        assert rc == 0, rc
+
+    # every rank tries three blocks; the timed part only runs when all of them got through
+    ok, why = 1, ""
+    try:
+        for _ in range(3):
+            call()
+        lib.iris_dev_sync()
+        lib.check()
+    except Exception as e:
+        ok, why = 0, repr(e)[:160]
+    flag = torch.tensor([ok], device="cuda", dtype=torch.int32)
+    job.dist.all_reduce(flag, op=job.dist.ReduceOp.MIN)
+    if int(flag.item()) == 0:
+        lib.iris_b200_clear_error()
+        return {"error": why or "another rank failed"}
+    job.barrier()
+    lib.iris_b200_mark(0)
+    for _ in range(reps):
+        call()
+    lib.iris_b200_mark(1)
+    job.barrier()
+    ms = job.max_over_ranks([lib.iris_b200_mark_elapsed_ms(0, 1) / reps])[0]
+    lib.check()
+    for p in (d_cos, d_sin, scratch):
+        lib.iris_dev_free(p)
+    flops = 2.0 * S * dim * (3 * dim + 2 * mlp) + 4.0 * S * S * dim + 2.0 * S * (dim + mlp) * dim
+    return {"shape": {"tokens": S, "dim": dim, "heads_per_rank": hl, "mlp_per_rank": ml}, "ms": round(ms, 4),
+            "tflops": round(flops / ms / 1e9, 1), "per_gpu_pct_bf16_sustained": round(100 * flops / ms / 1e9 / world / pk[1], 2),
+            "gathered_bytes_per_rank": int((S - int(rows_of[rank])) * dim * 2),
+            "scattered_bytes_per_rank": int((S - int(rows_of[rank])) * dim * 4)}
+
+
 def extra_run(job, name, mode, steps, warmup, pk, groups=1):
     """A further workload / decomposition measured in the same run: ms per
     step (max over ranks), aggregate TFLOP/s and per-GPU share of the peak."""
@@ -1156,6 +1225,7 @@ def run_b200(args):
                 extras[other] = extra_run(job, other, "shard", args.steps, args.warmup, pk)
         if mode == "ring" and not args.no_outproj:
             extras["klein4b-1024 out-projection, heads sharded"] = outproj_run(job, pk)
+            extras["klein4b-1024 single block, tensor parallel"] = tp_block_run(job, pk)
 
     # CPU leg on the same inputs (rank 0), and the parity of the two results.
     cpu = parity = ref_gpu = None

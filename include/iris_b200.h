@@ -240,6 +240,33 @@ int iris_b200_single_block_segments(float *x, void *scratch,
                                     int seq, int dim, int heads, int mlp, float eps,
                                     const int *key_mask);
 
+/* ---- one single-stream block, tensor parallel ------------------------------ */
+
+size_t iris_b200_single_block_tp_scratch_bytes(int seq, int heads_local, int mlp_local);
+
+/* iris_b200_single_block over the group of iris_b200_ring_init, one process
+ * per GPU (the reference is single device, iris_cuda.cu:122): the hidden state
+ * is sharded by rows (rank r owns rows_of[r] consecutive rows; x_rows is this
+ * rank's block, updated in place), the weights by heads and MLP columns: w_in
+ * [3 * heads_local * 128 + 2 * mlp_local, dim] holds this rank's Q, K and V
+ * head rows, then its gate rows, then its up rows; w_out [dim, heads_local *
+ * 128 + mlp_local] the matching columns of the output projection. Both
+ * collectives live inside kernels: LayerNorm stores this rank's normalised
+ * rows into every rank's buffer over NVLink (the all-gather) and the input
+ * projection waits, row tile by row tile, for the arrival words of the rows'
+ * owners; the output projection's epilogue sends its fp32 partial sums to the
+ * rows' owners (the reduce-scatter, iris_b200_outproj_residual), which apply
+ * the gated residual. Five launches per block and rank; no NCCL call after
+ * set-up; every wait is bounded (IRIS_B200_ETIMEOUT). rope tables [seq, 64]
+ * cover all rows; mod = shift | scale | gate [3 dim]. Collective: every rank of
+ * the group makes the same sequence of calls. */
+int iris_b200_single_block_tp(float *x_rows, void *scratch,
+                              const uint16_t *w_in, const uint16_t *w_out,
+                              const float *norm_q, const float *norm_k, const float *mod,
+                              const float *rope_cos, const float *rope_sin,
+                              const int *rows_of, int dim, int heads_local, int mlp_local,
+                              const int *key_mask);
+
 /* ---- one double-stream block --------------------------------------------- */
 
 /* The weights of one stream (text or image) of a double block, bf16 as the

@@ -68,6 +68,8 @@ SIGNATURES = {
     "iris_b200_single_block_segments": (INT, [VP, VP, VP, VP, VP, VP, VP, INT, VP, VP, INT, INT, INT, INT, FLT, VP]),
     "iris_b200_zimage_block_scratch_bytes": (SZ, [INT, INT, INT]),
     "iris_b200_zimage_block": (INT, [VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, VP]),
+    "iris_b200_single_block_tp_scratch_bytes": (SZ, [INT, INT, INT]),
+    "iris_b200_single_block_tp": (INT, [VP, VP, VP, VP, VP, VP, VP, VP, VP, VP, INT, INT, INT, VP]),
     "iris_b200_double_block_scratch_bytes": (SZ, [INT, INT, INT]),
     "iris_b200_double_block": (INT, [VP, VP, VP, VP, VP, VP, INT, INT, INT, INT, INT, VP]),
     "iris_b200_attention_ex": (INT, [VP, INT, VP, VP, VP, INT, INT, INT, INT, INT, INT, FLT, INT, VP, INT]),

@@ -122,6 +122,71 @@ k_layer_norm_mod_rows(uint16_t *__restrict__ out, const float *__restrict__ x, c
     }
 }
 
+/* The same for the rows a rank owns of a hidden state that is sharded by rows
+ * over several GPUs, with the all-gather in its stores: every output row goes
+ * to the same row of every destination (this GPU's buffer and the peers',
+ * plain 8-byte stores over NVLink), and the last block out advances this
+ * rank's arrival word on every destination once all stores are visible at
+ * system scope. The linear layer that follows on each GPU waits for those
+ * words per row tile (gemm_sm100.cu: rows_arrived). */
+template <int VPT>
+__global__ void __launch_bounds__(kRowThreads, VPT <= 2 ? 8 : 6)
+k_layer_norm_mod_gather(const __grid_constant__ GatherOut dst, const float *__restrict__ x, const float *__restrict__ shift,
+                        const float *__restrict__ scale, int rows, int dim, float eps) {
+    __shared__ float sh[kRowThreads / 32];
+    const int nvec = dim >> 2;
+    const float inv_dim = 1.0f / (float)dim;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * dim);
+        float4 v[VPT];
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * kRowThreads;
+            v[k] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+        const float mean = block_sum(s, sh) * inv_dim;
+        float q = 0.0f;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            if (threadIdx.x + k * kRowThreads < nvec) {
+                const float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean;
+                q += (a * a + b * b) + (c * c + d * d);
+            }
+        }
+        const float inv = rsqrtf(block_sum(q, sh) * inv_dim + eps);
+#pragma unroll
+        for (int k = 0; k < VPT; k++) {
+            const int i = threadIdx.x + k * kRowThreads;
+            if (i >= nvec) continue;
+            float n[4] = {(v[k].x - mean) * inv, (v[k].y - mean) * inv, (v[k].z - mean) * inv, (v[k].w - mean) * inv};
+            if (scale) {
+                const float4 sc = reinterpret_cast<const float4 *>(scale)[i];
+                n[0] *= 1.0f + sc.x; n[1] *= 1.0f + sc.y; n[2] *= 1.0f + sc.z; n[3] *= 1.0f + sc.w;
+            }
+            if (shift) {
+                const float4 sf = reinterpret_cast<const float4 *>(shift)[i];
+                n[0] += sf.x; n[1] += sf.y; n[2] += sf.z; n[3] += sf.w;
+            }
+            const uint2 packed = make_uint2(cvt_bf16x2(n[0], n[1]), cvt_bf16x2(n[2], n[3]));
+            for (int d = 0; d < dst.n; d++) reinterpret_cast<uint2 *>(dst.dst[d] + (size_t)row * dim)[i] = packed;
+        }
+    }
+    /* this thread's rows are out before the block counts itself out */
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(dst.done, 1u);
+        if (prev == gridDim.x - 1) {
+            *dst.done = 0u;
+            __threadfence_system();
+            for (int d = 0; d < dst.n; d++)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst.word[d]), "r"(dst.seq) : "memory");
+        }
+    }
+}
+
 /* Any other row length: one block per row at a time, the row re-read from
  * L1 / L2 for each pass. */
 __global__ void __launch_bounds__(kRowThreads)
@@ -332,6 +397,30 @@ int rms_norm_rows(uint16_t *out, float *xres, const float *x, const float *w, co
     }
     return after_launch("k_rms_norm") ? IRIS_B200_OK : IRIS_B200_ECUDA;
 }
+
+}  // namespace
+
+int launch_layer_norm_mod_gather(const GatherOut &out, const float *x, const float *shift, const float *scale, int rows,
+                                 int dim, float eps) {
+    if (!require_device("layer_norm_mod (gather)")) return IRIS_B200_ENODEV;
+    const int nvec = dim / 4;
+    bool ok = x && rows >= 0 && dim > 0 && out.n >= 1 && out.n <= 16 && out.done && dim % 4 == 0 && nvec <= 4 * kRowThreads &&
+              aligned16(x) && aligned16(shift) && aligned16(scale);
+    for (int d = 0; ok && d < out.n; d++) ok = out.dst[d] && out.word[d] && ((uintptr_t)out.dst[d] & 7) == 0;
+    if (!ok) {
+        set_error(IRIS_B200_EINVAL, "layer_norm_mod (gather)", "bad argument (dim a multiple of 4 up to 4096, aligned operands)");
+        return IRIS_B200_EINVAL;
+    }
+    /* rows == 0 still has to announce itself: one block, no rows */
+    const unsigned grid = blocks_for((size_t)(rows > 0 ? rows : 1), 1, 8);
+    if (nvec <= kRowThreads) k_layer_norm_mod_gather<1><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+    else if (nvec <= 2 * kRowThreads) k_layer_norm_mod_gather<2><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+    else if (nvec <= 3 * kRowThreads) k_layer_norm_mod_gather<3><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+    else k_layer_norm_mod_gather<4><<<grid, kRowThreads, 0, g.stream>>>(out, x, shift, scale, rows, dim, eps);
+    return after_launch("k_layer_norm_mod_gather") ? IRIS_B200_OK : IRIS_B200_ECUDA;
+}
+
+namespace {
 
 int swiglu(uint16_t *out, int ldo, const uint16_t *gate, const uint16_t *up, int ldi, int rows, int cols) {
     if (!require_device("swiglu")) return IRIS_B200_ENODEV;

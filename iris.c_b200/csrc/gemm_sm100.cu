@@ -110,6 +110,15 @@ struct Params {
     int split, tiles_m0;
     const float *wq1, *wk1, *gate1;
     int ctas;                   /* 1, or 2: a row tile is 256 rows worked on by a CTA pair (k_linear_pair_sm100) */
+    /* Rows of x that arrive while the kernel runs (an all-gather whose senders
+     * store straight into x: the tensor-parallel blocks): rows [guard_first[q],
+     * guard_first[q + 1]) are final once the word guard[q] has reached
+     * guard_seq. The producer waits (bounded) for the owners of a row tile
+     * before its first load of the tile. guard == NULL: everything is there. */
+    const uint32_t *guard;
+    int guard_n;
+    int guard_first[kMaxScatterRanks + 1];
+    uint32_t guard_seq;
     /* Gates by runs of rows that share the weights (the segments of a FLUX.3
      * block: text, image, reference rows, each with its own modulation):
      * rows below seg_end[i] (and not below seg_end[i - 1]) take seg_gate[i].
@@ -183,10 +192,44 @@ __device__ __forceinline__ bool wait(const Ctx &c, int idx, uint32_t parity, int
     }
 }
 
+/* The rows [m0, m0 + kTileM) of x: wait for the arrival words of their owners. `arrived` remembers the owners seen. */
+__device__ __forceinline__ bool rows_arrived(const Ctx &c, const Params &p, int m0, uint32_t *arrived) {
+    if (!p.guard) return true;
+    const int m1 = m0 + kTileM < p.rows ? m0 + kTileM : p.rows;
+    for (int q = 0; q < p.guard_n; q++) {
+        if (p.guard_first[q + 1] <= m0 || p.guard_first[q] >= m1 || ((*arrived >> q) & 1u)) continue;
+        const unsigned long long t0 = global_ns();
+        for (uint32_t spin = 0;; spin++) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.guard + q) : "memory");
+            if ((int32_t)(v - p.guard_seq) >= 0) break;
+            if ((spin & 7u) == 7u) {
+                if (*c.abort_flag) return false;
+                if (global_ns() - t0 > c.wait_ns || spin > (1u << 26)) {
+                    *c.abort_flag = 1u;
+                    if (c.peer_abort) st_cluster_u32(c.peer_abort, 1u);
+                    if (atomicCAS(c.status, 0u, 1u) == 0u) {
+                        c.status[1] = 480u;
+                        c.status[2] = blockIdx.x;
+                        c.status[3] = (unsigned)q;
+                    }
+                    return false;
+                }
+                __nanosleep(100);
+            }
+        }
+        *arrived |= 1u << q;
+        /* written by another GPU's stores; the loads below go through the asynchronous proxy */
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+    }
+    return true;
+}
+
 __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CUtensorMap *tmx, const CUtensorMap *tmw0,
                                          const CUtensorMap *tmw1, uint32_t smem) {
     const int nkb = (p.in + kBlockK - 1) / kBlockK;
     int issued = 0;
+    uint32_t arrived = 0u;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.tiles_m * p.tiles_n; tile += gridDim.x) {
         int tm, nt;
@@ -200,6 +243,7 @@ __device__ __forceinline__ void producer(const Ctx &c, const Params &p, const CU
             n0 = p.glu_col0 + (nt - p.glu_tile0) * (kTileN / 2);
             n1 = n0 + p.glu_cols;
         }
+        if (!(ok = rows_arrived(c, p, m0, &arrived))) break;
         for (int kb = 0; kb < nkb; kb++, issued++) {
             const int s = issued % kStages;
             if (issued >= kStages && !(ok = wait(c, BAR_EMPTY + s, ((issued / kStages) - 1) & 1u, 400 + s))) break;
@@ -630,6 +674,7 @@ __device__ __forceinline__ void pair_producer(const Ctx &c, const Params &p, con
     const int nkb = (p.in + kBlockK - 1) / kBlockK;
     const uint32_t full0 = map_to_cta(c.bars + PBAR_FULL * 8, 0);          /* the first CTA's FULL barriers */
     int issued = 0;
+    uint32_t arrived = 0u;
     bool ok = true;
     for (int tile = first; ok && tile < p.tiles_m * p.tiles_n; tile += stride) {
         int tm, nt;
@@ -639,6 +684,7 @@ __device__ __forceinline__ void pair_producer(const Ctx &c, const Params &p, con
         /* this CTA's 128 rows of W: an ordinary tile's first or second half, or the gate or the up rows */
         int n = nt * kTileN + rank * (kTileN / 2);
         if (nt >= p.glu_tile0) n = p.glu_col0 + (nt - p.glu_tile0) * (kTileN / 2) + rank * p.glu_cols;
+        if (!(ok = rows_arrived(c, p, rt.m0, &arrived))) break;
         for (int kb = 0; kb < nkb; kb++, issued++) {
             const int s = issued % kPairStages;
             if (issued >= kPairStages && !(ok = wait(c, PBAR_EMPTY + s, ((issued / kPairStages) - 1) & 1u, 600 + s))) break;
@@ -855,7 +901,8 @@ void gemm_release(void) {
 static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const uint16_t *W, int ldw, int rows, int in,
                          int out, int heads, const float *wq, const float *wk, const float *rope_cos,
                          const float *rope_sin, float eps, const ScatterArgs *sc, const char *op,
-                         const F32Out *f32 = NULL, const GluOut *glu = NULL, const SecondGroup *g2 = NULL) {
+                         const F32Out *f32 = NULL, const GluOut *glu = NULL, const SecondGroup *g2 = NULL,
+                         const RowGuard *guard = NULL) {
     using namespace gemm;
     if (!require_device(op)) return IRIS_B200_ENODEV;
     if ((!y && !sc && !f32 && !(glu && out == 0)) || (f32 && (!f32->y || f32->ld < out || f32->ld % 4 != 0 || ((uintptr_t)f32->y & 15) != 0 ||
@@ -954,6 +1001,16 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         p.seq = sc->seq;
         p.done = sc->done;
     }
+    if (guard) {
+        if (guard->n < 1 || guard->n > kMaxScatterRanks || !guard->words || guard->row_first[guard->n] != rows) {
+            set_error(IRIS_B200_EINVAL, op, "bad row guards");
+            return IRIS_B200_EINVAL;
+        }
+        p.guard = guard->words;
+        p.guard_n = guard->n;
+        for (int q = 0; q <= guard->n; q++) p.guard_first[q] = guard->row_first[q];
+        p.guard_seq = guard->seq;
+    }
     if (f32) {
         p.scatter = 2;
         p.y32 = f32->y;
@@ -1049,6 +1106,15 @@ int iris_b200::launch_linear_residual_segments(float *x_rows, int ldx, const uin
         }
     }
     return launch_linear(NULL, 0, a, lda, W, ldw, rows, in, out, 0, NULL, NULL, NULL, NULL, 0.0f, NULL, "linear_residual", &f);
+}
+
+int iris_b200::launch_linear_glu_guarded(uint16_t *qkv, int ldq, uint16_t *act, int lda, const uint16_t *x, int ldx,
+                                         const uint16_t *W, int rows, int in, int heads, int mlp, const float *wq,
+                                         const float *wk, const float *rope_cos, const float *rope_sin, float eps,
+                                         const RowGuard &guard) {
+    const GluOut glu = {act, lda, mlp};
+    return launch_linear(qkv, ldq, x, ldx, W, in, rows, in, 3 * heads * 128, heads, wq, wk, rope_cos, rope_sin, eps, NULL,
+                         "linear_glu (gathered rows)", NULL, &glu, NULL, &guard);
 }
 
 extern "C" int iris_b200_linear_glu(uint16_t *qkv, int ldq, uint16_t *act, int lda, const uint16_t *x, const uint16_t *W,

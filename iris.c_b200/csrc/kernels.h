@@ -150,6 +150,31 @@ struct TwoStreamLinear {
 };
 int launch_linear_two(const TwoStreamLinear &a);
 
+/* Rows of a linear layer's input that arrive while the kernel runs: rows
+ * [row_first[q], row_first[q + 1]) are final once words[q] has reached seq. */
+struct RowGuard {
+    const uint32_t *words;
+    int n;
+    const int *row_first;
+    uint32_t seq;
+};
+/* iris_b200_linear_glu on such an input (x with row stride ldx). */
+int launch_linear_glu_guarded(uint16_t *qkv, int ldq, uint16_t *act, int lda, const uint16_t *x, int ldx, const uint16_t *W,
+                              int rows, int in, int heads, int mlp, const float *wq, const float *wk, const float *rope_cos,
+                              const float *rope_sin, float eps, const RowGuard &guard);
+/* LayerNorm with modulation of this rank's rows, written to the same rows of
+ * every destination (local or peer memory); once all rows are out, word[q] of
+ * every destination is set to seq. done: a zeroed device word. */
+struct GatherOut {
+    int n;
+    uint16_t *dst[16];
+    uint32_t *word[16];
+    uint32_t seq;
+    unsigned int *done;
+};
+int launch_layer_norm_mod_gather(const GatherOut &out, const float *x, const float *shift, const float *scale, int rows,
+                                 int dim, float eps);
+
 /* Host-side fault injection: the next launch that splits its keys finds a
  * ticket that nobody took. */
 void sm100_inject_stale_ticket(void);

@@ -31,6 +31,7 @@
 #include <time.h>
 #include <unistd.h>
 
+#include "iris_dev.h"
 #include "kernels.h"
 
 using namespace iris_b200;
@@ -420,6 +421,8 @@ enum { kFlagArrive = 0, kFlagSeq = kMaxRanks, kFlagWords = kMaxRanks + 8 };
 /* staging of the row-parallel out-projection (further down), released with the group */
 void proj_close_peers(void);
 void proj_release(void);
+void gath_close_peers(void);
+void gath_release(void);
 
 bool nccl_load(void) {
     if (ring.dl) return true;
@@ -662,10 +665,12 @@ extern "C" void iris_b200_ring_destroy(void) {
     cuda_ok(cudaDeviceSynchronize(), "sync");
     ce_close_peers();
     proj_close_peers();
+    gath_close_peers();
     /* Every importer has unmapped before any exporter frees. A ring that
      * failed may have lost a peer: no collective is attempted on it. */
     if (ring.nranks > 1 && ring.xchg && !ring.failed) ring_barrier();
     proj_release();
+    gath_release();
     if (ring.pool) cuda_ok(cudaFree(ring.pool), "free");
     if (ring.flags) cuda_ok(cudaFree(ring.flags), "free");
     if (ring.xchg) cuda_ok(cudaFree(ring.xchg), "free");
@@ -980,6 +985,101 @@ void proj_release(void) {
     proj.seq = 0;
 }
 
+/* ---- the all-gather of a tensor-parallel block's normalised hidden state ----
+ * Two sets (alternate calls) of [rows, dim] bf16 on every rank, mapped on every
+ * peer: a rank's LayerNorm stores its rows into all of them. words: one arrival
+ * word per sender, then the completion counter of the LayerNorm launch. */
+struct Gath {
+    char *buf;
+    size_t set_bytes;
+    uint32_t *words;
+    char *peer_buf[kMaxRanks];
+    uint32_t *peer_words[kMaxRanks];
+    uint32_t seq;
+} gath = {};
+
+enum { kGathDone = kMaxRanks, kGathWords = kMaxRanks + 8 };
+
+void gath_close_peers(void) {
+    for (int r = 0; r < kMaxRanks; r++) {
+        if (r != ring.rank) {
+            if (gath.peer_buf[r]) cudaIpcCloseMemHandle(gath.peer_buf[r]);
+            if (gath.peer_words[r]) cudaIpcCloseMemHandle(gath.peer_words[r]);
+        }
+        gath.peer_buf[r] = NULL;
+        gath.peer_words[r] = NULL;
+    }
+    (void)cudaGetLastError();
+}
+
+/* Collective, like proj_setup(). */
+bool gath_setup(size_t set_bytes) {
+    const int G = ring.nranks;
+    if (gath.buf && set_bytes <= gath.set_bytes) return true;
+    if (!ring.xchg && !cuda_ok(cudaMalloc(&ring.xchg, sizeof(IpcPair) * (kMaxRanks + 1) + 4 * (kMaxRanks + 1)), "malloc"))
+        return false;
+    cuda_ok(cudaDeviceSynchronize(), "sync");
+    if (G > 1 && !ring_barrier()) return false;
+    gath_close_peers();
+    if (G > 1 && !ring_barrier()) return false;
+    if (gath.buf) cuda_ok(cudaFree(gath.buf), "free");
+    gath.buf = NULL;
+    gath.set_bytes = 0;
+    if (!gath.words) {
+        if (!cuda_ok(cudaMalloc((void **)&gath.words, kGathWords * 4), "malloc") ||
+            !cuda_ok(cudaMemset(gath.words, 0, kGathWords * 4), "memset"))
+            return false;
+    }
+    if (cudaMalloc((void **)&gath.buf, set_bytes * 2) != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_error(IRIS_B200_ENOMEM, "all-gather buffer", NULL);
+        return false;
+    }
+    gath.set_bytes = set_bytes;
+    gath.peer_buf[ring.rank] = gath.buf;
+    gath.peer_words[ring.rank] = gath.words;
+    if (G == 1) return true;
+    IpcPair *dev = (IpcPair *)ring.xchg;
+    IpcPair mine, all[kMaxRanks];
+    bool mapped = cudaIpcGetMemHandle(&mine.pool, gath.buf) == cudaSuccess &&
+                  cudaIpcGetMemHandle(&mine.flags, gath.words) == cudaSuccess;
+    if (!mapped) memset(&mine, 0, sizeof(mine));
+    if (!cuda_ok(cudaMemcpy(dev + kMaxRanks, &mine, sizeof(mine), cudaMemcpyHostToDevice), "memcpy") ||
+        !nccl_ok(ring.all_gather(dev + kMaxRanks, dev, sizeof(IpcPair), 1, ring.comm, g.stream), "ncclAllGather") ||
+        !nccl_wait(g.stream, 30.0, "ncclAllGather") ||
+        !cuda_ok(cudaMemcpy(all, dev, sizeof(IpcPair) * G, cudaMemcpyDeviceToHost), "memcpy"))
+        return false;
+    for (int r = 0; r < G && mapped; r++) {
+        if (r == ring.rank) continue;
+        void *pb = NULL, *pw = NULL;
+        if (cudaIpcOpenMemHandle(&pb, all[r].pool, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess ||
+            cudaIpcOpenMemHandle(&pw, all[r].flags, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+            mapped = false;
+        gath.peer_buf[r] = (char *)pb;
+        gath.peer_words[r] = (uint32_t *)pw;
+    }
+    (void)cudaGetLastError();
+    uint32_t votes[kMaxRanks];
+    if (!exchange_word(mapped ? 1u : 0u, votes)) return false;
+    for (int r = 0; r < G; r++) mapped = mapped && votes[r] == 1u;
+    if (!mapped) {
+        set_error(IRIS_B200_ECOMM, "all-gather buffer", "a peer's memory cannot be mapped (no peer access)");
+        gath_close_peers();
+        return false;
+    }
+    return true;
+}
+
+void gath_release(void) {
+    gath_close_peers();
+    if (gath.buf) cuda_ok(cudaFree(gath.buf), "free");
+    if (gath.words) cuda_ok(cudaFree(gath.words), "free");
+    gath.buf = NULL;
+    gath.words = NULL;
+    gath.set_bytes = 0;
+    gath.seq = 0;
+}
+
 }  // namespace
 
 extern "C" int iris_b200_outproj_residual(float *x_rows, const uint16_t *cat, int ldc, const uint16_t *W, int ldw,
@@ -1033,6 +1133,82 @@ extern "C" int iris_b200_outproj_residual(float *x_rows, const uint16_t *cat, in
                                         rows_of[me], dim, proj.words, seq);
     if (rc != IRIS_B200_OK) ring.failed = 1;
     return rc;
+}
+
+extern "C" size_t iris_b200_single_block_tp_scratch_bytes(int seq, int heads_local, int mlp_local) {
+    if (seq < 0 || heads_local <= 0 || mlp_local <= 0) return 0;
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const size_t hw = (size_t)heads_local * 128;
+    return up256((size_t)seq * 3 * hw * 2) + up256((size_t)seq * (hw + mlp_local) * 2);
+}
+
+extern "C" int iris_b200_single_block_tp(float *x_rows, void *scratch, const uint16_t *w_in, const uint16_t *w_out,
+                                         const float *norm_q, const float *norm_k, const float *mod,
+                                         const float *rope_cos, const float *rope_sin, const int *rows_of, int dim,
+                                         int heads_local, int mlp_local, const int *key_mask) {
+    if (!require_device("single_block_tp")) return IRIS_B200_ENODEV;
+    if (!ring.comm || !x_rows || !scratch || !w_in || !w_out || !norm_q || !norm_k || !mod || !rope_cos || !rope_sin ||
+        !rows_of || dim <= 0 || dim % 128 != 0 || heads_local <= 0 || mlp_local <= 0 || mlp_local % 8 != 0 ||
+        ((uintptr_t)scratch & 255) != 0) {
+        set_error(IRIS_B200_EINVAL, "single_block_tp", "group not initialised (iris_b200_ring_init) or bad argument");
+        return IRIS_B200_EINVAL;
+    }
+    if (ring.failed) {
+        set_error(IRIS_B200_ECOMM, "single_block_tp", "an earlier call failed: destroy and re-initialise the group");
+        return IRIS_B200_ECOMM;
+    }
+    const int G = ring.nranks, me = ring.rank;
+    int row_first[kMaxRanks + 1];
+    row_first[0] = 0;
+    for (int r = 0; r < G; r++) {
+        if (rows_of[r] < 0) {
+            set_error(IRIS_B200_EINVAL, "single_block_tp", "negative row count");
+            return IRIS_B200_EINVAL;
+        }
+        row_first[r + 1] = row_first[r] + rows_of[r];
+    }
+    const int seq = row_first[G];
+    if (seq == 0) return IRIS_B200_OK;
+    const size_t set_bytes = (((size_t)seq * dim * 2) + 255) & ~(size_t)255;
+    if (!gath_setup(set_bytes)) {
+        ring.failed = 1;
+        return g.last_error ? g.last_error : IRIS_B200_ECOMM;
+    }
+    const uint32_t call = ++gath.seq;
+    const size_t set_off = (size_t)(call & 1u) * gath.set_bytes;
+    /* 1. LayerNorm of this rank's rows, stored into every rank's copy of the normalised hidden state */
+    GatherOut go = {};
+    go.n = G;
+    for (int q = 0; q < G; q++) {
+        go.dst[q] = (uint16_t *)(gath.peer_buf[q] + set_off) + (size_t)row_first[me] * dim;
+        go.word[q] = gath.peer_words[q] + me;
+    }
+    go.seq = call;
+    go.done = gath.words + kGathDone;
+    int rc = launch_layer_norm_mod_gather(go, x_rows, mod, mod + dim, rows_of[me], dim, 1e-6f);
+    /* 2. this rank's heads and MLP columns of the input projection, row tiles as their owners' rows arrive */
+    auto up256 = [](size_t b) { return (b + 255) & ~(size_t)255; };
+    const int hw = heads_local * 128, ldc = hw + mlp_local;
+    uint16_t *qkv = static_cast<uint16_t *>(scratch);
+    uint16_t *cat = reinterpret_cast<uint16_t *>(static_cast<unsigned char *>(scratch) + up256((size_t)seq * 3 * hw * 2));
+    if (rc == IRIS_B200_OK) {
+        RowGuard guard = {gath.words, G, row_first, call};
+        rc = launch_linear_glu_guarded(qkv, 3 * hw, cat + hw, ldc, (const uint16_t *)(gath.buf + set_off), dim, w_in, seq, dim,
+                                       heads_local, mlp_local, norm_q, norm_k, rope_cos, rope_sin, 1e-6f, guard);
+    }
+    /* 3. attention over all rows for this rank's heads */
+    if (rc == IRIS_B200_OK) {
+        iris_b200_clear_error();
+        iris_dev_attention(cat, ldc, qkv, qkv + hw, qkv + 2 * hw, 3 * hw, seq, seq, heads_local, heads_local, 128,
+                           0.08838834764831845f, 0, key_mask);
+        rc = iris_b200_last_error();
+    }
+    if (rc != IRIS_B200_OK) {
+        ring.failed = 1;
+        return rc;
+    }
+    /* 4. this rank's columns of the output projection; partial sums to the rows' owners, gated residual there */
+    return iris_b200_outproj_residual(x_rows, cat, ldc, w_out, ldc, mod + 2 * dim, rows_of, ldc, dim);
 }
 
 /* A device wait ran out inside a ring call (iris_b200_check_device_status
