@@ -259,7 +259,9 @@ size_t iris_b200_single_block_tp_scratch_bytes(int seq, int heads_local, int mlp
  * the gated residual. Five launches per block and rank; no NCCL call after
  * set-up; every wait is bounded (IRIS_B200_ETIMEOUT). rope tables [seq, 64]
  * cover all rows; mod = shift | scale | gate [3 dim]. Collective: every rank of
- * the group makes the same sequence of calls. */
+ * the group makes the same sequence of calls, within the wait limit
+ * (iris_b200_set_wait_limit_us, 1 s by default) of one another: a rank whose
+ * peers do not show up returns IRIS_B200_ETIMEOUT instead of waiting. */
 int iris_b200_single_block_tp(float *x_rows, void *scratch,
                               const uint16_t *w_in, const uint16_t *w_out,
                               const float *norm_q, const float *norm_k, const float *mod,

@@ -64,6 +64,9 @@ def main():
         ptrs = [lib.to_device(t) for t in (win, wout, inp["norm_q"], inp["norm_k"], inp["mod"], inp["cos"], inp["sin"])]
         scratch = lib.alloc(lib.iris_b200_single_block_tp_scratch_bytes(seq, hl, ml))
         calls = 3
+        # The waits inside the kernels are bounded (1 s by default): the ranks have to enter a block within that
+        # time of one another, and rank 0 has just spent seconds in the CPU restatement of the previous case.
+        dist.barrier()
         for _ in range(calls):
             rc = lib.iris_b200_single_block_tp(dx, scratch, *ptrs, rows_of.ctypes.data, dim, hl, ml, None)
             assert rc == 0, rc
