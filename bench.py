@@ -1044,8 +1044,8 @@ def tp_block_run(job, pk, reps=10):
     w = WORKLOADS["klein4b-1024"]
     S, H = seq_len(w), w["heads"]
     dim, mlp = H * D, 3 * H * D
-    if H % world or mlp % (8 * world):
-        return None
+    if H % world or mlp % (8 * world) or (3 * (H // world) * D) % 256:
+        return None                 # the Q | K | V columns of a rank have to fill whole 256-column tiles
     hl, ml = H // world, mlp // world
     a, b = C.c_int(), C.c_int()
     rows_of = np.zeros(world, np.int32)
@@ -1130,7 +1130,10 @@ def run_b200(args):
     pk = peaks()
     groups, fallback = 1, None
     if mode == "ring":
-        groups = args.head_groups if args.head_groups else (2 if world >= 4 and world % 2 == 0 else 1)
+        # default: rings of two (each rank exchanges K/V rows with one partner: one push per call and a receiver
+        # with a single sender), the heads split over world / 2 such rings
+        groups = args.head_groups if args.head_groups else (
+            world // 2 if world >= 4 and world % 2 == 0 and w["heads"] % (world // 2) == 0 else 1)
     plan = B = None
     if mode == "ring" and groups > 1:
         # Head groups x rings: every rank tries two steps; unless all of them got through, all of them go back
@@ -1208,9 +1211,9 @@ def run_b200(args):
             one_gpu = job.max_over_ranks([one_gpu or 0.0])[0]
             speedup = one_gpu / ms_step
             if groups > 1:
-                # other splits of the same workload: more head groups (shorter rings), then ONE ring over
-                # all ranks with every rank holding all heads
-                for g2 in (4,):
+                # other splits of the same workload: fewer or more head groups (longer or shorter rings), then
+                # ONE ring over all ranks with every rank holding all heads
+                for g2 in (2, 4):
                     if g2 != groups and world % g2 == 0 and world // g2 >= 2 and H % g2 == 0:
                         job.ring_destroy()
                         job.ring_init(args.ring_parts, g2)
@@ -1525,7 +1528,7 @@ def main():
     ap.add_argument("--mode", default=None, choices=["single", "shard", "ring"],
                     help="N > 1: ring sequence parallelism (default) or independent cfg/head shards")
     ap.add_argument("--head-groups", type=int, default=0,
-                    help="ring mode: split the heads over this many independent rings (0: 2 from four GPUs up, else 1)")
+                    help="ring mode: split the heads over this many independent rings (0: rings of two from four GPUs up, else one ring)")
     ap.add_argument("--ring-parts", type=int, default=0, help="key parts of a ring call's launch (0: the library's choice)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the further measurements of the same run (N > 1: other workloads; N = 1: the QKV projection)")

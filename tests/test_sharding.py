@@ -289,6 +289,36 @@ def test_ring_launch_plan(lib, G):
                     assert t[i] == want
 
 
+@pytest.mark.parametrize("world,heads_per_ring", [(4, 12), (8, 6)])
+def test_launch_plan_of_rings_of_two(lib, world, heads_per_ring):
+    """Head groups x rings of two over the 16 896-token sequence (what the
+    bench runs from four GPUs up): when the one chunk is expected in time the
+    ring call asks for one part, and the launch's own cost model then cuts the
+    keys where it pays. At eight GPUs (198 query blocks on 148 SMs) that is
+    two parts whose boundary is the partner's slot: own rows first."""
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    a, b = C.c_int(), C.c_int()
+    rows_of = []
+    for r in range(2):
+        lib.iris_b200_seq_shard(16896, 2, r, C.byref(a), C.byref(b))
+        rows_of.append(b.value)
+    assert rows_of == [8448, 8448]
+    rows = np.array(rows_of, np.int32)
+    for rank in range(2):
+        runs = (pkg.binding.KeyRun * 16)()
+        tiles = (C.c_int * 9)()
+        nkv = C.c_int()
+        code = lib.iris_b200_ring_launch_plan(rank, 2, rows.ctypes.data, heads_per_ring, 1, 148, runs, tiles, C.byref(nkv))
+        nruns, nparts = divmod(code, 100)
+        assert nruns == 2 and nkv.value == 132
+        assert (runs[1].view, runs[1].row0, runs[1].rows, runs[1].arrive) == (1, 8448, 8448, 1)
+        if world == 8:
+            assert nparts == 2 and list(tiles[:3]) == [0, 66, 132]
+        else:
+            assert nparts == 1 and list(tiles[:2]) == [0, 132]      # 396 blocks: three full rounds, no cut
+
+
 # ---------------------------------------------------------------------------
 # work list of a linear-layer launch (host arithmetic shared with the launcher)
 # ---------------------------------------------------------------------------
