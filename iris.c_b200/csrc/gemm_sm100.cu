@@ -919,9 +919,11 @@ static int launch_linear(uint16_t *y, int ldy, const uint16_t *x, int ldx, const
         set_error(IRIS_B200_EUNSUPPORTED, op, "operands must be 16-byte aligned, in / out / row strides multiples of 8");
         return IRIS_B200_EUNSUPPORTED;
     }
-    /* With glu, `out` counts the ordinary columns only (may be 0); W has out + 2 * glu->cols rows. */
+    /* With glu, `out` counts the ordinary columns only (may be 0); W has out + 2 * glu->cols rows. The ordinary
+     * columns end on a half tile (an odd number of 128-column heads is fine): the other half of that last tile is
+     * computed from the gate rows that follow and never stored. */
     if (glu && (!glu->y || glu->cols <= 0 || glu->cols % 8 != 0 || glu->ld < glu->cols || glu->ld % 8 != 0 ||
-                ((uintptr_t)glu->y & 15) != 0 || out % kTileN != 0 || sc || f32)) {
+                ((uintptr_t)glu->y & 15) != 0 || out % (kTileN / 2) != 0 || sc || f32)) {
         set_error(IRIS_B200_EINVAL, op, "bad gated-linear-unit argument");
         return IRIS_B200_EINVAL;
     }

@@ -16,6 +16,7 @@ D = 128
 # klein4b widths on a short sequence, and a small case the CPU reference runs in seconds
 SMALL = dict(name="flux2-block-small", family="flux2", heads=2, mlp=768, txt=32, img=(8, 8), refs=[], eps=1e-6)
 MID = dict(name="flux2-block-mid", family="flux2", heads=4, mlp=1536, txt=40, img=(12, 11), refs=[], eps=1e-6)
+ODD_HEADS = dict(name="flux2-block-3-heads", family="flux2", heads=3, mlp=1152, txt=40, img=(12, 11), refs=[], eps=1e-6)
 KLEIN4B_SHORT = dict(name="klein4b-block-short", family="flux2", heads=24, mlp=9216, txt=64, img=(8, 16),
                      refs=[], eps=1e-6)
 KLEIN4B = dict(name="klein4b-block-1024", family="flux2", heads=24, mlp=9216, txt=512, img=(64, 64), refs=[],

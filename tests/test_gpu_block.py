@@ -170,7 +170,7 @@ def device_block(lib, inp, key_mask=None, calls=1):
         d.free()
 
 
-@pytest.mark.parametrize("case", [bc.SMALL, bc.MID, bc.KLEIN4B_SHORT], ids=lambda c: c["name"])
+@pytest.mark.parametrize("case", [bc.SMALL, bc.MID, bc.ODD_HEADS, bc.KLEIN4B_SHORT], ids=lambda c: c["name"])
 def test_single_block_against_the_restatement(lib, case):
     inp = bc.block_inputs(case)
     got = device_block(lib, inp)
@@ -320,7 +320,7 @@ def test_double_block_argument_checks(lib):
 # ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("rows,cin,heads,mlp", [(200, 256, 2, 384), (129, 512, 2, 200), (77, 256, 0, 136),
-                                                (300, 384, 0, 1024)])
+                                                (300, 384, 0, 1024), (260, 384, 3, 392), (70, 128, 1, 128)])
 def test_linear_glu(lib, rows, cin, heads, mlp):
     """Q / K / V columns as iris_b200_linear_qk_norm_rope stores them, and
     silu(gate) * up for the gate | up rows of W, against the restatement of
@@ -366,7 +366,11 @@ def test_linear_glu(lib, rows, cin, heads, mlp):
     assert (act[:, :mlp] != want_act).mean() < 0.1
     if heads:
         fq, fh = ol.from_bf16(qkv), ol.from_bf16(h[:, :nq])
-        assert (np.abs(fq - fh) <= np.maximum(np.abs(fh), 0.05) * 2.0 ** -6).all()
+        # two bf16 steps of the largest value of the (row, head): the rotation mixes a pair, so a product that
+        # rounded the other way shows up in an element that may itself be small
+        top = np.abs(fh).reshape(rows, 3 * heads, 128).max(axis=2, keepdims=True)
+        tol = np.broadcast_to(np.maximum(top, 0.05) * 2.0 ** -6, (rows, 3 * heads, 128)).reshape(rows, nq)
+        assert (np.abs(fq - fh) <= tol).all(), float(np.abs(fq - fh).max())
         assert (qkv != h[:, :nq]).mean() < 0.1
 
 
@@ -535,7 +539,8 @@ def test_single_ctas_linear_f32_and_residual(pairs, rows, cin, cout):
     test_linear_f32_and_linear_residual(pairs, rows, cin, cout)
 
 
-@pytest.mark.parametrize("rows,cin,heads,mlp", [(200, 256, 2, 384), (129, 512, 2, 200), (77, 256, 0, 136), (300, 384, 0, 1024)])
+@pytest.mark.parametrize("rows,cin,heads,mlp", [(200, 256, 2, 384), (129, 512, 2, 200), (77, 256, 0, 136), (300, 384, 0, 1024),
+                                                (260, 384, 3, 392)])
 def test_single_ctas_linear_glu(pairs, rows, cin, heads, mlp):
     test_linear_glu(pairs, rows, cin, heads, mlp)
 
@@ -563,7 +568,7 @@ def test_pairs_bf16_linear_matches_single_ctas(lib):
     assert np.abs(ol.from_bf16(outs[1]) - want).max() <= 0.02 * np.abs(want).max()
 
 
-@pytest.mark.parametrize("case", [bc.SMALL, bc.MID], ids=lambda c: c["name"])
+@pytest.mark.parametrize("case", [bc.SMALL, bc.MID, bc.ODD_HEADS], ids=lambda c: c["name"])
 def test_single_ctas_blocks(pairs, case):
     """Single, double (two row groups) and segmented blocks with every linear layer on single CTAs."""
     inp = bc.block_inputs(case)

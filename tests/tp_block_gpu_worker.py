@@ -46,7 +46,9 @@ def main():
     assert lib.iris_b200_ring_init(rank, world, ident[0]) == 0
     worst = torch.tensor([0.0, -1.0])
     base = dict(bc.MID, heads=2 * world, mlp=384 * world)
-    cases = [dict(base, name="tp-even", txt=64, img=(8, 3 * world * 4)), dict(base, name="tp-uneven", txt=40, img=(12, 11))]
+    cases = [dict(base, name="tp-even", txt=64, img=(8, 3 * world * 4)), dict(base, name="tp-uneven", txt=40, img=(12, 11)),
+             # an odd number of heads per rank: the Q | K | V columns end in the middle of a 256-column tile
+             dict(base, name="tp-odd-heads", heads=3 * world, mlp=392 * world, txt=40, img=(12, 11))]
     if len(sys.argv) > 1 and sys.argv[1] == "klein4b":
         cases = [dict(bc.KLEIN4B_SHORT, name="tp-klein4b", txt=128, img=(16, 24))]
     for case in cases:
