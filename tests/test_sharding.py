@@ -366,3 +366,36 @@ def test_linear_work_list_order_follows_the_l2_working_set(lib):
     _, tn, band, order = linear_plan(lib, 4608, 4608, 12288, 3072, 0)
     assert band == tn == 12 and (order[:12, 0] == 0).all() and sorted(order[:12, 2]) == list(range(12))
     assert lib.iris_b200_linear_plan(10, 11, 64, 8, 0, 148, None, None, None, None, 0) == -1
+
+
+# ---------------------------------------------------------------------------
+# what bench.py gives every rank of a multi-GPU run (host arithmetic only)
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("world,groups", [(2, 1), (4, 2), (8, 4), (8, 2), (8, 1)])
+def test_bench_head_groups_and_rings_cover_the_workload_once(lib, world, groups):
+    """Head groups x rings over the 16 896-token workload: the ranks of a ring
+    hold disjoint row blocks that tile the sequence, the rings hold disjoint
+    head groups that tile the heads, and every (row, head) belongs to exactly
+    one rank."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+
+    class Rank:
+        pass
+
+    w = bench.WORKLOADS["flux3-multiref"]
+    S, H = bench.seq_len(w), w["heads"]
+    owner = np.zeros((S, H), np.int32)
+    size = world // groups
+    for rank in range(world):
+        job = Rank()
+        job.lib, job.rank, job.world = lib, rank, world
+        p = bench.plan_of(job, w, "ring", groups)
+        assert p["S"] == int(p["rows_of"][rank % size]) and len(p["rows_of"]) == size
+        assert int(np.sum(p["rows_of"])) == S and p["row0"] == int(np.sum(p["rows_of"][:rank % size]))
+        assert p["nh"] == H // groups and p["h0"] == (rank // size) * (H // groups)
+        owner[p["row0"]:p["row0"] + p["S"], p["h0"]:p["h0"] + p["nh"]] += 1
+    assert (owner == 1).all()
