@@ -1188,7 +1188,7 @@ def run_b200(args):
                 if B is not None:
                     B.free()
                 lib.iris_b200_clear_error()
-                job.ring_destroy()
+                lib.iris_b200_ring_destroy()        # also when ring_init itself got only part of the way
             except Exception:
                 pass
             job.ring_ready = False
